@@ -1,0 +1,206 @@
+/* vaicu.h — C ABI of the B200 (sm_100a) backend for vAi's Linear node.
+ *
+ * This is the whole surface a host binds to replace the Vulkan device layer
+ * on the `vai::node::Linear` path.  Every function returns an int status
+ * (VAICU_OK == 0); nothing aborts or throws across this boundary.  All data
+ * pointers handed to vaicu_linear_run() are DEVICE pointers owned by the
+ * caller; the library never frees or keeps them.  There is no CPU fallback:
+ * a call that cannot run on the GPU returns an error status.
+ *
+ * Each declaration names the reference interface it stands in for
+ * (path inside the vAi source tree : line).
+ */
+#ifndef VAICU_H
+#define VAICU_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+/* Only the functions below are exported from libvaicu.so. */
+#if defined(__GNUC__)
+#define VAICU_API __attribute__((visibility("default")))
+#else
+#define VAICU_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+enum {
+    VAICU_OK                 = 0,
+    VAICU_ERR_INVALID_VALUE  = 1,  /* null pointer, bad enum, bad shape        */
+    VAICU_ERR_UNSUPPORTED    = 2,  /* dtype combination with no kernel         */
+    VAICU_ERR_CUDA           = 3,  /* a CUDA runtime/driver call failed        */
+    VAICU_ERR_NO_DEVICE      = 4,  /* no sm_100 device / driver present        */
+    VAICU_ERR_WORKSPACE      = 5,  /* workspace null or too small              */
+    VAICU_ERR_ALIGNMENT      = 6,  /* pointer not aligned to its element size  */
+    VAICU_ERR_TOO_LARGE      = 7,  /* shape beyond a fixed-capacity entry point */
+    VAICU_ERR_TIMEOUT        = 8   /* a bounded device-side wait gave up       */
+};
+
+/* vai::Dtype crosses the host/kernel boundary as an integer
+ * (vai/engine/tensor.h:19, vai/shaders/common/spec_constants.h:6-8).
+ * Fp32, Fp16 and None keep their reference values; bf16 is appended. */
+enum {
+    VAICU_DTYPE_F32  = 0,
+    VAICU_DTYPE_F16  = 1,
+    VAICU_DTYPE_NONE = 2,
+    VAICU_DTYPE_BF16 = 3
+};
+
+/* vai::Epilogue (vai/nodes/common.h:31-39; codes of
+ * vai/shaders/common/activation.h:8). */
+enum {
+    VAICU_EPILOGUE_NONE      = 0,
+    VAICU_EPILOGUE_RELU      = 1,
+    VAICU_EPILOGUE_GELU      = 2,
+    VAICU_EPILOGUE_GELU_TANH = 3,
+    VAICU_EPILOGUE_SILU      = 4,
+    VAICU_EPILOGUE_SIGMOID   = 5
+};
+
+/* vai::ResidualOrder (vai/nodes/common.h:42-45). */
+enum {
+    VAICU_RESIDUAL_AFTER_EPILOGUE  = 0,
+    VAICU_RESIDUAL_BEFORE_EPILOGUE = 1
+};
+
+/* Kernel families a plan can resolve to (reported by vaicu_linear_plan_info;
+ * the analogue of the pipeline name chosen in Linear::prepare(),
+ * vai/nodes/linear.h:2355-2666). */
+enum {
+    VAICU_KERNEL_GEMV     = 1,  /* M <= 8 weight-streaming kernel ("slab")     */
+    VAICU_KERNEL_FMA_TILE = 2,  /* fp32 FFMA tile GEMM (exact fp32, any shape) */
+    VAICU_KERNEL_TC_GEMM  = 3,  /* tcgen05/TMEM GEMM, activations on UMMA-M    */
+    VAICU_KERNEL_TC_SKINNY= 4   /* tcgen05/TMEM GEMM, weights on UMMA-M (swap) */
+};
+
+typedef struct vaicu_device      vaicu_device;
+typedef struct vaicu_buffer      vaicu_buffer;
+typedef struct vaicu_linear_plan vaicu_linear_plan;
+/* A stream handle is a cudaStream_t passed as void* (NULL = default stream). */
+typedef void* vaicu_stream_t;
+
+/* Everything Linear::prepare() freezes for one recording
+ * (vai/nodes/linear.h:2291-2353 and the spec/push constants of
+ * linear.h:2371-2386, 2677-2685, 2726, 2793).
+ *
+ *   O = s * epilogue(I . W^T + bias) + R        residual_order AFTER
+ *   O = s * epilogue(I . W^T + bias + R)        residual_order BEFORE
+ *
+ * I [M,K], W [N,K], O [M,N] dense row-major.  With gate_fuse != 0 the weight
+ * holds 2H rows (gate rows [0,H), value rows [H,2H), N == 2H) and the output
+ * is [M,H]: O = s * (epilogue(acc_gate + bias_gate) * (acc_up + bias_up)),
+ * the Linear followed by vai's GatedMul (vai/nodes/gated-mul.h:9-20) in one
+ * pass (no residual; a bias, if any, has one entry per weight row).  bias_elems / residual_elems: 0 means "covers O"; otherwise the
+ * operand has that many elements and is read at (flat index % elems)
+ * (linear.h:2333-2338). */
+typedef struct vaicu_linear_desc {
+    uint32_t M, N, K;
+    int32_t  i_dtype, w_dtype, o_dtype, b_dtype;
+    int32_t  has_bias;
+    uint32_t bias_elems;
+    int32_t  has_residual;
+    uint32_t residual_elems;
+    int32_t  residual_order;
+    int32_t  epilogue;
+    float    scalar_scale;
+    uint32_t split_size;     /* 0: library heuristic; else K span per split, >= 32 */
+    int32_t  gate_fuse;
+} vaicu_linear_desc;
+
+typedef struct vaicu_linear_info {
+    int32_t  kernel;         /* VAICU_KERNEL_*                                  */
+    uint32_t split_count;    /* K splits (1 = none)                             */
+    uint32_t tile_m, tile_n; /* CTA tile (rows of O, columns of O); 0 for GEMV  */
+    uint32_t launches;       /* kernels one vaicu_linear_run() enqueues         */
+    size_t   workspace_bytes;
+} vaicu_linear_info;
+
+/* ---- device (replaces eva::Device; vai/engine/neural-net.h:251-257) ------ */
+VAICU_API int  vaicu_device_open(int ordinal, vaicu_device** out);
+VAICU_API int  vaicu_device_close(vaicu_device* dev);
+VAICU_API int  vaicu_device_sm_count(const vaicu_device* dev, int* out);   /* eva::Device::computeBlockCount(), linear.h:613 */
+VAICU_API int  vaicu_device_synchronize(vaicu_device* dev);
+/* Synchronises the device and reads (then clears) the word the kernels set when
+ * one of their bounded waits ran out: *out != 0 and VAICU_ERR_TIMEOUT in that
+ * case.  Stands in for the lost-device report of NeuralNet::sync()
+ * (vai/engine/neural-net.cpp:206-217). */
+VAICU_API int  vaicu_device_status(vaicu_device* dev, int* out);
+
+/* ---- buffers (replace eva::Buffer / BufferPool::requestBuffer,
+ *      vai/engine/buffer-pool.h:77-134) ---------------------------------- */
+VAICU_API int   vaicu_buffer_alloc(vaicu_device* dev, size_t bytes, vaicu_buffer** out);
+VAICU_API int   vaicu_buffer_free(vaicu_buffer* buf);
+VAICU_API void* vaicu_buffer_ptr(const vaicu_buffer* buf);
+VAICU_API size_t vaicu_buffer_size(const vaicu_buffer* buf);
+
+/* Host<->device copies (replace the staging copy of
+ * NeuralNet::prepareInputs, vai/engine/neural-net.cpp:219-280, and
+ * Tensor::downloadToHost, vai/engine/tensor.cpp:459-489). Asynchronous on
+ * `stream` when the host memory is pinned. */
+VAICU_API int vaicu_memcpy_h2d(void* dst_device, const void* src_host, size_t bytes, vaicu_stream_t stream);
+VAICU_API int vaicu_memcpy_d2h(void* dst_host, const void* src_device, size_t bytes, vaicu_stream_t stream);
+VAICU_API int vaicu_memset(void* dst_device, int value, size_t bytes, vaicu_stream_t stream);
+VAICU_API int vaicu_host_alloc_pinned(size_t bytes, void** out);
+VAICU_API int vaicu_host_free_pinned(void* p);
+
+/* ---- streams (replace eva::CommandBuffer submit + TimelineSemaphore,
+ *      vai/engine/neural-net.h:432-438, neural-net.cpp:206-217) ----------- */
+VAICU_API int vaicu_stream_create(vaicu_device* dev, vaicu_stream_t* out);
+VAICU_API int vaicu_stream_sync(vaicu_stream_t stream);
+VAICU_API int vaicu_stream_destroy(vaicu_stream_t stream);
+
+/* ---- recorded launches (replace the command buffer that is recorded once and
+ *      resubmitted while shapes repeat, vai/engine/neural-net.h:391-438) --- */
+typedef struct vaicu_graph vaicu_graph;
+/* Everything enqueued on `stream` between begin and end is captured instead of
+ * executed; end returns an executable recording. */
+VAICU_API int vaicu_graph_capture_begin(vaicu_stream_t stream);
+VAICU_API int vaicu_graph_capture_end(vaicu_stream_t stream, vaicu_graph** out);
+VAICU_API int vaicu_graph_launch(vaicu_graph* graph, vaicu_stream_t stream);
+VAICU_API int vaicu_graph_destroy(vaicu_graph* graph);
+
+/* ---- the Linear plan (replaces Linear::prepare(), linear.h:2291-2704,
+ *      and the PipelinePool lookup, vai/engine/pipeline-pool.h:86-116) ---- */
+VAICU_API int vaicu_linear_plan_create(vaicu_device* dev, const vaicu_linear_desc* desc, vaicu_linear_plan** out);
+/* Same, but with the kernel family fixed by the caller (VAICU_KERNEL_*) instead
+ * of chosen by shape; VAICU_ERR_UNSUPPORTED when that family cannot run the
+ * desc.  The counterpart of the reference's per-node overrides such as
+ * Linear::setAccDtype (linear.h:291); used by the parity tests to drive every
+ * kernel over the same shapes. */
+VAICU_API int vaicu_linear_plan_create_forced(vaicu_device* dev, const vaicu_linear_desc* desc, int kernel, vaicu_linear_plan** out);
+VAICU_API int vaicu_linear_plan_destroy(vaicu_linear_plan* plan);
+VAICU_API int vaicu_linear_plan_info(const vaicu_linear_plan* plan, vaicu_linear_info* out);
+/* Size of the "partial" temporary slot (linear.h:2697-2698) plus any private
+ * staging the chosen kernel needs; 0 when the kernel needs none. */
+VAICU_API int vaicu_linear_workspace_bytes(const vaicu_linear_plan* plan, size_t* out);
+
+/* Replaces Linear::run() (linear.h:2706-2798): enqueues the plan's kernels on
+ * `stream`; no allocation, no synchronisation.  `bias` / `residual` may be
+ * NULL when the desc says they are absent; `workspace` may be NULL when
+ * vaicu_linear_workspace_bytes() reported 0. */
+VAICU_API int vaicu_linear_run(vaicu_linear_plan* plan, vaicu_stream_t stream,
+                     const void* I, const void* W, const void* bias, const void* residual,
+                     void* O, void* workspace);
+
+/* Column-split helper for the multi-GPU layout: the desc of rank `rank` of
+ * `world` when W's rows (output columns) are split evenly; for gate_fuse the
+ * split is per half.  Fills row offsets into W / bias for that rank. No
+ * reference counterpart (the reference is single-device). */
+VAICU_API int vaicu_linear_shard_desc(const vaicu_linear_desc* full, int rank, int world,
+                            vaicu_linear_desc* shard, uint32_t* w_row_begin, uint32_t* w_row_count);
+
+/* Status text (replaces the VAI_ASSERT message, vai/engine/error.h:8-24). */
+VAICU_API const char* vaicu_status_string(int status);
+/* Text of the last CUDA error seen by this thread (empty string if none). */
+VAICU_API const char* vaicu_last_cuda_error(void);
+/* Library version: major * 1000 + minor. */
+VAICU_API int vaicu_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VAICU_H */

@@ -1,0 +1,162 @@
+"""Python face of the CPU oracle (test infrastructure; see linear_oracle.c).
+
+Two oracles:
+  * linear_f64(): the reference's own test oracle — float64 linear + epilogue
+    (vAi python/tests/node_check.py:31-38,128-131; nodes/test_linear.py:34-35,
+    66-70), written with numpy.
+  * linear_c(): the C restatement of the shader arithmetic in fp32
+    (linear_oracle.c), which is also the timed CPU baseline.
+"""
+import ctypes
+import math
+import os
+
+import numpy as np
+
+from . import build_oracle
+
+F32, F16, NONE, BF16 = 0, 1, 2, 3
+EPILOGUES = {"NONE": 0, "RELU": 1, "GELU": 2, "GELU_TANH": 3, "SILU": 4, "SIGMOID": 5}
+
+_erf = np.vectorize(math.erf, otypes=[np.float64])
+
+
+def epilogue_f64(code, x):
+    """float64 epilogues, the functions torch computes in the reference's tests
+    (node_check.py:31-38)."""
+    x = np.asarray(x, dtype=np.float64)
+    if code == 0:
+        return x
+    if code == 1:
+        return np.maximum(x, 0.0)
+    if code == 2:
+        return 0.5 * x * (1.0 + _erf(x / math.sqrt(2.0)))
+    if code == 3:
+        return 0.5 * x * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x ** 3)))
+    if code == 4:
+        return x / (1.0 + np.exp(-x))
+    if code == 5:
+        return 1.0 / (1.0 + np.exp(-x))
+    raise ValueError(code)
+
+
+def linear_f64(x, w, bias=None, residual=None, *, epilogue=0, residual_order=0, scalar_scale=1.0,
+               gate_fuse=False):
+    """O = s*ep(x w^T + b) + R  (order 0)  or  s*ep(x w^T + b + R)  (order 1), in float64.
+    Operands may be any float arrays (already holding the values the device sees)."""
+    x = np.asarray(x, dtype=np.float64)
+    w = np.asarray(w, dtype=np.float64)
+    acc = x.reshape(-1, x.shape[-1]) @ w.T
+    if bias is not None:
+        b = np.asarray(bias, dtype=np.float64).reshape(-1)
+        acc = (acc.reshape(-1) + np.resize(b, acc.size)).reshape(acc.shape)
+    if gate_fuse:
+        h = acc.shape[1] // 2
+        out = scalar_scale * (epilogue_f64(epilogue, acc[:, :h]) * acc[:, h:])
+        return out
+    r = None
+    if residual is not None:
+        r = np.resize(np.asarray(residual, dtype=np.float64).reshape(-1), acc.size).reshape(acc.shape)
+    if r is not None and residual_order == 1:
+        return scalar_scale * epilogue_f64(epilogue, acc + r)
+    out = scalar_scale * epilogue_f64(epilogue, acc)
+    return out + r if r is not None else out
+
+
+class _Desc(ctypes.Structure):
+    _fields_ = [("M", ctypes.c_uint32), ("N", ctypes.c_uint32), ("K", ctypes.c_uint32),
+                ("i_dtype", ctypes.c_int32), ("w_dtype", ctypes.c_int32), ("o_dtype", ctypes.c_int32),
+                ("b_dtype", ctypes.c_int32), ("has_bias", ctypes.c_int32), ("bias_elems", ctypes.c_uint32),
+                ("has_residual", ctypes.c_int32), ("residual_elems", ctypes.c_uint32),
+                ("residual_order", ctypes.c_int32), ("epilogue", ctypes.c_int32),
+                ("scalar_scale", ctypes.c_float), ("split_size", ctypes.c_uint32), ("gate_fuse", ctypes.c_int32)]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(build_oracle.build())
+        _lib.vai_oracle_f32_to_f16.restype = ctypes.c_uint16
+        _lib.vai_oracle_f32_to_f16.argtypes = [ctypes.c_float]
+        _lib.vai_oracle_f16_to_f32.restype = ctypes.c_float
+        _lib.vai_oracle_f16_to_f32.argtypes = [ctypes.c_uint16]
+        _lib.vai_oracle_f32_to_bf16.restype = ctypes.c_uint16
+        _lib.vai_oracle_f32_to_bf16.argtypes = [ctypes.c_float]
+        _lib.vai_oracle_bf16_to_f32.restype = ctypes.c_float
+        _lib.vai_oracle_bf16_to_f32.argtypes = [ctypes.c_uint16]
+        _lib.vai_oracle_epilogue.restype = ctypes.c_float
+        _lib.vai_oracle_epilogue.argtypes = [ctypes.c_int, ctypes.c_float]
+        _lib.vai_oracle_convert_f32.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t]
+        _lib.vai_oracle_widen_f32.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t]
+        _lib.vai_oracle_num_threads.restype = ctypes.c_int
+    return _lib
+
+
+def num_threads():
+    return int(lib().vai_oracle_num_threads())
+
+
+def to_dtype(a, dtype):
+    """fp32 array -> device representation (np.float32, or uint16 bit patterns for
+    fp16/bf16) using the loader's conversions (vAi vai/engine/tensor.cpp:46-85)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    if dtype == F32:
+        return a.copy()
+    out = np.empty(a.shape, dtype=np.uint16)
+    lib().vai_oracle_convert_f32(a.ctypes.data, out.ctypes.data, dtype, a.size)
+    return out
+
+
+def to_f32(a, dtype):
+    """Device representation -> fp32 values."""
+    if dtype == F32:
+        return np.ascontiguousarray(a, dtype=np.float32)
+    a = np.ascontiguousarray(a, dtype=np.uint16)
+    out = np.empty(a.shape, dtype=np.float32)
+    lib().vai_oracle_widen_f32(a.ctypes.data, dtype, out.ctypes.data, a.size)
+    return out
+
+
+def _ptr(a):
+    return None if a is None else ctypes.c_void_p(a.ctypes.data)
+
+
+def make_desc(M, N, K, *, i_dtype=F32, w_dtype=F32, o_dtype=F32, b_dtype=NONE, bias_elems=None,
+              residual_elems=None, residual_order=0, epilogue=0, scalar_scale=1.0, split_size=0,
+              gate_fuse=False):
+    out_elems = M * (N // 2 if gate_fuse else N)
+    return _Desc(M, N, K, i_dtype, w_dtype, o_dtype, b_dtype if bias_elems else NONE,
+                 1 if bias_elems else 0, 0 if (not bias_elems or bias_elems == M * N) else bias_elems,
+                 1 if residual_elems else 0,
+                 0 if (not residual_elems or residual_elems == out_elems) else residual_elems,
+                 residual_order, epilogue, scalar_scale, split_size, 1 if gate_fuse else 0)
+
+
+def linear_c(desc, I, W, bias=None, residual=None, path="auto", wg_size=128, stage16=None, stage_dtype=F16):
+    """Run the C restatement. Arrays are device representations (float32 / uint16).
+    Returns O in its device representation."""
+    L = lib()
+    n_out = desc.N // 2 if desc.gate_fuse else desc.N
+    O = np.empty((desc.M, n_out), dtype=np.float32 if desc.o_dtype == F32 else np.uint16)
+    I = np.ascontiguousarray(I)
+    W = np.ascontiguousarray(W)
+    bias = None if bias is None else np.ascontiguousarray(bias)
+    residual = None if residual is None else np.ascontiguousarray(residual)
+    if path == "auto":
+        rc = L.vai_oracle_linear(ctypes.byref(desc), _ptr(I), _ptr(W), _ptr(bias), _ptr(residual), _ptr(O))
+    elif path == "slab":
+        rc = L.vai_oracle_linear_slab(ctypes.byref(desc), _ptr(I), _ptr(W), _ptr(bias), _ptr(residual), _ptr(O),
+                                      ctypes.c_uint32(wg_size))
+    elif path == "tile":
+        if stage16 is None:
+            stage16 = not (desc.i_dtype == F32 and desc.w_dtype == F32)
+        rc = L.vai_oracle_linear_tile(ctypes.byref(desc), _ptr(I), _ptr(W), _ptr(bias), _ptr(residual), _ptr(O),
+                                      ctypes.c_int(1 if stage16 else 0), ctypes.c_int(stage_dtype))
+    else:
+        raise ValueError(path)
+    if rc != 0:
+        raise RuntimeError(f"oracle returned {rc}")
+    return O

@@ -1,0 +1,198 @@
+"""GPU parity: the CUDA kernels, through the public host API and the C ABI,
+against the golden outputs of the reference's tests, the float64 oracle and the C
+restatement of the shaders."""
+import numpy as np
+import pytest
+from gpu_util import out_tol, run_linear, seen
+from linear_check import BOUND_FP32, FP32, assert_close, draw_case, load_golden
+
+from oracle import linear_oracle as orc
+from vai_b200 import Dtype, nodes
+
+pytestmark = pytest.mark.gpu
+
+META, ARRAYS = load_golden()
+PRIMARY = [k for k in sorted(META) if not META[k]["rerun_of"]]
+
+
+def _kw(cfg):
+    return dict(epilogue=cfg["epilogue"], residual_order=cfg.get("residual_order", "AFTER_EPILOGUE"),
+                split_size=cfg.get("split_size", 0))
+
+
+@pytest.mark.parametrize("key", sorted(META))
+def test_reference_cases_fp32(key, device):
+    """The reference's Linear cases (test_linear.py:11-27, 54-84) with fp32 weights,
+    kernel chosen by shape: slab cases at the reference's FP32 tier, tile cases at
+    1e-4 (fp32 staging, tighter than the FP16 tier the reference allows)."""
+    cfg, params, fed = draw_case(META, key)
+    got, want, node = run_linear(fed["in0"], params["weight"], params.get("bias"), fed.get("residual"), **_kw(cfg))
+    M = fed["in0"].shape[0]
+    assert node.info.kernel == (nodes.KERNEL_GEMV if M <= 8 else nodes.KERNEL_FMA_TILE)
+    assert_close(got, ARRAYS[key], FP32 if M <= 8 else BOUND_FP32, key)
+    assert_close(want, ARRAYS[key], (1e-12, 1e-12), key + " (oracle vs golden)")
+
+
+@pytest.mark.parametrize("key", PRIMARY)
+@pytest.mark.parametrize("kernel", ["fma", "tc", "skinny"])
+@pytest.mark.parametrize("w_dtype", ["f16", "bf16"])
+def test_reference_cases_16bit_weights(key, kernel, w_dtype, device):
+    """Same cases with the weights stored in 16 bits (the deployment default is fp16,
+    vAi neural-net.h:279), every kernel family forced in turn.  Against float64 over
+    the stored values the only error left is fp32 accumulation."""
+    cfg, params, fed = draw_case(META, key)
+    K = cfg["in_dim"]
+    kid = {"fma": nodes.KERNEL_FMA_TILE, "tc": nodes.KERNEL_TC_GEMM, "skinny": nodes.KERNEL_TC_SKINNY}[kernel]
+    if kernel != "fma" and K % 8:
+        pytest.skip("tensor-core path needs K % 8 == 0; the plan falls back (covered by the fma run)")
+    got, want, node = run_linear(fed["in0"], params["weight"], params.get("bias"), fed.get("residual"),
+                                 w_dtype=w_dtype, b_dtype="f32", kernel=kid, **_kw(cfg))
+    assert node.info.kernel == kid
+    assert_close(got, want, (1e-4, 2e-5), f"{key}/{kernel}/{w_dtype}")
+    # and within the reference's own tier of the float64 result on unrounded operands
+    golden_tol = (1e-3, 5e-3) if w_dtype == "f16" else (2e-2, 2e-2)
+    assert_close(got, ARRAYS[key], golden_tol, f"{key}/{kernel}/{w_dtype} vs golden")
+
+
+def test_identity_weight_plus_bias(device):
+    """vAi python/tests/test_nodes.py:28-41: identity weight + bias, exact."""
+    x = np.array([[1.0, 2.0, 3.0, 4.0]], dtype=np.float32)
+    got, _, _ = run_linear(x, np.eye(4, dtype=np.float32), np.array([10.0, 20.0, 30.0, 40.0], dtype=np.float32))
+    np.testing.assert_array_equal(got, [[11.0, 22.0, 33.0, 44.0]])
+
+
+SHAPES = [
+    # M, K, N
+    (1, 2048, 512), (1, 768, 2304), (2, 1024, 300), (3, 512, 64), (4, 8192, 256), (5, 640, 130), (7, 264, 97),
+    (8, 3072, 768), (1, 100, 33), (6, 101, 50),
+]
+
+
+@pytest.mark.parametrize("M,K,N", SHAPES)
+@pytest.mark.parametrize("dt", [("f32", "f32", "f32"), ("f32", "f16", "f32"), ("bf16", "bf16", "bf16"),
+                                ("f16", "f16", "f16"), ("f32", "bf16", "f32"), ("bf16", "bf16", "f32")])
+def test_gemv_dtypes(M, K, N, dt, device):
+    rng = np.random.default_rng(M * 1000 + K + N)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    r = rng.standard_normal((M, N)).astype(np.float32)
+    got, want, node = run_linear(x, w, b, r, i_dtype=dt[0], w_dtype=dt[1], o_dtype=dt[2], epilogue="GELU_TANH",
+                                 scalar_scale=0.5)
+    assert node.info.kernel == nodes.KERNEL_GEMV
+    assert_close(got, want, out_tol(dt[2]), f"gemv {M}x{K}x{N} {dt}")
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 5, 8])
+@pytest.mark.parametrize("w_dtype", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("act", ["SILU", "GELU_TANH", "RELU"])
+def test_gemv_gate_fuse(M, w_dtype, act, device):
+    """Linear + GatedMul in one pass against the two-node arithmetic
+    (vAi nodes/test_gated_mul.py: TRANS tier)."""
+    rng = np.random.default_rng(17 + M)
+    K, H = 512, 328
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((2 * H, K)) / np.sqrt(K)).astype(np.float32)
+    got, want, node = run_linear(x, w, w_dtype=w_dtype, epilogue=act, gate_fuse=True)
+    assert got.shape == (M, H)
+    assert_close(got, want, (1e-4, 1e-5), f"gate {M} {w_dtype} {act}")
+
+
+GEMM_SHAPES = [
+    # M, K, N: skinny and tiled, with ragged M / N / K-block tails
+    (16, 256, 64), (33, 1000, 100), (64, 2560, 512), (100, 512, 384), (128, 768, 3072), (129, 320, 264),
+    (300, 1024, 520), (1024, 768, 768), (200, 72, 40), (512, 4096, 256),
+]
+
+
+@pytest.mark.parametrize("M,K,N", GEMM_SHAPES)
+@pytest.mark.parametrize("dt", [("f32", "f16", "f32"), ("bf16", "bf16", "bf16"), ("f16", "f16", "f32"),
+                                ("f32", "bf16", "bf16")])
+@pytest.mark.parametrize("kernel", ["auto", "tc", "skinny"])
+def test_tensor_core_dtypes(M, K, N, dt, kernel, device):
+    rng = np.random.default_rng(M + K + N)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    r = rng.standard_normal((M, N)).astype(np.float32)
+    kid = {"auto": 0, "tc": nodes.KERNEL_TC_GEMM, "skinny": nodes.KERNEL_TC_SKINNY}[kernel]
+    if kernel == "skinny" and M > 256:
+        pytest.skip("skinny kernel is offered up to M = 256")
+    got, want, node = run_linear(x, w, b, r, i_dtype=dt[0], w_dtype=dt[1], o_dtype=dt[2], epilogue="SILU",
+                                 residual_order="BEFORE_EPILOGUE", kernel=kid)
+    assert node.info.kernel in (nodes.KERNEL_TC_GEMM, nodes.KERNEL_TC_SKINNY)
+    assert_close(got, want, out_tol(dt[2], 2e-4, 5e-5), f"tc {M}x{K}x{N} {dt} {kernel}")
+
+
+@pytest.mark.parametrize("M,K,H", [(16, 512, 256), (64, 2560, 640), (200, 1024, 384), (1024, 512, 1000), (130, 264, 72)])
+@pytest.mark.parametrize("kernel", ["auto", "tc", "skinny", "fma"])
+@pytest.mark.parametrize("act", ["SILU", "GELU_TANH"])
+def test_gemm_gate_fuse(M, K, H, kernel, act, device):
+    rng = np.random.default_rng(M + K + H)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((2 * H, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(2 * H).astype(np.float32)
+    kid = {"auto": 0, "tc": nodes.KERNEL_TC_GEMM, "skinny": nodes.KERNEL_TC_SKINNY, "fma": nodes.KERNEL_FMA_TILE}[kernel]
+    if kernel == "skinny" and M > 256:
+        pytest.skip("skinny kernel is offered up to M = 256")
+    got, want, node = run_linear(x, w, b, i_dtype="bf16", w_dtype="bf16", o_dtype="bf16", b_dtype="bf16", epilogue=act,
+                                 gate_fuse=True, kernel=kid)
+    assert got.shape == (M, H)
+    assert_close(got, want, out_tol("bf16", 2e-4, 5e-5), f"gate {M}x{K}x{H} {kernel} {act}")
+
+
+@pytest.mark.parametrize("M,K,N,split", [(64, 4096, 128, 0), (16, 2050, 64, 0), (33, 1024, 48, 128), (256, 8192, 128, 0),
+                                          (64, 10240, 2560, 0)])
+@pytest.mark.parametrize("kernel", ["auto", "fma"])
+def test_split_k(M, K, N, split, kernel, device):
+    rng = np.random.default_rng(K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    kid = {"auto": 0, "fma": nodes.KERNEL_FMA_TILE}[kernel]
+    got, want, node = run_linear(x, w, b, w_dtype="bf16", epilogue="RELU", split_size=split, kernel=kid)
+    if split or (kernel == "auto" and K >= 4096 and K % 8 == 0):
+        assert node.info.split_count > 1
+    assert_close(got, want, (2e-4, 5e-5), f"split {M}x{K}x{N}")
+
+
+def test_bias_table_and_residual_rows(device):
+    """bias / residual as rows that repeat over M (vAi linear.h:2333-2338): a
+    per-image [rows, N] table under a batch."""
+    rng = np.random.default_rng(9)
+    M, K, N, rows = 48, 128, 72, 12
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal((rows, N)).astype(np.float32)
+    r = rng.standard_normal((rows * 2, N)).astype(np.float32)
+    for w_dtype, kid in (("f32", 0), ("bf16", 0), ("bf16", nodes.KERNEL_TC_GEMM), ("bf16", nodes.KERNEL_FMA_TILE)):
+        got, want, _ = run_linear(x, w, b, r, w_dtype=w_dtype, b_dtype="f32", epilogue="SIGMOID", kernel=kid)
+        assert_close(got, want, (2e-4, 5e-5), f"tables {w_dtype} {kid}")
+    got, want, _ = run_linear(x[:4], w, b[:4], r[:2], epilogue="SIGMOID")
+    assert_close(got, want, (1e-5, 1e-5), "tables gemv")
+
+
+@pytest.mark.parametrize("M,K,N", [(4, 1024, 512), (64, 512, 256), (256, 1024, 512)])
+def test_cuda_matches_c_restatement(M, K, N, device):
+    """CUDA path vs oracle/linear_oracle.c on the same seeded inputs (fp32, and fp16
+    weights with the cooperative-matrix staging restated)."""
+    rng = np.random.default_rng(M)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    d = orc.make_desc(M, N, K, b_dtype=orc.F32, bias_elems=N, epilogue=3)
+    got, _, _ = run_linear(x, w, b, epilogue="GELU_TANH")
+    assert_close(got, orc.linear_c(d, x, w, b), BOUND_FP32, "fp32 vs C")
+    d16 = orc.make_desc(M, N, K, w_dtype=orc.F16, b_dtype=orc.F32, bias_elems=N, epilogue=3)
+    got, _, _ = run_linear(x, w, b, w_dtype="f16", b_dtype="f32", epilogue="GELU_TANH")
+    assert_close(got, orc.to_f32(orc.linear_c(d16, x, orc.to_dtype(w, orc.F16), b), orc.F32), (2e-4, 5e-5), "fp16 W vs C")
+
+
+def test_scalar_scale_negative(device):
+    """scalarScale = -1/steps as pi0's Euler step uses it (vAi models/production/pi0/net.h:154-159)."""
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((10, 64)).astype(np.float32)
+    w = (rng.standard_normal((32, 64)) / 8).astype(np.float32)
+    r = rng.standard_normal((10, 32)).astype(np.float32)
+    got, want, _ = run_linear(x, w, None, r, scalar_scale=-0.1, epilogue="SILU", residual_order="BEFORE_EPILOGUE")
+    assert_close(got, want, BOUND_FP32, "scale")

@@ -1,0 +1,676 @@
+// C ABI of the backend (include/vaicu.h): device, buffers, streams, and the
+// Linear plan — the shape -> kernel choice that vAi makes in Linear::prepare()
+// (vai/nodes/linear.h:2291-2704) and the launches it records in Linear::run()
+// (linear.h:2706-2798).  Nothing here falls back to the CPU.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "common.cuh"
+#include "tc_gemm.h"
+
+using namespace vaicu;
+
+struct vaicu_device {
+    int ordinal;
+    int sm_count;
+    int cc_major, cc_minor;
+    int* status_word;   // device memory; kernels set it when a bounded wait expires
+};
+struct vaicu_buffer {
+    void* ptr;
+    size_t bytes;
+    int ordinal;
+};
+struct vaicu_graph {
+    cudaGraphExec_t exec;
+};
+
+namespace {
+
+thread_local char g_last_error[256] = {0};
+
+int cuda_fail(cudaError_t e, const char* what)
+{
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver ? VAICU_ERR_NO_DEVICE : VAICU_ERR_CUDA;
+}
+#define VAICU_CUDA(call)                                              \
+    do {                                                              \
+        cudaError_t e__ = (call);                                     \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #call);         \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is resolved at run time so that the library carries no
+// link-time dependency on libcuda (it must load on machines without a driver).
+EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// [rows, K] row-major 16-bit matrix, boxes of box_rows x 64 elements, 128-byte swizzle.
+int encode_map(CUtensorMap* map, const void* base, int dtype, uint32_t rows, uint32_t K, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) { snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled unavailable"); return VAICU_ERR_CUDA; }
+    const cuuint64_t dims[2] = {K, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2u};
+    const cuuint32_t box[2] = {64u, box_rows};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = fn(map, dtype == VAICU_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                          2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled failed (%d)", (int)r);
+        return VAICU_ERR_CUDA;
+    }
+    return VAICU_OK;
+}
+
+bool valid_dtype(int d) { return d == VAICU_DTYPE_F32 || d == VAICU_DTYPE_F16 || d == VAICU_DTYPE_BF16; }
+bool is16(int d) { return d == VAICU_DTYPE_F16 || d == VAICU_DTYPE_BF16; }
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1u) / b; }
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+struct vaicu_linear_plan {
+    vaicu_device* dev;
+    vaicu_linear_desc d;
+    int kernel;               // VAICU_KERNEL_*
+    // GEMV
+    GemvConfig gemv_vec, gemv_any;
+    // FMA tile (also the fallback of the tensor-core plans)
+    FmaTileConfig fma;
+    bool fma_partial;
+    size_t fma_ws_bytes;
+    // tensor-core GEMM
+    bool tc, tc_swap, tc_cast;
+    TcParams tcp;
+    int tc_grid;
+    size_t tc_smem;
+    size_t ws_cast_bytes, ws_partial_bytes;
+    CUtensorMap map_a, map_b;
+    const void* map_a_base;
+    const void* map_b_base;
+    size_t workspace_bytes;
+    uint32_t launches;
+};
+
+namespace {
+
+int validate_desc(const vaicu_linear_desc* d)
+{
+    if (!d) return VAICU_ERR_INVALID_VALUE;
+    if (d->M == 0 || d->N == 0 || d->K == 0) return VAICU_ERR_INVALID_VALUE;
+    if (!valid_dtype(d->i_dtype) || !valid_dtype(d->w_dtype) || !valid_dtype(d->o_dtype)) return VAICU_ERR_INVALID_VALUE;
+    if (d->has_bias && !valid_dtype(d->b_dtype)) return VAICU_ERR_INVALID_VALUE;
+    if (d->epilogue < 0 || d->epilogue > VAICU_EPILOGUE_SIGMOID) return VAICU_ERR_INVALID_VALUE;
+    if (d->residual_order != 0 && d->residual_order != 1) return VAICU_ERR_INVALID_VALUE;
+    if (d->split_size != 0 && d->split_size < 32) return VAICU_ERR_INVALID_VALUE;   // vAi linear.h:2442
+    if ((uint64_t)d->M * d->N >= (1ull << 32)) return VAICU_ERR_INVALID_VALUE;       // vAi indexes with uint32
+    const uint64_t out_elems = (uint64_t)d->M * (d->gate_fuse ? d->N / 2u : d->N);
+    if (d->gate_fuse) {
+        if (d->N % 2u) return VAICU_ERR_INVALID_VALUE;
+        if (d->has_residual) return VAICU_ERR_UNSUPPORTED;
+        if (d->has_bias && d->bias_elems != d->N && !(d->bias_elems == 0 && d->M == 1u))
+            return VAICU_ERR_UNSUPPORTED;   // one bias per weight row
+    }
+    // broadcast rule of vAi linear.h:2333-2338: whole rows that tile O
+    if (d->has_bias && d->bias_elems && !d->gate_fuse &&
+        (d->bias_elems % d->N || ((uint64_t)d->M * d->N) % d->bias_elems)) return VAICU_ERR_INVALID_VALUE;
+    if (d->has_residual && d->residual_elems && (d->residual_elems % d->N || out_elems % d->residual_elems))
+        return VAICU_ERR_INVALID_VALUE;
+    return VAICU_OK;
+}
+
+LinearArgs make_args(const vaicu_linear_desc& d, const void* I, const void* W, const void* bias, const void* res, void* O)
+{
+    LinearArgs a{};
+    a.I = I; a.W = W; a.bias = bias; a.res = res; a.O = O;
+    a.M = d.M; a.N = d.N; a.K = d.K;
+    a.i_dtype = d.i_dtype; a.w_dtype = d.w_dtype; a.o_dtype = d.o_dtype; a.b_dtype = d.b_dtype;
+    a.has_bias = d.has_bias ? 1 : 0; a.has_res = d.has_residual ? 1 : 0;
+    a.residual_order = d.residual_order; a.epilogue = d.epilogue; a.gate_fuse = d.gate_fuse ? 1 : 0;
+    a.bias_elems = d.has_bias ? d.bias_elems : 0; a.res_elems = d.has_residual ? d.residual_elems : 0;
+    a.scale = d.scalar_scale;
+    return a;
+}
+
+int operand_mode(bool present, uint32_t elems, uint32_t row_len)
+{
+    if (!present) return OPERAND_NONE;
+    if (elems == 0) return OPERAND_FULL;
+    if (elems == row_len) return OPERAND_PER_COLUMN;
+    return OPERAND_MODULO;
+}
+
+// Split-K for the FMA tile kernel: the caller's span, else one span
+// (vAi linear.h:2440-2450 resolves the same two cases).
+void plan_fma(vaicu_linear_plan* pl)
+{
+    const vaicu_linear_desc& d = pl->d;
+    uint32_t split_size = d.K, split_count = 1;
+    if (d.split_size) {
+        split_size = d.split_size < d.K ? d.split_size : d.K;
+        split_count = ceil_div(d.K, split_size);
+    } else {
+        const uint32_t tiles = ceil_div(d.M, 64u) * ceil_div(d.N, 64u);
+        const uint32_t sms = (uint32_t)pl->dev->sm_count;
+        if (tiles * 2u <= sms && d.K >= 1024u) {
+            uint32_t want = sms / tiles;
+            if (want > 16u) want = 16u;
+            split_size = align_up(ceil_div(d.K, want), 64u);
+            split_count = ceil_div(d.K, split_size);
+        }
+    }
+    if (split_count > 65535u) { split_count = 65535u; split_size = ceil_div(d.K, split_count); split_count = ceil_div(d.K, split_size); }
+    pl->fma.split_size = split_size;
+    pl->fma.split_count = split_count;
+    pl->fma_partial = split_count > 1u || d.gate_fuse;
+    pl->fma_ws_bytes = pl->fma_partial ? (size_t)split_count * d.M * d.N * sizeof(float) : 0;
+}
+
+bool tc_eligible(const vaicu_linear_desc& d)
+{
+    if (!is16(d.w_dtype)) return false;
+    if (!(d.i_dtype == d.w_dtype || d.i_dtype == VAICU_DTYPE_F32)) return false;
+    if (d.K % 8u) return false;
+    return true;
+}
+
+// Tile / split choice of the tensor-core kernel (the role selectLinearTile plays
+// in the reference, vAi linear.h:2101-2119): fill the SMs with whole waves of
+// the widest tile, and split K only when the tile grid cannot occupy them.
+void plan_tc(vaicu_linear_plan* pl, bool swap)
+{
+    const vaicu_linear_desc& d = pl->d;
+    const uint32_t sms = (uint32_t)pl->dev->sm_count;
+    const bool gate = d.gate_fuse != 0;
+    const uint32_t H = gate ? d.N / 2u : d.N;
+    TcParams& t = pl->tcp;
+    memset(&t, 0, sizeof(t));
+    t.M = d.M; t.N = d.N; t.K = d.K; t.H = H;
+    t.kblocks = ceil_div(d.K, 64u);
+    uint32_t bn;
+    if (swap) {
+        bn = (uint32_t)align_up(d.M, 16u);
+        if (bn > 128u) bn = 128u;
+        t.tiles_a = ceil_div(H, 128u);
+        t.tiles_b = ceil_div(d.M, bn);
+    } else {
+        // output columns per tile: bn (bn / 2 with gate)
+        const uint32_t cand[3] = {256u, 128u, 64u};
+        double best = -1.0;
+        bn = 256u;
+        for (uint32_t c : cand) {
+            const uint32_t out_cols = gate ? c / 2u : c;
+            const uint32_t tiles = ceil_div(d.M, 128u) * ceil_div(H, out_cols);
+            const uint32_t waves = ceil_div(tiles, sms);
+            double eff = (double)tiles / ((double)waves * sms);
+            // narrower tiles re-read the activations more often and issue shorter MMAs
+            eff *= (c == 256u) ? 1.0 : (c == 128u ? 0.88 : 0.70);
+            // a tile wider than the whole output is wasted work
+            if (out_cols > (uint32_t)align_up(H, 16u) && c != 64u) eff *= (double)H / out_cols;
+            if (eff > best) { best = eff; bn = c; }
+        }
+        t.tiles_a = ceil_div(d.M, 128u);
+        t.tiles_b = ceil_div(H, gate ? bn / 2u : bn);
+    }
+    t.bn = bn;
+    t.num_tiles = t.tiles_a * t.tiles_b;
+    t.group = t.tiles_a < 16u ? t.tiles_a : 16u;
+    // split-K
+    uint32_t kb_per_split = t.kblocks;
+    if (d.split_size) {
+        kb_per_split = ceil_div(d.split_size, 64u);
+    } else if (t.num_tiles * 2u <= sms && t.kblocks >= 8u) {
+        uint32_t want = sms / t.num_tiles;
+        const uint32_t max_splits = t.kblocks / 4u;      // at least 4 k-blocks (256 of K) per split
+        if (want > max_splits) want = max_splits;
+        if (want > 32u) want = 32u;
+        if (want >= 2u) kb_per_split = ceil_div(t.kblocks, want);
+    }
+    if (kb_per_split == 0u) kb_per_split = 1u;
+    if (kb_per_split > t.kblocks) kb_per_split = t.kblocks;
+    t.kb_per_split = kb_per_split;
+    t.splits = ceil_div(t.kblocks, kb_per_split);
+    // descriptor: fp32 accumulate, A/B formats, both K-major, N >> 3, M >> 4
+    const uint32_t fmt = d.w_dtype == VAICU_DTYPE_BF16 ? 1u : 0u;
+    t.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((bn >> 3) << 17) | ((128u >> 4) << 24);
+    const uint32_t a_bytes = ((gate && swap) ? 2u : 1u) * 128u * 128u;
+    const uint32_t stage_bytes = a_bytes + bn * 128u;
+    uint32_t stages = (uint32_t)((kTcMaxSmem - 2048u) / stage_bytes);
+    if (stages > 8u) stages = 8u;
+    t.stages = stages;
+    pl->tc_smem = (size_t)stages * stage_bytes + 1024u + 256u;
+    const uint32_t acc_cols = (gate && swap) ? 2u * bn : bn;
+    uint32_t cols = 32u;
+    while (cols < 2u * acc_cols) cols *= 2u;
+    t.tmem_cols = cols;
+    t.o_dtype = d.o_dtype; t.b_dtype = d.b_dtype; t.epilogue = d.epilogue; t.residual_order = d.residual_order;
+    t.has_bias = d.has_bias ? 1 : 0; t.has_res = d.has_residual ? 1 : 0; t.gate = gate ? 1 : 0;
+    t.bias_mode = operand_mode(d.has_bias != 0, d.bias_elems, d.N);
+    t.res_mode = operand_mode(d.has_residual != 0, d.residual_elems, H);
+    t.bias_elems = d.bias_elems; t.res_elems = d.residual_elems;
+    t.scale = d.scalar_scale;
+    t.status = pl->dev->status_word;
+    const uint32_t work = t.num_tiles * t.splits;
+    pl->tc_grid = (int)(work < sms ? work : sms);
+    pl->tc_swap = swap;
+    pl->tc_cast = d.i_dtype == VAICU_DTYPE_F32;
+    pl->ws_cast_bytes = pl->tc_cast ? align_up((size_t)d.M * d.K * 2u, 256u) : 0;
+    pl->ws_partial_bytes = t.splits > 1u ? (size_t)t.splits * d.M * d.N * sizeof(float) : 0;
+}
+
+int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, int force_kernel, vaicu_linear_plan** out)
+{
+    if (!dev || !out) return VAICU_ERR_INVALID_VALUE;
+    int rc = validate_desc(desc);
+    if (rc != VAICU_OK) return rc;
+    vaicu_linear_plan* pl = new (std::nothrow) vaicu_linear_plan();
+    if (!pl) return VAICU_ERR_INVALID_VALUE;
+    pl->dev = dev;
+    pl->d = *desc;
+    if (!pl->d.has_bias) { pl->d.bias_elems = 0; pl->d.b_dtype = VAICU_DTYPE_NONE; }
+    if (!pl->d.has_residual) pl->d.residual_elems = 0;
+    // a [N] bias under M == 1 "covers O" (elems 0); name it per-row so every kernel takes the cheap index
+    if (pl->d.has_bias && pl->d.bias_elems == 0 && pl->d.M == 1u) pl->d.bias_elems = pl->d.N;
+    const vaicu_linear_desc& d = pl->d;
+    LinearArgs a = make_args(d, nullptr, nullptr, nullptr, nullptr, nullptr);
+    pl->gemv_vec = choose_gemv(a, dev->sm_count, true);
+    pl->gemv_any = choose_gemv(a, dev->sm_count, false);
+    plan_fma(pl);
+    pl->tc = false;
+    int kernel = force_kernel;
+    if (kernel == 0) {
+        // M <= 8: the weight-streaming kernel (vAi useSlabPath, linear.h:320)
+        if (d.M <= 8u) kernel = VAICU_KERNEL_GEMV;
+        else if (tc_eligible(d)) kernel = d.M <= 128u ? VAICU_KERNEL_TC_SKINNY : VAICU_KERNEL_TC_GEMM;
+        else kernel = VAICU_KERNEL_FMA_TILE;
+    }
+    switch (kernel) {
+    case VAICU_KERNEL_GEMV:
+        if (d.M > 8u) { delete pl; return VAICU_ERR_UNSUPPORTED; }
+        pl->workspace_bytes = 0;
+        pl->launches = 1;
+        break;
+    case VAICU_KERNEL_FMA_TILE:
+        pl->workspace_bytes = pl->fma_ws_bytes;
+        pl->launches = pl->fma_partial ? 2 : 1;
+        break;
+    case VAICU_KERNEL_TC_GEMM:
+    case VAICU_KERNEL_TC_SKINNY:
+        if (!tc_eligible(d) || (kernel == VAICU_KERNEL_TC_SKINNY && d.M > 256u)) { delete pl; return VAICU_ERR_UNSUPPORTED; }
+        pl->tc = true;
+        plan_tc(pl, kernel == VAICU_KERNEL_TC_SKINNY);
+        pl->workspace_bytes = pl->ws_cast_bytes + pl->ws_partial_bytes;
+        // unaligned operands fall back to the FMA tile kernel at run time
+        if (pl->fma_ws_bytes > pl->workspace_bytes) pl->workspace_bytes = pl->fma_ws_bytes;
+        pl->launches = 1u + (pl->tc_cast ? 1u : 0u) + (pl->tcp.splits > 1u ? 1u : 0u);
+        break;
+    default:
+        delete pl;
+        return VAICU_ERR_INVALID_VALUE;
+    }
+    pl->kernel = kernel;
+    pl->map_a_base = pl->map_b_base = nullptr;
+    *out = pl;
+    return VAICU_OK;
+}
+
+int run_fma(vaicu_linear_plan* pl, const LinearArgs& a, void* workspace, cudaStream_t s)
+{
+    if (pl->fma_partial && !workspace) return VAICU_ERR_WORKSPACE;
+    float* partial = pl->fma_partial ? reinterpret_cast<float*>(workspace) : nullptr;
+    VAICU_CUDA(launch_fma_tile(a, pl->fma, partial, s));
+    if (partial) VAICU_CUDA(launch_splitk_reduce(a, partial, pl->fma.split_count, s));
+    return VAICU_OK;
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+int vaicu_device_open(int ordinal, vaicu_device** out)
+{
+    if (!out) return VAICU_ERR_INVALID_VALUE;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceCount");
+    if (ordinal < 0 || ordinal >= count) return VAICU_ERR_NO_DEVICE;
+    cudaDeviceProp prop;
+    VAICU_CUDA(cudaGetDeviceProperties(&prop, ordinal));
+    if (prop.major != 10) {
+        snprintf(g_last_error, sizeof(g_last_error), "device %d is sm_%d%d; this library holds sm_100a code only", ordinal,
+                 prop.major, prop.minor);
+        return VAICU_ERR_NO_DEVICE;
+    }
+    VAICU_CUDA(cudaSetDevice(ordinal));
+    vaicu_device* d = new (std::nothrow) vaicu_device();
+    if (!d) return VAICU_ERR_INVALID_VALUE;
+    d->ordinal = ordinal;
+    d->sm_count = prop.multiProcessorCount;
+    d->cc_major = prop.major;
+    d->cc_minor = prop.minor;
+    e = cudaMalloc(&d->status_word, 256);
+    if (e != cudaSuccess) { delete d; return cuda_fail(e, "cudaMalloc(status)"); }
+    e = cudaMemset(d->status_word, 0, 256);
+    if (e != cudaSuccess) { cudaFree(d->status_word); delete d; return cuda_fail(e, "cudaMemset(status)"); }
+    *out = d;
+    return VAICU_OK;
+}
+
+int vaicu_device_close(vaicu_device* dev)
+{
+    if (!dev) return VAICU_ERR_INVALID_VALUE;
+    cudaSetDevice(dev->ordinal);
+    cudaFree(dev->status_word);
+    delete dev;
+    return VAICU_OK;
+}
+
+int vaicu_device_sm_count(const vaicu_device* dev, int* out)
+{
+    if (!dev || !out) return VAICU_ERR_INVALID_VALUE;
+    *out = dev->sm_count;
+    return VAICU_OK;
+}
+
+int vaicu_device_synchronize(vaicu_device* dev)
+{
+    if (!dev) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaSetDevice(dev->ordinal));
+    VAICU_CUDA(cudaDeviceSynchronize());
+    return VAICU_OK;
+}
+
+int vaicu_device_status(vaicu_device* dev, int* out)
+{
+    if (!dev || !out) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaSetDevice(dev->ordinal));
+    VAICU_CUDA(cudaDeviceSynchronize());
+    int word = 0;
+    VAICU_CUDA(cudaMemcpy(&word, dev->status_word, sizeof(int), cudaMemcpyDeviceToHost));
+    *out = word;
+    if (word) {
+        VAICU_CUDA(cudaMemset(dev->status_word, 0, sizeof(int)));
+        return VAICU_ERR_TIMEOUT;
+    }
+    return VAICU_OK;
+}
+
+int vaicu_buffer_alloc(vaicu_device* dev, size_t bytes, vaicu_buffer** out)
+{
+    if (!dev || !out) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaSetDevice(dev->ordinal));
+    vaicu_buffer* b = new (std::nothrow) vaicu_buffer();
+    if (!b) return VAICU_ERR_INVALID_VALUE;
+    // sizes round up to 4 bytes as in vAi's pool (vai/engine/buffer-pool.h:84); never 0
+    b->bytes = bytes ? align_up(bytes, 4) : 4;
+    b->ordinal = dev->ordinal;
+    cudaError_t e = cudaMalloc(&b->ptr, b->bytes);
+    if (e != cudaSuccess) { delete b; return cuda_fail(e, "cudaMalloc"); }
+    *out = b;
+    return VAICU_OK;
+}
+
+int vaicu_buffer_free(vaicu_buffer* buf)
+{
+    if (!buf) return VAICU_ERR_INVALID_VALUE;
+    cudaSetDevice(buf->ordinal);
+    cudaError_t e = cudaFree(buf->ptr);
+    delete buf;
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFree");
+    return VAICU_OK;
+}
+
+void* vaicu_buffer_ptr(const vaicu_buffer* buf) { return buf ? buf->ptr : nullptr; }
+size_t vaicu_buffer_size(const vaicu_buffer* buf) { return buf ? buf->bytes : 0; }
+
+int vaicu_memcpy_h2d(void* dst, const void* src, size_t bytes, vaicu_stream_t stream)
+{
+    if ((!dst || !src) && bytes) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    return VAICU_OK;
+}
+int vaicu_memcpy_d2h(void* dst, const void* src, size_t bytes, vaicu_stream_t stream)
+{
+    if ((!dst || !src) && bytes) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return VAICU_OK;
+}
+int vaicu_memset(void* dst, int value, size_t bytes, vaicu_stream_t stream)
+{
+    if (!dst && bytes) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaMemsetAsync(dst, value, bytes, (cudaStream_t)stream));
+    return VAICU_OK;
+}
+int vaicu_host_alloc_pinned(size_t bytes, void** out)
+{
+    if (!out) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaMallocHost(out, bytes ? bytes : 4));
+    return VAICU_OK;
+}
+int vaicu_host_free_pinned(void* p)
+{
+    if (!p) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaFreeHost(p));
+    return VAICU_OK;
+}
+
+int vaicu_stream_create(vaicu_device* dev, vaicu_stream_t* out)
+{
+    if (!dev || !out) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaSetDevice(dev->ordinal));
+    cudaStream_t s;
+    VAICU_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *out = (vaicu_stream_t)s;
+    return VAICU_OK;
+}
+int vaicu_stream_sync(vaicu_stream_t stream)
+{
+    VAICU_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return VAICU_OK;
+}
+int vaicu_stream_destroy(vaicu_stream_t stream)
+{
+    if (!stream) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaStreamDestroy((cudaStream_t)stream));
+    return VAICU_OK;
+}
+
+int vaicu_graph_capture_begin(vaicu_stream_t stream)
+{
+    if (!stream) return VAICU_ERR_INVALID_VALUE;   // the legacy default stream cannot be captured
+    VAICU_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+    return VAICU_OK;
+}
+int vaicu_graph_capture_end(vaicu_stream_t stream, vaicu_graph** out)
+{
+    if (!stream || !out) return VAICU_ERR_INVALID_VALUE;
+    cudaGraph_t g = nullptr;
+    VAICU_CUDA(cudaStreamEndCapture((cudaStream_t)stream, &g));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+    vaicu_graph* r = new (std::nothrow) vaicu_graph();
+    if (!r) { cudaGraphExecDestroy(exec); return VAICU_ERR_INVALID_VALUE; }
+    r->exec = exec;
+    *out = r;
+    return VAICU_OK;
+}
+int vaicu_graph_launch(vaicu_graph* graph, vaicu_stream_t stream)
+{
+    if (!graph) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaGraphLaunch(graph->exec, (cudaStream_t)stream));
+    return VAICU_OK;
+}
+int vaicu_graph_destroy(vaicu_graph* graph)
+{
+    if (!graph) return VAICU_ERR_INVALID_VALUE;
+    cudaGraphExecDestroy(graph->exec);
+    delete graph;
+    return VAICU_OK;
+}
+
+int vaicu_linear_plan_create(vaicu_device* dev, const vaicu_linear_desc* desc, vaicu_linear_plan** out)
+{
+    return build_plan(dev, desc, 0, out);
+}
+int vaicu_linear_plan_create_forced(vaicu_device* dev, const vaicu_linear_desc* desc, int kernel, vaicu_linear_plan** out)
+{
+    if (kernel < VAICU_KERNEL_GEMV || kernel > VAICU_KERNEL_TC_SKINNY) return VAICU_ERR_INVALID_VALUE;
+    return build_plan(dev, desc, kernel, out);
+}
+int vaicu_linear_plan_destroy(vaicu_linear_plan* plan)
+{
+    if (!plan) return VAICU_ERR_INVALID_VALUE;
+    delete plan;
+    return VAICU_OK;
+}
+int vaicu_linear_plan_info(const vaicu_linear_plan* plan, vaicu_linear_info* out)
+{
+    if (!plan || !out) return VAICU_ERR_INVALID_VALUE;
+    memset(out, 0, sizeof(*out));
+    out->kernel = plan->kernel;
+    out->launches = plan->launches;
+    out->workspace_bytes = plan->workspace_bytes;
+    out->split_count = 1;
+    if (plan->kernel == VAICU_KERNEL_FMA_TILE) {
+        out->split_count = plan->fma.split_count; out->tile_m = 64; out->tile_n = 64;
+    } else if (plan->tc) {
+        out->split_count = plan->tcp.splits;
+        const uint32_t outc = (plan->tcp.gate && !plan->tc_swap) ? plan->tcp.bn / 2u : plan->tcp.bn;
+        out->tile_m = plan->tc_swap ? outc : 128u;
+        out->tile_n = plan->tc_swap ? 128u : outc;
+    }
+    return VAICU_OK;
+}
+int vaicu_linear_workspace_bytes(const vaicu_linear_plan* plan, size_t* out)
+{
+    if (!plan || !out) return VAICU_ERR_INVALID_VALUE;
+    *out = plan->workspace_bytes;
+    return VAICU_OK;
+}
+
+int vaicu_linear_run(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W, const void* bias,
+                     const void* residual, void* O, void* workspace)
+{
+    if (!pl || !I || !W || !O) return VAICU_ERR_INVALID_VALUE;
+    const vaicu_linear_desc& d = pl->d;
+    if (d.has_bias && !bias) return VAICU_ERR_INVALID_VALUE;
+    if (d.has_residual && !residual) return VAICU_ERR_INVALID_VALUE;
+    auto elem_aligned = [](const void* p, int dt) { return (reinterpret_cast<uintptr_t>(p) & (dtype_size(dt) - 1u)) == 0; };
+    if (!elem_aligned(I, d.i_dtype) || !elem_aligned(W, d.w_dtype) || !elem_aligned(O, d.o_dtype)) return VAICU_ERR_ALIGNMENT;
+    if (d.has_bias && !elem_aligned(bias, d.b_dtype)) return VAICU_ERR_ALIGNMENT;
+    if (d.has_residual && !elem_aligned(residual, d.o_dtype)) return VAICU_ERR_ALIGNMENT;
+    if (pl->workspace_bytes && !workspace) return VAICU_ERR_WORKSPACE;
+    if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u)) return VAICU_ERR_ALIGNMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const LinearArgs a = make_args(d, I, W, d.has_bias ? bias : nullptr, d.has_residual ? residual : nullptr, O);
+
+    if (pl->kernel == VAICU_KERNEL_GEMV) {
+        const bool vec = aligned16(I) && aligned16(W);
+        VAICU_CUDA(launch_gemv(a, (vec && pl->gemv_vec.vectorized) ? pl->gemv_vec : pl->gemv_any, s));
+        return VAICU_OK;
+    }
+    if (pl->kernel == VAICU_KERNEL_FMA_TILE) return run_fma(pl, a, workspace, s);
+
+    // tensor-core path; operands TMA cannot address go to the FMA tile kernel
+    if (!aligned16(W) || (!pl->tc_cast && !aligned16(I))) return run_fma(pl, a, workspace, s);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    const void* act = I;
+    if (pl->tc_cast) {
+        VAICU_CUDA(launch_cast_f32_to_16(reinterpret_cast<const float*>(I), ws, d.w_dtype, (size_t)d.M * d.K, pl->dev->sm_count, s));
+        act = ws;
+    }
+    float* partial = pl->tcp.splits > 1u ? reinterpret_cast<float*>(ws + pl->ws_cast_bytes) : nullptr;
+    const bool gate = d.gate_fuse != 0;
+    const void* a_base = pl->tc_swap ? W : act;
+    const void* b_base = pl->tc_swap ? act : W;
+    if (a_base != pl->map_a_base) {
+        const uint32_t rows = pl->tc_swap ? d.N : d.M;
+        int rc = encode_map(&pl->map_a, a_base, d.w_dtype, rows, d.K, 128u);
+        if (rc != VAICU_OK) return rc;
+        pl->map_a_base = a_base;
+    }
+    if (b_base != pl->map_b_base) {
+        const uint32_t rows = pl->tc_swap ? d.M : d.N;
+        const uint32_t box = (gate && !pl->tc_swap) ? pl->tcp.bn / 2u : pl->tcp.bn;
+        int rc = encode_map(&pl->map_b, b_base, d.w_dtype, rows, d.K, box);
+        if (rc != VAICU_OK) return rc;
+        pl->map_b_base = b_base;
+    }
+    TcParams t = pl->tcp;
+    t.O = O; t.bias = a.bias; t.res = a.res; t.partial = partial;
+    t.o_aligned16 = aligned16(O) ? 1u : 0u;
+    VAICU_CUDA(launch_tc_gemm(pl->map_a, pl->map_b, t, pl->tc_swap, pl->tc_grid, pl->tc_smem, s));
+    if (partial) VAICU_CUDA(launch_splitk_reduce(a, partial, t.splits, s));
+    return VAICU_OK;
+}
+
+int vaicu_linear_shard_desc(const vaicu_linear_desc* full, int rank, int world, vaicu_linear_desc* shard,
+                            uint32_t* w_row_begin, uint32_t* w_row_count)
+{
+    if (!full || !shard || !w_row_begin || !w_row_count || world <= 0 || rank < 0 || rank >= world) return VAICU_ERR_INVALID_VALUE;
+    const uint32_t H = full->gate_fuse ? full->N / 2u : full->N;
+    if (full->gate_fuse && full->N % 2u) return VAICU_ERR_INVALID_VALUE;
+    // a column split keeps only per-column operands local; anything indexed over the whole of O is not sharded here
+    if (full->has_residual) return VAICU_ERR_UNSUPPORTED;
+    if (full->has_bias && full->bias_elems != full->N && !(full->bias_elems == 0 && full->M == 1u))
+        return VAICU_ERR_UNSUPPORTED;
+    const uint32_t base = H / (uint32_t)world, extra = H % (uint32_t)world;
+    const uint32_t begin = (uint32_t)rank * base + ((uint32_t)rank < extra ? (uint32_t)rank : extra);
+    const uint32_t count = base + ((uint32_t)rank < extra ? 1u : 0u);
+    if (count == 0) return VAICU_ERR_INVALID_VALUE;
+    *shard = *full;
+    shard->N = full->gate_fuse ? 2u * count : count;
+    if (full->has_bias) shard->bias_elems = shard->N;
+    *w_row_begin = begin;
+    *w_row_count = count;
+    return VAICU_OK;
+}
+
+const char* vaicu_status_string(int status)
+{
+    switch (status) {
+    case VAICU_OK: return "ok";
+    case VAICU_ERR_INVALID_VALUE: return "invalid value (null pointer, bad enum or shape)";
+    case VAICU_ERR_UNSUPPORTED: return "unsupported combination";
+    case VAICU_ERR_CUDA: return "CUDA call failed";
+    case VAICU_ERR_NO_DEVICE: return "no usable sm_100 device or driver";
+    case VAICU_ERR_WORKSPACE: return "workspace missing or too small";
+    case VAICU_ERR_ALIGNMENT: return "pointer alignment";
+    case VAICU_ERR_TOO_LARGE: return "shape exceeds the fixed capacity of this entry point";
+    case VAICU_ERR_TIMEOUT: return "a bounded device-side wait expired";
+    default: return "unknown status";
+    }
+}
+const char* vaicu_last_cuda_error(void) { return g_last_error; }
+int vaicu_version(void) { return 1000; }
+
+}  // extern "C"
+#pragma GCC visibility pop

@@ -1,0 +1,134 @@
+// Shared device/host helpers for the Linear kernels: dtype codes, element
+// load/store, the epilogue functions, the bias/residual broadcast rule.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/vaicu.h"
+
+namespace vaicu {
+
+// Internal, fully resolved description of one Linear call; filled by the plan.
+struct LinearArgs {
+    const void* I;
+    const void* W;
+    const void* bias;
+    const void* res;
+    void* O;
+    uint32_t M, N, K;      // N counts weight rows (2H when gate_fuse)
+    int32_t i_dtype, w_dtype, o_dtype, b_dtype;
+    int32_t has_bias, has_res, residual_order, epilogue, gate_fuse;
+    uint32_t bias_elems, res_elems;   // 0: covers O, else index modulo (vAi linear.h:2333-2338)
+    float scale;
+};
+
+__host__ __device__ inline uint32_t dtype_size(int dt) { return dt == VAICU_DTYPE_F32 ? 4u : 2u; }
+
+__device__ __forceinline__ float load_as_f32(const void* p, int dt, size_t i)
+{
+    if (dt == VAICU_DTYPE_F32) return reinterpret_cast<const float*>(p)[i];
+    if (dt == VAICU_DTYPE_F16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+__device__ __forceinline__ void store_from_f32(void* p, int dt, size_t i, float v)
+{
+    if (dt == VAICU_DTYPE_F32) reinterpret_cast<float*>(p)[i] = v;
+    else if (dt == VAICU_DTYPE_F16) reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+// Epilogue functions in fp32 with the reference's constants
+// (vAi vai/shaders/common/activation.h:19-58).
+__device__ __forceinline__ float erf_as(float x)   // Abramowitz-Stegun 7.1.26
+{
+    const float t = 1.0f / (1.0f + 0.3275911f * fabsf(x));
+    const float p = ((((1.061405429f * t - 1.453152027f) * t + 1.421413741f) * t - 0.284496736f) * t + 0.254829592f) * t;
+    const float s = (x > 0.0f) ? 1.0f : ((x < 0.0f) ? -1.0f : 0.0f);
+    return s * (1.0f - p * expf(-x * x));
+}
+
+__device__ __forceinline__ float apply_epilogue(int code, float x)
+{
+    switch (code) {
+    case VAICU_EPILOGUE_RELU: return fmaxf(x, 0.0f);
+    case VAICU_EPILOGUE_GELU: return 0.5f * x * (1.0f + erf_as(x * 0.707106781186547524400844f));
+    case VAICU_EPILOGUE_GELU_TANH: {
+        const float c = 0.797884560802865355879892f;
+        return 0.5f * x * (1.0f + tanhf(c * (x + 0.044715f * x * x * x)));
+    }
+    case VAICU_EPILOGUE_SILU: return x / (1.0f + expf(-x));
+    case VAICU_EPILOGUE_SIGMOID: return 1.0f / (1.0f + expf(-x));
+    default: return x;
+    }
+}
+
+// Everything after the dot product for one output element.
+struct EpilogueArgs {
+    const void* bias;
+    const void* res;
+    int32_t b_dtype, o_dtype;
+    int32_t has_bias, has_res, residual_order, epilogue;
+    uint32_t bias_elems, res_elems;
+    float scale;
+};
+
+__host__ __device__ inline EpilogueArgs make_epilogue_args(const LinearArgs& a)
+{
+    EpilogueArgs e;
+    e.bias = a.bias; e.res = a.res; e.b_dtype = a.b_dtype; e.o_dtype = a.o_dtype;
+    e.has_bias = a.has_bias; e.has_res = a.has_res; e.residual_order = a.residual_order;
+    e.epilogue = a.epilogue; e.bias_elems = a.bias_elems; e.res_elems = a.res_elems; e.scale = a.scale;
+    return e;
+}
+
+__device__ __forceinline__ float read_bias(const EpilogueArgs& e, size_t flat)
+{
+    if (!e.has_bias) return 0.0f;
+    return load_as_f32(e.bias, e.b_dtype, e.bias_elems ? flat % e.bias_elems : flat);
+}
+__device__ __forceinline__ float read_res(const EpilogueArgs& e, size_t flat)
+{
+    if (!e.has_res) return 0.0f;
+    return load_as_f32(e.res, e.o_dtype, e.res_elems ? flat % e.res_elems : flat);
+}
+
+// O = s*ep(acc + b) + R   or   s*ep(acc + b + R)   (vAi linear-slab.comp:236-241,
+// linear-reduce.comp:108-112).  `flat` is the row-major index into O [M, N].
+__device__ __forceinline__ float finish_output(const EpilogueArgs& e, float acc, size_t flat)
+{
+    const float a = acc + read_bias(e, flat);
+    const float r = read_res(e, flat);
+    return e.residual_order == VAICU_RESIDUAL_BEFORE_EPILOGUE ? e.scale * apply_epilogue(e.epilogue, a + r)
+                                                              : e.scale * apply_epilogue(e.epilogue, a) + r;
+}
+
+// Fused Linear + GatedMul (vAi vai/nodes/gated-mul.h:9-20): gate and value
+// accumulators of output column j; bias holds 2H entries, gate half first.
+// `flat` indexes O [M, H]; bias index is the weight row.
+__device__ __forceinline__ float finish_gated(const EpilogueArgs& e, float acc_gate, float acc_up,
+                                              uint32_t j, uint32_t H, size_t flat)
+{
+    float g = acc_gate, u = acc_up;
+    if (e.has_bias) {
+        g += load_as_f32(e.bias, e.b_dtype, j);
+        u += load_as_f32(e.bias, e.b_dtype, (size_t)H + j);
+    }
+    return e.scale * (apply_epilogue(e.epilogue, g) * u) + read_res(e, flat);
+}
+
+// Launchers implemented in the .cu files; each returns a cudaError_t.
+struct GemvConfig { int rows_per_warp; int k_warps; int grid; size_t smem; int vectorized; };
+
+cudaError_t launch_gemv(const LinearArgs& a, const GemvConfig& cfg, cudaStream_t stream);
+GemvConfig  choose_gemv(const LinearArgs& a, int sm_count, bool w_aligned16);
+
+struct FmaTileConfig { uint32_t split_count, split_size; };
+cudaError_t launch_fma_tile(const LinearArgs& a, const FmaTileConfig& cfg, float* partial, cudaStream_t stream);
+cudaError_t launch_splitk_reduce(const LinearArgs& a, const float* partial, uint32_t split_count, cudaStream_t stream);
+cudaError_t launch_cast_f32_to_16(const float* src, void* dst, int dst_dtype, size_t n, int sm_count, cudaStream_t stream);
+
+}  // namespace vaicu

@@ -1,0 +1,369 @@
+// Decode path of Linear: M <= 8 rows of activations against W [N, K].
+//
+// Stands where vAi's slab kernel does (vai/shaders/linear-slab.comp, chosen by
+// Linear::useSlabPath, vai/nodes/linear.h:320): one pass over the weights, fp32
+// accumulation, bias / epilogue / residual / scale fused into the store.  The
+// design is for HBM bandwidth on B200 rather than a translation of that shader:
+//   * every lane streams 16-byte weight vectors with ld.global.nc (no L1
+//     allocation); a warp reads 512 contiguous bytes of each of its R rows per
+//     step and keeps 2*R such loads in flight;
+//   * the activations are converted to fp32 once per block and kept in shared
+//     memory, laid out so that the float4 reads are bank-conflict free;
+//   * K is split over `k_warps` warps of a block when N alone cannot fill
+//     148 SMs; the fold goes through shared memory, no global scratch;
+//   * blocks are persistent over row groups (grid sized to the SM count).
+#include "common.cuh"
+
+namespace vaicu {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+template <typename TW> struct WTraits;
+template <> struct WTraits<float> {
+    static constexpr int VEC = 4;
+    __device__ static __forceinline__ void unpack(const uint4& v, float* f)
+    {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+        f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    }
+};
+template <> struct WTraits<__half> {
+    static constexpr int VEC = 8;
+    __device__ static __forceinline__ void unpack(const uint4& v, float* f)
+    {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            f[2 * i] = p.x; f[2 * i + 1] = p.y;
+        }
+    }
+};
+template <> struct WTraits<__nv_bfloat16> {
+    static constexpr int VEC = 8;
+    __device__ static __forceinline__ void unpack(const uint4& v, float* f)
+    {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p)
+{
+    uint4 v;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// Position of chunk-relative element kk inside the staged activations.  With
+// 8-element weight vectors a lane needs two float4 per step; splitting every
+// 256-element segment into two 128-float planes keeps both reads conflict free.
+template <int VEC> __device__ __forceinline__ uint32_t xs_pos(uint32_t kk)
+{
+    if (VEC == 4) return kk;
+    const uint32_t seg = kk & ~255u, r = kk & 255u;
+    return seg + ((r & 4u) << 5) + ((r >> 3) << 2) + (r & 3u);
+}
+
+struct GemvParams {
+    LinearArgs a;
+    uint32_t H;          // output columns (N, or N/2 when gate_fuse)
+    uint32_t cols_per_warp;
+    uint32_t k_warps;    // warps splitting K inside a block
+    uint32_t k_chunk;    // activations staged per round (multiple of 256)
+    uint32_t k_pad;      // floats reserved per activation row in shared memory
+};
+
+// R rows of W per warp step.  With gate_fuse the R rows are R/2 gate rows and
+// the R/2 value rows of the same output columns.
+template <typename TW, int M, int R>
+__global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p)
+{
+    constexpr int VEC = WTraits<TW>::VEC;
+    extern __shared__ __align__(16) float smem_f[];
+    float* xs = smem_f;                               // [M][k_pad]
+    float* red = smem_f + (size_t)M * p.k_pad;        // [kWarps][R*M]
+
+    const LinearArgs& a = p.a;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t KS = p.k_warps, RG = kWarps / KS;
+    const uint32_t rg = warp / KS, ks = warp % KS;
+    const uint32_t K = a.K, H = p.H;
+    const bool gate = a.gate_fuse != 0;
+    const uint32_t C = p.cols_per_warp;               // R, or R/2 with gate
+    const uint32_t ngroups = (H + C - 1u) / C;
+    const uint32_t nblocks = (ngroups + RG - 1u) / RG;
+    const uint32_t stride = KS * 32u * VEC;
+    const uint32_t nchunks = (K + p.k_chunk - 1u) / p.k_chunk;
+    const EpilogueArgs ep = make_epilogue_args(a);
+    const TW* Wp = reinterpret_cast<const TW*>(a.W);
+    bool staged = false;
+
+    for (uint32_t pb = blockIdx.x; pb < nblocks; pb += gridDim.x) {
+        const uint32_t g = pb * RG + rg;              // may be >= ngroups: rows clamp, stores skip
+        const uint32_t j0 = g * C;
+        const TW* rowp[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            uint32_t row;
+            if (gate) row = (r < R / 2) ? (j0 + r) : (H + j0 + (r - R / 2));
+            else row = j0 + r;
+            const uint32_t lim = gate ? ((r < R / 2) ? H - 1u : 2u * H - 1u) : (a.N - 1u);
+            row = row < lim ? row : lim;
+            rowp[r] = Wp + (size_t)row * K;
+        }
+        float acc[R][M];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+
+        for (uint32_t ch = 0; ch < nchunks; ++ch) {
+            const uint32_t c0 = ch * p.k_chunk;
+            const uint32_t c1 = (c0 + p.k_chunk < K) ? c0 + p.k_chunk : K;
+            if (nchunks > 1u || !staged) {
+                if (staged) __syncthreads();
+                for (uint32_t i = threadIdx.x; i < (uint32_t)M * (c1 - c0); i += kThreads) {
+                    const uint32_t m = i / (c1 - c0), kk = i - m * (c1 - c0);
+                    xs[(size_t)m * p.k_pad + xs_pos<VEC>(kk)] = load_as_f32(a.I, a.i_dtype, (size_t)m * K + c0 + kk);
+                }
+                __syncthreads();
+                staged = true;
+            }
+            const uint32_t span = c1 - c0;
+            const uint32_t iters = (span + stride - 1u) / stride;
+            const uint32_t kk0 = (ks * 32u + lane) * VEC;
+            for (uint32_t it = 0; it < iters; it += 2u) {
+                const uint32_t kkA = kk0 + it * stride, kkB = kkA + stride;
+                const bool vA = kkA < span, vB = (it + 1u < iters) && (kkB < span);
+                uint4 wA[R], wB[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    wA[r] = vA ? ldg_stream(rowp[r] + c0 + kkA) : make_uint4(0, 0, 0, 0);
+                    wB[r] = vB ? ldg_stream(rowp[r] + c0 + kkB) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const bool v = half ? vB : vA;
+                    if (!v) continue;
+                    const uint32_t kk = half ? kkB : kkA;
+                    float wf[R][VEC];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) WTraits<TW>::unpack(half ? wB[r] : wA[r], wf[r]);
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        float xf[VEC];
+                        const float* xrow = xs + (size_t)m * p.k_pad;
+                        if (VEC == 4) {
+                            const float4 t = *reinterpret_cast<const float4*>(xrow + kk);
+                            xf[0] = t.x; xf[1] = t.y; xf[2] = t.z; xf[3] = t.w;
+                        } else {
+                            const uint32_t base = (kk & ~255u) + ((kk & 255u) >> 1);   // lane*4 within the segment
+                            const float4 t0 = *reinterpret_cast<const float4*>(xrow + base);
+                            const float4 t1 = *reinterpret_cast<const float4*>(xrow + base + 128);
+                            xf[0] = t0.x; xf[1] = t0.y; xf[2] = t0.z; xf[3] = t0.w;
+                            xf[4 % VEC] = t1.x; xf[5 % VEC] = t1.y; xf[6 % VEC] = t1.z; xf[7 % VEC] = t1.w;
+                        }
+#pragma unroll
+                        for (int r = 0; r < R; ++r)
+#pragma unroll
+                            for (int e = 0; e < VEC; ++e) acc[r][m] = fmaf(wf[r][e], xf[e], acc[r][m]);
+                    }
+                }
+            }
+        }
+
+        // fold the 32 lanes of each warp
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float v = acc[r][m];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+                acc[r][m] = v;
+            }
+        // this lane's (row r, batch m) pair
+        float mine = 0.0f;
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+                if (lane == (uint32_t)(r * M + m)) mine = acc[r][m];
+        if (KS > 1u) {
+            if (lane < (uint32_t)(R * M)) red[warp * (R * M) + lane] = mine;
+            __syncthreads();
+            if (ks == 0u && lane < (uint32_t)(R * M)) {
+                mine = 0.0f;
+                for (uint32_t s = 0; s < KS; ++s) mine += red[(rg * KS + s) * (R * M) + lane];
+            }
+        }
+        if (ks == 0u && g < ngroups) {
+            if (!gate) {
+                if (lane < (uint32_t)(R * M)) {
+                    const uint32_t r = lane / M, m = lane % M;
+                    const uint32_t n = j0 + r;
+                    if (n < a.N) {
+                        const size_t flat = (size_t)m * a.N + n;
+                        store_from_f32(a.O, a.o_dtype, flat, finish_output(ep, mine, flat));
+                    }
+                }
+            } else {
+                // rows r < R/2 hold gate sums, rows r + R/2 the value sums of the same column
+                const float up = __shfl_sync(0xFFFFFFFFu, mine, (lane + (R / 2) * M) & 31u);
+                if (lane < (uint32_t)((R / 2) * M)) {
+                    const uint32_t r = lane / M, m = lane % M;
+                    const uint32_t j = j0 + r;
+                    if (j < H) {
+                        const size_t flat = (size_t)m * H + j;
+                        store_from_f32(a.O, a.o_dtype, flat, finish_gated(ep, mine, up, j, H, flat));
+                    }
+                }
+            }
+        }
+        if (KS > 1u) __syncthreads();   // red is reused by the next row group
+    }
+}
+
+// Any K, any alignment, any dtype mix: one warp per output column, scalar loads.
+// Used when K is not a multiple of the vector width or a pointer is not 16-byte
+// aligned (vAi's slab kernel has the same split: linear-slab.comp:98-116).
+__global__ void __launch_bounds__(kThreads) gemv_generic_kernel(const GemvParams p)
+{
+    const LinearArgs& a = p.a;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t col = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const uint32_t H = p.H;
+    if (col >= H) return;
+    const bool gate = a.gate_fuse != 0;
+    const EpilogueArgs ep = make_epilogue_args(a);
+    float acc[8], acc2[8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) { acc[m] = 0.0f; acc2[m] = 0.0f; }
+    for (uint32_t k = lane; k < a.K; k += 32u) {
+        const float w = load_as_f32(a.W, a.w_dtype, (size_t)col * a.K + k);
+        const float w2 = gate ? load_as_f32(a.W, a.w_dtype, (size_t)(H + col) * a.K + k) : 0.0f;
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+            if ((uint32_t)m < a.M) {
+                const float x = load_as_f32(a.I, a.i_dtype, (size_t)m * a.K + k);
+                acc[m] = fmaf(w, x, acc[m]);
+                acc2[m] = fmaf(w2, x, acc2[m]);
+            }
+    }
+#pragma unroll
+    for (int m = 0; m < 8; ++m)
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            acc[m] += __shfl_xor_sync(0xFFFFFFFFu, acc[m], off);
+            acc2[m] += __shfl_xor_sync(0xFFFFFFFFu, acc2[m], off);
+        }
+#pragma unroll
+    for (int m = 0; m < 8; ++m)
+        if (lane == (uint32_t)m && (uint32_t)m < a.M) {
+            const size_t flat = (size_t)m * H + col;
+            const float v = gate ? finish_gated(ep, acc[m], acc2[m], col, H, flat) : finish_output(ep, acc[m], flat);
+            store_from_f32(a.O, a.o_dtype, flat, v);
+        }
+}
+
+template <typename TW, int M, int R>
+cudaError_t launch_one(const GemvParams& p, const GemvConfig& cfg, cudaStream_t stream)
+{
+    auto kern = gemv_kernel<TW, M, R>;
+    if (cfg.smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.smem);
+        if (e != cudaSuccess) return e;
+    }
+    kern<<<cfg.grid, kThreads, cfg.smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename TW>
+cudaError_t launch_typed(const GemvParams& p, const GemvConfig& cfg, cudaStream_t stream)
+{
+    switch (p.a.M) {
+    case 1: return launch_one<TW, 1, 4>(p, cfg, stream);
+    case 2: return launch_one<TW, 2, 4>(p, cfg, stream);
+    case 3: return launch_one<TW, 3, 4>(p, cfg, stream);
+    case 4: return launch_one<TW, 4, 4>(p, cfg, stream);
+    case 5: return launch_one<TW, 5, 2>(p, cfg, stream);
+    case 6: return launch_one<TW, 6, 2>(p, cfg, stream);
+    case 7: return launch_one<TW, 7, 2>(p, cfg, stream);
+    case 8: return launch_one<TW, 8, 2>(p, cfg, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace
+
+// Shape -> launch geometry (the analogue of ggmlSlabWgSize, vAi linear.h:655-663:
+// deep-K layers with few rows get their K split over several warps).
+GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
+{
+    GemvConfig c{};
+    const int vec = a.w_dtype == VAICU_DTYPE_F32 ? 4 : 8;
+    const uint32_t H = a.gate_fuse ? a.N / 2u : a.N;
+    c.vectorized = ptrs_aligned16 && (a.K % (uint32_t)vec == 0u) && a.M >= 1u && a.M <= 8u;
+    if (!c.vectorized) {
+        c.rows_per_warp = 1; c.k_warps = 1; c.smem = 0;
+        c.grid = (int)((H + kWarps - 1u) / kWarps);
+        return c;
+    }
+    const int R = a.M <= 4u ? 4 : 2;
+    const uint32_t cols = a.gate_fuse ? (uint32_t)R / 2u : (uint32_t)R;
+    const uint32_t groups = (H + cols - 1u) / cols;
+    // split K over warps until there are about two 8-warp blocks per SM, while
+    // every warp keeps at least two 16-byte steps
+    int ks = 1;
+    while (ks < kWarps && (uint64_t)groups * ks < (uint64_t)sm_count * kWarps * 2u &&
+           a.K / (uint32_t)(ks * 2 * 32 * vec) >= 2u)
+        ks *= 2;
+    c.rows_per_warp = R;
+    c.k_warps = ks;
+    const uint32_t budget_floats = (96u * 1024u) / 4u / a.M;
+    uint32_t k_chunk = (budget_floats / 256u) * 256u;
+    const uint32_t k_round = ((a.K + 255u) / 256u) * 256u;
+    if (k_chunk > k_round) k_chunk = k_round;
+    c.smem = ((size_t)a.M * k_chunk + (size_t)kWarps * R * a.M) * sizeof(float);
+    const uint32_t rg = (uint32_t)kWarps / (uint32_t)ks;
+    const uint32_t nblocks = (groups + rg - 1u) / rg;
+    const uint32_t cap = (uint32_t)sm_count * 2u;
+    c.grid = (int)(nblocks < cap ? nblocks : cap);
+    return c;
+}
+
+cudaError_t launch_gemv(const LinearArgs& a, const GemvConfig& cfg, cudaStream_t stream)
+{
+    GemvParams p{};
+    p.a = a;
+    p.H = a.gate_fuse ? a.N / 2u : a.N;
+    if (!cfg.vectorized) {
+        gemv_generic_kernel<<<cfg.grid, kThreads, 0, stream>>>(p);
+        return cudaGetLastError();
+    }
+    p.cols_per_warp = a.gate_fuse ? (uint32_t)cfg.rows_per_warp / 2u : (uint32_t)cfg.rows_per_warp;
+    p.k_warps = (uint32_t)cfg.k_warps;
+    const uint32_t budget_floats = (96u * 1024u) / 4u / a.M;
+    uint32_t k_chunk = (budget_floats / 256u) * 256u;
+    const uint32_t k_round = ((a.K + 255u) / 256u) * 256u;
+    if (k_chunk > k_round) k_chunk = k_round;
+    p.k_chunk = k_chunk;
+    p.k_pad = k_chunk;
+    switch (a.w_dtype) {
+    case VAICU_DTYPE_F32: return launch_typed<float>(p, cfg, stream);
+    case VAICU_DTYPE_F16: return launch_typed<__half>(p, cfg, stream);
+    case VAICU_DTYPE_BF16: return launch_typed<__nv_bfloat16>(p, cfg, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace vaicu

@@ -1,0 +1,481 @@
+// Tensor-core kernel of the Linear path for M > 8: D = A . B^T with both
+// operands K-major 16-bit (bf16 or fp16), fp32 accumulation in tensor memory.
+//
+// Stands where vAi's cooperative-matrix tile kernel does
+// (vai/shaders/linear-cm-nv.comp, selected in vai/nodes/linear.h:2436), with the
+// bias / epilogue / residual / scale that the reference leaves to a second pass
+// (vai/shaders/linear-reduce.comp) fused into the store, and optionally the
+// GatedMul that follows a gate|value Linear (vai/nodes/gated-mul.h:9-20).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0    one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
+//             into a ring of shared-memory stages, signalled through mbarriers;
+//   warp 1    allocates tensor memory; one lane issues tcgen05.mma
+//             (cta_group::1, M = 128, N = bn, K = 16) and commits each stage back
+//             to the producer and each finished tile to the epilogue;
+//   warps 2-5 read the accumulator with tcgen05.ld (each warp owns 32 TMEM
+//             lanes), apply the epilogue and store.  Two accumulator buffers let
+//             the epilogue of tile i overlap the main loop of tile i+1.
+// "rows" operand A sits on the UMMA M axis (128 TMEM lanes), "cols" operand B on
+// the UMMA N axis (TMEM columns).  Large M: A = activations, B = weights.
+// Small M ("swap"): A = weights, B = activations, so a 128-row slab of W is
+// streamed once and the batch rides on N.
+// Every wait is bounded; on expiry the kernel records a status word and leaves.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tc_gemm.h"
+
+namespace vaicu {
+
+namespace {
+
+constexpr uint32_t BLOCK_K = 64;          // 64 x 2 bytes = one 128-byte swizzle row
+constexpr uint32_t UMMA_K = 16;
+constexpr uint32_t TILE_ROWS = 128;       // UMMA M
+constexpr uint32_t kTcThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 24; // bounded waits (each probe may sleep in hardware)
+
+// ---- PTX wrappers ---------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another role already
+// gave up (abort flag), so that no role spins forever.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
+{
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1u;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int32_t x, int32_t y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes,
+// stored with the 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO),
+// LBO is unused for swizzled K-major layouts (encoded 1), descriptor version 1,
+// layout type 2 (SWIZZLE_128B).  The tile base must be 1024-byte aligned.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
+{
+    const uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | (1u << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+// ---- epilogue store helpers -----------------------------------------------
+__device__ __forceinline__ void store16(void* O, int o_dtype, size_t flat, const float* v, bool vec_ok)
+{
+    if (vec_ok) {
+        if (o_dtype == VAICU_DTYPE_F32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(O) + flat);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else {
+            uint32_t w[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                if (o_dtype == VAICU_DTYPE_F16) {
+                    __half2 h = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
+                    w[q] = *reinterpret_cast<uint32_t*>(&h);
+                } else {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+                    w[q] = *reinterpret_cast<uint32_t*>(&h);
+                }
+            }
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(O) + flat);
+            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+    }
+}
+
+// Epilogue functions with the reference's formulas (vAi
+// vai/shaders/common/activation.h:19-58) on the fast exp / divide units; the
+// tanh is written through exp so that no slow path is taken per element.
+__device__ __forceinline__ float act_fast(int code, float x)
+{
+    switch (code) {
+    case VAICU_EPILOGUE_RELU: return fmaxf(x, 0.0f);
+    case VAICU_EPILOGUE_GELU: {
+        const float y = x * 0.707106781186547524400844f;
+        const float t = __fdividef(1.0f, 1.0f + 0.3275911f * fabsf(y));
+        const float pl = ((((1.061405429f * t - 1.453152027f) * t + 1.421413741f) * t - 0.284496736f) * t + 0.254829592f) * t;
+        const float e = 1.0f - pl * __expf(-y * y);
+        return 0.5f * x * (1.0f + copysignf(e, y));
+    }
+    case VAICU_EPILOGUE_GELU_TANH: {
+        const float u = 0.797884560802865355879892f * (x + 0.044715f * x * x * x);
+        const float th = 1.0f - __fdividef(2.0f, __expf(2.0f * u) + 1.0f);
+        return 0.5f * x * (1.0f + th);
+    }
+    case VAICU_EPILOGUE_SILU: return __fdividef(x, 1.0f + __expf(-x));
+    case VAICU_EPILOGUE_SIGMOID: return __fdividef(1.0f, 1.0f + __expf(-x));
+    default: return x;
+    }
+}
+
+// bias of weight row n for activation row m
+__device__ __forceinline__ float tc_bias(const TcParams& p, uint32_t m, uint32_t n)
+{
+    switch (p.bias_mode) {
+    case OPERAND_PER_COLUMN: return load_as_f32(p.bias, p.b_dtype, n);
+    case OPERAND_FULL: return load_as_f32(p.bias, p.b_dtype, (size_t)m * p.N + n);
+    case OPERAND_MODULO: return load_as_f32(p.bias, p.b_dtype, ((size_t)m * p.N + n) % p.bias_elems);
+    default: return 0.0f;
+    }
+}
+// residual of output element `flat` (row-major O), column j
+__device__ __forceinline__ float tc_res(const TcParams& p, size_t flat, uint32_t j)
+{
+    switch (p.res_mode) {
+    case OPERAND_PER_COLUMN: return load_as_f32(p.res, p.o_dtype, j);
+    case OPERAND_FULL: return load_as_f32(p.res, p.o_dtype, flat);
+    case OPERAND_MODULO: return load_as_f32(p.res, p.o_dtype, flat % p.res_elems);
+    default: return 0.0f;
+    }
+}
+__device__ __forceinline__ float tc_finish(const TcParams& p, float acc, uint32_t m, uint32_t n, size_t flat)
+{
+    const float a = acc + tc_bias(p, m, n);
+    const float r = tc_res(p, flat, n);
+    return p.residual_order == VAICU_RESIDUAL_BEFORE_EPILOGUE ? p.scale * act_fast(p.epilogue, a + r)
+                                                              : p.scale * act_fast(p.epilogue, a) + r;
+}
+__device__ __forceinline__ float tc_finish_gated(const TcParams& p, float g, float u, uint32_t m, uint32_t j, size_t flat)
+{
+    g += tc_bias(p, m, j);
+    u += tc_bias(p, m, p.H + j);
+    return p.scale * (act_fast(p.epilogue, g) * u) + tc_res(p, flat, j);
+}
+
+}  // namespace
+
+// SWAP: A (TMEM lanes) = weights, B (TMEM columns) = activations.
+// GATE: fused Linear + GatedMul.  Non-swap: the B stage holds bn/2 gate rows then
+//       bn/2 value rows; swap: the A stage holds 128 gate rows then 128 value rows
+//       and two MMAs per k-step fill two accumulators.
+template <bool SWAP, bool GATE>
+__global__ void __launch_bounds__(kTcThreads, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment is required by the 128-byte swizzle atoms
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t bn = p.bn;
+    const uint32_t a_boxes = (GATE && SWAP) ? 2u : 1u;
+    const uint32_t a_bytes = a_boxes * TILE_ROWS * BLOCK_K * 2u;
+    const uint32_t b_bytes = bn * BLOCK_K * 2u;
+    const uint32_t stage_bytes = a_bytes + b_bytes;        // multiple of 1024 (bn % 8 == 0)
+    const uint32_t stages = p.stages;
+    const uint32_t acc_cols = (GATE && SWAP) ? 2u * bn : bn;   // TMEM columns per accumulator buffer
+
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + stages;
+    uint64_t* acc_full = empty_bar + stages;      // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (uint32_t b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, p.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t num_work = p.num_tiles * p.splits;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+                const uint32_t tile = w / p.splits, z = w - tile * p.splits;
+                uint32_t ta, tb;
+                tile_coords(p, tile, ta, tb);
+                const uint32_t kb0 = z * p.kb_per_split;
+                const uint32_t kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
+                for (uint32_t kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    uint8_t* sa = smem + (size_t)stage * stage_bytes;
+                    uint8_t* sb = sa + a_bytes;
+                    mbar_expect_tx(&full_bar[stage], stage_bytes);
+                    const int32_t kx = (int32_t)(kb * BLOCK_K);
+                    if (GATE && SWAP) {
+                        tma_load_2d(sa, &tmap_a, &full_bar[stage], kx, (int32_t)(ta * TILE_ROWS));
+                        tma_load_2d(sa + TILE_ROWS * BLOCK_K * 2u, &tmap_a, &full_bar[stage], kx,
+                                    (int32_t)(p.H + ta * TILE_ROWS));
+                    } else {
+                        tma_load_2d(sa, &tmap_a, &full_bar[stage], kx, (int32_t)(ta * TILE_ROWS));
+                    }
+                    if (GATE && !SWAP) {
+                        const uint32_t half = bn / 2u;
+                        tma_load_2d(sb, &tmap_b, &full_bar[stage], kx, (int32_t)(tb * half));
+                        tma_load_2d(sb + half * BLOCK_K * 2u, &tmap_b, &full_bar[stage], kx, (int32_t)(p.H + tb * half));
+                    } else {
+                        tma_load_2d(sb, &tmap_b, &full_bar[stage], kx, (int32_t)(tb * bn));
+                    }
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, iter = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++iter) {
+                const uint32_t tile = w / p.splits, z = w - tile * p.splits;
+                const uint32_t kb0 = z * p.kb_per_split;
+                const uint32_t kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
+                const uint32_t buf = iter & 1u, use = iter >> 1;
+                if (!mbar_wait(&acc_empty[buf], (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * acc_cols;
+                for (uint32_t kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
+                    const uint32_t sb = sa + a_bytes;
+                    const uint64_t a_desc = make_smem_desc(sa);
+                    const uint64_t b_desc = make_smem_desc(sb);
+#pragma unroll
+                    for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+                        // advancing K by 16 elements = 32 bytes inside the swizzled row: +2 in the encoded address
+                        umma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, accum);
+                        if (GATE && SWAP) {
+                            const uint64_t a2_desc = make_smem_desc(sa + TILE_ROWS * BLOCK_K * 2u);
+                            umma_f16(d_tmem + bn, a2_desc + 2u * k, b_desc + 2u * k, p.idesc, accum);
+                        }
+                    }
+                    umma_commit(&empty_bar[stage]);     // stage reusable once these MMAs retire
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit(&acc_full[buf]);     // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const uint32_t q = warp & 3u;                    // TMEM lane quarter this warp may read
+        const uint32_t row_in_tile = q * 32u + lane;
+        const uint32_t out_cols = GATE ? p.H : p.N;      // width of O
+        const uint32_t osz = p.partial ? 4u : dtype_size(p.o_dtype);
+        uint32_t iter = 0;
+        bool ok = true;
+        for (uint32_t w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++iter) {
+            const uint32_t tile = w / p.splits, z = w - tile * p.splits;
+            uint32_t ta, tb;
+            tile_coords(p, tile, ta, tb);
+            const uint32_t buf = iter & 1u, use = iter >> 1;
+            if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((q * 32u) << 16) + buf * acc_cols;
+            // columns of the accumulator that map to distinct outputs
+            const uint32_t ncols = (GATE && !SWAP) ? bn / 2u : bn;
+            for (uint32_t c0 = 0; c0 < ncols; c0 += 16u) {
+                uint32_t r0[16], r1[16];
+                tmem_ld16(t_row + c0, r0);
+                if (GATE) tmem_ld16(t_row + c0 + (SWAP ? bn : bn / 2u), r1);
+                tmem_ld_wait();
+                if (p.partial) {
+                    // split-K: raw fp32 partial sums, [z][M][N]; epilogue runs in the reduce pass
+                    float* P = p.partial + (size_t)z * p.M * p.N;
+                    if (!SWAP) {
+                        const uint32_t m = ta * TILE_ROWS + row_in_tile;
+                        if (m < p.M) {
+#pragma unroll
+                            for (uint32_t c = 0; c < 16u; ++c) {
+                                const uint32_t col = c0 + c;
+                                if (GATE) {
+                                    const uint32_t j = tb * (bn / 2u) + col;
+                                    if (j < p.H) {
+                                        P[(size_t)m * p.N + j] = __uint_as_float(r0[c]);
+                                        P[(size_t)m * p.N + p.H + j] = __uint_as_float(r1[c]);
+                                    }
+                                } else {
+                                    const uint32_t n = tb * bn + col;
+                                    if (n < p.N) P[(size_t)m * p.N + n] = __uint_as_float(r0[c]);
+                                }
+                            }
+                        }
+                    } else {
+                        const uint32_t n = ta * TILE_ROWS + row_in_tile;
+                        const bool row_ok = GATE ? (n < p.H) : (n < p.N);
+#pragma unroll
+                        for (uint32_t c = 0; c < 16u; ++c) {
+                            const uint32_t m = tb * bn + c0 + c;
+                            if (row_ok && m < p.M) {
+                                P[(size_t)m * p.N + n] = __uint_as_float(r0[c]);
+                                if (GATE) P[(size_t)m * p.N + p.H + n] = __uint_as_float(r1[c]);
+                            }
+                        }
+                    }
+                } else if (!SWAP) {
+                    const uint32_t m = ta * TILE_ROWS + row_in_tile;
+                    const uint32_t j0 = (GATE ? tb * (bn / 2u) : tb * bn) + c0;
+                    if (m < p.M && j0 < out_cols) {
+                        float v[16];
+                        const size_t flat0 = (size_t)m * out_cols + j0;
+#pragma unroll
+                        for (uint32_t c = 0; c < 16u; ++c) {
+                            const uint32_t j = j0 + c;
+                            const uint32_t jj = j < out_cols ? j : out_cols - 1u;   // keep reads in range
+                            const size_t flat = (size_t)m * out_cols + jj;
+                            v[c] = GATE ? tc_finish_gated(p, __uint_as_float(r0[c]), __uint_as_float(r1[c]), m, jj, flat)
+                                        : tc_finish(p, __uint_as_float(r0[c]), m, jj, flat);
+                        }
+                        const bool vec_ok = (j0 + 16u <= out_cols) && (((size_t)flat0 * osz) % 16u == 0u) && p.o_aligned16;
+                        if (vec_ok) store16(p.O, p.o_dtype, flat0, v, true);
+                        else
+                            for (uint32_t c = 0; c < 16u && j0 + c < out_cols; ++c)
+                                store_from_f32(p.O, p.o_dtype, flat0 + c, v[c]);
+                    }
+                } else {
+                    const uint32_t n = ta * TILE_ROWS + row_in_tile;
+                    if (n < out_cols) {
+#pragma unroll
+                        for (uint32_t c = 0; c < 16u; ++c) {
+                            const uint32_t m = tb * bn + c0 + c;
+                            if (m < p.M) {
+                                const size_t flat = (size_t)m * out_cols + n;
+                                const float v = GATE ? tc_finish_gated(p, __uint_as_float(r0[c]), __uint_as_float(r1[c]), m, n, flat)
+                                                     : tc_finish(p, __uint_as_float(r0[c]), m, n, flat);
+                                store_from_f32(p.O, p.o_dtype, flat, v);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) {
+        atomicExch(p.status, 1);
+        // let copies that are still in flight land before the CTA's shared memory is released
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, p.tmem_cols);
+    }
+}
+
+template <bool SWAP, bool GATE>
+static cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, size_t smem,
+                                  cudaStream_t stream)
+{
+    auto kern = tc_gemm_kernel<SWAP, GATE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcMaxSmem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    kern<<<grid, kTcThreads, smem, stream>>>(ma, mb, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p, bool swap, int grid,
+                           size_t smem, cudaStream_t stream)
+{
+    const bool gate = p.gate != 0;
+    if (swap) return gate ? launch_variant<true, true>(map_a, map_b, p, grid, smem, stream)
+                          : launch_variant<true, false>(map_a, map_b, p, grid, smem, stream);
+    return gate ? launch_variant<false, true>(map_a, map_b, p, grid, smem, stream)
+                : launch_variant<false, false>(map_a, map_b, p, grid, smem, stream);
+}
+
+}  // namespace vaicu

@@ -1,0 +1,52 @@
+// Parameters shared by the host planner and the tcgen05 GEMM kernel.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vaicu {
+
+constexpr size_t kTcMaxSmem = 227u * 1024u;   // opt-in shared memory per CTA on sm_100
+
+// How bias / residual are indexed, resolved on the host so the epilogue avoids a
+// 64-bit modulo per element (rule: vAi vai/nodes/linear.h:2333-2338).
+enum { OPERAND_NONE = 0, OPERAND_PER_COLUMN = 1, OPERAND_FULL = 2, OPERAND_MODULO = 3 };
+
+struct TcParams {
+    void* O;
+    const void* bias;
+    const void* res;
+    float* partial;        // non-null: split-K, raw fp32 partials [splits][M][N]
+    int* status;           // device word set to 1 when a bounded wait expired
+    uint32_t M, N, K;      // Linear dims; N counts weight rows (2H with gate)
+    uint32_t H;            // output columns when gate (N / 2), else N
+    uint32_t bn;           // UMMA N
+    uint32_t idesc;        // tcgen05 instruction descriptor
+    uint32_t tiles_a, tiles_b, num_tiles, group;
+    uint32_t kblocks, kb_per_split, splits;
+    uint32_t stages, tmem_cols;
+    int32_t o_dtype, b_dtype, epilogue, residual_order, has_bias, has_res, gate;
+    int32_t bias_mode, res_mode;
+    uint32_t bias_elems, res_elems;
+    uint32_t o_aligned16;
+    float scale;
+};
+
+// Tile order: groups of `group` A-tiles (UMMA-M side) sweep all B-tiles before the
+// next group starts, so CTAs running at the same time share operand slabs in L2.
+__host__ __device__ inline void tile_coords(const TcParams& p, uint32_t tile, uint32_t& ta, uint32_t& tb)
+{
+    const uint32_t per_group = p.group * p.tiles_b;
+    const uint32_t g = tile / per_group;
+    const uint32_t first = g * p.group;
+    const uint32_t rows = (p.tiles_a - first < p.group) ? p.tiles_a - first : p.group;
+    const uint32_t local = tile - g * per_group;
+    ta = first + local % rows;
+    tb = local / rows;
+}
+
+cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p, bool swap, int grid,
+                           size_t smem, cudaStream_t stream);
+
+}  // namespace vaicu

@@ -1,0 +1,485 @@
+"""Host side of the Linear path, mirroring the `pyvai` surface the reference's
+node tests use (vAi python/bindings, python/tests/node_check.py): Dtype,
+Epilogue, ResidualOrder, Tensor, Node, NeuralNet and the `input - node - output`
+wiring.  Everything that touches the GPU goes through the C ABI (vai_b200._lib).
+
+Scope: what a graph of Linear nodes needs.  A net records once per input-shape
+set (prepare() + buffer binding + run(), vAi vai/engine/neural-net.cpp:406-518)
+and afterwards replays the recording (neural-net.h:391-438) — here a CUDA graph.
+"""
+import ctypes
+import enum
+import threading
+
+import numpy as np
+
+from . import _lib
+
+
+class Dtype(enum.IntEnum):
+    """vai::Dtype (vai/engine/tensor.h:19); BF16 is the one added value."""
+    F32 = 0
+    F16 = 1
+    NONE = 2
+    BF16 = 3
+
+
+class Epilogue(enum.IntEnum):
+    """vai::Epilogue (vai/nodes/common.h:31-39)."""
+    NONE = 0
+    RELU = 1
+    GELU = 2
+    GELU_TANH = 3
+    SILU = 4
+    SIGMOID = 5
+
+
+class ResidualOrder(enum.IntEnum):
+    """vai::ResidualOrder (vai/nodes/common.h:42-45)."""
+    AFTER_EPILOGUE = 0
+    BEFORE_EPILOGUE = 1
+
+
+def dtype_size(dt):
+    return 4 if dt == Dtype.F32 else 2
+
+
+# ---- host conversions (the loader's, vAi vai/engine/tensor.cpp:46-85) ---------
+
+def f32_to_f16_bits(a):
+    """fp32 -> fp16 bit patterns: round to nearest even, results below the smallest
+    normal flush to zero, overflow saturates to inf."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    with np.errstate(over="ignore"):
+        h = a.astype(np.float16)
+    tiny = np.abs(a) < np.float32(2.0 ** -14)
+    h = np.where(tiny, np.copysign(np.float16(0), a).astype(np.float16), h)
+    return h.view(np.uint16)
+
+
+def f32_to_bf16_bits(a):
+    """fp32 -> bf16 bit patterns, round to nearest even, NaN quieted."""
+    b = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    nan = ((b >> 23) & 0xFF == 0xFF) & ((b & 0x7FFFFF) != 0)
+    r = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+    return np.where(nan, ((b >> 16) | 0x40).astype(np.uint16), r)
+
+
+def bits_to_f32(bits, dt):
+    bits = np.ascontiguousarray(bits, dtype=np.uint16)
+    if dt == Dtype.F16:
+        return bits.view(np.float16).astype(np.float32)
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def encode(a, dt):
+    """fp32 values -> the array a device buffer of dtype `dt` holds."""
+    if dt == Dtype.F32:
+        return np.ascontiguousarray(a, dtype=np.float32)
+    return f32_to_f16_bits(a) if dt == Dtype.F16 else f32_to_bf16_bits(a)
+
+
+# ---- device objects ---------------------------------------------------------------
+
+class Device:
+    """One GPU (stands where eva::Device does, vAi vai/engine/neural-net.h:251-257)."""
+    _default = None
+    _lock = threading.Lock()
+
+    def __init__(self, ordinal=0):
+        self.lib = _lib.load()
+        h = ctypes.c_void_p()
+        _lib.check(self.lib.vaicu_device_open(ordinal, ctypes.byref(h)), "vaicu_device_open")
+        self.handle = h
+        self.ordinal = ordinal
+        n = ctypes.c_int()
+        _lib.check(self.lib.vaicu_device_sm_count(h, ctypes.byref(n)), "vaicu_device_sm_count")
+        self.sm_count = n.value
+
+    @classmethod
+    def default(cls):
+        with cls._lock:
+            if cls._default is None:
+                cls._default = Device(0)
+            return cls._default
+
+    def synchronize(self):
+        _lib.check(self.lib.vaicu_device_synchronize(self.handle), "vaicu_device_synchronize")
+
+    def check_status(self):
+        """Raises if a kernel reported an expired bounded wait since the last check."""
+        word = ctypes.c_int()
+        _lib.check(self.lib.vaicu_device_status(self.handle, ctypes.byref(word)), "vaicu_device_status")
+
+    def create_stream(self):
+        s = ctypes.c_void_p()
+        _lib.check(self.lib.vaicu_stream_create(self.handle, ctypes.byref(s)), "vaicu_stream_create")
+        return s
+
+
+class DeviceBuffer:
+    """cudaMalloc'ed range owned through the C ABI (eva::Buffer's place)."""
+
+    def __init__(self, device, nbytes):
+        self.device = device
+        h = ctypes.c_void_p()
+        _lib.check(device.lib.vaicu_buffer_alloc(device.handle, nbytes, ctypes.byref(h)), "vaicu_buffer_alloc")
+        self.handle = h
+        self.ptr = device.lib.vaicu_buffer_ptr(h)
+        self.nbytes = device.lib.vaicu_buffer_size(h)
+
+    def free(self):
+        if self.handle:
+            self.device.lib.vaicu_buffer_free(self.handle)
+            self.handle = None
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def upload(self, array, stream=None):
+        a = np.ascontiguousarray(array)
+        assert a.nbytes <= self.nbytes
+        _lib.check(self.device.lib.vaicu_memcpy_h2d(self.ptr, a.ctypes.data, a.nbytes, stream), "vaicu_memcpy_h2d")
+        if stream is not None:
+            _lib.check(self.device.lib.vaicu_stream_sync(stream), "vaicu_stream_sync")
+
+    def download(self, array, stream=None):
+        assert array.flags["C_CONTIGUOUS"] and array.nbytes <= self.nbytes
+        _lib.check(self.device.lib.vaicu_memcpy_d2h(array.ctypes.data, self.ptr, array.nbytes, stream), "vaicu_memcpy_d2h")
+        if stream is not None:
+            _lib.check(self.device.lib.vaicu_stream_sync(stream), "vaicu_stream_sync")
+        return array
+
+
+class BufferPool:
+    """Size-keyed reuse of device buffers (vAi vai/engine/buffer-pool.h:77-153)."""
+
+    def __init__(self, device):
+        self.device = device
+        self.free = {}
+
+    def request(self, nbytes):
+        nbytes = max(256, (nbytes + 255) // 256 * 256)
+        lst = self.free.get(nbytes)
+        return lst.pop() if lst else DeviceBuffer(self.device, nbytes)
+
+    def release(self, buf):
+        self.free.setdefault(buf.nbytes, []).append(buf)
+
+
+class Tensor:
+    """Shape + dtype + host array and/or device buffer (vAi vai/engine/tensor.h:111-332).
+    Copies share storage, as the reference's handle does."""
+
+    def __init__(self, shape=None, dtype=Dtype.F32):
+        self.shape = tuple(int(s) for s in shape) if shape is not None else None
+        self.dtype = Dtype(dtype)
+        self.host = None        # np.float32, or np.uint16 bit patterns for F16 / BF16
+        self.buffer = None      # DeviceBuffer
+        self.byte_offset = 0
+
+    @staticmethod
+    def from_numpy(array, dtype=None):
+        a = np.asarray(array)
+        if dtype is None:
+            dtype = Dtype.F16 if a.dtype == np.float16 else Dtype.F32
+        t = Tensor(a.shape, dtype)
+        if a.dtype == np.float16 and dtype == Dtype.F16:
+            t.host = np.ascontiguousarray(a).view(np.uint16)
+        elif a.dtype == np.uint16 and dtype != Dtype.F32:
+            t.host = np.ascontiguousarray(a)
+        else:
+            t.host = encode(a.astype(np.float32), dtype)
+        return t
+
+    def valid_shape(self):
+        return self.shape is not None
+
+    def num_elements(self):
+        return int(np.prod(self.shape)) if self.shape is not None else 0
+
+    def nbytes(self):
+        return self.num_elements() * dtype_size(self.dtype)
+
+    def astype(self, dtype):
+        """Host-side conversion (vAi Tensor dtype conversion, tensor.h:31-41)."""
+        if Dtype(dtype) == self.dtype:
+            return self
+        assert self.host is not None
+        vals = self.host if self.dtype == Dtype.F32 else bits_to_f32(self.host, self.dtype)
+        t = Tensor(self.shape, dtype)
+        t.host = encode(vals.reshape(self.shape), dtype)
+        return t
+
+    @property
+    def ptr(self):
+        return None if self.buffer is None else self.buffer.ptr + self.byte_offset
+
+    def to_device(self, device, pool=None):
+        if self.buffer is None:
+            self.buffer = pool.request(self.nbytes()) if pool else DeviceBuffer(device, self.nbytes())
+            if self.host is not None:
+                self.buffer.upload(self.host)
+        return self
+
+    def download_bits(self):
+        assert self.buffer is not None
+        self.buffer.device.synchronize()
+        out = np.empty(self.shape, dtype=np.float32 if self.dtype == Dtype.F32 else np.uint16)
+        return self.buffer.download(out)
+
+    def to_numpy(self):
+        """float32 for F32 / BF16, float16 for F16."""
+        raw = self.download_bits() if self.buffer is not None else self.host
+        if self.dtype == Dtype.F32:
+            return np.array(raw, dtype=np.float32)
+        if self.dtype == Dtype.F16:
+            return np.array(raw).view(np.float16)
+        return bits_to_f32(raw, Dtype.BF16)
+
+
+# ---- graph: slots, nodes, flows ----------------------------------------------------
+
+INPUT, OUTPUT, TEMPORARY, PERSISTENT = "input", "output", "temporary", "persistent"
+
+
+class Node:
+    """Operator base (vAi vai/engine/neural-net.h:150-226): named slots, prepare(),
+    run(stream).  A node attaches to the net being constructed on this thread."""
+
+    def __init__(self):
+        self.slots = {}
+        self.slot_types = {}
+        self.links = {}          # input slot -> (producer node, producer slot)
+        self.o_dtype = Dtype.NONE
+        self.net = NeuralNet._current()
+        if self.net is not None:
+            self.net._nodes.append(self)
+
+    def add_slot(self, name, kind):
+        self.slots[name] = Tensor()
+        self.slot_types[name] = kind
+
+    def __getitem__(self, name):
+        return self.slots[name]
+
+    def __setitem__(self, name, tensor):
+        if name not in self.slots:
+            raise KeyError(name)
+        self.slots[name] = tensor
+        if self.net is not None:
+            self.net._dirty = True
+
+    def set_o_dtype(self, dtype):
+        self.o_dtype = Dtype(dtype)
+
+    # `"slot" / node` picks the input slot, `node / "slot"` the output slot
+    def __rtruediv__(self, slot):
+        return Flow(self, in_slot=slot)
+
+    def __truediv__(self, slot):
+        return Flow(self, out_slot=slot)
+
+    def __sub__(self, other):
+        return Flow(self) - other
+
+    def prepare(self):
+        raise NotImplementedError
+
+    def bind(self):
+        """The launches of this node with the buffers bound right now, as a
+        callable(stream); what run() would record into a command buffer."""
+        raise NotImplementedError
+
+    def run(self, stream):
+        self.bind()(stream)
+
+
+class Flow:
+    """One hop of `a - b - c` (vAi vai/engine/graph-flow.h:26-63)."""
+
+    def __init__(self, node, in_slot="in0", out_slot="out0"):
+        self.node, self.in_slot, self.out_slot = node, in_slot, out_slot
+
+    def __truediv__(self, slot):
+        return Flow(self.node, self.in_slot, slot)
+
+    def __sub__(self, other):
+        nxt = other if isinstance(other, Flow) else Flow(other)
+        nxt.node.links[nxt.in_slot] = (self.node, self.out_slot)
+        return nxt
+
+
+class InputNode(Node):
+    def __init__(self, name):
+        super().__init__()
+        self.name = name
+        self.add_slot("out0", OUTPUT)
+
+    def prepare(self):
+        pass
+
+    def bind(self):
+        return lambda stream: None
+
+
+class OutputNode(Node):
+    def __init__(self, name):
+        super().__init__()
+        self.name = name
+        self.add_slot("in0", INPUT)
+
+    def prepare(self):
+        pass
+
+    def bind(self):
+        return lambda stream: None
+
+
+class _Recording:
+    def __init__(self):
+        self.input_tensors = {}
+        self.outputs = {}
+        self.graph = None
+        self.keep = []
+
+
+class NeuralNet:
+    """Graph owner (vAi vai/engine/neural-net.h:293-449) for graphs of the nodes in
+    this package.  `net(x)` / `net(in0=x, residual=r)` returns the output Tensor (a
+    dict when there are several outputs)."""
+    _tls = threading.local()
+
+    @classmethod
+    def _current(cls):
+        return getattr(cls._tls, "net", None)
+
+    def __init__(self, w_default_dtype=Dtype.F16, o_default_dtype=Dtype.F32, device=None, use_graph=True):
+        if Dtype(w_default_dtype) == Dtype.NONE or Dtype(o_default_dtype) == Dtype.NONE:
+            raise ValueError("default dtypes may not be NONE")
+        self.w_default_dtype = Dtype(w_default_dtype)
+        self.o_default_dtype = Dtype(o_default_dtype)
+        self.device = device or Device.default()
+        self.pool = BufferPool(self.device)
+        self.stream = self.device.create_stream()
+        self.use_graph = use_graph
+        self._nodes = []
+        self._inputs = {}
+        self._outputs = {}
+        self._recordings = {}
+        self._dirty = False
+        NeuralNet._tls.net = self
+
+    def input(self, name):
+        if name not in self._inputs:
+            self._inputs[name] = InputNode(name)
+        return Flow(self._inputs[name])
+
+    def output(self, name):
+        if name not in self._outputs:
+            self._outputs[name] = OutputNode(name)
+        return Flow(self._outputs[name])
+
+    def _sorted(self):
+        # Kahn's algorithm over the links (vAi neural-net.cpp:282-354)
+        indeg = {n: 0 for n in self._nodes}
+        users = {n: [] for n in self._nodes}
+        for n in self._nodes:
+            for src, _ in n.links.values():
+                indeg[n] += 1
+                users[src].append(n)
+        ready = [n for n in self._nodes if indeg[n] == 0]
+        order = []
+        while ready:
+            n = ready.pop(0)
+            order.append(n)
+            for u in users[n]:
+                indeg[u] -= 1
+                if indeg[u] == 0:
+                    ready.append(u)
+        if len(order) != len(self._nodes):
+            raise RuntimeError("the graph has a cycle")
+        return order
+
+    def _upload_params(self):
+        # persistent slots -> device in the dtype their tensor carries; a slot the
+        # loader left empty (Linear's "bias") stays off (vAi neural-net.cpp:356-404)
+        for n in self._nodes:
+            for name, kind in n.slot_types.items():
+                t = n.slots[name]
+                if kind == PERSISTENT and t.valid_shape() and t.buffer is None:
+                    t.to_device(self.device)
+
+    def _record(self, fed):
+        lib = self.device.lib
+        rec = _Recording()
+        for name, t in fed.items():
+            dev_t = Tensor(t.shape, t.dtype)
+            dev_t.buffer = self.pool.request(dev_t.nbytes())
+            rec.input_tensors[name] = dev_t
+            self._inputs[name].slots["out0"] = dev_t
+        order = self._sorted()
+        # prepare() fixes shapes and plans, then outputs / temporaries get buffers
+        steps = []
+        for n in order:
+            for slot, (src, src_slot) in n.links.items():
+                n.slots[slot] = src.slots[src_slot]
+            n.prepare()
+            for name, kind in n.slot_types.items():
+                t = n.slots[name]
+                if kind in (OUTPUT, TEMPORARY) and t.valid_shape() and t.buffer is None and t.nbytes() > 0:
+                    t.buffer = self.pool.request(t.nbytes())
+                    rec.keep.append(t)
+            steps.append(n.bind())
+        for name, out in self._outputs.items():
+            rec.outputs[name] = out.slots["in0"] if "in0" not in out.links else out.links["in0"][0].slots[out.links["in0"][1]]
+        if self.use_graph:
+            _lib.check(lib.vaicu_graph_capture_begin(self.stream), "vaicu_graph_capture_begin")
+            try:
+                for launch in steps:
+                    launch(self.stream)
+            finally:
+                g = ctypes.c_void_p()
+                rc = lib.vaicu_graph_capture_end(self.stream, ctypes.byref(g))
+            _lib.check(rc, "vaicu_graph_capture_end")
+            rec.graph = g
+        else:
+            rec.steps = steps
+        return rec
+
+    def __call__(self, *args, **kwargs):
+        names = list(self._inputs)
+        fed = dict(zip(names, args))
+        fed.update(kwargs)
+        if set(fed) != set(names):
+            raise ValueError(f"inputs {sorted(fed)} do not match the net's {sorted(names)}")
+        lib = self.device.lib
+        self._upload_params()
+        key = tuple((k, fed[k].shape, int(fed[k].dtype)) for k in sorted(fed))
+        if self._dirty:
+            self._recordings.clear()
+            self._dirty = False
+        rec = self._recordings.get(key)
+        if rec is None:
+            rec = self._record(fed)
+            self._recordings[key] = rec
+        for name, t in fed.items():
+            dst = rec.input_tensors[name]
+            _lib.check(lib.vaicu_memcpy_h2d(dst.ptr, t.host.ctypes.data, t.host.nbytes, self.stream), "vaicu_memcpy_h2d")
+        if rec.graph is not None:
+            _lib.check(lib.vaicu_graph_launch(rec.graph, self.stream), "vaicu_graph_launch")
+        else:
+            for launch in rec.steps:
+                launch(self.stream)
+        _lib.check(lib.vaicu_stream_sync(self.stream), "vaicu_stream_sync")
+        self.device.check_status()
+        outs = {}
+        for name, t in rec.outputs.items():
+            host = Tensor(t.shape, t.dtype)
+            host.host = t.download_bits()
+            outs[name] = host
+        return outs[next(iter(outs))] if len(outs) == 1 else outs

@@ -1,0 +1,147 @@
+"""LinearNode: the host side of vAi's `vai::node::Linear` (vai/nodes/linear.h:59-348),
+with the same Config fields, slot names, shapes and formula, launching the sm_100a
+kernels through the C ABI.  Python-facing signature as in the reference's binding
+(python/bindings/nodes/linear.cpp:7-29).
+"""
+import ctypes
+
+from . import _lib
+from .engine import (INPUT, OUTPUT, PERSISTENT, TEMPORARY, Dtype, Epilogue, Node, ResidualOrder, Tensor)
+
+KERNEL_AUTO, KERNEL_GEMV, KERNEL_FMA_TILE, KERNEL_TC_GEMM, KERNEL_TC_SKINNY = 0, 1, 2, 3, 4
+
+
+class LinearNode(Node):
+    """out0 = scalar_scale * epilogue(in0 W^T + bias) + residual, or with the residual
+    inside the epilogue per residual_order.  `bias` applies when it is set.
+    accept_residual opens the `residual` input; bias and residual are each
+    [..., out_dim] or rows that repeat over the output, such as [out_dim].
+    split_size is the K length per split-K span (0 = the kernel's heuristic, otherwise
+    >= 32) and only matters past 8 input rows.
+
+    gate_fuse (extension): `weight` holds [2H, K] with gate rows first (the layout of
+    vAi's gateValue Linear, vai/groups/gated-feed-forward.h:38) and out0 is
+    [..., H] = epilogue(gate) * value, i.e. the Linear and the GatedMul node that
+    follows it (vai/nodes/gated-mul.h:9-20) in one pass; out_dim stays 2H.
+    """
+
+    def __init__(self, in_dim, out_dim, accept_residual=False, residual_order=ResidualOrder.AFTER_EPILOGUE,
+                 epilogue=Epilogue.NONE, scalar_scale=1.0, split_size=0, gate_fuse=False, kernel=KERNEL_AUTO):
+        super().__init__()
+        if not (split_size == 0 or split_size >= 32):
+            raise ValueError("split_size: must be 0 or >= 32")
+        if in_dim <= 0 or out_dim <= 0:
+            raise ValueError("in_dim and out_dim must be positive")
+        if gate_fuse and (out_dim % 2 or accept_residual):
+            raise ValueError("gate_fuse needs an even out_dim and takes no residual")
+        self.in_dim, self.out_dim = int(in_dim), int(out_dim)
+        self.accept_residual = bool(accept_residual)
+        self.residual_order = ResidualOrder(residual_order)
+        self.epilogue = Epilogue(epilogue)
+        self.scalar_scale = float(scalar_scale)
+        self.split_size = int(split_size)
+        self.gate_fuse = bool(gate_fuse)
+        self.kernel = int(kernel)
+        # slot set of Linear::Linear (linear.h:2134-2144)
+        self.add_slot("out0", OUTPUT)
+        self.add_slot("in0", INPUT)
+        self.add_slot("weight", PERSISTENT)
+        self.add_slot("partial", TEMPORARY)
+        self.add_slot("bias", PERSISTENT)
+        if self.accept_residual:
+            self.add_slot("residual", INPUT)
+        self._plans = {}
+        self._plan = None
+        self.info = None
+
+    def has_bias(self):
+        return self["bias"].valid_shape()
+
+    def _device(self):
+        from .engine import Device
+        return self.net.device if self.net is not None else Device.default()
+
+    def prepare(self):
+        """Shape -> plan (Linear::prepare, linear.h:2291-2704): resolves dtypes, M, the
+        bias / residual repeat lengths, asks the library for a plan, sizes `partial`
+        and `out0`.  Touches no device memory."""
+        x, w = self["in0"], self["weight"]
+        if x.shape[-1] != self.in_dim:
+            raise ValueError(f"in0 last axis {x.shape[-1]} != in_dim {self.in_dim}")
+        if tuple(w.shape) != (self.out_dim, self.in_dim):
+            raise ValueError(f"weight shape {w.shape} != {(self.out_dim, self.in_dim)}")
+        o_dtype = self.o_dtype if self.o_dtype != Dtype.NONE else (self.net.o_default_dtype if self.net else Dtype.F32)
+        M = 1
+        for s in x.shape[:-1]:
+            M *= s
+        N, K = self.out_dim, self.in_dim
+        out_cols = N // 2 if self.gate_fuse else N
+
+        def repeat_of(t, row_len, total):
+            elems = t.num_elements()
+            if t.shape[-1] != row_len or elems == 0 or total % elems:
+                raise ValueError("operand does not tile the output")
+            return 0 if elems == total else elems
+
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = M, N, K
+        d.i_dtype, d.w_dtype, d.o_dtype = int(x.dtype), int(w.dtype), int(o_dtype)
+        d.b_dtype = int(Dtype.NONE)
+        if self.has_bias():
+            b = self["bias"]
+            d.has_bias, d.b_dtype = 1, int(b.dtype)
+            d.bias_elems = N if self.gate_fuse else repeat_of(b, N, M * N)
+        if self.accept_residual:
+            r = self["residual"]
+            if r.dtype != o_dtype:
+                raise ValueError("residual dtype must equal the output dtype")
+            d.has_residual = 1
+            d.residual_elems = repeat_of(r, out_cols, M * out_cols)
+        d.residual_order = int(self.residual_order)
+        d.epilogue = int(self.epilogue)
+        d.scalar_scale = self.scalar_scale
+        d.split_size = self.split_size
+        d.gate_fuse = 1 if self.gate_fuse else 0
+        key = bytes(d)
+        dev = self._device()
+        plan = self._plans.get(key)
+        if plan is None:
+            h = ctypes.c_void_p()
+            if self.kernel == KERNEL_AUTO:
+                rc = dev.lib.vaicu_linear_plan_create(dev.handle, ctypes.byref(d), ctypes.byref(h))
+            else:
+                rc = dev.lib.vaicu_linear_plan_create_forced(dev.handle, ctypes.byref(d), self.kernel, ctypes.byref(h))
+            _lib.check(rc, "vaicu_linear_plan_create")
+            info = _lib.LinearInfo()
+            _lib.check(dev.lib.vaicu_linear_plan_info(h, ctypes.byref(info)), "vaicu_linear_plan_info")
+            plan = (h, info)
+            self._plans[key] = plan
+        self._plan, self.info = plan
+        # `partial` carries the plan's whole workspace, as raw bytes
+        ws = self.info.workspace_bytes
+        self.slots["partial"] = Tensor((ws // 4,), Dtype.F32) if ws else Tensor()
+        self.slots["out0"] = Tensor(tuple(x.shape[:-1]) + (out_cols,), o_dtype)
+
+    def bind(self):
+        """Linear::run (linear.h:2706-2798) with today's buffers: a callable(stream)
+        that only enqueues work."""
+        dev = self._device()
+        plan = self._plan
+        x, w, o = self["in0"].ptr, self["weight"].ptr, self["out0"].ptr
+        b = self["bias"].ptr if self.has_bias() else None
+        r = self["residual"].ptr if self.accept_residual else None
+        ws = self["partial"].ptr if self["partial"].valid_shape() else None
+        run = dev.lib.vaicu_linear_run
+
+        def launch(stream):
+            _lib.check(run(plan, stream, x, w, b, r, o, ws), "vaicu_linear_run")
+
+        return launch
+
+    def __del__(self):
+        try:
+            lib = _lib.load()
+            for h, _ in self._plans.values():
+                lib.vaicu_linear_plan_destroy(h)
+        except Exception:
+            pass
