@@ -153,6 +153,16 @@ VAICU_API int vaicu_stream_create(vaicu_device* dev, vaicu_stream_t* out);
 VAICU_API int vaicu_stream_sync(vaicu_stream_t stream);
 VAICU_API int vaicu_stream_destroy(vaicu_stream_t stream);
 
+/* ---- events (replace the timestamp queries of NodeProfiler,
+ *      vai/engine/node-profiler.h:118-178) --------------------------------- */
+typedef struct vaicu_event vaicu_event;
+VAICU_API int vaicu_event_create(vaicu_event** out);
+VAICU_API int vaicu_event_record(vaicu_event* ev, vaicu_stream_t stream);
+VAICU_API int vaicu_event_synchronize(vaicu_event* ev);
+/* Milliseconds between two recorded, completed events. */
+VAICU_API int vaicu_event_elapsed_ms(vaicu_event* start, vaicu_event* stop, float* out_ms);
+VAICU_API int vaicu_event_destroy(vaicu_event* ev);
+
 /* ---- recorded launches (replace the command buffer that is recorded once and
  *      resubmitted while shapes repeat, vai/engine/neural-net.h:391-438) --- */
 typedef struct vaicu_graph vaicu_graph;

@@ -47,6 +47,11 @@ SIGNATURES = {
     "vaicu_stream_create": (ctypes.c_int, [ctypes.c_void_p, c_void_pp]),
     "vaicu_stream_sync": (ctypes.c_int, [ctypes.c_void_p]),
     "vaicu_stream_destroy": (ctypes.c_int, [ctypes.c_void_p]),
+    "vaicu_event_create": (ctypes.c_int, [c_void_pp]),
+    "vaicu_event_record": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+    "vaicu_event_synchronize": (ctypes.c_int, [ctypes.c_void_p]),
+    "vaicu_event_elapsed_ms": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]),
+    "vaicu_event_destroy": (ctypes.c_int, [ctypes.c_void_p]),
     "vaicu_graph_capture_begin": (ctypes.c_int, [ctypes.c_void_p]),
     "vaicu_graph_capture_end": (ctypes.c_int, [ctypes.c_void_p, c_void_pp]),
     "vaicu_graph_launch": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),

@@ -29,6 +29,9 @@ struct vaicu_buffer {
 struct vaicu_graph {
     cudaGraphExec_t exec;
 };
+struct vaicu_event {
+    cudaEvent_t ev;
+};
 
 namespace {
 
@@ -498,6 +501,43 @@ int vaicu_stream_destroy(vaicu_stream_t stream)
 {
     if (!stream) return VAICU_ERR_INVALID_VALUE;
     VAICU_CUDA(cudaStreamDestroy((cudaStream_t)stream));
+    return VAICU_OK;
+}
+
+int vaicu_event_create(vaicu_event** out)
+{
+    if (!out) return VAICU_ERR_INVALID_VALUE;
+    cudaEvent_t e;
+    VAICU_CUDA(cudaEventCreate(&e));
+    vaicu_event* r = new (std::nothrow) vaicu_event();
+    if (!r) { cudaEventDestroy(e); return VAICU_ERR_INVALID_VALUE; }
+    r->ev = e;
+    *out = r;
+    return VAICU_OK;
+}
+int vaicu_event_record(vaicu_event* ev, vaicu_stream_t stream)
+{
+    if (!ev) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaEventRecord(ev->ev, (cudaStream_t)stream));
+    return VAICU_OK;
+}
+int vaicu_event_synchronize(vaicu_event* ev)
+{
+    if (!ev) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaEventSynchronize(ev->ev));
+    return VAICU_OK;
+}
+int vaicu_event_elapsed_ms(vaicu_event* start, vaicu_event* stop, float* out_ms)
+{
+    if (!start || !stop || !out_ms) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaEventElapsedTime(out_ms, start->ev, stop->ev));
+    return VAICU_OK;
+}
+int vaicu_event_destroy(vaicu_event* ev)
+{
+    if (!ev) return VAICU_ERR_INVALID_VALUE;
+    cudaEventDestroy(ev->ev);
+    delete ev;
     return VAICU_OK;
 }
 
