@@ -21,37 +21,32 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 
+// A 16-byte weight vector as packed float2 pairs (element 2i, element 2i+1).
 template <typename TW> struct WTraits;
 template <> struct WTraits<float> {
     static constexpr int VEC = 4;
-    __device__ static __forceinline__ void unpack(const uint4& v, float* f)
+    __device__ static __forceinline__ void unpack(const uint4& v, float2* f)
     {
-        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
-        f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+        f[0] = make_float2(__uint_as_float(v.x), __uint_as_float(v.y));
+        f[1] = make_float2(__uint_as_float(v.z), __uint_as_float(v.w));
     }
 };
 template <> struct WTraits<__half> {
     static constexpr int VEC = 8;
-    __device__ static __forceinline__ void unpack(const uint4& v, float* f)
+    __device__ static __forceinline__ void unpack(const uint4& v, float2* f)
     {
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-            f[2 * i] = p.x; f[2 * i + 1] = p.y;
-        }
+        for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
     }
 };
 template <> struct WTraits<__nv_bfloat16> {
     static constexpr int VEC = 8;
-    __device__ static __forceinline__ void unpack(const uint4& v, float* f)
+    __device__ static __forceinline__ void unpack(const uint4& v, float2* f)
     {
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            f[2 * i] = __uint_as_float(w[i] << 16);
-            f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-        }
+        for (int i = 0; i < 4; ++i) f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
     }
 };
 
@@ -62,6 +57,15 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p)
         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// Programmatic dependent launch: the kernel after this one in the stream may start
+// its prologue as soon as every block here has passed launch_dependents(); a kernel
+// launched that way must not touch what its predecessor writes before
+// dependency_wait() returns (predecessor complete, its writes visible).  Both are
+// no-ops for a plain launch.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // Position of chunk-relative element kk inside the staged activations.  With
 // 8-element weight vectors a lane needs two float4 per step; splitting every
@@ -82,15 +86,43 @@ struct GemvParams {
     uint32_t k_pad;      // floats reserved per activation row in shared memory
 };
 
+// Four consecutive activations (chunk-relative kk, kk % 4 == 0) of row m -> fp32 in
+// shared memory.  K % 4 == 0 and a 16-byte aligned base make every load aligned.
+template <int VEC>
+__device__ __forceinline__ void stage4(const LinearArgs& a, float* xs_row, uint32_t m, uint32_t c0, uint32_t kk)
+{
+    const size_t g = (size_t)m * a.K + c0 + kk;
+    float4 v;
+    if (a.i_dtype == VAICU_DTYPE_F32) {
+        v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.I) + g);
+    } else {
+        const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(a.I) + g);
+        if (a.i_dtype == VAICU_DTYPE_F16) {
+            const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+            const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+            v = make_float4(p0.x, p0.y, p1.x, p1.y);
+        } else {
+            v = make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xFFFF0000u),
+                            __uint_as_float(w.y << 16), __uint_as_float(w.y & 0xFFFF0000u));
+        }
+    }
+    *reinterpret_cast<float4*>(xs_row + xs_pos<VEC>(kk)) = v;
+}
+
 // R rows of W per warp step.  With gate_fuse the R rows are R/2 gate rows and
-// the R/2 value rows of the same output columns.
+// the R/2 value rows of the same output columns.  Sums are kept as float2 pairs
+// (even / odd elements) and advanced with the packed fp32 FMA of sm_100, which
+// halves the FMA issue count: the kernel must stay memory-bound up to M = 8.
 template <typename TW, int M, int R>
-__global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p)
+__global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const GemvParams p)
 {
     constexpr int VEC = WTraits<TW>::VEC;
+    constexpr int PAIRS = VEC / 2;
     extern __shared__ __align__(16) float smem_f[];
     float* xs = smem_f;                               // [M][k_pad]
     float* red = smem_f + (size_t)M * p.k_pad;        // [kWarps][R*M]
+
+    launch_dependents();
 
     const LinearArgs& a = p.a;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -105,6 +137,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p)
     const uint32_t nchunks = (K + p.k_chunk - 1u) / p.k_chunk;
     const EpilogueArgs ep = make_epilogue_args(a);
     const TW* Wp = reinterpret_cast<const TW*>(a.W);
+    const uint32_t kk0 = (ks * 32u + lane) * VEC;
     bool staged = false;
 
     for (uint32_t pb = blockIdx.x; pb < nblocks; pb += gridDim.x) {
@@ -120,27 +153,39 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p)
             row = row < lim ? row : lim;
             rowp[r] = Wp + (size_t)row * K;
         }
-        float acc[R][M];
+        if (!staged) {
+            // The weights do not depend on the previous kernel: pull this warp's first
+            // vectors toward L2 while that kernel drains, then wait for its results.
+            const uint32_t first_span = p.k_chunk < K ? p.k_chunk : K;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                if (kk0 < first_span) prefetch_l2(rowp[r] + kk0);
+                if (kk0 + stride < first_span) prefetch_l2(rowp[r] + kk0 + stride);
+            }
+            dependency_wait();
+        }
+        float2 acc[R][M];
 #pragma unroll
         for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+            for (int m = 0; m < M; ++m) acc[r][m] = make_float2(0.0f, 0.0f);
 
         for (uint32_t ch = 0; ch < nchunks; ++ch) {
             const uint32_t c0 = ch * p.k_chunk;
             const uint32_t c1 = (c0 + p.k_chunk < K) ? c0 + p.k_chunk : K;
+            const uint32_t span = c1 - c0;
             if (nchunks > 1u || !staged) {
                 if (staged) __syncthreads();
-                for (uint32_t i = threadIdx.x; i < (uint32_t)M * (c1 - c0); i += kThreads) {
-                    const uint32_t m = i / (c1 - c0), kk = i - m * (c1 - c0);
-                    xs[(size_t)m * p.k_pad + xs_pos<VEC>(kk)] = load_as_f32(a.I, a.i_dtype, (size_t)m * K + c0 + kk);
+                const uint32_t quads = span >> 2;
+                for (uint32_t i = threadIdx.x; i < (uint32_t)M * quads; i += kThreads) {
+                    const uint32_t m = (M == 1) ? 0u : i / quads;
+                    const uint32_t kk = (i - m * quads) << 2;
+                    stage4<VEC>(a, xs + (size_t)m * p.k_pad, m, c0, kk);
                 }
                 __syncthreads();
                 staged = true;
             }
-            const uint32_t span = c1 - c0;
             const uint32_t iters = (span + stride - 1u) / stride;
-            const uint32_t kk0 = (ks * 32u + lane) * VEC;
             for (uint32_t it = 0; it < iters; it += 2u) {
                 const uint32_t kkA = kk0 + it * stride, kkB = kkA + stride;
                 const bool vA = kkA < span, vB = (it + 1u < iters) && (kkB < span);
@@ -155,41 +200,44 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p)
                     const bool v = half ? vB : vA;
                     if (!v) continue;
                     const uint32_t kk = half ? kkB : kkA;
-                    float wf[R][VEC];
-#pragma unroll
-                    for (int r = 0; r < R; ++r) WTraits<TW>::unpack(half ? wB[r] : wA[r], wf[r]);
+                    float2 xf[M][PAIRS];
 #pragma unroll
                     for (int m = 0; m < M; ++m) {
-                        float xf[VEC];
                         const float* xrow = xs + (size_t)m * p.k_pad;
                         if (VEC == 4) {
                             const float4 t = *reinterpret_cast<const float4*>(xrow + kk);
-                            xf[0] = t.x; xf[1] = t.y; xf[2] = t.z; xf[3] = t.w;
+                            xf[m][0] = make_float2(t.x, t.y); xf[m][1] = make_float2(t.z, t.w);
                         } else {
                             const uint32_t base = (kk & ~255u) + ((kk & 255u) >> 1);   // lane*4 within the segment
                             const float4 t0 = *reinterpret_cast<const float4*>(xrow + base);
                             const float4 t1 = *reinterpret_cast<const float4*>(xrow + base + 128);
-                            xf[0] = t0.x; xf[1] = t0.y; xf[2] = t0.z; xf[3] = t0.w;
-                            xf[4 % VEC] = t1.x; xf[5 % VEC] = t1.y; xf[6 % VEC] = t1.z; xf[7 % VEC] = t1.w;
+                            xf[m][0] = make_float2(t0.x, t0.y); xf[m][1] = make_float2(t0.z, t0.w);
+                            xf[m][2 % PAIRS] = make_float2(t1.x, t1.y); xf[m][3 % PAIRS] = make_float2(t1.z, t1.w);
                         }
+                    }
 #pragma unroll
-                        for (int r = 0; r < R; ++r)
+                    for (int r = 0; r < R; ++r) {
+                        float2 wf[PAIRS];
+                        WTraits<TW>::unpack(half ? wB[r] : wA[r], wf);
 #pragma unroll
-                            for (int e = 0; e < VEC; ++e) acc[r][m] = fmaf(wf[r][e], xf[e], acc[r][m]);
+                        for (int m = 0; m < M; ++m)
+#pragma unroll
+                            for (int e = 0; e < PAIRS; ++e) acc[r][m] = __ffma2_rn(wf[e], xf[m][e], acc[r][m]);
                     }
                 }
             }
         }
 
-        // fold the 32 lanes of each warp
+        // fold the pair and the 32 lanes of each warp
+        float sums[R][M];
 #pragma unroll
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int m = 0; m < M; ++m) {
-                float v = acc[r][m];
+                float v = acc[r][m].x + acc[r][m].y;
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
-                acc[r][m] = v;
+                sums[r][m] = v;
             }
         // this lane's (row r, batch m) pair
         float mine = 0.0f;
@@ -197,7 +245,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvParams p)
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int m = 0; m < M; ++m)
-                if (lane == (uint32_t)(r * M + m)) mine = acc[r][m];
+                if (lane == (uint32_t)(r * M + m)) mine = sums[r][m];
         if (KS > 1u) {
             if (lane < (uint32_t)(R * M)) red[warp * (R * M) + lane] = mine;
             __syncthreads();
@@ -279,12 +327,26 @@ template <typename TW, int M, int R>
 cudaError_t launch_one(const GemvParams& p, const GemvConfig& cfg, cudaStream_t stream)
 {
     auto kern = gemv_kernel<TW, M, R>;
-    if (cfg.smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.smem);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
         if (e != cudaSuccess) return e;
+        configured = true;
     }
-    kern<<<cfg.grid, kThreads, cfg.smem, stream>>>(p);
-    return cudaGetLastError();
+    // Programmatic stream serialization: this launch may begin while the kernel ahead
+    // of it in the stream drains; gemv_kernel itself waits (dependency_wait) before it
+    // reads anything that kernel produced.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)cfg.grid);
+    lc.blockDim = dim3(kThreads);
+    lc.dynamicSmemBytes = cfg.smem;
+    lc.stream = stream;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    return cudaLaunchKernelEx(&lc, kern, p);
 }
 
 template <typename TW>

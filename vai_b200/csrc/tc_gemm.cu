@@ -160,62 +160,186 @@ __device__ __forceinline__ void store16(void* O, int o_dtype, size_t flat, const
 }
 
 // Epilogue functions with the reference's formulas (vAi
-// vai/shaders/common/activation.h:19-58) on the fast exp / divide units; the
-// tanh is written through exp so that no slow path is taken per element.
-__device__ __forceinline__ float act_fast(int code, float x)
+// vai/shaders/common/activation.h:19-58) on the fast exp / divide units; the tanh
+// is written through exp.  Sixteen values at a time with the switch outside the
+// loops: each case is straight-line code, so the epilogue warps fetch one short
+// path instead of a branch tree per element.
+__device__ __forceinline__ void act16(int code, float* v)
 {
     switch (code) {
-    case VAICU_EPILOGUE_RELU: return fmaxf(x, 0.0f);
-    case VAICU_EPILOGUE_GELU: {
-        const float y = x * 0.707106781186547524400844f;
-        const float t = __fdividef(1.0f, 1.0f + 0.3275911f * fabsf(y));
-        const float pl = ((((1.061405429f * t - 1.453152027f) * t + 1.421413741f) * t - 0.284496736f) * t + 0.254829592f) * t;
-        const float e = 1.0f - pl * __expf(-y * y);
-        return 0.5f * x * (1.0f + copysignf(e, y));
-    }
-    case VAICU_EPILOGUE_GELU_TANH: {
-        const float u = 0.797884560802865355879892f * (x + 0.044715f * x * x * x);
-        const float th = 1.0f - __fdividef(2.0f, __expf(2.0f * u) + 1.0f);
-        return 0.5f * x * (1.0f + th);
-    }
-    case VAICU_EPILOGUE_SILU: return __fdividef(x, 1.0f + __expf(-x));
-    case VAICU_EPILOGUE_SIGMOID: return __fdividef(1.0f, 1.0f + __expf(-x));
-    default: return x;
+    case VAICU_EPILOGUE_RELU:
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] = fmaxf(v[c], 0.0f);
+        break;
+    case VAICU_EPILOGUE_GELU:
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            const float x = v[c], y = x * 0.707106781186547524400844f;
+            const float t = __fdividef(1.0f, 1.0f + 0.3275911f * fabsf(y));
+            const float pl = ((((1.061405429f * t - 1.453152027f) * t + 1.421413741f) * t - 0.284496736f) * t + 0.254829592f) * t;
+            v[c] = 0.5f * x * (1.0f + copysignf(1.0f - pl * __expf(-y * y), y));
+        }
+        break;
+    case VAICU_EPILOGUE_GELU_TANH:
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            const float x = v[c];
+            const float u = 0.797884560802865355879892f * (x + 0.044715f * x * x * x);
+            v[c] = 0.5f * x * (2.0f - __fdividef(2.0f, __expf(2.0f * u) + 1.0f));
+        }
+        break;
+    case VAICU_EPILOGUE_SILU:
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] = __fdividef(v[c], 1.0f + __expf(-v[c]));
+        break;
+    case VAICU_EPILOGUE_SIGMOID:
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] = __fdividef(1.0f, 1.0f + __expf(-v[c]));
+        break;
+    default: break;
     }
 }
 
-// bias of weight row n for activation row m
-__device__ __forceinline__ float tc_bias(const TcParams& p, uint32_t m, uint32_t n)
+// f[c] = element idx0 + c of a dtype'd array, c < 16; elements at or past n_valid
+// repeat the last valid one (their results are never stored).
+__device__ __forceinline__ void load16(const void* base, int dt, size_t idx0, uint32_t n_valid, float* f)
 {
-    switch (p.bias_mode) {
-    case OPERAND_PER_COLUMN: return load_as_f32(p.bias, p.b_dtype, n);
-    case OPERAND_FULL: return load_as_f32(p.bias, p.b_dtype, (size_t)m * p.N + n);
-    case OPERAND_MODULO: return load_as_f32(p.bias, p.b_dtype, ((size_t)m * p.N + n) % p.bias_elems);
-    default: return 0.0f;
+    const uint32_t esz = dtype_size(dt);
+    const bool vec = n_valid >= 16u && (((reinterpret_cast<uintptr_t>(base) + idx0 * esz) & 15u) == 0);
+    if (dt == VAICU_DTYPE_F32) {
+        const float* s = reinterpret_cast<const float*>(base) + idx0;
+        if (vec) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 t = reinterpret_cast<const float4*>(s)[q];
+                f[4 * q] = t.x; f[4 * q + 1] = t.y; f[4 * q + 2] = t.z; f[4 * q + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (uint32_t c = 0; c < 16u; ++c) f[c] = s[c < n_valid ? c : n_valid - 1u];
+        }
+    } else {
+        const uint16_t* s = reinterpret_cast<const uint16_t*>(base) + idx0;
+        uint32_t w[8];
+        if (vec) {
+            const uint4 t0 = reinterpret_cast<const uint4*>(s)[0], t1 = reinterpret_cast<const uint4*>(s)[1];
+            w[0] = t0.x; w[1] = t0.y; w[2] = t0.z; w[3] = t0.w; w[4] = t1.x; w[5] = t1.y; w[6] = t1.z; w[7] = t1.w;
+        } else {
+#pragma unroll
+            for (uint32_t q = 0; q < 8u; ++q) {
+                const uint32_t i0 = 2u * q < n_valid ? 2u * q : n_valid - 1u;
+                const uint32_t i1 = 2u * q + 1u < n_valid ? 2u * q + 1u : n_valid - 1u;
+                w[q] = (uint32_t)s[i0] | ((uint32_t)s[i1] << 16);
+            }
+        }
+        if (dt == VAICU_DTYPE_F16) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[q]));
+                f[2 * q] = t.x; f[2 * q + 1] = t.y;
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                f[2 * q] = __uint_as_float(w[q] << 16);
+                f[2 * q + 1] = __uint_as_float(w[q] & 0xFFFF0000u);
+            }
+        }
     }
 }
-// residual of output element `flat` (row-major O), column j
-__device__ __forceinline__ float tc_res(const TcParams& p, size_t flat, uint32_t j)
+
+// 16 consecutive output columns [j0, j0+16) of activation row m (kernel without swap).
+// v: accumulators (gate half with GATE), u: value-half accumulators.
+template <bool GATE>
+__device__ __forceinline__ void finish_row16(const TcParams& p, float* v, float* u, uint32_t m, uint32_t j0,
+                                             uint32_t out_cols, uint32_t n_valid)
 {
-    switch (p.res_mode) {
-    case OPERAND_PER_COLUMN: return load_as_f32(p.res, p.o_dtype, j);
-    case OPERAND_FULL: return load_as_f32(p.res, p.o_dtype, flat);
-    case OPERAND_MODULO: return load_as_f32(p.res, p.o_dtype, flat % p.res_elems);
-    default: return 0.0f;
+    const size_t flat0 = (size_t)m * out_cols + j0;
+    float t[16];
+    if (p.bias_mode == OPERAND_PER_COLUMN) {
+        load16(p.bias, p.b_dtype, j0, n_valid, t);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] += t[c];
+        if (GATE) {
+            load16(p.bias, p.b_dtype, (size_t)p.H + j0, n_valid, t);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) u[c] += t[c];
+        }
+    } else if (p.bias_mode != OPERAND_NONE) {   // [M,N] or repeating tables (never with GATE)
+        for (uint32_t c = 0; c < 16u; ++c) {
+            const size_t i = (size_t)m * p.N + j0 + (c < n_valid ? c : n_valid - 1u);
+            v[c] += load_as_f32(p.bias, p.b_dtype, p.bias_mode == OPERAND_MODULO ? i % p.bias_elems : i);
+        }
+    }
+    if (p.res_mode == OPERAND_FULL) load16(p.res, p.o_dtype, flat0, n_valid, t);
+    else if (p.res_mode == OPERAND_PER_COLUMN) load16(p.res, p.o_dtype, j0, n_valid, t);
+    else if (p.res_mode == OPERAND_MODULO)
+        for (uint32_t c = 0; c < 16u; ++c) t[c] = load_as_f32(p.res, p.o_dtype, (flat0 + (c < n_valid ? c : n_valid - 1u)) % p.res_elems);
+    const bool before = p.res_mode != OPERAND_NONE && p.residual_order == VAICU_RESIDUAL_BEFORE_EPILOGUE;
+    const bool after = p.res_mode != OPERAND_NONE && !before;
+    if (before) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] += t[c];
+    }
+    act16(p.epilogue, v);
+    if (GATE) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] *= u[c];
+    }
+    if (p.scale != 1.0f) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] *= p.scale;
+    }
+    if (after) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] += t[c];
     }
 }
-__device__ __forceinline__ float tc_finish(const TcParams& p, float acc, uint32_t m, uint32_t n, size_t flat)
+
+// Swapped kernel: this thread owns weight row n; the 16 values are activation rows
+// m0 .. m0+15 of that output column.
+template <bool GATE>
+__device__ __forceinline__ void finish_col16(const TcParams& p, float* v, float* u, uint32_t n, uint32_t m0,
+                                             uint32_t out_cols, float bias_n, float bias_up)
 {
-    const float a = acc + tc_bias(p, m, n);
-    const float r = tc_res(p, flat, n);
-    return p.residual_order == VAICU_RESIDUAL_BEFORE_EPILOGUE ? p.scale * act_fast(p.epilogue, a + r)
-                                                              : p.scale * act_fast(p.epilogue, a) + r;
-}
-__device__ __forceinline__ float tc_finish_gated(const TcParams& p, float g, float u, uint32_t m, uint32_t j, size_t flat)
-{
-    g += tc_bias(p, m, j);
-    u += tc_bias(p, m, p.H + j);
-    return p.scale * (act_fast(p.epilogue, g) * u) + tc_res(p, flat, j);
+    float t[16];
+    if (p.bias_mode == OPERAND_PER_COLUMN) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) { v[c] += bias_n; if (GATE) u[c] += bias_up; }
+    } else if (p.bias_mode != OPERAND_NONE) {
+        for (uint32_t c = 0; c < 16u; ++c) {
+            const uint32_t m = m0 + c < p.M ? m0 + c : p.M - 1u;
+            const size_t i = (size_t)m * p.N + n;
+            v[c] += load_as_f32(p.bias, p.b_dtype, p.bias_mode == OPERAND_MODULO ? i % p.bias_elems : i);
+        }
+    }
+    if (p.res_mode != OPERAND_NONE) {
+        for (uint32_t c = 0; c < 16u; ++c) {
+            const uint32_t m = m0 + c < p.M ? m0 + c : p.M - 1u;
+            const size_t flat = (size_t)m * out_cols + n;
+            t[c] = load_as_f32(p.res, p.o_dtype,
+                               p.res_mode == OPERAND_FULL ? flat : (p.res_mode == OPERAND_PER_COLUMN ? n : flat % p.res_elems));
+        }
+    }
+    const bool before = p.res_mode != OPERAND_NONE && p.residual_order == VAICU_RESIDUAL_BEFORE_EPILOGUE;
+    const bool after = p.res_mode != OPERAND_NONE && !before;
+    if (before) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] += t[c];
+    }
+    act16(p.epilogue, v);
+    if (GATE) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] *= u[c];
+    }
+    if (p.scale != 1.0f) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] *= p.scale;
+    }
+    if (after) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] += t[c];
+    }
 }
 
 }  // namespace
@@ -355,6 +479,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((q * 32u) << 16) + buf * acc_cols;
+            float bias_n = 0.0f, bias_up = 0.0f;
+            if (SWAP && !p.partial && p.bias_mode == OPERAND_PER_COLUMN) {
+                const uint32_t n = ta * TILE_ROWS + row_in_tile;
+                if (n < out_cols) {
+                    bias_n = load_as_f32(p.bias, p.b_dtype, n);
+                    if (GATE) bias_up = load_as_f32(p.bias, p.b_dtype, (size_t)p.H + n);
+                }
+            }
             // columns of the accumulator that map to distinct outputs
             const uint32_t ncols = (GATE && !SWAP) ? bn / 2u : bn;
             for (uint32_t c0 = 0; c0 < ncols; c0 += 16u) {
@@ -399,34 +531,40 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint32_t m = ta * TILE_ROWS + row_in_tile;
                     const uint32_t j0 = (GATE ? tb * (bn / 2u) : tb * bn) + c0;
                     if (m < p.M && j0 < out_cols) {
-                        float v[16];
-                        const size_t flat0 = (size_t)m * out_cols + j0;
+                        float v[16], u[16];
 #pragma unroll
-                        for (uint32_t c = 0; c < 16u; ++c) {
-                            const uint32_t j = j0 + c;
-                            const uint32_t jj = j < out_cols ? j : out_cols - 1u;   // keep reads in range
-                            const size_t flat = (size_t)m * out_cols + jj;
-                            v[c] = GATE ? tc_finish_gated(p, __uint_as_float(r0[c]), __uint_as_float(r1[c]), m, jj, flat)
-                                        : tc_finish(p, __uint_as_float(r0[c]), m, jj, flat);
-                        }
-                        const bool vec_ok = (j0 + 16u <= out_cols) && (((size_t)flat0 * osz) % 16u == 0u) && p.o_aligned16;
+                        for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
+                        const uint32_t n_valid = out_cols - j0 < 16u ? out_cols - j0 : 16u;
+                        finish_row16<GATE>(p, v, u, m, j0, out_cols, n_valid);
+                        const size_t flat0 = (size_t)m * out_cols + j0;
+                        const bool vec_ok = n_valid == 16u && (((size_t)flat0 * osz) % 16u == 0u) && p.o_aligned16;
                         if (vec_ok) store16(p.O, p.o_dtype, flat0, v, true);
                         else
-                            for (uint32_t c = 0; c < 16u && j0 + c < out_cols; ++c)
-                                store_from_f32(p.O, p.o_dtype, flat0 + c, v[c]);
+                            for (uint32_t c = 0; c < n_valid; ++c) store_from_f32(p.O, p.o_dtype, flat0 + c, v[c]);
                     }
                 } else {
                     const uint32_t n = ta * TILE_ROWS + row_in_tile;
                     if (n < out_cols) {
+                        float v[16], u[16];
 #pragma unroll
-                        for (uint32_t c = 0; c < 16u; ++c) {
-                            const uint32_t m = tb * bn + c0 + c;
-                            if (m < p.M) {
-                                const size_t flat = (size_t)m * out_cols + n;
-                                const float v = GATE ? tc_finish_gated(p, __uint_as_float(r0[c]), __uint_as_float(r1[c]), m, n, flat)
-                                                     : tc_finish(p, __uint_as_float(r0[c]), m, n, flat);
-                                store_from_f32(p.O, p.o_dtype, flat, v);
-                            }
+                        for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
+                        const uint32_t m0 = tb * bn + c0;
+                        finish_col16<GATE>(p, v, u, n, m0, out_cols, bias_n, bias_up);
+                        if (p.o_dtype == VAICU_DTYPE_F32) {
+                            float* O = reinterpret_cast<float*>(p.O);
+#pragma unroll
+                            for (uint32_t c = 0; c < 16u; ++c)
+                                if (m0 + c < p.M) O[(size_t)(m0 + c) * out_cols + n] = v[c];
+                        } else if (p.o_dtype == VAICU_DTYPE_F16) {
+                            __half* O = reinterpret_cast<__half*>(p.O);
+#pragma unroll
+                            for (uint32_t c = 0; c < 16u; ++c)
+                                if (m0 + c < p.M) O[(size_t)(m0 + c) * out_cols + n] = __float2half_rn(v[c]);
+                        } else {
+                            __nv_bfloat16* O = reinterpret_cast<__nv_bfloat16*>(p.O);
+#pragma unroll
+                            for (uint32_t c = 0; c < 16u; ++c)
+                                if (m0 + c < p.M) O[(size_t)(m0 + c) * out_cols + n] = __float2bfloat16_rn(v[c]);
                         }
                     }
                 }

@@ -8,7 +8,10 @@ nodes for q, k, v, the attention output (+residual), one gate|value Linear
 (vai/groups/gated-feed-forward.h:38) and the down projection (+residual); the lm_head
 follows the last block.  Only the Linear nodes are built here: attention, norms and
 rope are other operators.  The stand-in wiring keeps every Linear's shape, dtype and
-epilogue: `o` reads q's output in place of the attention result.
+epilogue: `o` reads q's output in place of the attention result, the residual inputs
+read the net input (unit variance) and the o / down projections carry a scalar_scale,
+which together do the job of the missing norms: activations stay O(1) through any
+number of blocks with N(0, 0.02) weights.
 """
 import numpy as np
 
@@ -101,14 +104,15 @@ def build_linear_chain(net, name, *, w_dtype=Dtype.BF16, fuse_gate=True, seed=0,
     src = _BitsSource(w_dtype, 0.02, seed)
     act = getattr(Epilogue, p["act"])
     nodes = []
-    x = net.input("x")
+    x = x0 = net.input("x")
     for _ in range(p["layers"] if layers is None else layers):
         specs = block_linears(p)
         made = {}
         for lname, k, n, ex in specs:
             gate = bool(ex.get("gate")) and fuse_gate
             node = LinearNode(in_dim=k, out_dim=n, accept_residual=bool(ex.get("residual")),
-                              epilogue=act if (gate or ex.get("act")) else Epilogue.NONE, gate_fuse=gate)
+                              epilogue=act if (gate or ex.get("act")) else Epilogue.NONE, gate_fuse=gate,
+                              scalar_scale={"o": 0.5, "down": 0.25, "fc2": 0.25}.get(lname, 1.0))
             node["weight"] = src.take((n, k))
             if ex.get("bias"):
                 node["bias"] = src.take((n,))
@@ -119,21 +123,21 @@ def build_linear_chain(net, name, *, w_dtype=Dtype.BF16, fuse_gate=True, seed=0,
             x - made["k"]
             x - made["v"]
             h = made["q"] - made["o"]
-            x - "residual" / made["o"]
+            x0 - "residual" / made["o"]
             h - made["gate_up"]
             if fuse_gate:
                 made["gate_up"] - made["down"]
             else:
                 raise NotImplementedError("the unfused chain needs a GatedMul node between gate_up and down")
-            h - "residual" / made["down"]
+            x0 - "residual" / made["down"]
             x = Flow_of(made["down"])
         else:
             x - made["qkv"]
             # attention stand-in: o reads the block input (the reference feeds it the attention output)
             h = x - made["o"]
-            x - "residual" / made["o"]
+            x0 - "residual" / made["o"]
             h - made["fc1"] - made["fc2"]
-            h - "residual" / made["fc2"]
+            x0 - "residual" / made["fc2"]
             x = Flow_of(made["fc2"])
     if lm_head:
         v = p["vocab"] if vocab_rows is None else vocab_rows
