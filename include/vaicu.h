@@ -196,6 +196,29 @@ VAICU_API int vaicu_linear_run(vaicu_linear_plan* plan, vaicu_stream_t stream,
                      const void* I, const void* W, const void* bias, const void* residual,
                      void* O, void* workspace);
 
+/* Split-K Linear that allocates nothing (no counterpart in the reference, whose
+ * engine always has a buffer pool to draw the "partial" slot from).
+ *
+ * For hosts that cannot obtain device memory at call time: processes that carve
+ * up the whole device heap at start-up and forbid allocation afterwards, and
+ * plugin hosts that expose no allocator.  They pass the operands they already
+ * own; the fp32 partial sums go to an 8 MiB array built into the library (held
+ * by every GPU that loads the library until exit), so the call is limited to
+ * split_count * M * N * 4 <= 8 MiB and returns VAICU_ERR_TOO_LARGE beyond that.
+ * It runs the fp32 FFMA tile kernel with K split per desc->split_size (0: a
+ * per-shape choice) and the fold + bias/epilogue/residual/scale pass; gate_fuse
+ * is not offered.  It calls no cudaMalloc / cudaFree and no other allocator.
+ *
+ * The first call on each device looks the array's address up
+ * (cudaGetSymbolAddress, with that device current); make that first call before
+ * any stream capture.  All calls share the one array and it keeps whatever the
+ * previous call left: calls that overlap on the GPU (different streams) race;
+ * calls on one stream, or otherwise ordered, are safe.  Nothing needs clearing:
+ * every partial the fold reads is written first by the same call. */
+VAICU_API int vaicu_linear_splitk_static(const vaicu_linear_desc* desc, vaicu_stream_t stream,
+                                         const void* I, const void* W, const void* bias, const void* residual,
+                                         void* O);
+
 /* Column-split helper for the multi-GPU layout: the desc of rank `rank` of
  * `world` when W's rows (output columns) are split evenly; for gate_fuse the
  * split is per half.  Fills row offsets into W / bias for that rank. No

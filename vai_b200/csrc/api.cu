@@ -97,6 +97,13 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 }  // namespace
 
+namespace vaicu {
+void set_last_error(const char* where, const char* what)
+{
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s", where ? where : "", what ? what : "");
+}
+}  // namespace vaicu
+
 struct vaicu_linear_plan {
     vaicu_device* dev;
     vaicu_linear_desc d;

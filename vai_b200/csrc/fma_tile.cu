@@ -10,6 +10,8 @@
 //   * cast_kernel — fp32 activations -> the weights' 16-bit type, the staging the
 //     reference's cooperative-matrix kernel does on load
 //     (vai/shaders/linear-cm-nv.comp:128-135), as a pre-pass into workspace.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace vaicu {
@@ -179,4 +181,123 @@ cudaError_t launch_cast_f32_to_16(const float* src, void* dst, int dst_dtype, si
     return cudaGetLastError();
 }
 
+
+// ---------------------------------------------------------------------------
+// Split-K Linear for hosts that may not allocate.
+//
+// Some embedders own every byte of device memory themselves — a serving process
+// that pre-partitions the heap at start-up and forbids allocation afterwards, or a
+// plugin host whose sandbox exposes no allocator — so they can hand over the
+// operands they already hold but have no way to obtain the `workspace` that
+// vaicu_linear_run() wants for split-K partial sums.  For them the partial sums
+// live in the fixed array below, which is part of the library image: every GPU
+// that loads the library carries these 8 MiB until the process exits.
+//
+// The array's name is only meaningful to device code and to cudaGetSymbolAddress;
+// host code must never pass `g_splitk_scratch` itself to a kernel.  The address is
+// looked up once per device (with that device current) and cached.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = 8u << 20;   // 8 MiB: split_count * M * N fp32 partials must fit
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_splitk_scratch[kStaticScratchBytes];
+
+std::mutex g_scratch_mutex;
+void* g_scratch_addr[kMaxDevices] = {};
+int g_scratch_sms[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device; looked up on the first
+// call per device.  Returns a status code.
+int static_scratch_for_current_device(float** out, int* sm_count)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_last_error("cudaGetDevice", cudaGetErrorString(e)); return VAICU_ERR_CUDA; }
+    if (dev < 0 || dev >= kMaxDevices) { set_last_error("vaicu_linear_splitk_static", "device ordinal out of range"); return VAICU_ERR_INVALID_VALUE; }
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_addr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_splitk_scratch);
+        if (e != cudaSuccess || !ptr) {
+            set_last_error("cudaGetSymbolAddress(g_splitk_scratch)", cudaGetErrorString(e));
+            (void)cudaGetLastError();
+            return VAICU_ERR_CUDA;
+        }
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) { set_last_error("cudaDeviceGetAttribute", cudaGetErrorString(e)); return VAICU_ERR_CUDA; }
+        g_scratch_sms[dev] = sms;
+        g_scratch_addr[dev] = ptr;
+    }
+    *out = reinterpret_cast<float*>(g_scratch_addr[dev]);
+    *sm_count = g_scratch_sms[dev];
+    return VAICU_OK;
+}
+
+}  // namespace
 }  // namespace vaicu
+
+#pragma GCC visibility push(default)
+extern "C" int vaicu_linear_splitk_static(const vaicu_linear_desc* d, vaicu_stream_t stream, const void* I, const void* W,
+                                          const void* bias, const void* residual, void* O)
+{
+    using namespace vaicu;
+    if (!d || !I || !W || !O) return VAICU_ERR_INVALID_VALUE;
+    if (d->M == 0 || d->N == 0 || d->K == 0) return VAICU_ERR_INVALID_VALUE;
+    auto ok_dtype = [](int t) { return t == VAICU_DTYPE_F32 || t == VAICU_DTYPE_F16 || t == VAICU_DTYPE_BF16; };
+    if (!ok_dtype(d->i_dtype) || !ok_dtype(d->w_dtype) || !ok_dtype(d->o_dtype)) return VAICU_ERR_INVALID_VALUE;
+    if (d->has_bias && (!ok_dtype(d->b_dtype) || !bias)) return VAICU_ERR_INVALID_VALUE;
+    if (d->has_residual && !residual) return VAICU_ERR_INVALID_VALUE;
+    if (d->epilogue < 0 || d->epilogue > VAICU_EPILOGUE_SIGMOID) return VAICU_ERR_INVALID_VALUE;
+    if (d->residual_order != 0 && d->residual_order != 1) return VAICU_ERR_INVALID_VALUE;
+    if (d->split_size != 0 && d->split_size < 32) return VAICU_ERR_INVALID_VALUE;
+    if (d->gate_fuse) return VAICU_ERR_UNSUPPORTED;
+    if ((uint64_t)d->M * d->N >= (1ull << 32)) return VAICU_ERR_INVALID_VALUE;
+    if (d->has_bias && d->bias_elems && (d->bias_elems % d->N || ((uint64_t)d->M * d->N) % d->bias_elems)) return VAICU_ERR_INVALID_VALUE;
+    if (d->has_residual && d->residual_elems && (d->residual_elems % d->N || ((uint64_t)d->M * d->N) % d->residual_elems))
+        return VAICU_ERR_INVALID_VALUE;
+
+    float* scratch = nullptr;
+    int sms = 0;
+    const int rc = static_scratch_for_current_device(&scratch, &sms);
+    if (rc != VAICU_OK) return rc;
+
+    // K spans: the caller's split_size, else enough spans to occupy the SMs
+    FmaTileConfig cfg;
+    cfg.split_size = d->K;
+    cfg.split_count = 1;
+    if (d->split_size) {
+        cfg.split_size = d->split_size < d->K ? d->split_size : d->K;
+    } else {
+        const uint32_t tiles = ((d->M + 63u) / 64u) * ((d->N + 63u) / 64u);
+        if (tiles * 2u <= (uint32_t)sms && d->K >= 1024u) {
+            uint32_t want = (uint32_t)sms / tiles;
+            if (want > 16u) want = 16u;
+            cfg.split_size = ((d->K + want - 1u) / want + 63u) / 64u * 64u;
+        }
+    }
+    cfg.split_count = (d->K + cfg.split_size - 1u) / cfg.split_size;
+    const uint64_t need = (uint64_t)cfg.split_count * d->M * d->N * sizeof(float);
+    if (cfg.split_count > 65535u || need > kStaticScratchBytes) {
+        set_last_error("vaicu_linear_splitk_static", "split_count * M * N * 4 bytes exceeds the 8 MiB built-in scratch");
+        return VAICU_ERR_TOO_LARGE;
+    }
+
+    LinearArgs a{};
+    a.I = I; a.W = W; a.bias = d->has_bias ? bias : nullptr; a.res = d->has_residual ? residual : nullptr; a.O = O;
+    a.M = d->M; a.N = d->N; a.K = d->K;
+    a.i_dtype = d->i_dtype; a.w_dtype = d->w_dtype; a.o_dtype = d->o_dtype; a.b_dtype = d->has_bias ? d->b_dtype : VAICU_DTYPE_NONE;
+    a.has_bias = d->has_bias ? 1 : 0; a.has_res = d->has_residual ? 1 : 0;
+    a.residual_order = d->residual_order; a.epilogue = d->epilogue; a.gate_fuse = 0;
+    a.bias_elems = d->has_bias ? d->bias_elems : 0; a.res_elems = d->has_residual ? d->residual_elems : 0;
+    a.scale = d->scalar_scale;
+    // Every partial element [z, m, n] that the fold reads is written by the tile kernel
+    // first, so nothing in the shared array has to start at zero.
+    cudaError_t e = launch_fma_tile(a, cfg, scratch, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = launch_splitk_reduce(a, scratch, cfg.split_count, (cudaStream_t)stream);
+    if (e != cudaSuccess) { set_last_error("vaicu_linear_splitk_static launch", cudaGetErrorString(e)); return VAICU_ERR_CUDA; }
+    return VAICU_OK;
+}
+#pragma GCC visibility pop
