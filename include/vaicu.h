@@ -152,6 +152,12 @@ VAICU_API int vaicu_host_free_pinned(void* p);
 VAICU_API int vaicu_stream_create(vaicu_device* dev, vaicu_stream_t* out);
 VAICU_API int vaicu_stream_sync(vaicu_stream_t stream);
 VAICU_API int vaicu_stream_destroy(vaicu_stream_t stream);
+/* Orders `waiter` after everything enqueued so far on `signaler` (an event record +
+ * wait; also valid while `signaler` is being captured, which pulls `waiter` into the
+ * recording).  Stands in for the buffer barriers between independent dispatches of one
+ * command buffer (linear.h:2746): nodes that do not depend on each other may run on
+ * side streams and join again. */
+VAICU_API int vaicu_stream_wait_stream(vaicu_stream_t waiter, vaicu_stream_t signaler);
 
 /* ---- events (replace the timestamp queries of NodeProfiler,
  *      vai/engine/node-profiler.h:118-178) --------------------------------- */

@@ -78,7 +78,7 @@ def test_gemv_dtypes(M, K, N, dt, device):
     b = rng.standard_normal(N).astype(np.float32)
     r = rng.standard_normal((M, N)).astype(np.float32)
     got, want, node = run_linear(x, w, b, r, i_dtype=dt[0], w_dtype=dt[1], o_dtype=dt[2], epilogue="GELU_TANH",
-                                 scalar_scale=0.5)
+                                 scalar_scale=0.5, kernel=nodes.KERNEL_GEMV)
     assert node.info.kernel == nodes.KERNEL_GEMV
     assert_close(got, want, out_tol(dt[2]), f"gemv {M}x{K}x{N} {dt}")
 
@@ -196,3 +196,56 @@ def test_scalar_scale_negative(device):
     r = rng.standard_normal((10, 32)).astype(np.float32)
     got, want, _ = run_linear(x, w, None, r, scalar_scale=-0.1, epilogue="SILU", residual_order="BEFORE_EPILOGUE")
     assert_close(got, want, BOUND_FP32, "scale")
+
+
+def test_chain_parallel_branches_match_serial(device):
+    """Independent nodes of one level (q / k / v) recorded on side streams give the
+    same logits as the one-stream recording, replayed or not."""
+    import vai_b200
+    from vai_b200 import Tensor, presets
+    x = Tensor.from_numpy(np.random.default_rng(4).standard_normal((1, 2048), dtype=np.float32))
+    outs = []
+    for parallel, graph in ((False, True), (True, True), (True, False)):
+        net = vai_b200.NeuralNet(w_default_dtype=Dtype.BF16, device=device, parallel_branches=parallel, use_graph=graph)
+        presets.build_linear_chain(net, "llama-3.2-1b", layers=2, vocab_rows=4096, seed=7)
+        a = net(x).to_numpy()
+        b = net(x).to_numpy()
+        np.testing.assert_array_equal(a, b)
+        outs.append(a)
+    assert np.isfinite(outs[0]).all() and np.abs(outs[0]).max() > 0
+    np.testing.assert_array_equal(outs[0], outs[1])
+    np.testing.assert_array_equal(outs[0], outs[2])
+
+
+@pytest.mark.parametrize("M,K,w_dtype,expect", [(1, 512, "bf16", "gemv"), (4, 512, "bf16", "gemv"), (5, 512, "bf16", "skinny"),
+                                                 (8, 512, "f16", "skinny"), (8, 512, "f32", "gemv"), (6, 500, "bf16", "gemv"),
+                                                 (9, 512, "bf16", "skinny"), (200, 512, "bf16", "tc"), (9, 500, "bf16", "fma"),
+                                                 (64, 512, "f32", "fma")])
+def test_kernel_choice_by_shape(M, K, w_dtype, expect, device):
+    """Plan selection (the place of Linear::prepare's slab / tile choice, vAi linear.h:2355,2395)."""
+    rng = np.random.default_rng(M + K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((96, K)) / np.sqrt(K)).astype(np.float32)
+    got, want, node = run_linear(x, w, w_dtype=w_dtype)
+    ids = {"gemv": nodes.KERNEL_GEMV, "skinny": nodes.KERNEL_TC_SKINNY, "tc": nodes.KERNEL_TC_GEMM, "fma": nodes.KERNEL_FMA_TILE}
+    assert node.info.kernel == ids[expect]
+    assert_close(got, want, (2e-4, 5e-5), f"choice {M} {K} {w_dtype}")
+
+
+@pytest.mark.parametrize("M,K,N", [(1300, 320, 520), (512, 1024, 256), (2048, 192, 1000)])
+@pytest.mark.parametrize("gate", [False, True])
+def test_wide_tiles(M, K, N, gate, device, monkeypatch):
+    """256-row tiles of the unswapped tensor-core kernel (two accumulators, one TMEM
+    buffer), forced on small shapes: ragged M, N and K tails, bias + residual, gate."""
+    monkeypatch.setenv("VAICU_TC_WIDE", "1")
+    monkeypatch.setenv("VAICU_TC_BN", "256")
+    rng = np.random.default_rng(M + N)
+    rows = 2 * N if gate else N
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((rows, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(rows).astype(np.float32)
+    r = None if gate else rng.standard_normal((M, N)).astype(np.float32)
+    got, want, node = run_linear(x, w, b, r, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", b_dtype="f32",
+                                 epilogue="SILU", gate_fuse=gate, kernel=nodes.KERNEL_TC_GEMM)
+    assert node.info.tile_m == 256
+    assert_close(got, want, (2e-4, 5e-5), f"wide {M}x{K}x{N} gate={gate}")

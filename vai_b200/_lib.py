@@ -47,6 +47,7 @@ SIGNATURES = {
     "vaicu_stream_create": (ctypes.c_int, [ctypes.c_void_p, c_void_pp]),
     "vaicu_stream_sync": (ctypes.c_int, [ctypes.c_void_p]),
     "vaicu_stream_destroy": (ctypes.c_int, [ctypes.c_void_p]),
+    "vaicu_stream_wait_stream": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "vaicu_event_create": (ctypes.c_int, [c_void_pp]),
     "vaicu_event_record": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "vaicu_event_synchronize": (ctypes.c_int, [ctypes.c_void_p]),

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -244,7 +245,18 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
             if (out_cols > (uint32_t)align_up(H, 16u) && c != 64u) eff *= (double)H / out_cols;
             if (eff > best) { best = eff; bn = c; }
         }
-        t.tiles_a = ceil_div(d.M, 128u);
+        if (const char* e = getenv("VAICU_TC_BN")) {   // tuning override: UMMA N of the unswapped kernel
+            const uint32_t v = (uint32_t)atoi(e);
+            if (v >= 16u && v <= 256u && v % 16u == 0u) bn = v;
+        }
+        // 256-row tiles (two A boxes per stage) halve the re-reads of the weights' tile;
+        // they need all 512 TMEM columns at bn = 256, so the epilogue no longer overlaps
+        // the next tile.  Worth it when the problem is tensor-bound and has tiles to spare.
+        bool wide = bn == 256u && d.M >= 1024u &&
+                    ceil_div(d.M, 256u) * ceil_div(H, gate ? bn / 2u : bn) >= 2u * sms;
+        if (const char* e = getenv("VAICU_TC_WIDE")) wide = atoi(e) != 0 && bn * 2u <= 512u;
+        t.wide = wide ? 1u : 0u;
+        t.tiles_a = ceil_div(d.M, wide ? 256u : 128u);
         t.tiles_b = ceil_div(H, gate ? bn / 2u : bn);
     }
     t.bn = bn;
@@ -261,6 +273,10 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
         if (want > 32u) want = 32u;
         if (want >= 2u) kb_per_split = ceil_div(t.kblocks, want);
     }
+    if (const char* e = getenv("VAICU_TC_SPLITS")) {   // tuning override: number of K splits
+        const uint32_t v = (uint32_t)atoi(e);
+        if (v >= 1u && !d.split_size) kb_per_split = ceil_div(t.kblocks, v);
+    }
     if (kb_per_split == 0u) kb_per_split = 1u;
     if (kb_per_split > t.kblocks) kb_per_split = t.kblocks;
     t.kb_per_split = kb_per_split;
@@ -268,15 +284,17 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
     // descriptor: fp32 accumulate, A/B formats, both K-major, N >> 3, M >> 4
     const uint32_t fmt = d.w_dtype == VAICU_DTYPE_BF16 ? 1u : 0u;
     t.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((bn >> 3) << 17) | ((128u >> 4) << 24);
-    const uint32_t a_bytes = ((gate && swap) ? 2u : 1u) * 128u * 128u;
+    const uint32_t a_boxes = ((gate && swap) || t.wide) ? 2u : 1u;
+    const uint32_t a_bytes = a_boxes * 128u * 128u;
     const uint32_t stage_bytes = a_bytes + bn * 128u;
     uint32_t stages = (uint32_t)((kTcMaxSmem - 2048u) / stage_bytes);
     if (stages > 8u) stages = 8u;
     t.stages = stages;
     pl->tc_smem = (size_t)stages * stage_bytes + 1024u + 256u;
-    const uint32_t acc_cols = (gate && swap) ? 2u * bn : bn;
+    const uint32_t acc_cols = a_boxes * bn;
+    t.acc_bufs = 2u * acc_cols <= 512u ? 2u : 1u;
     uint32_t cols = 32u;
-    while (cols < 2u * acc_cols) cols *= 2u;
+    while (cols < t.acc_bufs * acc_cols) cols *= 2u;
     t.tmem_cols = cols;
     t.o_dtype = d.o_dtype; t.b_dtype = d.b_dtype; t.epilogue = d.epilogue; t.residual_order = d.residual_order;
     t.has_bias = d.has_bias ? 1 : 0; t.has_res = d.has_residual ? 1 : 0; t.gate = gate ? 1 : 0;
@@ -314,8 +332,12 @@ int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, int force_kerne
     pl->tc = false;
     int kernel = force_kernel;
     if (kernel == 0) {
-        // M <= 8: the weight-streaming kernel (vAi useSlabPath, linear.h:320)
-        if (d.M <= 8u) kernel = VAICU_KERNEL_GEMV;
+        // Few rows: the weight-streaming kernel (vAi useSlabPath takes M <= 8,
+        // linear.h:320).  Measured on B200 the FMA kernel stops being memory-bound past
+        // M = 4 (shared-memory reads of the activations), while the swapped tensor-core
+        // kernel streams weights at full rate for any M, so M = 5..8 go there when the
+        // operands allow it.
+        if (d.M <= 4u || (d.M <= 8u && !tc_eligible(d))) kernel = VAICU_KERNEL_GEMV;
         else if (tc_eligible(d)) kernel = d.M <= 128u ? VAICU_KERNEL_TC_SKINNY : VAICU_KERNEL_TC_GEMM;
         else kernel = VAICU_KERNEL_FMA_TILE;
     }
@@ -511,6 +533,18 @@ int vaicu_stream_destroy(vaicu_stream_t stream)
     return VAICU_OK;
 }
 
+int vaicu_stream_wait_stream(vaicu_stream_t waiter, vaicu_stream_t signaler)
+{
+    if (!waiter || !signaler) return VAICU_ERR_INVALID_VALUE;
+    cudaEvent_t e;
+    VAICU_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    cudaError_t rc = cudaEventRecord(e, (cudaStream_t)signaler);
+    if (rc == cudaSuccess) rc = cudaStreamWaitEvent((cudaStream_t)waiter, e, 0);
+    cudaEventDestroy(e);   // released once the recorded work has completed
+    if (rc != cudaSuccess) return cuda_fail(rc, "vaicu_stream_wait_stream");
+    return VAICU_OK;
+}
+
 int vaicu_event_create(vaicu_event** out)
 {
     if (!out) return VAICU_ERR_INVALID_VALUE;
@@ -551,7 +585,9 @@ int vaicu_event_destroy(vaicu_event* ev)
 int vaicu_graph_capture_begin(vaicu_stream_t stream)
 {
     if (!stream) return VAICU_ERR_INVALID_VALUE;   // the legacy default stream cannot be captured
-    VAICU_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+    // Relaxed: other work of the host (e.g. a buffer of an older net being freed by a
+    // destructor) must not invalidate the recording.
+    VAICU_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeRelaxed));
     return VAICU_OK;
 }
 int vaicu_graph_capture_end(vaicu_stream_t stream, vaicu_graph** out)
@@ -611,7 +647,7 @@ int vaicu_linear_plan_info(const vaicu_linear_plan* plan, vaicu_linear_info* out
     } else if (plan->tc) {
         out->split_count = plan->tcp.splits;
         const uint32_t outc = (plan->tcp.gate && !plan->tc_swap) ? plan->tcp.bn / 2u : plan->tcp.bn;
-        out->tile_m = plan->tc_swap ? outc : 128u;
+        out->tile_m = plan->tc_swap ? outc : (plan->tcp.wide ? 256u : 128u);
         out->tile_n = plan->tc_swap ? 128u : outc;
     }
     return VAICU_OK;

@@ -158,10 +158,10 @@ __global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const 
             // vectors toward L2 while that kernel drains, then wait for its results.
             const uint32_t first_span = p.k_chunk < K ? p.k_chunk : K;
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                if (kk0 < first_span) prefetch_l2(rowp[r] + kk0);
-                if (kk0 + stride < first_span) prefetch_l2(rowp[r] + kk0 + stride);
-            }
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (uint32_t it = 0; it < 8u; ++it)
+                    if (kk0 + it * stride < first_span) prefetch_l2(rowp[r] + kk0 + it * stride);
             dependency_wait();
         }
         float2 acc[R][M];
@@ -352,11 +352,12 @@ cudaError_t launch_one(const GemvParams& p, const GemvConfig& cfg, cudaStream_t 
 template <typename TW>
 cudaError_t launch_typed(const GemvParams& p, const GemvConfig& cfg, cudaStream_t stream)
 {
+    const bool r4 = cfg.rows_per_warp == 4;
     switch (p.a.M) {
-    case 1: return launch_one<TW, 1, 4>(p, cfg, stream);
-    case 2: return launch_one<TW, 2, 4>(p, cfg, stream);
-    case 3: return launch_one<TW, 3, 4>(p, cfg, stream);
-    case 4: return launch_one<TW, 4, 4>(p, cfg, stream);
+    case 1: return r4 ? launch_one<TW, 1, 4>(p, cfg, stream) : launch_one<TW, 1, 2>(p, cfg, stream);
+    case 2: return r4 ? launch_one<TW, 2, 4>(p, cfg, stream) : launch_one<TW, 2, 2>(p, cfg, stream);
+    case 3: return r4 ? launch_one<TW, 3, 4>(p, cfg, stream) : launch_one<TW, 3, 2>(p, cfg, stream);
+    case 4: return r4 ? launch_one<TW, 4, 4>(p, cfg, stream) : launch_one<TW, 4, 2>(p, cfg, stream);
     case 5: return launch_one<TW, 5, 2>(p, cfg, stream);
     case 6: return launch_one<TW, 6, 2>(p, cfg, stream);
     case 7: return launch_one<TW, 7, 2>(p, cfg, stream);
@@ -380,15 +381,28 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
         c.grid = (int)((H + kWarps - 1u) / kWarps);
         return c;
     }
-    const int R = a.M <= 4u ? 4 : 2;
+    // Blocks resident at once: 3 per SM for M = 1 (launch bounds), else 2.  One
+    // block-task = (8 / ks) row groups of R rows, K split over ks warps.  Wanted: all
+    // tasks in flight together (no ragged second round), and at least half the
+    // resident slots used; so few rows get a smaller R and a deeper K split, while
+    // every warp keeps two 16-byte steps.
+    const uint32_t capacity = (uint32_t)sm_count * (a.M == 1u ? 3u : 2u);
+    int R = a.M <= 4u ? 4 : 2, ks = 1;
+    uint32_t best_tasks = 0;
+    for (int r = (a.M <= 4u ? 4 : 2); r >= 2; r -= 2) {
+        const uint32_t cols_r = a.gate_fuse ? (uint32_t)r / 2u : (uint32_t)r;
+        const uint32_t groups_r = (H + cols_r - 1u) / cols_r;
+        bool done = false;
+        for (int k = 1; k <= kWarps; k *= 2) {
+            if (k > 1 && a.K / (uint32_t)(k * 32 * vec) < 2u) break;
+            const uint32_t tasks = (groups_r + (uint32_t)(kWarps / k) - 1u) / (uint32_t)(kWarps / k);
+            if (tasks > best_tasks) { best_tasks = tasks; R = r; ks = k; }
+            if (tasks * 2u >= capacity) { done = true; break; }
+        }
+        if (done) break;
+    }
     const uint32_t cols = a.gate_fuse ? (uint32_t)R / 2u : (uint32_t)R;
     const uint32_t groups = (H + cols - 1u) / cols;
-    // split K over warps until there are about two 8-warp blocks per SM, while
-    // every warp keeps at least two 16-byte steps
-    int ks = 1;
-    while (ks < kWarps && (uint64_t)groups * ks < (uint64_t)sm_count * kWarps * 2u &&
-           a.K / (uint32_t)(ks * 2 * 32 * vec) >= 2u)
-        ks *= 2;
     c.rows_per_warp = R;
     c.k_warps = ks;
     const uint32_t budget_floats = (96u * 1024u) / 4u / a.M;
@@ -398,8 +412,10 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
     c.smem = ((size_t)a.M * k_chunk + (size_t)kWarps * R * a.M) * sizeof(float);
     const uint32_t rg = (uint32_t)kWarps / (uint32_t)ks;
     const uint32_t nblocks = (groups + rg - 1u) / rg;
-    const uint32_t cap = (uint32_t)sm_count * 2u;
-    c.grid = (int)(nblocks < cap ? nblocks : cap);
+    // equal passes per block: with more tasks than resident slots, shrink the grid so
+    // that every block runs the same number of passes instead of leaving a short tail
+    const uint32_t rounds = (nblocks + capacity - 1u) / capacity;
+    c.grid = (int)((nblocks + rounds - 1u) / rounds);
     return c;
 }
 

@@ -358,12 +358,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t bn = p.bn;
-    const uint32_t a_boxes = (GATE && SWAP) ? 2u : 1u;
+    // wide: two 128-row A boxes per stage and two MMAs per k-step give a 256-row tile;
+    // the weights' B tile is then fetched once per 256 rows instead of once per 128,
+    // which is what the operand traffic from L2 allows at full tensor rate.
+    const bool wide = !SWAP && p.wide != 0u;
+    const uint32_t a_boxes = ((GATE && SWAP) || wide) ? 2u : 1u;
+    const uint32_t a_rows = wide ? 2u * TILE_ROWS : TILE_ROWS;   // rows per tile on the A side
     const uint32_t a_bytes = a_boxes * TILE_ROWS * BLOCK_K * 2u;
     const uint32_t b_bytes = bn * BLOCK_K * 2u;
     const uint32_t stage_bytes = a_bytes + b_bytes;        // multiple of 1024 (bn % 8 == 0)
     const uint32_t stages = p.stages;
-    const uint32_t acc_cols = (GATE && SWAP) ? 2u * bn : bn;   // TMEM columns per accumulator buffer
+    const uint32_t acc_cols = a_boxes * bn;            // TMEM columns per accumulator buffer
+    const uint32_t acc_bufs = p.acc_bufs;              // 2: epilogue overlaps the next tile; 1: 512 columns in use
 
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_bytes);
     uint64_t* empty_bar = full_bar + stages;
@@ -409,13 +415,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     uint8_t* sb = sa + a_bytes;
                     mbar_expect_tx(&full_bar[stage], stage_bytes);
                     const int32_t kx = (int32_t)(kb * BLOCK_K);
-                    if (GATE && SWAP) {
-                        tma_load_2d(sa, &tmap_a, &full_bar[stage], kx, (int32_t)(ta * TILE_ROWS));
+                    tma_load_2d(sa, &tmap_a, &full_bar[stage], kx, (int32_t)(ta * a_rows));
+                    if (a_boxes == 2u)
                         tma_load_2d(sa + TILE_ROWS * BLOCK_K * 2u, &tmap_a, &full_bar[stage], kx,
-                                    (int32_t)(p.H + ta * TILE_ROWS));
-                    } else {
-                        tma_load_2d(sa, &tmap_a, &full_bar[stage], kx, (int32_t)(ta * TILE_ROWS));
-                    }
+                                    (int32_t)(wide ? ta * a_rows + TILE_ROWS : p.H + ta * TILE_ROWS));
                     if (GATE && !SWAP) {
                         const uint32_t half = bn / 2u;
                         tma_load_2d(sb, &tmap_b, &full_bar[stage], kx, (int32_t)(tb * half));
@@ -436,7 +439,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const uint32_t tile = w / p.splits, z = w - tile * p.splits;
                 const uint32_t kb0 = z * p.kb_per_split;
                 const uint32_t kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
-                const uint32_t buf = iter & 1u, use = iter >> 1;
+                const uint32_t buf = iter % acc_bufs, use = iter / acc_bufs;
                 if (!mbar_wait(&acc_empty[buf], (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * acc_cols;
@@ -452,7 +455,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
                         // advancing K by 16 elements = 32 bytes inside the swizzled row: +2 in the encoded address
                         umma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, accum);
-                        if (GATE && SWAP) {
+                        if (a_boxes == 2u) {
                             const uint64_t a2_desc = make_smem_desc(sa + TILE_ROWS * BLOCK_K * 2u);
                             umma_f16(d_tmem + bn, a2_desc + 2u * k, b_desc + 2u * k, p.idesc, accum);
                         }
@@ -475,10 +478,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t tile = w / p.splits, z = w - tile * p.splits;
             uint32_t ta, tb;
             tile_coords(p, tile, ta, tb);
-            const uint32_t buf = iter & 1u, use = iter >> 1;
+            const uint32_t buf = iter % acc_bufs, use = iter / acc_bufs;
             if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t t_row = tmem_base + ((q * 32u) << 16) + buf * acc_cols;
+            const uint32_t t_buf = tmem_base + ((q * 32u) << 16) + buf * acc_cols;
             float bias_n = 0.0f, bias_up = 0.0f;
             if (SWAP && !p.partial && p.bias_mode == OPERAND_PER_COLUMN) {
                 const uint32_t n = ta * TILE_ROWS + row_in_tile;
@@ -489,6 +492,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
             // columns of the accumulator that map to distinct outputs
             const uint32_t ncols = (GATE && !SWAP) ? bn / 2u : bn;
+            for (uint32_t sub = 0; sub < (wide ? 2u : 1u); ++sub) {
+            const uint32_t t_row = t_buf + sub * bn;                         // second accumulator of a wide tile
+            const uint32_t row_base = ta * a_rows + sub * TILE_ROWS;
             for (uint32_t c0 = 0; c0 < ncols; c0 += 16u) {
                 uint32_t r0[16], r1[16];
                 tmem_ld16(t_row + c0, r0);
@@ -498,7 +504,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     // split-K: raw fp32 partial sums, [z][M][N]; epilogue runs in the reduce pass
                     float* P = p.partial + (size_t)z * p.M * p.N;
                     if (!SWAP) {
-                        const uint32_t m = ta * TILE_ROWS + row_in_tile;
+                        const uint32_t m = row_base + row_in_tile;
                         if (m < p.M) {
 #pragma unroll
                             for (uint32_t c = 0; c < 16u; ++c) {
@@ -516,7 +522,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             }
                         }
                     } else {
-                        const uint32_t n = ta * TILE_ROWS + row_in_tile;
+                        const uint32_t n = row_base + row_in_tile;
                         const bool row_ok = GATE ? (n < p.H) : (n < p.N);
 #pragma unroll
                         for (uint32_t c = 0; c < 16u; ++c) {
@@ -528,7 +534,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         }
                     }
                 } else if (!SWAP) {
-                    const uint32_t m = ta * TILE_ROWS + row_in_tile;
+                    const uint32_t m = row_base + row_in_tile;
                     const uint32_t j0 = (GATE ? tb * (bn / 2u) : tb * bn) + c0;
                     if (m < p.M && j0 < out_cols) {
                         float v[16], u[16];
@@ -543,7 +549,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             for (uint32_t c = 0; c < n_valid; ++c) store_from_f32(p.O, p.o_dtype, flat0 + c, v[c]);
                     }
                 } else {
-                    const uint32_t n = ta * TILE_ROWS + row_in_tile;
+                    const uint32_t n = row_base + row_in_tile;
                     if (n < out_cols) {
                         float v[16], u[16];
 #pragma unroll
@@ -568,6 +574,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         }
                     }
                 }
+            }
             }
             tc_fence_before();
             __syncwarp();

@@ -26,6 +26,8 @@ struct TcParams {
     uint32_t tiles_a, tiles_b, num_tiles, group;
     uint32_t kblocks, kb_per_split, splits;
     uint32_t stages, tmem_cols;
+    uint32_t wide;         // unswapped kernel only: 256-row tiles (two A boxes, two accumulators)
+    uint32_t acc_bufs;     // accumulator buffers in TMEM: 2, or 1 when one tile needs all 512 columns
     int32_t o_dtype, b_dtype, epilogue, residual_order, has_bias, has_res, gate;
     int32_t bias_mode, res_mode;
     uint32_t bias_elems, res_elems;

@@ -128,11 +128,27 @@ class DeviceBuffer:
         self.ptr = device.lib.vaicu_buffer_ptr(h)
         self.nbytes = device.lib.vaicu_buffer_size(h)
 
+    # Buffers whose last reference dies while a recording is being captured (the
+    # garbage collector can run at any time) are freed after the capture ends.
+    _capturing = 0
+    _deferred = []
+
     def free(self):
         if self.handle:
-            self.device.lib.vaicu_buffer_free(self.handle)
+            if DeviceBuffer._capturing:
+                DeviceBuffer._deferred.append((self.device.lib, self.handle))
+            else:
+                self.device.lib.vaicu_buffer_free(self.handle)
             self.handle = None
             self.ptr = None
+
+    @classmethod
+    def end_capture(cls):
+        cls._capturing -= 1
+        if cls._capturing == 0:
+            pending, cls._deferred = cls._deferred, []
+            for lib, h in pending:
+                lib.vaicu_buffer_free(h)
 
     def __del__(self):
         try:
@@ -358,7 +374,8 @@ class NeuralNet:
     def _current(cls):
         return getattr(cls._tls, "net", None)
 
-    def __init__(self, w_default_dtype=Dtype.F16, o_default_dtype=Dtype.F32, device=None, use_graph=True):
+    def __init__(self, w_default_dtype=Dtype.F16, o_default_dtype=Dtype.F32, device=None, use_graph=True,
+                 parallel_branches=True):
         if Dtype(w_default_dtype) == Dtype.NONE or Dtype(o_default_dtype) == Dtype.NONE:
             raise ValueError("default dtypes may not be NONE")
         self.w_default_dtype = Dtype(w_default_dtype)
@@ -366,6 +383,9 @@ class NeuralNet:
         self.device = device or Device.default()
         self.pool = BufferPool(self.device)
         self.stream = self.device.create_stream()
+        self._streams = [self.stream]
+        self.parallel_branches = parallel_branches
+        self.max_side_streams = 3
         self.use_graph = use_graph
         self._nodes = []
         self._inputs = {}
@@ -427,7 +447,8 @@ class NeuralNet:
             self._inputs[name].slots["out0"] = dev_t
         order = self._sorted()
         # prepare() fixes shapes and plans, then outputs / temporaries get buffers
-        steps = []
+        bound = {}
+        level = {}
         for n in order:
             for slot, (src, src_slot) in n.links.items():
                 n.slots[slot] = src.slots[src_slot]
@@ -437,22 +458,55 @@ class NeuralNet:
                 if kind in (OUTPUT, TEMPORARY) and t.valid_shape() and t.buffer is None and t.nbytes() > 0:
                     t.buffer = self.pool.request(t.nbytes())
                     rec.keep.append(t)
-            steps.append(n.bind())
+            bound[n] = n.bind()
+            level[n] = 1 + max((level[src] for src, _ in n.links.values()), default=-1)
         for name, out in self._outputs.items():
             rec.outputs[name] = out.slots["in0"] if "in0" not in out.links else out.links["in0"][0].slots[out.links["in0"][1]]
+        # Nodes of one level do not depend on each other (q / k / v of a block): they go to
+        # side streams between a fork and a join, so their launch latencies overlap.
+        by_level = {}
+        for n in order:
+            if not isinstance(n, (InputNode, OutputNode)):
+                by_level.setdefault(level[n], []).append(n)
+        ops = []
+        for lv in sorted(by_level):
+            group = by_level[lv]
+            if len(group) == 1 or not self.parallel_branches:
+                ops += [("run", 0, bound[n]) for n in group]
+                continue
+            width = min(len(group), 1 + self.max_side_streams)
+            sides = list(range(1, width))
+            ops.append(("fork", sides, None))
+            ops += [("run", i % width, bound[n]) for i, n in enumerate(group)]
+            ops.append(("join", sides, None))
+        while len(self._streams) < 1 + self.max_side_streams and any(op[0] == "fork" for op in ops):
+            self._streams.append(self.device.create_stream())
+        rec.ops = ops
         if self.use_graph:
             _lib.check(lib.vaicu_graph_capture_begin(self.stream), "vaicu_graph_capture_begin")
+            DeviceBuffer._capturing += 1
             try:
-                for launch in steps:
-                    launch(self.stream)
+                self._play(ops)
             finally:
                 g = ctypes.c_void_p()
                 rc = lib.vaicu_graph_capture_end(self.stream, ctypes.byref(g))
+                DeviceBuffer.end_capture()
             _lib.check(rc, "vaicu_graph_capture_end")
             rec.graph = g
-        else:
-            rec.steps = steps
         return rec
+
+    def _play(self, ops):
+        lib = self.device.lib
+        st = self._streams
+        for kind, where, fn in ops:
+            if kind == "run":
+                fn(st[where])
+            elif kind == "fork":
+                for i in where:
+                    _lib.check(lib.vaicu_stream_wait_stream(st[i], st[0]), "vaicu_stream_wait_stream")
+            else:
+                for i in where:
+                    _lib.check(lib.vaicu_stream_wait_stream(st[0], st[i]), "vaicu_stream_wait_stream")
 
     def _pinned(self, nbytes, np_dtype, shape):
         """Page-locked host staging viewed as a numpy array (vAi stages inputs the same
@@ -492,8 +546,7 @@ class NeuralNet:
         if rec.graph is not None:
             _lib.check(lib.vaicu_graph_launch(rec.graph, self.stream), "vaicu_graph_launch")
         else:
-            for launch in rec.steps:
-                launch(self.stream)
+            self._play(rec.ops)
         for name, t in rec.outputs.items():
             view, hp = rec.stage_out[name]
             _lib.check(lib.vaicu_memcpy_d2h(hp, t.ptr, view.nbytes, self.stream), "vaicu_memcpy_d2h")
