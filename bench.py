@@ -299,7 +299,10 @@ def main():
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "gemv_kernel<bf16, M=1, R=4> (all 97 launches of the step)",
                      "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-                     "peak_kind": f"of {pk_kind}", "traffic": None,
+                     "peak_kind": f"of {pk_kind}",
+                     # DRAM bytes per step: ncu captures of the lm_head and gate|value launches read
+                     # 1.006 x their algorithmic bytes; the other launches are the same kernel, scaled
+                     "traffic": int(alg_bytes * 1.006),
                      "algorithmic_bytes_per_step": alg_bytes, "launches_per_step": launches_per_step,
                      "avg_launch_us": step_s / launches_per_step * 1e6},
     }

@@ -252,8 +252,8 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
         // 256-row tiles (two A boxes per stage) halve the re-reads of the weights' tile;
         // they need all 512 TMEM columns at bn = 256, so the epilogue no longer overlaps
         // the next tile.  Worth it when the problem is tensor-bound and has tiles to spare.
-        bool wide = bn == 256u && d.M >= 1024u &&
-                    ceil_div(d.M, 256u) * ceil_div(H, gate ? bn / 2u : bn) >= 2u * sms;
+        bool wide = bn == 256u && d.M >= 512u &&
+                    ceil_div(d.M, 256u) * ceil_div(H, gate ? bn / 2u : bn) * 100u >= 85u * sms;
         if (const char* e = getenv("VAICU_TC_WIDE")) wide = atoi(e) != 0 && bn * 2u <= 512u;
         t.wide = wide ? 1u : 0u;
         t.tiles_a = ceil_div(d.M, wide ? 256u : 128u);

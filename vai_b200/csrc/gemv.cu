@@ -12,6 +12,8 @@
 //   * K is split over `k_warps` warps of a block when N alone cannot fill
 //     148 SMs; the fold goes through shared memory, no global scratch;
 //   * blocks are persistent over row groups (grid sized to the SM count).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace vaicu {
@@ -109,6 +111,37 @@ __device__ __forceinline__ void stage4(const LinearArgs& a, float* xs_row, uint3
     *reinterpret_cast<float4*>(xs_row + xs_pos<VEC>(kk)) = v;
 }
 
+// VEC consecutive activations of row 0 straight from global memory as float2 pairs
+// (M = 1 only: with a single activation row there is nothing to share through shared
+// memory, and skipping the staging round removes a barrier from every short kernel).
+template <int VEC>
+__device__ __forceinline__ void load_x_direct(const LinearArgs& a, uint32_t k, float2* xf)
+{
+    if (a.i_dtype == VAICU_DTYPE_F32) {
+        const float4* s = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.I) + k);
+        const float4 t0 = s[0];
+        xf[0] = make_float2(t0.x, t0.y); xf[1] = make_float2(t0.z, t0.w);
+        if (VEC == 8) {
+            const float4 t1 = s[1];
+            xf[2 % (VEC / 2)] = make_float2(t1.x, t1.y); xf[3 % (VEC / 2)] = make_float2(t1.z, t1.w);
+        }
+    } else {
+        uint32_t w[4];
+        const uint16_t* s = reinterpret_cast<const uint16_t*>(a.I) + k;
+        if (VEC == 8) {
+            const uint4 t = *reinterpret_cast<const uint4*>(s);
+            w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+        } else {
+            const uint2 t = *reinterpret_cast<const uint2*>(s);
+            w[0] = t.x; w[1] = t.y; w[2] = 0; w[3] = 0;
+        }
+#pragma unroll
+        for (int i = 0; i < VEC / 2; ++i)
+            xf[i] = a.i_dtype == VAICU_DTYPE_F16 ? __half22float2(*reinterpret_cast<const __half2*>(&w[i]))
+                                                 : make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
+    }
+}
+
 // R rows of W per warp step.  With gate_fuse the R rows are R/2 gate rows and
 // the R/2 value rows of the same output columns.  Sums are kept as float2 pairs
 // (even / odd elements) and advanced with the packed fp32 FMA of sm_100, which
@@ -118,6 +151,7 @@ __global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const 
 {
     constexpr int VEC = WTraits<TW>::VEC;
     constexpr int PAIRS = VEC / 2;
+    constexpr bool DIRECT = (M == 1);     // activations read from global memory, not staged
     extern __shared__ __align__(16) float smem_f[];
     float* xs = smem_f;                               // [M][k_pad]
     float* red = smem_f + (size_t)M * p.k_pad;        // [kWarps][R*M]
@@ -163,6 +197,7 @@ __global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const 
                 for (uint32_t it = 0; it < 8u; ++it)
                     if (kk0 + it * stride < first_span) prefetch_l2(rowp[r] + kk0 + it * stride);
             dependency_wait();
+            if (DIRECT) staged = true;
         }
         float2 acc[R][M];
 #pragma unroll
@@ -174,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const 
             const uint32_t c0 = ch * p.k_chunk;
             const uint32_t c1 = (c0 + p.k_chunk < K) ? c0 + p.k_chunk : K;
             const uint32_t span = c1 - c0;
-            if (nchunks > 1u || !staged) {
+            if (!DIRECT && (nchunks > 1u || !staged)) {
                 if (staged) __syncthreads();
                 const uint32_t quads = span >> 2;
                 for (uint32_t i = threadIdx.x; i < (uint32_t)M * quads; i += kThreads) {
@@ -195,14 +230,23 @@ __global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const 
                     wA[r] = vA ? ldg_stream(rowp[r] + c0 + kkA) : make_uint4(0, 0, 0, 0);
                     wB[r] = vB ? ldg_stream(rowp[r] + c0 + kkB) : make_uint4(0, 0, 0, 0);
                 }
+                float2 xd[2][PAIRS];
+                if (DIRECT) {
+                    if (vA) load_x_direct<VEC>(a, c0 + kkA, xd[0]);
+                    if (vB) load_x_direct<VEC>(a, c0 + kkB, xd[1]);
+                }
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     const bool v = half ? vB : vA;
                     if (!v) continue;
                     const uint32_t kk = half ? kkB : kkA;
                     float2 xf[M][PAIRS];
+                    if (DIRECT) {
 #pragma unroll
-                    for (int m = 0; m < M; ++m) {
+                        for (int e = 0; e < PAIRS; ++e) xf[0][e] = xd[half][e];
+                    }
+#pragma unroll
+                    for (int m = 0; m < (DIRECT ? 0 : M); ++m) {
                         const float* xrow = xs + (size_t)m * p.k_pad;
                         if (VEC == 4) {
                             const float4 t = *reinterpret_cast<const float4*>(xrow + kk);
@@ -345,7 +389,8 @@ cudaError_t launch_one(const GemvParams& p, const GemvConfig& cfg, cudaStream_t 
     lc.dynamicSmemBytes = cfg.smem;
     lc.stream = stream;
     lc.attrs = attr;
-    lc.numAttrs = 1;
+    static const bool no_pdl = getenv("VAICU_NO_PDL") != nullptr;   // diagnostic: plain stream order
+    lc.numAttrs = no_pdl ? 0 : 1;
     return cudaLaunchKernelEx(&lc, kern, p);
 }
 
@@ -387,6 +432,9 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
     // resident slots used; so few rows get a smaller R and a deeper K split, while
     // every warp keeps two 16-byte steps.
     const uint32_t capacity = (uint32_t)sm_count * (a.M == 1u ? 3u : 2u);
+    // Measured: a deeper K split than needed is costly (lm_head 76 -> 108 us with ks = 2:
+    // every pass then ends in a block-wide fold), so K is split only until about half
+    // the resident slots are used, and R shrinks only when even that cannot be reached.
     int R = a.M <= 4u ? 4 : 2, ks = 1;
     uint32_t best_tasks = 0;
     for (int r = (a.M <= 4u ? 4 : 2); r >= 2; r -= 2) {
@@ -409,6 +457,7 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
     uint32_t k_chunk = (budget_floats / 256u) * 256u;
     const uint32_t k_round = ((a.K + 255u) / 256u) * 256u;
     if (k_chunk > k_round) k_chunk = k_round;
+    if (a.M == 1u) k_chunk = 0;   // M = 1 reads its activations from global memory: only the fold buffer
     c.smem = ((size_t)a.M * k_chunk + (size_t)kWarps * R * a.M) * sizeof(float);
     const uint32_t rg = (uint32_t)kWarps / (uint32_t)ks;
     const uint32_t nblocks = (groups + rg - 1u) / rg;
@@ -434,8 +483,8 @@ cudaError_t launch_gemv(const LinearArgs& a, const GemvConfig& cfg, cudaStream_t
     uint32_t k_chunk = (budget_floats / 256u) * 256u;
     const uint32_t k_round = ((a.K + 255u) / 256u) * 256u;
     if (k_chunk > k_round) k_chunk = k_round;
-    p.k_chunk = k_chunk;
-    p.k_pad = k_chunk;
+    p.k_chunk = a.M == 1u ? k_round : k_chunk;   // M = 1: one span, nothing staged
+    p.k_pad = a.M == 1u ? 0u : k_chunk;
     switch (a.w_dtype) {
     case VAICU_DTYPE_F32: return launch_typed<float>(p, cfg, stream);
     case VAICU_DTYPE_F16: return launch_typed<__half>(p, cfg, stream);
