@@ -279,6 +279,17 @@ def main():
     e2e_ms = max_over_ranks(dist, e2e_ms)
     e2e_tok_s = world * args.steps / (e2e_ms / 1e3)
 
+    # Column split of the large-N layers over the GPUs (Gemma-3-4B-shaped lm_head and
+    # gate|value Linear at batch 64, NCCL all-gather of the output slabs): reported beside
+    # the headline, never part of it.
+    sharded = None
+    if world > 1:
+        try:
+            from vai_b200 import sharded as sharded_mod
+            sharded = sharded_mod.bench_sharded(dev, dist, "gemma-3-4b", 64, iters=10, warmup=3)
+        except Exception as e:   # a report only
+            sharded = {"error": str(e)[:200]}
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -306,6 +317,8 @@ def main():
                      "algorithmic_bytes_per_step": alg_bytes, "launches_per_step": launches_per_step,
                      "avg_launch_us": step_s / launches_per_step * 1e6},
     }
+    if sharded is not None:
+        line["sharded"] = sharded
     if world == 1 and not args.no_cpu_baseline:
         try:
             v, cores, t, sample = cpu_sample(5, 1)

@@ -193,10 +193,24 @@ int vai_oracle_linear_slab(const oracle_desc* d, const void* I, const void* W, c
             for (uint32_t j = 0; j < M; ++j) {
                 const float* x = Iw + (size_t)j * K;
                 for (uint32_t t = 0; t < wg_size; ++t) lane[t] = 0.0f;
-                for (uint32_t c = 0; c < chunks; ++c) {
+                /* thread t takes chunks t, t + wg, t + 2 wg, ...: sweeping the chunks in
+                 * order visits the lanes round-robin, each lane's sum in its own order */
+                const uint32_t full = K / 4u;            /* chunks with no masked element */
+                uint32_t c = 0;
+                for (; c + wg_size <= full; c += wg_size) {
+                    const float* wp = wrow + (size_t)c * 4u;
+                    const float* xp = x + (size_t)c * 4u;
+#pragma omp simd
+                    for (uint32_t t = 0; t < wg_size; ++t) {
+                        /* dot(vec4, vec4) left to right */
+                        const float dot = ((wp[4 * t] * xp[4 * t] + wp[4 * t + 1] * xp[4 * t + 1]) + wp[4 * t + 2] * xp[4 * t + 2]) +
+                                          wp[4 * t + 3] * xp[4 * t + 3];
+                        lane[t] += dot;
+                    }
+                }
+                for (; c < chunks; ++c) {
                     const uint32_t t = c % wg_size, k0 = c * 4u;
-                    /* dot(vec4, vec4): x*x + y*y + z*z + w*w left to right, tail masked to 0 */
-                    float dot = 0.0f;
+                    float dot = 0.0f;                    /* K tail masked to 0 (linear-slab.comp:98-116) */
                     for (uint32_t e = 0; e < 4u; ++e)
                         if (k0 + e < K) dot += wrow[k0 + e] * x[k0 + e];
                     lane[t] += dot;

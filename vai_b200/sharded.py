@@ -128,3 +128,113 @@ class ShardedLinear:
             return local[:, :self.count]
         self.dist.all_gather_into_tensor(self.gathered, local)
         return assemble(self.gathered, self.n_out) if assemble_output else self.gathered
+
+
+def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5):
+    """Column-split lm_head and gate|value Linear of `preset` at batch M on this rank's
+    GPU, with the NCCL all-gather of the output slabs; device-timed, max over ranks.
+    Returns a dict (rank 0 reports it)."""
+    import torch
+
+    from . import presets
+    from .engine import Dtype, Epilogue
+    p = presets.PRESETS[preset]
+    world = dist.get_world_size() if dist is not None else 1
+    rank = dist.get_rank() if dist is not None else 0
+    cuda = torch.device("cuda", device.ordinal)
+    gen = torch.Generator(device="cpu").manual_seed(1234)
+    out = {"preset": preset, "M": M, "world": world, "layers": {}}
+    x = (torch.randn(M, p["d"], generator=gen)).to(torch.bfloat16).to(cuda)
+    cases = [("lm_head", p["vocab"], False), ("gate_up", 2 * p["ffn"], True)]
+    for name, n_rows, gate in cases:
+        full = _lib.LinearDesc()
+        full.M, full.N, full.K = M, n_rows, p["d"]
+        full.i_dtype = full.w_dtype = full.o_dtype = int(Dtype.BF16)
+        full.b_dtype = int(Dtype.NONE)
+        full.scalar_scale = 1.0
+        full.gate_fuse = 1 if gate else 0
+        full.epilogue = int(getattr(Epilogue, p["act"])) if gate else 0
+        # only this rank's rows are ever materialised: draw them directly
+        n_out = n_rows // 2 if gate else n_rows
+        _, cnt = shard_rows(n_out, world, rank)
+        rows_local = 2 * cnt if gate else cnt
+        w_local = (torch.randn(rows_local, p["d"], generator=gen) * 0.02).to(torch.bfloat16)
+
+        lin = ShardedLinear.__new__(ShardedLinear)
+        lin.torch, lin.dist, lin.dev, lin.rank, lin.world = torch, dist, device, rank, world
+        lin.full, lin.gate, lin.n_out = full, gate, n_out
+        lin.desc, lin.begin, lin.count = shard_desc(full, rank, world)
+        lin.w, lin.b = w_local.to(cuda), None
+        h = ctypes.c_void_p()
+        _lib.check(device.lib.vaicu_linear_plan_create(device.handle, ctypes.byref(lin.desc), ctypes.byref(h)), "plan")
+        lin.plan = h
+        lin.info = _lib.LinearInfo()
+        _lib.check(device.lib.vaicu_linear_plan_info(h, ctypes.byref(lin.info)), "info")
+        lin.ws = torch.empty(max(lin.info.workspace_bytes, 256), dtype=torch.uint8, device=cuda)
+        cmax = gathered_shape(M, n_out, world)[2]
+        lin.local = torch.zeros((M, cmax), dtype=torch.bfloat16, device=cuda)
+        lin.slab = lin.local if cmax == lin.count else torch.empty((M, lin.count), dtype=torch.bfloat16, device=cuda)
+        lin.gathered = torch.empty((world, M, cmax), dtype=torch.bfloat16, device=cuda)
+
+        def timed(fn):
+            for _ in range(warmup):
+                fn()
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            if dist is not None:
+                t = torch.tensor([ms], dtype=torch.float64, device=cuda)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms
+
+        local_ms = timed(lambda: lin.local_forward(x))
+        total_ms = timed(lambda: lin.forward(x, assemble_output=True))
+        w_bytes_all = n_rows * p["d"] * 2
+        out["layers"][name] = {"rows": n_rows, "rows_per_gpu": rows_local, "kernel": int(lin.info.kernel),
+                               "local_us": local_ms * 1e3, "with_allgather_us": total_ms * 1e3,
+                               "aggregate_GBps_local": w_bytes_all / (local_ms * 1e-3) / 1e9,
+                               "aggregate_GBps_with_allgather": w_bytes_all / (total_ms * 1e-3) / 1e9,
+                               "allgather_bytes_per_gpu": M * cmax * 2}
+        device.lib.vaicu_linear_plan_destroy(h)
+    return out
+
+
+def main():
+    """torchrun --nproc-per-node N -m vai_b200.sharded [--preset gemma-3-4b] [--M 64]"""
+    import argparse
+    import json
+    import os
+
+    import torch
+    import torch.distributed as dist
+
+    from .engine import Device
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--preset", default="gemma-3-4b")
+    ap.add_argument("--M", type=int, default=64)
+    a = ap.parse_args()
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    d = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        d = dist
+    res = bench_sharded(Device(local), d, a.preset, a.M)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(res))
+    if d is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
