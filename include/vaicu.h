@@ -202,6 +202,16 @@ VAICU_API int vaicu_linear_run(vaicu_linear_plan* plan, vaicu_stream_t stream,
                      const void* I, const void* W, const void* bias, const void* residual,
                      void* O, void* workspace);
 
+/* Two or three Linears that read the same activations (q / k / v of a block) as ONE
+ * launch over the concatenation of their weight rows: plans[i] was created for
+ * W[i] -> O[i]; all must be plain (no bias, epilogue, residual, scale or gate), share
+ * M, K and dtypes, and resolve to the weight-streaming kernel with 16-byte aligned
+ * operands.  Returns VAICU_ERR_UNSUPPORTED otherwise, and the caller issues the runs
+ * one by one.  No counterpart in the reference, which records one dispatch per node
+ * (linear.h:2706-2748); this only removes launch latency between sibling nodes. */
+VAICU_API int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_stream_t stream,
+                                     const void* I, const void* const* W, void* const* O);
+
 /* Split-K Linear that allocates nothing (no counterpart in the reference, whose
  * engine always has a buffer pool to draw the "partial" slot from).
  *

@@ -205,16 +205,18 @@ def test_chain_parallel_branches_match_serial(device):
     from vai_b200 import Tensor, presets
     x = Tensor.from_numpy(np.random.default_rng(4).standard_normal((1, 2048), dtype=np.float32))
     outs = []
-    for parallel, graph in ((False, True), (True, True), (True, False)):
-        net = vai_b200.NeuralNet(w_default_dtype=Dtype.BF16, device=device, parallel_branches=parallel, use_graph=graph)
+    for parallel, graph, grouped in ((False, True, False), (True, True, False), (True, False, False), (True, True, True),
+                                     (False, False, True)):
+        net = vai_b200.NeuralNet(w_default_dtype=Dtype.BF16, device=device, parallel_branches=parallel, use_graph=graph,
+                                 group_siblings=grouped)
         presets.build_linear_chain(net, "llama-3.2-1b", layers=2, vocab_rows=4096, seed=7)
         a = net(x).to_numpy()
         b = net(x).to_numpy()
         np.testing.assert_array_equal(a, b)
         outs.append(a)
     assert np.isfinite(outs[0]).all() and np.abs(outs[0]).max() > 0
-    np.testing.assert_array_equal(outs[0], outs[1])
-    np.testing.assert_array_equal(outs[0], outs[2])
+    for other in outs[1:]:
+        np.testing.assert_array_equal(outs[0], other)
 
 
 @pytest.mark.parametrize("M,K,w_dtype,expect", [(1, 512, "bf16", "gemv"), (4, 512, "bf16", "gemv"), (5, 512, "bf16", "skinny"),
@@ -249,3 +251,51 @@ def test_wide_tiles(M, K, N, gate, device, monkeypatch):
                                  epilogue="SILU", gate_fuse=gate, kernel=nodes.KERNEL_TC_GEMM)
     assert node.info.tile_m == 256
     assert_close(got, want, (2e-4, 5e-5), f"wide {M}x{K}x{N} gate={gate}")
+
+
+@pytest.mark.parametrize("M", [1, 3])
+@pytest.mark.parametrize("w_dtype", ["bf16", "f32"])
+def test_grouped_siblings_match_separate_runs(M, w_dtype, device):
+    """vaicu_linear_run_group: q / k / v-like Linears with ragged row counts in one launch."""
+    import ctypes
+
+    from vai_b200 import _lib
+    from vai_b200.engine import DeviceBuffer, encode
+    from gpu_util import DT
+    lib = device.lib
+    rng = np.random.default_rng(M)
+    K, rows = 512, [203, 64, 37]
+    dt = DT[w_dtype]
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    xb = DeviceBuffer(device, x.nbytes)
+    xb.upload(x)
+    plans, wbufs, obufs, wants = [], [], [], []
+    for n in rows:
+        w = (rng.standard_normal((n, K)) / np.sqrt(K)).astype(np.float32)
+        wb = DeviceBuffer(device, n * K * (4 if w_dtype == "f32" else 2))
+        wb.upload(encode(w, dt))
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = M, n, K
+        d.i_dtype, d.w_dtype, d.o_dtype, d.b_dtype = 0, int(dt), 0, 2
+        d.scalar_scale = 1.0
+        h = ctypes.c_void_p()
+        _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
+        plans.append(h)
+        wbufs.append(wb)
+        obufs.append(DeviceBuffer(device, M * n * 4))
+        wants.append(orc.linear_f64(x, seen(w, dt)))
+    n = len(rows)
+    _lib.check(lib.vaicu_linear_run_group((ctypes.c_void_p * n)(*plans), n, None, xb.ptr,
+                                          (ctypes.c_void_p * n)(*[b.ptr for b in wbufs]),
+                                          (ctypes.c_void_p * n)(*[b.ptr for b in obufs])), "group")
+    device.synchronize()
+    for nrows, ob, want in zip(rows, obufs, wants):
+        got = ob.download(np.empty((M, nrows), dtype=np.float32))
+        assert_close(got, want, (1e-5, 1e-5), f"group {nrows}")
+    # a Linear with an epilogue cannot join a group
+    d.epilogue = 1
+    h = ctypes.c_void_p()
+    _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
+    rc = lib.vaicu_linear_run_group((ctypes.c_void_p * 2)(plans[0], h), 2, None, xb.ptr,
+                                    (ctypes.c_void_p * 2)(wbufs[0].ptr, wbufs[2].ptr), (ctypes.c_void_p * 2)(obufs[0].ptr, obufs[2].ptr))
+    assert rc == 2

@@ -63,6 +63,8 @@ SIGNATURES = {
     "vaicu_linear_plan_info": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(LinearInfo)]),
     "vaicu_linear_workspace_bytes": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
     "vaicu_linear_run": (ctypes.c_int, [ctypes.c_void_p] * 8),
+    "vaicu_linear_run_group": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                              ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p)]),
     "vaicu_linear_splitk_static": (ctypes.c_int, [ctypes.POINTER(LinearDesc)] + [ctypes.c_void_p] * 6),
     "vaicu_linear_shard_desc": (ctypes.c_int, [ctypes.POINTER(LinearDesc), ctypes.c_int, ctypes.c_int,
                                                ctypes.POINTER(LinearDesc), ctypes.POINTER(ctypes.c_uint32),

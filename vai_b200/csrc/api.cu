@@ -715,6 +715,40 @@ int vaicu_linear_run(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I
     return VAICU_OK;
 }
 
+int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_stream_t stream, const void* I,
+                           const void* const* W, void* const* O)
+{
+    if (!plans || !W || !O || !I || count < 2 || count > 3) return VAICU_ERR_INVALID_VALUE;
+    const vaicu_linear_plan* p0 = plans[0];
+    if (!p0) return VAICU_ERR_INVALID_VALUE;
+    uint32_t rows[3] = {0, 0, 0};
+    uint64_t total = 0;
+    if (!aligned16(I)) return VAICU_ERR_UNSUPPORTED;
+    for (int i = 0; i < count; ++i) {
+        const vaicu_linear_plan* pl = plans[i];
+        if (!pl || !W[i] || !O[i]) return VAICU_ERR_INVALID_VALUE;
+        const vaicu_linear_desc& d = pl->d;
+        const vaicu_linear_desc& d0 = p0->d;
+        // one kernel family, one activation matrix, nothing after the dot product
+        if (pl->dev != p0->dev || pl->kernel != VAICU_KERNEL_GEMV || !pl->gemv_vec.vectorized) return VAICU_ERR_UNSUPPORTED;
+        if (d.M != d0.M || d.K != d0.K || d.i_dtype != d0.i_dtype || d.w_dtype != d0.w_dtype || d.o_dtype != d0.o_dtype)
+            return VAICU_ERR_UNSUPPORTED;
+        if (d.has_bias || d.has_residual || d.epilogue != VAICU_EPILOGUE_NONE || d.gate_fuse || d.scalar_scale != 1.0f)
+            return VAICU_ERR_UNSUPPORTED;
+        if (!aligned16(W[i])) return VAICU_ERR_UNSUPPORTED;
+        rows[i] = d.N;
+        total += d.N;
+    }
+    if (total * p0->d.M >= (1ull << 32)) return VAICU_ERR_UNSUPPORTED;
+    vaicu_linear_desc all = p0->d;
+    all.N = (uint32_t)total;
+    LinearArgs a = make_args(all, I, W[0], nullptr, nullptr, O[0]);
+    const GemvConfig cfg = choose_gemv(a, p0->dev->sm_count, true);
+    if (!cfg.vectorized) return VAICU_ERR_UNSUPPORTED;
+    VAICU_CUDA(launch_gemv_group(a, cfg, (uint32_t)count, rows, W, O, (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
 int vaicu_linear_shard_desc(const vaicu_linear_desc* full, int rank, int world, vaicu_linear_desc* shard,
                             uint32_t* w_row_begin, uint32_t* w_row_count)
 {

@@ -121,10 +121,13 @@ __device__ __forceinline__ float finish_gated(const EpilogueArgs& e, float acc_g
 }
 
 // Launchers implemented in the .cu files; each returns a cudaError_t.
-struct GemvConfig { int rows_per_warp; int k_warps; int grid; size_t smem; int vectorized; };
+struct GemvConfig { int rows_per_warp; int k_warps; int grid; size_t smem; int vectorized; int unroll; };
 
 cudaError_t launch_gemv(const LinearArgs& a, const GemvConfig& cfg, cudaStream_t stream);
 GemvConfig  choose_gemv(const LinearArgs& a, int sm_count, bool w_aligned16);
+// `a` describes the concatenation (a.N = sum of rows); plain Linears only.
+cudaError_t launch_gemv_group(const LinearArgs& a, const GemvConfig& cfg, uint32_t nseg, const uint32_t* rows,
+                              const void* const* w, void* const* o, cudaStream_t stream);
 
 struct FmaTileConfig { uint32_t split_count, split_size; };
 cudaError_t launch_fma_tile(const LinearArgs& a, const FmaTileConfig& cfg, float* partial, cudaStream_t stream);

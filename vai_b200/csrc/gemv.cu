@@ -86,6 +86,12 @@ struct GemvParams {
     uint32_t k_warps;    // warps splitting K inside a block
     uint32_t k_chunk;    // activations staged per round (multiple of 256)
     uint32_t k_pad;      // floats reserved per activation row in shared memory
+    // Grouped launch (nseg > 0): up to 3 plain Linears that share the activations run
+    // as one kernel over the concatenation of their weight rows.
+    uint32_t nseg;
+    uint32_t seg_begin[4];   // first virtual row of each segment; [nseg] = total rows
+    const void* seg_w[3];
+    void* seg_o[3];
 };
 
 // Four consecutive activations (chunk-relative kk, kk % 4 == 0) of row m -> fp32 in
@@ -146,8 +152,8 @@ __device__ __forceinline__ void load_x_direct(const LinearArgs& a, uint32_t k, f
 // the R/2 value rows of the same output columns.  Sums are kept as float2 pairs
 // (even / odd elements) and advanced with the packed fp32 FMA of sm_100, which
 // halves the FMA issue count: the kernel must stay memory-bound up to M = 8.
-template <typename TW, int M, int R>
-__global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const GemvParams p)
+template <typename TW, int M, int R, int U>
+__global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_kernel(const GemvParams p)
 {
     constexpr int VEC = WTraits<TW>::VEC;
     constexpr int PAIRS = VEC / 2;
@@ -185,7 +191,12 @@ __global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const 
             else row = j0 + r;
             const uint32_t lim = gate ? ((r < R / 2) ? H - 1u : 2u * H - 1u) : (a.N - 1u);
             row = row < lim ? row : lim;
-            rowp[r] = Wp + (size_t)row * K;
+            if (p.nseg) {
+                const uint32_t sg = (row >= p.seg_begin[1] ? 1u : 0u) + (row >= p.seg_begin[2] ? 1u : 0u);
+                rowp[r] = reinterpret_cast<const TW*>(p.seg_w[sg]) + (size_t)(row - p.seg_begin[sg]) * K;
+            } else {
+                rowp[r] = Wp + (size_t)row * K;
+            }
         }
         if (!staged) {
             // The weights do not depend on the previous kernel: pull this warp's first
@@ -221,30 +232,24 @@ __global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const 
                 staged = true;
             }
             const uint32_t iters = (span + stride - 1u) / stride;
-            for (uint32_t it = 0; it < iters; it += 2u) {
-                const uint32_t kkA = kk0 + it * stride, kkB = kkA + stride;
-                const bool vA = kkA < span, vB = (it + 1u < iters) && (kkB < span);
-                uint4 wA[R], wB[R];
+            for (uint32_t it = 0; it < iters; it += U) {
+                // U k-steps of R rows: U * R 16-byte loads in flight per lane
+                uint4 wv[U][R];
+                bool valid[U];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    wA[r] = vA ? ldg_stream(rowp[r] + c0 + kkA) : make_uint4(0, 0, 0, 0);
-                    wB[r] = vB ? ldg_stream(rowp[r] + c0 + kkB) : make_uint4(0, 0, 0, 0);
-                }
-                float2 xd[2][PAIRS];
-                if (DIRECT) {
-                    if (vA) load_x_direct<VEC>(a, c0 + kkA, xd[0]);
-                    if (vB) load_x_direct<VEC>(a, c0 + kkB, xd[1]);
+                for (int u = 0; u < U; ++u) {
+                    const uint32_t kk = kk0 + (it + u) * stride;
+                    valid[u] = (it + u < iters) && (kk < span);
+#pragma unroll
+                    for (int r = 0; r < R; ++r)
+                        wv[u][r] = valid[u] ? ldg_stream(rowp[r] + c0 + kk) : make_uint4(0, 0, 0, 0);
                 }
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const bool v = half ? vB : vA;
-                    if (!v) continue;
-                    const uint32_t kk = half ? kkB : kkA;
+                for (int u = 0; u < U; ++u) {
+                    if (!valid[u]) continue;
+                    const uint32_t kk = kk0 + (it + u) * stride;
                     float2 xf[M][PAIRS];
-                    if (DIRECT) {
-#pragma unroll
-                        for (int e = 0; e < PAIRS; ++e) xf[0][e] = xd[half][e];
-                    }
+                    if (DIRECT) load_x_direct<VEC>(a, c0 + kk, xf[0]);
 #pragma unroll
                     for (int m = 0; m < (DIRECT ? 0 : M); ++m) {
                         const float* xrow = xs + (size_t)m * p.k_pad;
@@ -262,7 +267,7 @@ __global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const 
 #pragma unroll
                     for (int r = 0; r < R; ++r) {
                         float2 wf[PAIRS];
-                        WTraits<TW>::unpack(half ? wB[r] : wA[r], wf);
+                        WTraits<TW>::unpack(wv[u][r], wf);
 #pragma unroll
                         for (int m = 0; m < M; ++m)
 #pragma unroll
@@ -304,8 +309,14 @@ __global__ void __launch_bounds__(kThreads, (M == 1 ? 3 : 2)) gemv_kernel(const 
                     const uint32_t r = lane / M, m = lane % M;
                     const uint32_t n = j0 + r;
                     if (n < a.N) {
-                        const size_t flat = (size_t)m * a.N + n;
-                        store_from_f32(a.O, a.o_dtype, flat, finish_output(ep, mine, flat));
+                        if (p.nseg) {
+                            const uint32_t sg = (n >= p.seg_begin[1] ? 1u : 0u) + (n >= p.seg_begin[2] ? 1u : 0u);
+                            const uint32_t width = p.seg_begin[sg + 1] - p.seg_begin[sg];
+                            store_from_f32(p.seg_o[sg], a.o_dtype, (size_t)m * width + (n - p.seg_begin[sg]), mine);
+                        } else {
+                            const size_t flat = (size_t)m * a.N + n;
+                            store_from_f32(a.O, a.o_dtype, flat, finish_output(ep, mine, flat));
+                        }
                     }
                 }
             } else {
@@ -367,10 +378,10 @@ __global__ void __launch_bounds__(kThreads) gemv_generic_kernel(const GemvParams
         }
 }
 
-template <typename TW, int M, int R>
+template <typename TW, int M, int R, int U = 2>
 cudaError_t launch_one(const GemvParams& p, const GemvConfig& cfg, cudaStream_t stream)
 {
-    auto kern = gemv_kernel<TW, M, R>;
+    auto kern = gemv_kernel<TW, M, R, U>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
@@ -399,7 +410,9 @@ cudaError_t launch_typed(const GemvParams& p, const GemvConfig& cfg, cudaStream_
 {
     const bool r4 = cfg.rows_per_warp == 4;
     switch (p.a.M) {
-    case 1: return r4 ? launch_one<TW, 1, 4>(p, cfg, stream) : launch_one<TW, 1, 2>(p, cfg, stream);
+    case 1:
+        if (cfg.unroll == 4) return r4 ? launch_one<TW, 1, 4, 4>(p, cfg, stream) : launch_one<TW, 1, 2, 4>(p, cfg, stream);
+        return r4 ? launch_one<TW, 1, 4, 2>(p, cfg, stream) : launch_one<TW, 1, 2, 2>(p, cfg, stream);
     case 2: return r4 ? launch_one<TW, 2, 4>(p, cfg, stream) : launch_one<TW, 2, 2>(p, cfg, stream);
     case 3: return r4 ? launch_one<TW, 3, 4>(p, cfg, stream) : launch_one<TW, 3, 2>(p, cfg, stream);
     case 4: return r4 ? launch_one<TW, 4, 4>(p, cfg, stream) : launch_one<TW, 4, 2>(p, cfg, stream);
@@ -426,12 +439,15 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
         c.grid = (int)((H + kWarps - 1u) / kWarps);
         return c;
     }
-    // Blocks resident at once: 3 per SM for M = 1 (launch bounds), else 2.  One
+    // Blocks resident at once: 2 per SM (launch bounds).  One
     // block-task = (8 / ks) row groups of R rows, K split over ks warps.  Wanted: all
     // tasks in flight together (no ragged second round), and at least half the
     // resident slots used; so few rows get a smaller R and a deeper K split, while
     // every warp keeps two 16-byte steps.
-    const uint32_t capacity = (uint32_t)sm_count * (a.M == 1u ? 3u : 2u);
+    // M = 1 comes in two depths: U = 2 k-steps in flight at 3 blocks per SM, or U = 4 at 2
+    static const int m1_unroll = getenv("VAICU_GEMV_U") ? atoi(getenv("VAICU_GEMV_U")) : 2;
+    c.unroll = (a.M == 1u && m1_unroll == 4) ? 4 : 2;
+    const uint32_t capacity = (uint32_t)sm_count * ((a.M == 1u && c.unroll == 2) ? 3u : 2u);
     // Measured: a deeper K split than needed is costly (lm_head 76 -> 108 us with ks = 2:
     // every pass then ends in a block-wide fold), so K is split only until about half
     // the resident slots are used, and R shrinks only when even that cannot be reached.
@@ -466,6 +482,40 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
     const uint32_t rounds = (nblocks + capacity - 1u) / capacity;
     c.grid = (int)((nblocks + rounds - 1u) / rounds);
     return c;
+}
+
+cudaError_t launch_gemv_group(const LinearArgs& a, const GemvConfig& cfg, uint32_t nseg, const uint32_t* rows,
+                              const void* const* w, void* const* o, cudaStream_t stream)
+{
+    if (nseg < 2u || nseg > 3u || !cfg.vectorized || a.gate_fuse) return cudaErrorInvalidValue;
+    GemvParams p{};
+    p.a = a;
+    p.H = a.N;
+    p.nseg = nseg;
+    uint32_t total = 0;
+    for (uint32_t i = 0; i < 4u; ++i) p.seg_begin[i] = 0xFFFFFFFFu;
+    for (uint32_t i = 0; i < nseg; ++i) {
+        p.seg_begin[i] = total;
+        p.seg_w[i] = w[i];
+        p.seg_o[i] = o[i];
+        total += rows[i];
+    }
+    p.seg_begin[nseg] = total;
+    if (total != a.N) return cudaErrorInvalidValue;
+    p.cols_per_warp = (uint32_t)cfg.rows_per_warp;
+    p.k_warps = (uint32_t)cfg.k_warps;
+    const uint32_t budget_floats = (96u * 1024u) / 4u / a.M;
+    uint32_t k_chunk = (budget_floats / 256u) * 256u;
+    const uint32_t k_round = ((a.K + 255u) / 256u) * 256u;
+    if (k_chunk > k_round) k_chunk = k_round;
+    p.k_chunk = a.M == 1u ? k_round : k_chunk;
+    p.k_pad = a.M == 1u ? 0u : k_chunk;
+    switch (a.w_dtype) {
+    case VAICU_DTYPE_F32: return launch_typed<float>(p, cfg, stream);
+    case VAICU_DTYPE_F16: return launch_typed<__half>(p, cfg, stream);
+    case VAICU_DTYPE_BF16: return launch_typed<__nv_bfloat16>(p, cfg, stream);
+    default: return cudaErrorInvalidValue;
+    }
 }
 
 cudaError_t launch_gemv(const LinearArgs& a, const GemvConfig& cfg, cudaStream_t stream)

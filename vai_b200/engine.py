@@ -375,7 +375,7 @@ class NeuralNet:
         return getattr(cls._tls, "net", None)
 
     def __init__(self, w_default_dtype=Dtype.F16, o_default_dtype=Dtype.F32, device=None, use_graph=True,
-                 parallel_branches=True):
+                 parallel_branches=True, group_siblings=True):
         if Dtype(w_default_dtype) == Dtype.NONE or Dtype(o_default_dtype) == Dtype.NONE:
             raise ValueError("default dtypes may not be NONE")
         self.w_default_dtype = Dtype(w_default_dtype)
@@ -385,6 +385,7 @@ class NeuralNet:
         self.stream = self.device.create_stream()
         self._streams = [self.stream]
         self.parallel_branches = parallel_branches
+        self.group_siblings = group_siblings
         self.max_side_streams = 3
         self.use_graph = use_graph
         self._nodes = []
@@ -471,17 +472,36 @@ class NeuralNet:
         ops = []
         for lv in sorted(by_level):
             group = by_level[lv]
-            if len(group) == 1 or not self.parallel_branches:
-                ops += [("run", 0, bound[n]) for n in group]
+            launches = []
+            if self.group_siblings:
+                # sibling Linears that read the same tensor and do nothing after the dot
+                # product (q / k / v) share one launch
+                rest, by_input = [], {}
+                for n in group:
+                    if getattr(n, "groupable", None) and n.groupable():
+                        by_input.setdefault((id(n.slots["in0"]), int(n.slots["weight"].dtype), int(n.slots["out0"].dtype)), []).append(n)
+                    else:
+                        rest.append(n)
+                for members in by_input.values():
+                    while len(members) >= 2:
+                        take, members = members[:3], members[3:]
+                        launches.append(type(take[0]).bind_group(take))
+                    rest += members
+                launches += [bound[n] for n in rest]
+            else:
+                launches = [bound[n] for n in group]
+            if len(launches) == 1 or not self.parallel_branches:
+                ops += [("run", 0, fn) for fn in launches]
                 continue
-            width = min(len(group), 1 + self.max_side_streams)
+            width = min(len(launches), 1 + self.max_side_streams)
             sides = list(range(1, width))
             ops.append(("fork", sides, None))
-            ops += [("run", i % width, bound[n]) for i, n in enumerate(group)]
+            ops += [("run", i % width, fn) for i, fn in enumerate(launches)]
             ops.append(("join", sides, None))
         while len(self._streams) < 1 + self.max_side_streams and any(op[0] == "fork" for op in ops):
             self._streams.append(self.device.create_stream())
         rec.ops = ops
+        rec.kernel_launches = sum(getattr(op[2], "kernel_launches", 0) for op in ops if op[0] == "run")
         if self.use_graph:
             _lib.check(lib.vaicu_graph_capture_begin(self.stream), "vaicu_graph_capture_begin")
             DeviceBuffer._capturing += 1

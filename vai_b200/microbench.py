@@ -30,7 +30,7 @@ def algorithmic_bytes(M, N, K, i_dt, w_dt, o_dt, bias, residual, gate):
 
 
 def run(M, K, N, i_dtype="f32", w_dtype="bf16", o_dtype="f32", epilogue="NONE", gate=False, bias=False,
-        residual=False, kernel=0, copies=0, iters=50, warmup=5, split_size=0, device=None, graph=False):
+        residual=False, kernel=0, copies=0, iters=50, warmup=5, split_size=0, device=None, graph=False, clocks=False):
     dev = device or Device.default()
     lib = dev.lib
     i_dt, w_dt, o_dt = DT[i_dtype], DT[w_dtype], DT[o_dtype]
@@ -90,6 +90,13 @@ def run(M, K, N, i_dtype="f32", w_dtype="bf16", o_dtype="f32", epilogue="NONE", 
     for i in range(max(warmup, copies)):
         launch(i)
     lib.vaicu_stream_sync(stream)
+    sampler = None
+    if clocks:
+        import subprocess
+        sampler = subprocess.Popen(["nvidia-smi", "--query-gpu=clocks.sm,power.draw,clocks_event_reasons.sw_power_cap,"
+                                    "clocks_event_reasons.hw_slowdown,clocks_event_reasons.sw_thermal_slowdown",
+                                    "--format=csv,noheader,nounits", "-lms", "100", "-i", str(dev.ordinal)],
+                                   stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
     if graph:
         # record `iters` launches once and replay the recording: no host launch cost
         # between kernels, as in a net's replayed step
@@ -111,12 +118,27 @@ def run(M, K, N, i_dtype="f32", w_dtype="bf16", o_dtype="f32", epilogue="NONE", 
     ms = ctypes.c_float()
     lib.vaicu_event_elapsed_ms(e0, e1, ctypes.byref(ms))
     dev.check_status()
+    clock_info = None
+    if sampler is not None:
+        import statistics
+        import time
+        time.sleep(0.15)
+        sampler.terminate()
+        rows = [ln.split(",") for ln in sampler.stdout.read().strip().splitlines() if ln.strip()]
+        mhz = [float(r[0]) for r in rows if r[0].strip().replace(".", "").isdigit()]
+        watts = [float(r[1]) for r in rows if len(r) > 1 and r[1].strip().replace(".", "").isdigit()]
+        clock_info = {"sm_mhz_median": statistics.median(mhz) if mhz else None, "sm_mhz_min": min(mhz) if mhz else None,
+                      "power_w_max": max(watts) if watts else None, "samples": len(mhz),
+                      "power_cap_seen": any("Active" in r[2] for r in rows if len(r) > 2),
+                      "slowdown_seen": any("Active" in c and "Not" not in c for r in rows for c in r[3:5])}
     us = ms.value * 1e3 / iters
     ab = algorithmic_bytes(M, N, K, i_dt, w_dt, o_dt, bias, residual, gate)
     res = {"M": M, "K": K, "N": N, "dtypes": [i_dtype, w_dtype, o_dtype], "gate": gate, "kernel": info.kernel,
            "split_count": info.split_count, "tile": [info.tile_m, info.tile_n], "launches": info.launches,
            "us_per_call": us, "GBps": ab / us / 1e3, "TFLOPs": 2.0 * M * N * K / us / 1e6, "copies": copies,
            "algorithmic_bytes": ab}
+    if clock_info:
+        res["clocks"] = clock_info
     for h in plans:
         lib.vaicu_linear_plan_destroy(h)
     for b in weights:
@@ -142,9 +164,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--split-size", type=int, default=0)
     ap.add_argument("--graph", action="store_true", help="time a replayed recording of the launches")
+    ap.add_argument("--clocks", action="store_true", help="sample nvidia-smi SM clock and power during the timed loop")
     a = ap.parse_args()
     print(json.dumps(run(a.M, a.K, a.N, a.i_dtype, a.w_dtype, a.o_dtype, a.epilogue, a.gate, a.bias, a.residual,
-                         a.kernel, a.copies, a.iters, a.warmup, a.split_size, graph=a.graph)))
+                         a.kernel, a.copies, a.iters, a.warmup, a.split_size, graph=a.graph, clocks=a.clocks)))
 
 
 if __name__ == "__main__":

@@ -136,6 +136,32 @@ class LinearNode(Node):
         def launch(stream):
             _lib.check(run(plan, stream, x, w, b, r, o, ws), "vaicu_linear_run")
 
+        launch.kernel_launches = int(self.info.launches)
+        return launch
+
+    def groupable(self):
+        """Plain (nothing after the dot product) and on the weight-streaming kernel: may
+        share one launch with sibling Linears that read the same activations."""
+        return (self.info is not None and self.info.kernel == KERNEL_GEMV and not self.has_bias()
+                and not self.accept_residual and self.epilogue == Epilogue.NONE and not self.gate_fuse
+                and self.scalar_scale == 1.0)
+
+    @staticmethod
+    def bind_group(group):
+        """One launch for 2-3 groupable nodes with the same in0 (vaicu_linear_run_group)."""
+        first = group[0]
+        dev = first._device()
+        n = len(group)
+        plans = (ctypes.c_void_p * n)(*[g._plan for g in group])
+        ws = (ctypes.c_void_p * n)(*[g["weight"].ptr for g in group])
+        outs = (ctypes.c_void_p * n)(*[g["out0"].ptr for g in group])
+        x = first["in0"].ptr
+        run = dev.lib.vaicu_linear_run_group
+
+        def launch(stream):
+            _lib.check(run(plans, n, stream, x, ws, outs), "vaicu_linear_run_group")
+
+        launch.kernel_launches = 1
         return launch
 
     def __del__(self):
