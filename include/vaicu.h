@@ -235,6 +235,13 @@ VAICU_API int vaicu_linear_splitk_static(const vaicu_linear_desc* desc, vaicu_st
                                          const void* I, const void* W, const void* bias, const void* residual,
                                          void* O);
 
+/* Row-wise argmax of logits [M, N] (fp32 / fp16 / bf16) into M raw uint32 indices:
+ * vAi's Argmax node, the greedy-decode consumer of the lm_head Linear
+ * (vai/nodes/argmax.h:9-18, 57-79; vai/shaders/argmax.comp).  Ties resolve to the
+ * lowest index, as torch.argmax (the reference's test oracle) does.  Enqueues one
+ * kernel on `stream`; no allocation, no synchronisation. */
+VAICU_API int vaicu_argmax_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, void* out_u32);
+
 /* Column-split helper for the multi-GPU layout: the desc of rank `rank` of
  * `world` when W's rows (output columns) are split evenly; for gate_fuse the
  * split is per half.  Fills row offsets into W / bias for that rank. No

@@ -330,6 +330,34 @@ int vai_oracle_linear(const oracle_desc* d, const void* I, const void* W, const 
     return vai_oracle_linear_tile(d, I, W, bias, R, O, stage16, d->w_dtype == DT_F32 ? d->i_dtype : d->w_dtype);
 }
 
+/* Argmax node (vai/shaders/argmax.comp:50-95): 256 threads each scan a strided slice of
+ * the row keeping the first strict maximum, then a tree merge keeps the lower thread's
+ * candidate unless the other is strictly greater.  With ties between different threads
+ * the shader's result therefore depends on thread order, not on index order; distinct
+ * values (the case the reference tests) give the plain argmax. */
+int vai_oracle_argmax(const void* in, int dtype, uint32_t M, uint32_t N, uint32_t* out)
+{
+    enum { LOCAL = 256 };
+    for (uint32_t row = 0; row < M; ++row) {
+        float smax[LOCAL];
+        uint32_t sidx[LOCAL];
+        for (uint32_t tid = 0; tid < LOCAL; ++tid) {
+            float best = -3.4028235e38f;
+            uint32_t bi = 0;
+            for (uint32_t i = tid; i < N; i += LOCAL) {
+                const float v = load_elem(in, dtype, (size_t)row * N + i);
+                if (v > best) { best = v; bi = i; }
+            }
+            smax[tid] = best; sidx[tid] = bi;
+        }
+        for (uint32_t stride = LOCAL / 2; stride > 0; stride >>= 1)
+            for (uint32_t tid = 0; tid < stride; ++tid)
+                if (smax[tid + stride] > smax[tid]) { smax[tid] = smax[tid + stride]; sidx[tid] = sidx[tid + stride]; }
+        out[row] = sidx[0];
+    }
+    return 0;
+}
+
 int vai_oracle_num_threads(void)
 {
 #ifdef _OPENMP

@@ -160,3 +160,14 @@ def linear_c(desc, I, W, bias=None, residual=None, path="auto", wg_size=128, sta
     if rc != 0:
         raise RuntimeError(f"oracle returned {rc}")
     return O
+
+
+def argmax_c(logits, dtype=F32):
+    """The C restatement of vAi's argmax shader on a [M, N] array in device representation."""
+    a = np.ascontiguousarray(logits)
+    out = np.empty(a.shape[0], dtype=np.uint32)
+    rc = lib().vai_oracle_argmax(ctypes.c_void_p(a.ctypes.data), ctypes.c_int(dtype), ctypes.c_uint32(a.shape[0]),
+                                 ctypes.c_uint32(a.shape[1]), ctypes.c_void_p(out.ctypes.data))
+    if rc != 0:
+        raise RuntimeError(f"oracle returned {rc}")
+    return out

@@ -37,6 +37,7 @@ def _stub_pyvai():
     pyvai.Tensor = object
     nodes = types.ModuleType("pyvai.nodes")
     nodes.LinearNode = lambda **kw: dict(kw)
+    nodes.ArgmaxNode = lambda **kw: {"node": "argmax", **kw}
     pyvai.nodes = nodes
     sys.modules["pyvai"] = pyvai
     sys.modules["pyvai.nodes"] = nodes
@@ -47,6 +48,7 @@ def main(ref_root):
     sys.path.insert(0, os.path.join(ref_root, "python", "tests"))
     sys.path.insert(0, os.path.join(ref_root, "python", "tests", "nodes"))
     import node_check
+    import test_argmax
     import test_linear
 
     records = {}
@@ -113,6 +115,10 @@ def main(ref_root):
         for p in mark.args[1]:
             test_linear.test_linear_residual(*p.values)
             record(f"residual_{p.id}")
+
+    # the lm_head's consumer: Argmax (python/tests/nodes/test_argmax.py), exact uint32 indices
+    test_argmax.test_argmax()
+    record("argmax")
 
     here = os.path.dirname(os.path.abspath(__file__))
     np.savez_compressed(os.path.join(here, "linear_golden.npz"), **arrays)

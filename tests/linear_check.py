@@ -42,7 +42,7 @@ def draw_case(meta, key):
     rec = meta[key]
     base = meta[rec["rerun_of"]] if rec["rerun_of"] else rec
     rng = np.random.default_rng(0)
-    k = base["config"]["in_dim"]
+    k = base["config"].get("in_dim", 1)
     params = {}
     for slot in base["param_order"]:
         shape = tuple(base["param_shapes"][slot])

@@ -749,6 +749,16 @@ int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_str
     return VAICU_OK;
 }
 
+int vaicu_argmax_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, void* out_u32)
+{
+    if (!logits || !out_u32 || M == 0 || N == 0) return VAICU_ERR_INVALID_VALUE;
+    if (!valid_dtype(dtype)) return VAICU_ERR_INVALID_VALUE;
+    if ((reinterpret_cast<uintptr_t>(logits) & (dtype_size(dtype) - 1u)) || (reinterpret_cast<uintptr_t>(out_u32) & 3u))
+        return VAICU_ERR_ALIGNMENT;
+    VAICU_CUDA(launch_argmax(logits, dtype, M, N, reinterpret_cast<uint32_t*>(out_u32), (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
 int vaicu_linear_shard_desc(const vaicu_linear_desc* full, int rank, int world, vaicu_linear_desc* shard,
                             uint32_t* w_row_begin, uint32_t* w_row_count)
 {

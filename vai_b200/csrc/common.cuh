@@ -134,6 +134,8 @@ cudaError_t launch_fma_tile(const LinearArgs& a, const FmaTileConfig& cfg, float
 cudaError_t launch_splitk_reduce(const LinearArgs& a, const float* partial, uint32_t split_count, cudaStream_t stream);
 cudaError_t launch_cast_f32_to_16(const float* src, void* dst, int dst_dtype, size_t n, int sm_count, cudaStream_t stream);
 
+cudaError_t launch_argmax(const void* in, int dtype, uint32_t M, uint32_t N, uint32_t* out, cudaStream_t stream);
+
 // Records "<where>: <what>" as the calling thread's last error text
 // (vaicu_last_cuda_error).
 void set_last_error(const char* where, const char* what);

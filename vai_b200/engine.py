@@ -248,6 +248,11 @@ class Tensor:
         out = np.empty(self.shape, dtype=np.float32 if self.dtype == Dtype.F32 else np.uint16)
         return self.buffer.download(out)
 
+    def to_u32(self):
+        """The 4-byte slots read as raw uint32 (index outputs such as Argmax's)."""
+        raw = self.download_bits() if self.buffer is not None else self.host
+        return np.array(raw, dtype=np.float32).view(np.uint32)
+
     def to_numpy(self):
         """float32 for F32 / BF16, float16 for F16."""
         raw = self.download_bits() if self.buffer is not None else self.host

@@ -171,3 +171,35 @@ class LinearNode(Node):
                 lib.vaicu_linear_plan_destroy(h)
         except Exception:
             pass
+
+
+class ArgmaxNode(Node):
+    """Row-wise argmax (greedy decode) over logits: in0 [M, N] -> out0 [M] raw uint32
+    indices in 4-byte slots (vAi vai/nodes/argmax.h:9-18; read them with
+    Tensor.to_u32()).  Ties go to the lowest index."""
+
+    def __init__(self):
+        super().__init__()
+        self.add_slot("out0", OUTPUT)
+        self.add_slot("in0", INPUT)
+
+    def prepare(self):
+        x = self["in0"]
+        if not x.valid_shape() or len(x.shape) != 2:
+            raise ValueError("in0 must be [M, N]")
+        # a [M] tensor of raw uint32; the dtype enum has no integer kind, so fp32 is the
+        # 4-byte container, as in the reference (argmax.h:75-78)
+        self.slots["out0"] = Tensor((x.shape[0],), Dtype.F32)
+
+    def bind(self):
+        from .engine import Device
+        dev = self.net.device if self.net is not None else Device.default()
+        x, o = self["in0"], self["out0"]
+        xp, op, dt, M, N = x.ptr, o.ptr, int(x.dtype), x.shape[0], x.shape[1]
+        run = dev.lib.vaicu_argmax_run
+
+        def launch(stream):
+            _lib.check(run(stream, xp, dt, M, N, op), "vaicu_argmax_run")
+
+        launch.kernel_launches = 1
+        return launch

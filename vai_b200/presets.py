@@ -96,12 +96,26 @@ class _BitsSource:
 
 
 def build_linear_chain(net, name, *, w_dtype=Dtype.BF16, fuse_gate=True, seed=0, layers=None, lm_head=True,
-                       vocab_rows=None):
+                       vocab_rows=None, argmax=False, share_weights=None):
     """Adds one step's Linear nodes to `net` and wires them; returns the list of nodes.
     Input slot "x" [M, d]; output "logits" [M, vocab] (or the last hidden state when
-    lm_head is False).  Weights ~ N(0, 0.02) in `w_dtype`."""
+    lm_head is False).  With argmax=True an Argmax node follows the lm_head and the
+    output is "token" [M] (raw uint32), the greedy-decode step of the reference's nets.
+    Weights ~ N(0, 0.02) in `w_dtype`; share_weights = the node list of another chain of
+    the same preset makes this chain use those nodes' weight tensors (same storage)."""
     p = PRESETS[name]
-    src = _BitsSource(w_dtype, 0.02, seed)
+    src = _BitsSource(w_dtype, 0.02, seed) if share_weights is None else None
+    shared = iter(share_weights) if share_weights is not None else None
+
+    def weight_for(node, shape):
+        if shared is None:
+            return src.take(shape)
+        other = next(shared)
+        assert tuple(other["weight"].shape) == tuple(shape)
+        if other.has_bias():
+            node["bias"] = other["bias"]
+        return other["weight"]
+
     act = getattr(Epilogue, p["act"])
     nodes = []
     x = x0 = net.input("x")
@@ -113,8 +127,8 @@ def build_linear_chain(net, name, *, w_dtype=Dtype.BF16, fuse_gate=True, seed=0,
             node = LinearNode(in_dim=k, out_dim=n, accept_residual=bool(ex.get("residual")),
                               epilogue=act if (gate or ex.get("act")) else Epilogue.NONE, gate_fuse=gate,
                               scalar_scale={"o": 0.5, "down": 0.25, "fc2": 0.25}.get(lname, 1.0))
-            node["weight"] = src.take((n, k))
-            if ex.get("bias"):
+            node["weight"] = weight_for(node, (n, k))
+            if ex.get("bias") and shared is None:
                 node["bias"] = src.take((n,))
             made[lname] = node
             nodes.append(node)
@@ -142,9 +156,13 @@ def build_linear_chain(net, name, *, w_dtype=Dtype.BF16, fuse_gate=True, seed=0,
     if lm_head:
         v = p["vocab"] if vocab_rows is None else vocab_rows
         head = LinearNode(in_dim=p["d"], out_dim=v)
-        head["weight"] = src.take((v, p["d"]))
+        head["weight"] = weight_for(head, (v, p["d"]))
         nodes.append(head)
-        x - head - net.output("logits")
+        if argmax:
+            from .nodes import ArgmaxNode
+            x - head - ArgmaxNode() - net.output("token")
+        else:
+            x - head - net.output("logits")
     else:
         x - net.output("logits")
     return nodes
