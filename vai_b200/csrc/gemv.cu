@@ -179,6 +179,8 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
     const TW* Wp = reinterpret_cast<const TW*>(a.W);
     const uint32_t kk0 = (ks * 32u + lane) * VEC;
     bool staged = false;
+    uint4 wv[U][R];           // one trip of weights: U k-steps of R rows per lane
+    bool preloaded = false;   // wv already holds the first trip (loaded ahead of the dependency wait)
 
     for (uint32_t pb = blockIdx.x; pb < nblocks; pb += gridDim.x) {
         const uint32_t g = pb * RG + rg;              // may be >= ngroups: rows clamp, stores skip
@@ -207,6 +209,17 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
 #pragma unroll
                 for (uint32_t it = 0; it < 8u; ++it)
                     if (kk0 + it * stride < first_span) prefetch_l2(rowp[r] + kk0 + it * stride);
+            // ... and this warp's first trip goes all the way into registers: its loads are
+            // in flight while the wait below and the activation staging run
+            const uint32_t iters0 = (first_span + stride - 1u) / stride;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t kk = kk0 + (uint32_t)u * stride;
+                const bool v = ((uint32_t)u < iters0) && (kk < first_span);
+#pragma unroll
+                for (int r = 0; r < R; ++r) wv[u][r] = v ? ldg_stream(rowp[r] + kk) : make_uint4(0, 0, 0, 0);
+            }
+            preloaded = true;
             dependency_wait();
             if (DIRECT) staged = true;
         }
@@ -234,16 +247,22 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
             const uint32_t iters = (span + stride - 1u) / stride;
             for (uint32_t it = 0; it < iters; it += U) {
                 // U k-steps of R rows: U * R 16-byte loads in flight per lane
-                uint4 wv[U][R];
                 bool valid[U];
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const uint32_t kk = kk0 + (it + u) * stride;
                     valid[u] = (it + u < iters) && (kk < span);
-#pragma unroll
-                    for (int r = 0; r < R; ++r)
-                        wv[u][r] = valid[u] ? ldg_stream(rowp[r] + c0 + kk) : make_uint4(0, 0, 0, 0);
                 }
+                if (!preloaded) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const uint32_t kk = kk0 + (it + u) * stride;
+#pragma unroll
+                        for (int r = 0; r < R; ++r)
+                            wv[u][r] = valid[u] ? ldg_stream(rowp[r] + c0 + kk) : make_uint4(0, 0, 0, 0);
+                    }
+                }
+                preloaded = false;
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     if (!valid[u]) continue;
