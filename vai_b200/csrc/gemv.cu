@@ -484,6 +484,24 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
         }
         if (done) break;
     }
+    {
+        // Between one and two rounds the equal-pass grid leaves ~40 % of the resident slots
+        // empty (gate|value of Llama-1B: 512 tasks -> 256 blocks of 2 passes).  One more K
+        // doubling then fills more slots (1024 tasks -> 342 blocks of 3 passes: 14.7 -> 13.1 us
+        // measured); doubling further loses again to the per-pass fold.
+        const uint32_t cols_r = a.gate_fuse ? (uint32_t)R / 2u : (uint32_t)R;
+        const uint32_t groups_r = (H + cols_r - 1u) / cols_r;
+        auto resident = [&](int k) {
+            const uint32_t tasks = (groups_r + (uint32_t)(kWarps / k) - 1u) / (uint32_t)(kWarps / k);
+            const uint32_t rounds_k = (tasks + capacity - 1u) / capacity;
+            return (tasks + rounds_k - 1u) / rounds_k;
+        };
+        if (ks < kWarps && a.K / (uint32_t)(2 * ks * 32 * vec) >= 2u && resident(ks) * 10u < capacity * 7u &&
+            resident(2 * ks) > resident(ks))
+            ks *= 2;
+    }
+    if (const char* e = getenv("VAICU_GEMV_R")) { const int v = atoi(e); if ((v == 2 || v == 4) && (v == 2 || a.M <= 4u)) R = v; }   // tuning overrides
+    if (const char* e = getenv("VAICU_GEMV_KS")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8) ks = v; }
     const uint32_t cols = a.gate_fuse ? (uint32_t)R / 2u : (uint32_t)R;
     const uint32_t groups = (H + cols - 1u) / cols;
     c.rows_per_warp = R;
@@ -500,6 +518,7 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
     // that every block runs the same number of passes instead of leaving a short tail
     const uint32_t rounds = (nblocks + capacity - 1u) / capacity;
     c.grid = (int)((nblocks + rounds - 1u) / rounds);
+    if (const char* e = getenv("VAICU_GEMV_GRID")) { const int v = atoi(e); if (v > 0) c.grid = v < (int)nblocks ? v : (int)nblocks; }
     return c;
 }
 
