@@ -1,0 +1,102 @@
+// vai::NeuralNet (vai_b200/host/net.h) with vai::node::Linear nodes: wiring, ordering and,
+// with --gpu, a two-layer MLP with a residual run end to end and replayed.
+#include <cmath>
+#include <cstdio>
+
+#include "../../vai_b200/host/net.h"
+
+using namespace vai;
+using vai::node::Linear;
+
+static int fails = 0;
+#define EXPECT(cond)                                                                          \
+    do {                                                                                      \
+        if (!(cond)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #cond); ++fails; } \
+    } while (0)
+
+static void wiring()
+{
+    NeuralNet net;
+    Linear a({.inDim = 8, .outDim = 16, .epilogue = Epilogue::Relu});
+    Linear b({.inDim = 16, .outDim = 8, .acceptResidual = true});
+    net.input("x") - a - b - net.output("y");
+    net.input("x") - "residual" / b;
+    net.finish();
+    Linear stray({.inDim = 2, .outDim = 2});      // constructed after finish(): not part of the net
+    EXPECT(net.nodes().size() == 4);              // a, b, input x, output y
+    auto order = net.sortedNodes();
+    auto pos = [&](Node* n) { return std::find(order.begin(), order.end(), n) - order.begin(); };
+    EXPECT(pos(&a) < pos(&b));
+    EXPECT(b.links().at("in0").first == &a && b.links().at("residual").second == "out0");
+    bool threw = false;
+    try { net.input("x") - "nope" / a; } catch (const std::invalid_argument&) { threw = true; }
+    EXPECT(threw);
+    // a cycle is reported, not looped over
+    NeuralNet loop;
+    Linear c({.inDim = 4, .outDim = 4}), d({.inDim = 4, .outDim = 4});
+    c - d;
+    d - c;
+    threw = false;
+    try { loop.sortedNodes(); } catch (const std::runtime_error&) { threw = true; }
+    EXPECT(threw);
+}
+
+static void mlp_on_gpu(bool useGraph)
+{
+    const uint32_t M = 5, D = 64, H = 96;
+    std::vector<float> x(M * D), w1(H * D), b1(H), w2(D * H);
+    unsigned s = 777;
+    auto rnd = [&] { s = s * 1664525u + 1013904223u; return ((s >> 8) & 0xFFFF) / 32768.0f - 1.0f; };
+    for (auto& v : x) v = rnd();
+    for (auto& v : w1) v = rnd() * 0.2f;
+    for (auto& v : b1) v = rnd();
+    for (auto& v : w2) v = rnd() * 0.2f;
+    initVAIEngine(0);
+    NeuralNet net({.wDefaultDtype = Dtype::Fp32, .useGraph = useGraph});
+    Linear fc1({.inDim = D, .outDim = H, .epilogue = Epilogue::Relu});
+    Linear fc2({.inDim = H, .outDim = D, .acceptResidual = true, .scalarScale = 0.5f});
+    net.input("x") - fc1 - fc2 - net.output("y");
+    net.input("x") - "residual" / fc2;
+    net.finish();
+    fc1["weight"] = Tensor({H, D}, Dtype::Fp32); fc1["weight"].upload(w1.data());
+    fc1["bias"] = Tensor({H}, Dtype::Fp32); fc1["bias"].upload(b1.data());
+    fc2["weight"] = Tensor({D, H}, Dtype::Fp32); fc2["weight"].upload(w2.data());
+    vaicu_device_synchronize(deviceHandle());
+    for (uint32_t rows : {M, 3u, M}) {          // a second shape re-records; the first is replayed afterwards
+        std::vector<float> xin(x.begin(), x.begin() + rows * D);
+        auto out = net({{"x", HostTensor::fromFloats({rows, D}, xin)}});
+        auto again = net({{"x", HostTensor::fromFloats({rows, D}, xin)}});
+        const std::vector<float> y = out.at("y").floats();
+        EXPECT(y == again.at("y").floats());
+        EXPECT(out.at("y").shape == (std::vector<uint32_t>{rows, D}));
+        double worst = 0;
+        for (uint32_t m = 0; m < rows; ++m) {
+            std::vector<double> h(H);
+            for (uint32_t j = 0; j < H; ++j) {
+                double acc = b1[j];
+                for (uint32_t k = 0; k < D; ++k) acc += double(xin[m * D + k]) * w1[j * D + k];
+                h[j] = acc > 0 ? acc : 0;
+            }
+            for (uint32_t n = 0; n < D; ++n) {
+                double acc = 0;
+                for (uint32_t j = 0; j < H; ++j) acc += h[j] * w2[n * H + j];
+                const double want = 0.5 * acc + xin[m * D + n];
+                worst = std::fmax(worst, std::fabs(want - y[m * D + n]) / std::fmax(1.0, std::fabs(want)));
+            }
+        }
+        std::printf("graph=%d rows=%u worst rel err %.3g\n", (int)useGraph, rows, worst);
+        EXPECT(worst < 1e-4);
+    }
+    EXPECT(net.recordingCount() == (useGraph ? 2u : 1u));
+}
+
+int main(int argc, char** argv)
+{
+    wiring();
+    if (argc > 1 && std::string(argv[1]) == "--gpu") {
+        mlp_on_gpu(true);
+        mlp_on_gpu(false);
+    }
+    std::printf(fails ? "FAILED (%d)\n" : "ok\n", fails);
+    return fails ? 1 : 0;
+}

@@ -94,6 +94,7 @@ public:
         buffer_.reset(b, [](vaicu_buffer* p) { vaicu_buffer_free(p); });
     }
     void bindExternal(void* devicePtr, size_t byteOffset = 0) { external_ = devicePtr; byteOffset_ = byteOffset; }
+    void bindPooled(std::shared_ptr<vaicu_buffer> buffer) { buffer_ = std::move(buffer); }   // a range handed out by a pool
     void* devicePtr() const
     {
         char* base = static_cast<char*>(external_ ? external_ : (buffer_ ? vaicu_buffer_ptr(buffer_.get()) : nullptr));
@@ -124,11 +125,28 @@ private:
     Tensor value_;
 };
 
+class Node;
+
+// Whoever is collecting nodes on this thread (a NeuralNet under construction); nodes
+// attach to it from their constructor, as vAi's do to NeuralNet::currentNet_
+// (vai/engine/neural-net.h:293).
+struct NodeOwner {
+    virtual void attach(Node* node) = 0;
+    virtual ~NodeOwner() = default;
+};
+inline NodeOwner*& currentOwner()
+{
+    thread_local NodeOwner* owner = nullptr;
+    return owner;
+}
+
 // Operator base: named slots, prepare(), run() (vai/engine/neural-net.h:150-226);
 // run() takes the backend's stream where the reference takes a command buffer.
 class Node
 {
     std::map<std::string, NodeSlot> slots_;
+    // input slot -> (producer, its output slot); written by the wiring operators
+    std::map<std::string, std::pair<Node*, std::string>> links_;
 
 protected:
     Dtype oDtype_ = Dtype::None;
@@ -136,7 +154,16 @@ protected:
     void addSlot(const std::string& name, NodeSlot::Type type) { slots_.try_emplace(name, type); }
 
 public:
+    Node()
+    {
+        if (currentOwner()) currentOwner()->attach(this);
+    }
+    Node(const Node&) = delete;
+    Node& operator=(const Node&) = delete;
     virtual ~Node() = default;
+    std::map<std::string, std::pair<Node*, std::string>>& links() { return links_; }
+    const std::map<std::string, std::pair<Node*, std::string>>& links() const { return links_; }
+    bool hasSlot(const std::string& name) const { return slots_.count(name) != 0; }
     Tensor& operator[](const std::string& name) { return slots_.at(name).getValueRef(); }
     const Tensor& operator[](const std::string& name) const { return slots_.at(name).getValueRef(); }
     const std::map<std::string, NodeSlot>& slots() const { return slots_; }
@@ -182,9 +209,6 @@ public:
     {
         if (plan_) vaicu_linear_plan_destroy(plan_);
     }
-    Linear(const Linear&) = delete;
-    Linear& operator=(const Linear&) = delete;
-
     bool hasBias() const { return (*this)["bias"].validShape(); }   // linear.h:287
     const vaicu_linear_info& info() const { return info_; }
 
