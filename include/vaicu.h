@@ -235,6 +235,17 @@ VAICU_API int vaicu_linear_splitk_static(const vaicu_linear_desc* desc, vaicu_st
                                          const void* I, const void* W, const void* bias, const void* residual,
                                          void* O);
 
+/* RMS normalisation over the last axis: vAi's RmsNorm node, the producer of a Linear's
+ * activations in the Llama / Gemma blocks (vai/nodes/rms-norm.h:9-24, 100-170;
+ * vai/shaders/rms-norm.comp):
+ *   O[i,j] = I[i,j] * rsqrt(mean(I[i,:]^2) + eps) (* scale[j]) (+ shift[j]) (+ R[i,j])
+ * I, R in i_dtype, scale / shift [feat] in w_dtype (either may be NULL), O in o_dtype;
+ * the row statistic is accumulated in fp32.  A 16-bit o_dtype feeds the tensor-core
+ * Linear without its fp32 -> 16-bit staging pass.  Enqueues one kernel. */
+VAICU_API int vaicu_rms_norm_run(vaicu_device* dev, vaicu_stream_t stream, const void* in, const void* scale,
+                                 const void* shift, const void* residual, void* out, uint32_t rows, uint32_t feat,
+                                 int i_dtype, int w_dtype, int o_dtype, float eps);
+
 /* Row-wise argmax of logits [M, N] (fp32 / fp16 / bf16) into M raw uint32 indices:
  * vAi's Argmax node, the greedy-decode consumer of the lm_head Linear
  * (vai/nodes/argmax.h:9-18, 57-79; vai/shaders/argmax.comp).  Ties resolve to the

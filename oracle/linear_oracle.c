@@ -358,6 +358,44 @@ int vai_oracle_argmax(const void* in, int dtype, uint32_t M, uint32_t N, uint32_
     return 0;
 }
 
+/* RmsNorm (vai/shaders/rms-norm.comp:92-175): wg_size threads accumulate strided partial
+ * sums of squares in fp32, subgroupAdd over 32 lanes (pairwise here), the per-subgroup
+ * sums are added in order, invRms = inversesqrt(sum / F + eps), then
+ * O = I * invRms * scale + shift + R, evaluated left to right in fp32. */
+int vai_oracle_rms_norm(const void* in, const void* scale, const void* shift, const void* res, void* out,
+                        uint32_t rows, uint32_t feat, int i_dtype, int w_dtype, int o_dtype, float eps, uint32_t wg_size)
+{
+    if (wg_size == 0 || wg_size % 32u || wg_size > 1024u) return 1;
+    float* lane = (float*)malloc(sizeof(float) * wg_size);
+    if (!lane) return 2;
+    for (uint32_t row = 0; row < rows; ++row) {
+        const size_t base = (size_t)row * feat;
+        for (uint32_t t = 0; t < wg_size; ++t) lane[t] = 0.0f;
+        for (uint32_t j = 0; j < feat; ++j) {
+            const float x = load_elem(in, i_dtype, base + j);
+            lane[j % wg_size] += x * x;
+        }
+        float q = 0.0f;
+        for (uint32_t sg = 0; sg < wg_size / 32u; ++sg) {
+            float v[32];
+            for (int l = 0; l < 32; ++l) v[l] = lane[sg * 32u + l];
+            for (int off = 16; off > 0; off >>= 1)
+                for (int l = 0; l < off; ++l) v[l] += v[l + off];
+            q += v[0];
+        }
+        const float inv = 1.0f / sqrtf(q / (float)feat + eps);
+        for (uint32_t j = 0; j < feat; ++j) {
+            float v = load_elem(in, i_dtype, base + j) * inv;
+            v = v * (scale ? load_elem(scale, w_dtype, j) : 1.0f);
+            v = v + (shift ? load_elem(shift, w_dtype, j) : 0.0f);
+            v = v + (res ? load_elem(res, i_dtype, base + j) : 0.0f);
+            store_elem(out, o_dtype, base + j, v);
+        }
+    }
+    free(lane);
+    return 0;
+}
+
 int vai_oracle_num_threads(void)
 {
 #ifdef _OPENMP

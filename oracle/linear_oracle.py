@@ -171,3 +171,31 @@ def argmax_c(logits, dtype=F32):
     if rc != 0:
         raise RuntimeError(f"oracle returned {rc}")
     return out
+
+
+def rms_norm_f64(x, scale=None, shift=None, residual=None, eps=1e-5):
+    """float64 RMS norm, what torch.nn.functional.rms_norm computes in the reference's tests
+    (vAi python/tests/nodes/test_rms_norm.py)."""
+    x = np.asarray(x, dtype=np.float64)
+    out = x / np.sqrt((x * x).mean(axis=-1, keepdims=True) + eps)
+    if scale is not None:
+        out = out * np.asarray(scale, dtype=np.float64).reshape(-1)
+    if shift is not None:
+        out = out + np.asarray(shift, dtype=np.float64).reshape(-1)
+    if residual is not None:
+        out = out + np.asarray(residual, dtype=np.float64)
+    return out
+
+
+def rms_norm_c(x, scale=None, shift=None, residual=None, eps=1e-5, i_dtype=F32, w_dtype=F32, o_dtype=F32, wg_size=32):
+    """The C restatement of vAi's rms-norm shader; arrays in device representation."""
+    x = np.ascontiguousarray(x)
+    rows, feat = int(np.prod(x.shape[:-1])), x.shape[-1]
+    out = np.empty(x.shape, dtype=np.float32 if o_dtype == F32 else np.uint16)
+    keep = [None if a is None else np.ascontiguousarray(a) for a in (scale, shift, residual)]
+    rc = lib().vai_oracle_rms_norm(_ptr(x), _ptr(keep[0]), _ptr(keep[1]), _ptr(keep[2]), _ptr(out), ctypes.c_uint32(rows),
+                                   ctypes.c_uint32(feat), ctypes.c_int(i_dtype), ctypes.c_int(w_dtype), ctypes.c_int(o_dtype),
+                                   ctypes.c_float(eps), ctypes.c_uint32(wg_size))
+    if rc != 0:
+        raise RuntimeError(f"oracle returned {rc}")
+    return out

@@ -38,6 +38,7 @@ def _stub_pyvai():
     nodes = types.ModuleType("pyvai.nodes")
     nodes.LinearNode = lambda **kw: dict(kw)
     nodes.ArgmaxNode = lambda **kw: {"node": "argmax", **kw}
+    nodes.RmsNormNode = lambda **kw: {"node": "rms_norm", **kw}
     pyvai.nodes = nodes
     sys.modules["pyvai"] = pyvai
     sys.modules["pyvai.nodes"] = nodes
@@ -49,6 +50,7 @@ def main(ref_root):
     sys.path.insert(0, os.path.join(ref_root, "python", "tests", "nodes"))
     import node_check
     import test_argmax
+    import test_rms_norm
     import test_linear
 
     records = {}
@@ -119,6 +121,11 @@ def main(ref_root):
     # the lm_head's consumer: Argmax (python/tests/nodes/test_argmax.py), exact uint32 indices
     test_argmax.test_argmax()
     record("argmax")
+
+    # the producer of a Linear's activations: RmsNorm (python/tests/nodes/test_rms_norm.py)
+    for fn in ("test_rms_norm", "test_rms_norm_scale_shift_residual", "test_rms_norm_coeffs_as_inputs"):
+        getattr(test_rms_norm, fn)()
+        record(fn.replace("test_", ""))
 
     here = os.path.dirname(os.path.abspath(__file__))
     np.savez_compressed(os.path.join(here, "linear_golden.npz"), **arrays)

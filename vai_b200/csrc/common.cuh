@@ -136,6 +136,9 @@ cudaError_t launch_cast_f32_to_16(const float* src, void* dst, int dst_dtype, si
 
 cudaError_t launch_argmax(const void* in, int dtype, uint32_t M, uint32_t N, uint32_t* out, cudaStream_t stream);
 
+cudaError_t launch_rms_norm(const void* in, const void* scale, const void* shift, const void* res, void* out, uint32_t rows,
+                            uint32_t feat, int i_dtype, int w_dtype, int o_dtype, float eps, int sm_count, cudaStream_t stream);
+
 // Records "<where>: <what>" as the calling thread's last error text
 // (vaicu_last_cuda_error).
 void set_last_error(const char* where, const char* what);

@@ -203,3 +203,69 @@ class ArgmaxNode(Node):
 
         launch.kernel_launches = 1
         return launch
+
+
+class RmsNormNode(Node):
+    """RMS normalisation over the last axis (vAi vai/nodes/rms-norm.h:9-24):
+    out0 = in0 * rsqrt(mean(in0^2) + eps) (* scale) (+ shift) (+ residual).
+    `scale` / `shift` [D] apply when set (parameters, or inputs under coeffs_as_inputs);
+    accept_residual opens the `residual` input (same shape and dtype as in0).  With
+    set_o_dtype(F16 / BF16) the node hands 16-bit activations to the Linear after it."""
+
+    def __init__(self, eps=1e-5, coeffs_as_inputs=False, accept_residual=False):
+        super().__init__()
+        self.eps = float(eps)
+        self.coeffs_as_inputs = bool(coeffs_as_inputs)
+        self.accept_residual = bool(accept_residual)
+        self.add_slot("out0", OUTPUT)
+        self.add_slot("in0", INPUT)
+        kind = INPUT if self.coeffs_as_inputs else PERSISTENT
+        self.add_slot("scale", kind)
+        self.add_slot("shift", kind)
+        if self.accept_residual:
+            self.add_slot("residual", INPUT)
+
+    def has_scale(self):
+        return self["scale"].valid_shape()
+
+    def has_shift(self):
+        return self["shift"].valid_shape()
+
+    def prepare(self):
+        x = self["in0"]
+        if not x.valid_shape() or len(x.shape) < 2:
+            raise ValueError("in0 must have at least two axes")
+        feat = x.shape[-1]
+        w_dtype = Dtype.NONE
+        for name in ("scale", "shift"):
+            t = self[name]
+            if t.valid_shape():
+                if t.shape[-1] != feat or t.num_elements() != feat:
+                    raise ValueError(f"{name} must hold {feat} elements")
+                if w_dtype != Dtype.NONE and t.dtype != w_dtype:
+                    raise ValueError("scale and shift must share a dtype")
+                w_dtype = t.dtype
+        if self.accept_residual:
+            r = self["residual"]
+            if tuple(r.shape) != tuple(x.shape) or r.dtype != x.dtype:
+                raise ValueError("residual must match in0's shape and dtype")
+        self._w_dtype = w_dtype
+        o_dtype = self.o_dtype if self.o_dtype != Dtype.NONE else (self.net.o_default_dtype if self.net else Dtype.F32)
+        self.slots["out0"] = Tensor(x.shape, o_dtype)
+
+    def bind(self):
+        from .engine import Device
+        dev = self.net.device if self.net is not None else Device.default()
+        x, o = self["in0"], self["out0"]
+        rows = x.num_elements() // x.shape[-1]
+        args = (dev.handle, x.ptr, self["scale"].ptr if self.has_scale() else None,
+                self["shift"].ptr if self.has_shift() else None,
+                self["residual"].ptr if self.accept_residual else None, o.ptr, rows, x.shape[-1],
+                int(x.dtype), int(self._w_dtype), int(o.dtype), self.eps)
+        run = dev.lib.vaicu_rms_norm_run
+
+        def launch(stream):
+            _lib.check(run(args[0], stream, *args[1:]), "vaicu_rms_norm_run")
+
+        launch.kernel_launches = 1
+        return launch
