@@ -212,6 +212,24 @@ VAICU_API int vaicu_linear_run(vaicu_linear_plan* plan, vaicu_stream_t stream,
 VAICU_API int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_stream_t stream,
                                      const void* I, const void* const* W, void* const* O);
 
+/* Column-split Linear whose output slab is written straight into wider buffers: element
+ * (m, j) of the plan's output goes to dsts[i][m * ldo + col0 + j] for every i < n_dst
+ * (1..8).  With dsts = {this GPU's [M, N_full] output, its peers' outputs opened through
+ * vaicu_ipc_open} the epilogue of the tensor-core kernel performs the all-gather itself
+ * with plain stores over NVLink, tile by tile, instead of a collective after the kernel;
+ * the ranks still need one synchronisation before anyone reads the gathered output.
+ * Tensor-core plans without split-K and without residual only (VAICU_ERR_UNSUPPORTED
+ * otherwise); destinations 16-byte aligned.  No counterpart in the single-device reference. */
+VAICU_API int vaicu_linear_run_scatter(vaicu_linear_plan* plan, vaicu_stream_t stream, const void* I, const void* W,
+                                       const void* bias, void* const* dsts, int n_dst, uint32_t ldo, uint32_t col0,
+                                       void* workspace);
+/* Share a vaicu_buffer_alloc'ed range with the other processes of this host: export fills a
+ * 64-byte handle to send to them, open maps a peer's range into this process (peer access
+ * over NVLink), close unmaps it.  No counterpart in the reference. */
+VAICU_API int vaicu_ipc_export(const void* device_ptr, void* handle64);
+VAICU_API int vaicu_ipc_open(const void* handle64, void** out_ptr);
+VAICU_API int vaicu_ipc_close(void* ptr);
+
 /* Split-K Linear that allocates nothing (no counterpart in the reference, whose
  * engine always has a buffer pool to draw the "partial" slot from).
  *

@@ -1,0 +1,30 @@
+"""GPU, 2 ranks on 2 GPUs (skipped on a one-GPU box): the column-split Linear whose
+tensor-core epilogue stores its slab into every rank's output over NVLink
+(vaicu_linear_run_scatter + CUDA IPC) gives bit-identical results to the NCCL all-gather
+of the same plan's dense output.  Runs vai_b200.sharded under torch.distributed.run."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_fused_gather_matches_nccl_on_two_gpus():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29541", "-m", "vai_b200.sharded", "--M", "64"]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1]
+    res = json.loads(line)
+    for name, layer in res["layers"].items():
+        assert layer["fused_gather_matches_nccl"] is True, name
+        assert layer["fused_gather_us"] > 0

@@ -300,3 +300,56 @@ def test_grouped_siblings_match_separate_runs(M, w_dtype, device):
     rc = lib.vaicu_linear_run_group((ctypes.c_void_p * 2)(plans[0], h), 2, None, xb.ptr,
                                     (ctypes.c_void_p * 2)(wbufs[0].ptr, wbufs[2].ptr), (ctypes.c_void_p * 2)(obufs[0].ptr, obufs[2].ptr))
     assert rc == 2
+
+
+@pytest.mark.parametrize("M,K,N,gate", [(64, 512, 384, False), (33, 256, 200, False), (300, 512, 520, False), (64, 512, 256, True)])
+def test_scatter_run_writes_slabs_into_wider_outputs(M, K, N, gate, device):
+    """vaicu_linear_run_scatter on one GPU: the plan's output lands as a column slab at col0
+    inside two wider buffers (what a column-split rank does to its own and its peers'
+    outputs), bit-identical to the dense run, and nothing outside the slab is touched."""
+    import ctypes
+
+    from vai_b200 import _lib
+    from vai_b200.engine import DeviceBuffer, encode
+    from vai_b200 import Dtype
+    lib = device.lib
+    rng = np.random.default_rng(M + N)
+    rows = 2 * N if gate else N
+    x = encode(rng.standard_normal((M, K)).astype(np.float32), Dtype.BF16)
+    w = encode((rng.standard_normal((rows, K)) / np.sqrt(K)).astype(np.float32), Dtype.BF16)
+    xb, wb = DeviceBuffer(device, x.nbytes), DeviceBuffer(device, w.nbytes)
+    xb.upload(x)
+    wb.upload(w)
+    d = _lib.LinearDesc()
+    d.M, d.N, d.K = M, rows, K
+    d.i_dtype = d.w_dtype = d.o_dtype = int(Dtype.BF16)
+    d.b_dtype = 2
+    d.scalar_scale = 1.0
+    d.gate_fuse = 1 if gate else 0
+    d.epilogue = 4 if gate else 0
+    d.split_size = 0
+    plan = ctypes.c_void_p()
+    _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(plan)), "plan")
+    info = _lib.LinearInfo()
+    lib.vaicu_linear_plan_info(plan, ctypes.byref(info))
+    ws = DeviceBuffer(device, max(info.workspace_bytes, 256))
+    dense = DeviceBuffer(device, M * N * 2)
+    _lib.check(lib.vaicu_linear_run(plan, None, xb.ptr, wb.ptr, None, None, dense.ptr, ws.ptr), "run")
+    ldo, col0 = N + 3 * 16 + 8, 24              # col0 keeps 16-byte alignment of the rows only when ldo does too
+    wide = [DeviceBuffer(device, M * ldo * 2) for _ in range(2)]
+    canary = np.full((M, ldo), 0x7FC1, dtype=np.uint16)
+    for b in wide:
+        b.upload(canary)
+    ptrs = (ctypes.c_void_p * 2)(wide[0].ptr, wide[1].ptr)
+    rc = lib.vaicu_linear_run_scatter(plan, None, xb.ptr, wb.ptr, None, ptrs, 2, ldo, col0, ws.ptr)
+    if info.split_count > 1:
+        assert rc == 2          # plans with a split-K fold do not scatter
+        return
+    _lib.check(rc, "scatter")
+    device.synchronize()
+    want = dense.download(np.empty((M, N), dtype=np.uint16))
+    for b in wide:
+        got = b.download(np.empty((M, ldo), dtype=np.uint16))
+        np.testing.assert_array_equal(got[:, col0:col0 + N], want)
+        np.testing.assert_array_equal(got[:, :col0], canary[:, :col0])
+        np.testing.assert_array_equal(got[:, col0 + N:], canary[:, col0 + N:])

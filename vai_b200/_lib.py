@@ -65,6 +65,11 @@ SIGNATURES = {
     "vaicu_linear_run": (ctypes.c_int, [ctypes.c_void_p] * 8),
     "vaicu_linear_run_group": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
                                               ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p)]),
+    "vaicu_linear_run_scatter": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+                                                                        ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]),
+    "vaicu_ipc_export": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+    "vaicu_ipc_open": (ctypes.c_int, [ctypes.c_void_p, c_void_pp]),
+    "vaicu_ipc_close": (ctypes.c_int, [ctypes.c_void_p]),
     "vaicu_linear_splitk_static": (ctypes.c_int, [ctypes.POINTER(LinearDesc)] + [ctypes.c_void_p] * 6),
     "vaicu_rms_norm_run": (ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, ctypes.c_int,
                                                                    ctypes.c_int, ctypes.c_float]),

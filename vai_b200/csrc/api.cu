@@ -659,8 +659,47 @@ int vaicu_linear_workspace_bytes(const vaicu_linear_plan* plan, size_t* out)
     return VAICU_OK;
 }
 
+namespace {
+// Where the output goes: one dense buffer (n_dst == 1, ldo = width of O, col0 = 0), or the
+// same column slab inside several wider buffers.
+struct OutputSpec {
+    uint32_t n_dst, ldo, col0;
+    void* dst[8];
+};
+int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W, const void* bias,
+             const void* residual, void* O, void* workspace, const OutputSpec* spec);
+}  // namespace
+
 int vaicu_linear_run(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W, const void* bias,
                      const void* residual, void* O, void* workspace)
+{
+    return run_impl(pl, stream, I, W, bias, residual, O, workspace, nullptr);
+}
+
+int vaicu_linear_run_scatter(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W, const void* bias,
+                             void* const* dsts, int n_dst, uint32_t ldo, uint32_t col0, void* workspace)
+{
+    if (!pl || !dsts || n_dst < 1 || n_dst > 8) return VAICU_ERR_INVALID_VALUE;
+    const vaicu_linear_desc& d = pl->d;
+    const uint32_t width = d.gate_fuse ? d.N / 2u : d.N;
+    if (ldo < width || col0 > ldo - width) return VAICU_ERR_INVALID_VALUE;
+    // only the tensor-core kernels write strided slabs, and only without a split-K fold or a residual
+    if (!pl->tc || pl->tcp.splits > 1u || d.has_residual) return VAICU_ERR_UNSUPPORTED;
+    OutputSpec spec{};
+    spec.n_dst = (uint32_t)n_dst;
+    spec.ldo = ldo;
+    spec.col0 = col0;
+    for (int i = 0; i < n_dst; ++i) {
+        if (!dsts[i]) return VAICU_ERR_INVALID_VALUE;
+        if (reinterpret_cast<uintptr_t>(dsts[i]) & 15u) return VAICU_ERR_ALIGNMENT;
+        spec.dst[i] = dsts[i];
+    }
+    return run_impl(pl, stream, I, W, bias, nullptr, dsts[0], workspace, &spec);
+}
+
+namespace {
+int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W, const void* bias,
+             const void* residual, void* O, void* workspace, const OutputSpec* spec)
 {
     if (!pl || !I || !W || !O) return VAICU_ERR_INVALID_VALUE;
     const vaicu_linear_desc& d = pl->d;
@@ -683,7 +722,10 @@ int vaicu_linear_run(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I
     if (pl->kernel == VAICU_KERNEL_FMA_TILE) return run_fma(pl, a, workspace, s);
 
     // tensor-core path; operands TMA cannot address go to the FMA tile kernel
-    if (!aligned16(W) || (!pl->tc_cast && !aligned16(I))) return run_fma(pl, a, workspace, s);
+    if (!aligned16(W) || (!pl->tc_cast && !aligned16(I))) {
+        if (spec) return VAICU_ERR_ALIGNMENT;      // the fallback kernel writes dense outputs only
+        return run_fma(pl, a, workspace, s);
+    }
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
     const void* act = I;
     if (pl->tc_cast) {
@@ -710,8 +752,40 @@ int vaicu_linear_run(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I
     TcParams t = pl->tcp;
     t.O = O; t.bias = a.bias; t.res = a.res; t.partial = partial;
     t.o_aligned16 = aligned16(O) ? 1u : 0u;
+    t.n_dst = 1u;
+    t.ldo = gate ? d.N / 2u : d.N;
+    t.col0 = 0u;
+    if (spec) {
+        t.n_dst = spec->n_dst; t.ldo = spec->ldo; t.col0 = spec->col0;
+        for (uint32_t i = 0; i < spec->n_dst; ++i) t.dst[i] = spec->dst[i];
+    }
     VAICU_CUDA(launch_tc_gemm(pl->map_a, pl->map_b, t, pl->tc_swap, pl->tc_grid, pl->tc_smem, s));
     if (partial) VAICU_CUDA(launch_splitk_reduce(a, partial, t.splits, s));
+    return VAICU_OK;
+}
+}  // namespace
+
+int vaicu_ipc_export(const void* device_ptr, void* handle64)
+{
+    if (!device_ptr || !handle64) return VAICU_ERR_INVALID_VALUE;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    VAICU_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(device_ptr)));
+    memcpy(handle64, &h, sizeof(h));
+    return VAICU_OK;
+}
+int vaicu_ipc_open(const void* handle64, void** out_ptr)
+{
+    if (!handle64 || !out_ptr) return VAICU_ERR_INVALID_VALUE;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    VAICU_CUDA(cudaIpcOpenMemHandle(out_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return VAICU_OK;
+}
+int vaicu_ipc_close(void* ptr)
+{
+    if (!ptr) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaIpcCloseMemHandle(ptr));
     return VAICU_OK;
 }
 

@@ -542,11 +542,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
                         const uint32_t n_valid = out_cols - j0 < 16u ? out_cols - j0 : 16u;
                         finish_row16<GATE>(p, v, u, m, j0, out_cols, n_valid);
-                        const size_t flat0 = (size_t)m * out_cols + j0;
+                        // O may be a column slab of wider destinations (ldo, col0), one per GPU
+                        const size_t flat0 = (size_t)m * p.ldo + p.col0 + j0;
                         const bool vec_ok = n_valid == 16u && (((size_t)flat0 * osz) % 16u == 0u) && p.o_aligned16;
-                        if (vec_ok) store16(p.O, p.o_dtype, flat0, v, true);
-                        else
-                            for (uint32_t c = 0; c < n_valid; ++c) store_from_f32(p.O, p.o_dtype, flat0 + c, v[c]);
+                        for (uint32_t d = 0; d < p.n_dst; ++d) {
+                            void* dst = p.n_dst == 1u ? p.O : p.dst[d];
+                            if (vec_ok) store16(dst, p.o_dtype, flat0, v, true);
+                            else
+                                for (uint32_t c = 0; c < n_valid; ++c) store_from_f32(dst, p.o_dtype, flat0 + c, v[c]);
+                        }
                     }
                 } else {
                     const uint32_t n = row_base + row_in_tile;
@@ -556,21 +560,24 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
                         const uint32_t m0 = tb * bn + c0;
                         finish_col16<GATE>(p, v, u, n, m0, out_cols, bias_n, bias_up);
-                        if (p.o_dtype == VAICU_DTYPE_F32) {
-                            float* O = reinterpret_cast<float*>(p.O);
+                        for (uint32_t d = 0; d < p.n_dst; ++d) {
+                            void* dst = p.n_dst == 1u ? p.O : p.dst[d];
+                            if (p.o_dtype == VAICU_DTYPE_F32) {
+                                float* O = reinterpret_cast<float*>(dst);
 #pragma unroll
-                            for (uint32_t c = 0; c < 16u; ++c)
-                                if (m0 + c < p.M) O[(size_t)(m0 + c) * out_cols + n] = v[c];
-                        } else if (p.o_dtype == VAICU_DTYPE_F16) {
-                            __half* O = reinterpret_cast<__half*>(p.O);
+                                for (uint32_t c = 0; c < 16u; ++c)
+                                    if (m0 + c < p.M) O[(size_t)(m0 + c) * p.ldo + p.col0 + n] = v[c];
+                            } else if (p.o_dtype == VAICU_DTYPE_F16) {
+                                __half* O = reinterpret_cast<__half*>(dst);
 #pragma unroll
-                            for (uint32_t c = 0; c < 16u; ++c)
-                                if (m0 + c < p.M) O[(size_t)(m0 + c) * out_cols + n] = __float2half_rn(v[c]);
-                        } else {
-                            __nv_bfloat16* O = reinterpret_cast<__nv_bfloat16*>(p.O);
+                                for (uint32_t c = 0; c < 16u; ++c)
+                                    if (m0 + c < p.M) O[(size_t)(m0 + c) * p.ldo + p.col0 + n] = __float2half_rn(v[c]);
+                            } else {
+                                __nv_bfloat16* O = reinterpret_cast<__nv_bfloat16*>(dst);
 #pragma unroll
-                            for (uint32_t c = 0; c < 16u; ++c)
-                                if (m0 + c < p.M) O[(size_t)(m0 + c) * out_cols + n] = __float2bfloat16_rn(v[c]);
+                                for (uint32_t c = 0; c < 16u; ++c)
+                                    if (m0 + c < p.M) O[(size_t)(m0 + c) * p.ldo + p.col0 + n] = __float2bfloat16_rn(v[c]);
+                            }
                         }
                     }
                 }

@@ -32,6 +32,11 @@ struct TcParams {
     int32_t bias_mode, res_mode;
     uint32_t bias_elems, res_elems;
     uint32_t o_aligned16;
+    // Output addressing: element (m, j) goes to dst[m * ldo + col0 + j].  A plain run has
+    // n_dst = 1, ldo = the output width, col0 = 0; a column-split run writes its slab into
+    // up to 8 wider destinations at once (its own and its peers' over NVLink).
+    uint32_t ldo, col0, n_dst;
+    void* dst[8];
     float scale;
 };
 

@@ -130,6 +130,80 @@ class ShardedLinear:
         return assemble(self.gathered, self.n_out) if assemble_output else self.gathered
 
 
+class _CudaView:
+    """A [rows, cols] view of a device range for torch.as_tensor (CUDA array interface)."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 3}
+
+
+class FusedGatherLinear(ShardedLinear):
+    """Column-split Linear whose tensor-core epilogue writes this rank's slab straight into
+    every rank's [M, n_out] output (vaicu_linear_run_scatter): the all-gather happens
+    tile by tile as plain stores over NVLink, and the only collective left is a tiny
+    stream-ordered all-reduce that tells every rank that all slabs have landed.
+
+    The outputs are cudaMalloc'ed ranges shared through CUDA IPC handles; no TMA descriptor
+    and no multicast load touches peer memory — peers are only ever stored to."""
+
+    def __init__(self, device, dist, full_desc, w_local, bias_local=None):
+        import torch
+        self.torch, self.dist, self.dev = torch, dist, device
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.full = full_desc
+        self.gate = bool(full_desc.gate_fuse)
+        self.n_out = full_desc.N // 2 if self.gate else full_desc.N
+        self.desc, self.begin, self.count = shard_desc(full_desc, self.rank, self.world)
+        self.desc.split_size = max(32, full_desc.K)     # one K span: a split-K fold cannot scatter
+        self.w, self.b = w_local, bias_local
+        lib = device.lib
+        h = ctypes.c_void_p()
+        _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(self.desc), ctypes.byref(h)), "plan")
+        self.plan = h
+        self.info = _lib.LinearInfo()
+        _lib.check(lib.vaicu_linear_plan_info(h, ctypes.byref(self.info)), "info")
+        cuda = torch.device("cuda", device.ordinal)
+        self.ws = torch.empty(max(self.info.workspace_bytes, 256), dtype=torch.uint8, device=cuda)
+        from .engine import DeviceBuffer
+        esz = 4 if self.desc.o_dtype == 0 else 2
+        self.out = DeviceBuffer(device, self.desc.M * self.n_out * esz)      # the gathered [M, n_out] of this rank
+        handle = (ctypes.c_uint8 * 64)()
+        _lib.check(lib.vaicu_ipc_export(self.out.ptr, handle), "vaicu_ipc_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle))
+        self._opened = []
+        ptrs = []
+        for r, raw in enumerate(handles):
+            if r == self.rank:
+                ptrs.append(self.out.ptr)
+                continue
+            p = ctypes.c_void_p()
+            _lib.check(lib.vaicu_ipc_open((ctypes.c_uint8 * 64).from_buffer_copy(raw), ctypes.byref(p)), "vaicu_ipc_open")
+            self._opened.append(p)
+            ptrs.append(p.value)
+        self.ptrs = (ctypes.c_void_p * self.world)(*ptrs)
+        self.flag = torch.zeros(1, dtype=torch.float32, device=cuda)
+        typestr = {0: "<f4", 1: "<f2", 3: "<u2"}[self.desc.o_dtype]
+        view = torch.as_tensor(_CudaView(self.out.ptr, (self.desc.M, self.n_out), typestr), device=cuda)
+        self.result = view.view(torch.bfloat16) if self.desc.o_dtype == 3 else view
+
+    def forward(self, x):
+        stream = self.torch.cuda.current_stream().cuda_stream
+        _lib.check(self.dev.lib.vaicu_linear_run_scatter(self.plan, stream, x.data_ptr(), self.w.data_ptr(),
+                                                         self.b.data_ptr() if self.b is not None else None,
+                                                         self.ptrs, self.world, self.n_out, self.begin,
+                                                         self.ws.data_ptr()), "vaicu_linear_run_scatter")
+        # every rank's kernel precedes its contribution on the stream: when the reduction
+        # returns, all slabs are in this rank's output
+        self.dist.all_reduce(self.flag)
+        return self.result
+
+    def close(self):
+        for p in self._opened:
+            self.dev.lib.vaicu_ipc_close(p)
+        self._opened = []
+
+
 def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5):
     """Column-split lm_head and gate|value Linear of `preset` at batch M on this rank's
     GPU, with the NCCL all-gather of the output slabs; device-timed, max over ranks.
@@ -197,12 +271,34 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5):
 
         local_ms = timed(lambda: lin.local_forward(x))
         total_ms = timed(lambda: lin.forward(x, assemble_output=True))
+        fused_ms, fused_equal = None, None
+        if dist is not None and world > 1:
+            fused = FusedGatherLinear(device, dist, full, lin.w, None)
+            got = fused.forward(x)
+            # the same plan run densely on this rank, gathered by NCCL: must be bit-identical
+            stream = torch.cuda.current_stream().cuda_stream
+            _lib.check(device.lib.vaicu_linear_run(fused.plan, stream, x.data_ptr(), lin.w.data_ptr(), None, None,
+                                                   lin.slab.data_ptr(), fused.ws.data_ptr()), "vaicu_linear_run")
+            if lin.slab is not lin.local:
+                lin.local[:, :lin.count].copy_(lin.slab)
+            dist.all_gather_into_tensor(lin.gathered, lin.local)
+            ref = assemble(lin.gathered, n_out)
+            torch.cuda.synchronize()
+            dist.barrier()
+            fused_equal = bool(torch.equal(got.view(torch.int16), ref.view(torch.int16)))
+            fused_ms = timed(lambda: fused.forward(x))
+            torch.cuda.synchronize()
+            dist.barrier()
+            fused.close()
         w_bytes_all = n_rows * p["d"] * 2
         out["layers"][name] = {"rows": n_rows, "rows_per_gpu": rows_local, "kernel": int(lin.info.kernel),
                                "local_us": local_ms * 1e3, "with_allgather_us": total_ms * 1e3,
                                "aggregate_GBps_local": w_bytes_all / (local_ms * 1e-3) / 1e9,
                                "aggregate_GBps_with_allgather": w_bytes_all / (total_ms * 1e-3) / 1e9,
-                               "allgather_bytes_per_gpu": M * cmax * 2}
+                               "allgather_bytes_per_gpu": M * cmax * 2,
+                               "fused_gather_us": None if fused_ms is None else fused_ms * 1e3,
+                               "fused_gather_matches_nccl": fused_equal,
+                               "aggregate_GBps_fused_gather": None if fused_ms is None else w_bytes_all / (fused_ms * 1e-3) / 1e9}
         device.lib.vaicu_linear_plan_destroy(h)
     return out
 
