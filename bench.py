@@ -50,55 +50,68 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons while the timed region runs: NVML polled from a thread
+    every few milliseconds (read-only queries), nvidia-smi as the fallback."""
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, index):
         self.index = index
-        self.proc = None
-        self.lines = []
+        self.sm, self.bits = [], 0
+        self.max_mhz = None
+        self.stop_flag = False
+        self.thread = None
+        self.how = None
+
+    def _poll_nvml(self):
+        import pynvml
+        h = self.handle
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+            except Exception:
+                pass
+            time.sleep(0.004)
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+            pynvml.nvmlInit()
+            try:     # the CUDA ordinal is not NVML's index when CUDA_VISIBLE_DEVICES reorders
+                import torch
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(self.index).uuid)
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.how = "nvml"
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
             self.thread.start()
         except Exception:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.how = None
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 7:
-                continue
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=1.0)
+        if not self.sm:      # NVML unavailable: one nvidia-smi reading right after the region
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                out = subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+                                      "clocks_event_reasons.sw_power_cap,clocks_event_reasons.sw_thermal_slowdown,"
+                                      "clocks_event_reasons.hw_thermal_slowdown", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=10).stdout
+                parts = [q.strip() for q in out.strip().split(",")]
+                self.sm = [float(parts[0])]
+                self.max_mhz = float(parts[1])
+                for name, v in zip(["hw_slowdown", "sw_power_cap", "sw_thermal_slowdown", "hw_thermal_slowdown"], parts[2:6]):
+                    if v.lower().startswith("active"):
+                        self.bits |= self.REASONS[name]
+                self.how = "nvidia-smi after the region"
+            except Exception:
+                return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["clock query unavailable"]}
+        reasons = sorted(n for n, bit in self.REASONS.items() if self.bits & bit)
+        return {"sm_mhz": statistics.median(self.sm), "sm_max_mhz": self.max_mhz, "samples": len(self.sm),
+                "reasons": reasons, "source": self.how}
 
 
 def dist_setup(n_gpus):
@@ -212,7 +225,7 @@ def run_reference(args, rank):
 def workload_config():
     from vai_b200 import presets
     return {"workload": "Llama-3.2-1B-shaped decode step, batch 1 (M=1): 16 blocks x {q,k,v,o,gate|value,down} + lm_head "
-                        "128256; bf16 weights N(0,0.02), fp32 activations; 97 Linear launches per step",
+                        "128256; bf16 weights N(0,0.02), fp32 activations; 97 Linear nodes, 65 kernel launches per step",
             "weight_bytes_per_step": presets.weight_elements(PRESET) * 2,
             "l2": "weights per step (2.47 GB) exceed L2 (126 MB); no flush needed",
             "parallelism": "one token stream per GPU"}
@@ -221,7 +234,7 @@ def workload_config():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
