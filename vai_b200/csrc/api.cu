@@ -255,19 +255,26 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
         bool wide = bn == 256u && d.M >= 512u &&
                     ceil_div(d.M, 256u) * ceil_div(H, gate ? bn / 2u : bn) * 100u >= 85u * sms;
         if (const char* e = getenv("VAICU_TC_WIDE")) wide = atoi(e) != 0 && bn * 2u <= 512u;
+        // CTA pairs (cta_group::2): two neighbouring SMs share one 256-row tile and each
+        // stages half of the weights' tile; both accumulator buffers stay in use.
+        bool pair = d.M > 128u;
+        if (const char* e = getenv("VAICU_TC_PAIR")) pair = atoi(e) != 0;
+        if (pair) wide = false;
+        t.pair = pair ? 1u : 0u;
         t.wide = wide ? 1u : 0u;
-        t.tiles_a = ceil_div(d.M, wide ? 256u : 128u);
+        t.tiles_a = ceil_div(d.M, (wide || pair) ? 256u : 128u);
         t.tiles_b = ceil_div(H, gate ? bn / 2u : bn);
     }
     t.bn = bn;
     t.num_tiles = t.tiles_a * t.tiles_b;
     t.group = t.tiles_a < 16u ? t.tiles_a : 16u;
     // split-K
+    const uint32_t units = t.pair ? sms / 2u : sms;      // tiles that run at the same time
     uint32_t kb_per_split = t.kblocks;
     if (d.split_size) {
         kb_per_split = ceil_div(d.split_size, 64u);
-    } else if (t.num_tiles * 2u <= sms && t.kblocks >= 8u) {
-        uint32_t want = sms / t.num_tiles;
+    } else if (t.num_tiles * 2u <= units && t.kblocks >= 8u) {
+        uint32_t want = units / t.num_tiles;
         const uint32_t max_splits = t.kblocks / 4u;      // at least 4 k-blocks (256 of K) per split
         if (want > max_splits) want = max_splits;
         if (want > 32u) want = 32u;
@@ -283,10 +290,10 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
     t.splits = ceil_div(t.kblocks, kb_per_split);
     // descriptor: fp32 accumulate, A/B formats, both K-major, N >> 3, M >> 4
     const uint32_t fmt = d.w_dtype == VAICU_DTYPE_BF16 ? 1u : 0u;
-    t.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((bn >> 3) << 17) | ((128u >> 4) << 24);
+    t.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((bn >> 3) << 17) | (((t.pair ? 256u : 128u) >> 4) << 24);
     const uint32_t a_boxes = ((gate && swap) || t.wide) ? 2u : 1u;
     const uint32_t a_bytes = a_boxes * 128u * 128u;
-    const uint32_t stage_bytes = a_bytes + bn * 128u;
+    const uint32_t stage_bytes = a_bytes + (t.pair ? bn / 2u : bn) * 128u;      // per CTA
     uint32_t stages = (uint32_t)((kTcMaxSmem - 2048u) / stage_bytes);
     if (stages > 8u) stages = 8u;
     t.stages = stages;
@@ -305,6 +312,15 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
     t.status = pl->dev->status_word;
     const uint32_t work = t.num_tiles * t.splits;
     pl->tc_grid = (int)(work < sms ? work : sms);
+    if (t.pair) {
+        int clusters = 0;
+        if (tc_pair_max_clusters(pl->tc_smem, &clusters) != cudaSuccess || clusters <= 0) {
+            cudaGetLastError();
+            clusters = (int)(sms / 2u);
+        }
+        if ((uint32_t)clusters > work) clusters = (int)work;
+        pl->tc_grid = 2 * clusters;
+    }
     pl->tc_swap = swap;
     pl->tc_cast = d.i_dtype == VAICU_DTYPE_F32;
     pl->ws_cast_bytes = pl->tc_cast ? align_up((size_t)d.M * d.K * 2u, 256u) : 0;
@@ -647,7 +663,7 @@ int vaicu_linear_plan_info(const vaicu_linear_plan* plan, vaicu_linear_info* out
     } else if (plan->tc) {
         out->split_count = plan->tcp.splits;
         const uint32_t outc = (plan->tcp.gate && !plan->tc_swap) ? plan->tcp.bn / 2u : plan->tcp.bn;
-        out->tile_m = plan->tc_swap ? outc : (plan->tcp.wide ? 256u : 128u);
+        out->tile_m = plan->tc_swap ? outc : ((plan->tcp.wide || plan->tcp.pair) ? 256u : 128u);
         out->tile_n = plan->tc_swap ? 128u : outc;
     }
     return VAICU_OK;
@@ -744,7 +760,7 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
     }
     if (b_base != pl->map_b_base) {
         const uint32_t rows = pl->tc_swap ? d.M : d.N;
-        const uint32_t box = (gate && !pl->tc_swap) ? pl->tcp.bn / 2u : pl->tcp.bn;
+        const uint32_t box = ((gate && !pl->tc_swap) || pl->tcp.pair) ? pl->tcp.bn / 2u : pl->tcp.bn;
         int rc = encode_map(&pl->map_b, b_base, d.w_dtype, rows, d.K, box);
         if (rc != VAICU_OK) return rc;
         pl->map_b_base = b_base;

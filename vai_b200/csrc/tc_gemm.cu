@@ -342,6 +342,54 @@ __device__ __forceinline__ void finish_col16(const TcParams& p, float* v, float*
     }
 }
 
+// Unswapped epilogue for 16 accumulator columns starting at c0 of one 128-row block:
+// this thread owns activation row m.  r0 / r1 hold the raw accumulators (r1: the value
+// half with GATE).  Either raw split-K partials or the finished outputs are stored.
+template <bool GATE>
+__device__ __forceinline__ void store_rows16(const TcParams& p, const uint32_t* r0, const uint32_t* r1, uint32_t m,
+                                             uint32_t tb, uint32_t c0, uint32_t z, uint32_t out_cols, uint32_t osz)
+{
+    const uint32_t bn = p.bn;
+    if (p.partial) {
+        // split-K: raw fp32 partial sums, [z][M][N]; epilogue runs in the reduce pass
+        float* P = p.partial + (size_t)z * p.M * p.N;
+        if (m < p.M) {
+#pragma unroll
+            for (uint32_t c = 0; c < 16u; ++c) {
+                const uint32_t col = c0 + c;
+                if (GATE) {
+                    const uint32_t j = tb * (bn / 2u) + col;
+                    if (j < p.H) {
+                        P[(size_t)m * p.N + j] = __uint_as_float(r0[c]);
+                        P[(size_t)m * p.N + p.H + j] = __uint_as_float(r1[c]);
+                    }
+                } else {
+                    const uint32_t n = tb * bn + col;
+                    if (n < p.N) P[(size_t)m * p.N + n] = __uint_as_float(r0[c]);
+                }
+            }
+        }
+        return;
+    }
+    const uint32_t j0 = (GATE ? tb * (bn / 2u) : tb * bn) + c0;
+    if (m < p.M && j0 < out_cols) {
+        float v[16], u[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
+        const uint32_t n_valid = out_cols - j0 < 16u ? out_cols - j0 : 16u;
+        finish_row16<GATE>(p, v, u, m, j0, out_cols, n_valid);
+        // O may be a column slab of wider destinations (ldo, col0), one per GPU
+        const size_t flat0 = (size_t)m * p.ldo + p.col0 + j0;
+        const bool vec_ok = n_valid == 16u && (((size_t)flat0 * osz) % 16u == 0u) && p.o_aligned16;
+        for (uint32_t d = 0; d < p.n_dst; ++d) {
+            void* dst = p.n_dst == 1u ? p.O : p.dst[d];
+            if (vec_ok) store16(dst, p.o_dtype, flat0, v, true);
+            else
+                for (uint32_t c = 0; c < n_valid; ++c) store_from_f32(dst, p.o_dtype, flat0 + c, v[c]);
+        }
+    }
+}
+
 }  // namespace
 
 // SWAP: A (TMEM lanes) = weights, B (TMEM columns) = activations.
@@ -500,56 +548,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 tmem_ld16(t_row + c0, r0);
                 if (GATE) tmem_ld16(t_row + c0 + (SWAP ? bn : bn / 2u), r1);
                 tmem_ld_wait();
-                if (p.partial) {
-                    // split-K: raw fp32 partial sums, [z][M][N]; epilogue runs in the reduce pass
+                if (!SWAP) {
+                    store_rows16<GATE>(p, r0, r1, row_base + row_in_tile, tb, c0, z, out_cols, osz);
+                } else if (p.partial) {
                     float* P = p.partial + (size_t)z * p.M * p.N;
-                    if (!SWAP) {
-                        const uint32_t m = row_base + row_in_tile;
-                        if (m < p.M) {
+                    const uint32_t n = row_base + row_in_tile;
+                    const bool row_ok = GATE ? (n < p.H) : (n < p.N);
 #pragma unroll
-                            for (uint32_t c = 0; c < 16u; ++c) {
-                                const uint32_t col = c0 + c;
-                                if (GATE) {
-                                    const uint32_t j = tb * (bn / 2u) + col;
-                                    if (j < p.H) {
-                                        P[(size_t)m * p.N + j] = __uint_as_float(r0[c]);
-                                        P[(size_t)m * p.N + p.H + j] = __uint_as_float(r1[c]);
-                                    }
-                                } else {
-                                    const uint32_t n = tb * bn + col;
-                                    if (n < p.N) P[(size_t)m * p.N + n] = __uint_as_float(r0[c]);
-                                }
-                            }
-                        }
-                    } else {
-                        const uint32_t n = row_base + row_in_tile;
-                        const bool row_ok = GATE ? (n < p.H) : (n < p.N);
-#pragma unroll
-                        for (uint32_t c = 0; c < 16u; ++c) {
-                            const uint32_t m = tb * bn + c0 + c;
-                            if (row_ok && m < p.M) {
-                                P[(size_t)m * p.N + n] = __uint_as_float(r0[c]);
-                                if (GATE) P[(size_t)m * p.N + p.H + n] = __uint_as_float(r1[c]);
-                            }
-                        }
-                    }
-                } else if (!SWAP) {
-                    const uint32_t m = row_base + row_in_tile;
-                    const uint32_t j0 = (GATE ? tb * (bn / 2u) : tb * bn) + c0;
-                    if (m < p.M && j0 < out_cols) {
-                        float v[16], u[16];
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
-                        const uint32_t n_valid = out_cols - j0 < 16u ? out_cols - j0 : 16u;
-                        finish_row16<GATE>(p, v, u, m, j0, out_cols, n_valid);
-                        // O may be a column slab of wider destinations (ldo, col0), one per GPU
-                        const size_t flat0 = (size_t)m * p.ldo + p.col0 + j0;
-                        const bool vec_ok = n_valid == 16u && (((size_t)flat0 * osz) % 16u == 0u) && p.o_aligned16;
-                        for (uint32_t d = 0; d < p.n_dst; ++d) {
-                            void* dst = p.n_dst == 1u ? p.O : p.dst[d];
-                            if (vec_ok) store16(dst, p.o_dtype, flat0, v, true);
-                            else
-                                for (uint32_t c = 0; c < n_valid; ++c) store_from_f32(dst, p.o_dtype, flat0 + c, v[c]);
+                    for (uint32_t c = 0; c < 16u; ++c) {
+                        const uint32_t m = tb * bn + c0 + c;
+                        if (row_ok && m < p.M) {
+                            P[(size_t)m * p.N + n] = __uint_as_float(r0[c]);
+                            if (GATE) P[(size_t)m * p.N + p.H + n] = __uint_as_float(r1[c]);
                         }
                     }
                 } else {
@@ -605,6 +615,261 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
 }
 
+
+// ---- CTA-pair variant ------------------------------------------------------
+// PTX wrappers for the forms that address the peer CTA of a 2-CTA cluster.
+namespace {
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of this CTA's shared-memory location `local` inside CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion bytes are counted on an mbarrier of either CTA of the pair
+// (no multicast: every CTA fetches its own boxes).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int32_t x, int32_t y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// One MMA over both CTAs: D[256 x bn] (rows 0-127 in the leader's tensor memory, 128-255
+// in the peer's) += A[256 x 16] . B[bn x 16]^T with each CTA holding its 128 rows of A
+// and its half of B's rows at the same shared-memory offsets.
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the mbarrier at this offset in both CTAs once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+}  // namespace
+
+// Two CTAs on neighbouring SMs (a cluster of 2) compute one 256 x bn tile with
+// tcgen05.mma.cta_group::2: each CTA stages its 128 rows of A and HALF of the weights'
+// tile, so shared-memory traffic per MMA cycle halves against the single-CTA kernel
+// and both accumulator buffers (2 x 256 columns) stay available for overlap.
+//   warp 0  (both CTAs) TMA producer for this CTA's boxes; completion bytes of both CTAs
+//           are counted on the leader's "full" barrier;
+//   warp 1  allocates tensor memory in both CTAs; in the leader (cluster rank 0) one
+//           lane issues the MMAs and commits to the barriers of both CTAs;
+//   warps 2-5 (both CTAs) epilogue over this CTA's 128 rows; they release an accumulator
+//           by arriving on the leader's barrier.
+// With GATE the leader's half of B holds the gate rows and the peer's the value rows.
+template <bool GATE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
+tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    const uint32_t bn = p.bn, half = bn / 2u;
+    const uint32_t a_bytes = TILE_ROWS * BLOCK_K * 2u;
+    const uint32_t b_bytes = half * BLOCK_K * 2u;
+    const uint32_t stage_bytes = a_bytes + b_bytes;      // per CTA; multiple of 1024 (bn % 16 == 0)
+    const uint32_t stages = p.stages;
+    const uint32_t acc_cols = bn;
+
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + stages;
+    uint64_t* acc_full = empty_bar + stages;      // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2], used in the leader
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (uint32_t b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }   // 4 warps x 2 CTAs
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, p.tmem_cols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the peer's barriers are initialised before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t num_work = p.num_tiles * p.splits;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t w = cluster_id; w < num_work && ok; w += num_clusters) {
+                const uint32_t tile = w / p.splits, z = w - tile * p.splits;
+                uint32_t ta, tb;
+                tile_coords(p, tile, ta, tb);
+                const uint32_t kb0 = z * p.kb_per_split;
+                const uint32_t kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
+                const int32_t ya = (int32_t)(ta * 2u * TILE_ROWS + rank * TILE_ROWS);
+                const int32_t yb = GATE ? (int32_t)((rank ? p.H : 0u) + tb * half) : (int32_t)(tb * bn + rank * half);
+                for (uint32_t kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    uint8_t* sa = smem + (size_t)stage * stage_bytes;
+                    if (rank == 0u) mbar_expect_tx(&full_bar[stage], 2u * stage_bytes);   // both CTAs' boxes
+                    const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0u);
+                    const int32_t kx = (int32_t)(kb * BLOCK_K);
+                    tma_load_2d_pair(sa, &tmap_a, bar, kx, ya);
+                    tma_load_2d_pair(sa + a_bytes, &tmap_b, bar, kx, yb);
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            // the leader's last commits land on this CTA's barriers before it may leave
+            for (uint32_t s = 0; s < stages && ok; ++s) {
+                if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) ok = false;
+                if (++stage == stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && rank == 0u) {
+            uint32_t stage = 0, phase = 0, iter = 0;
+            bool ok = true;
+            for (uint32_t w = cluster_id; w < num_work && ok; w += num_clusters, ++iter) {
+                const uint32_t tile = w / p.splits, z = w - tile * p.splits;
+                const uint32_t kb0 = z * p.kb_per_split;
+                const uint32_t kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
+                const uint32_t buf = iter & 1u, use = iter >> 1;
+                if (!mbar_wait(&acc_empty[buf], (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * acc_cols;
+                for (uint32_t kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
+                    const uint64_t a_desc = make_smem_desc(sa);
+                    const uint64_t b_desc = make_smem_desc(sa + a_bytes);
+#pragma unroll
+                    for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&empty_bar[stage]);    // frees the stage in both CTAs
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit_pair(&acc_full[buf]);    // wakes the epilogues of both CTAs
+            }
+        }
+    } else {
+        // ---------------- epilogue warps (both CTAs, 128 rows each) ----------------
+        const uint32_t q = warp & 3u;
+        const uint32_t row_in_tile = q * 32u + lane;
+        const uint32_t out_cols = GATE ? p.H : p.N;
+        const uint32_t osz = p.partial ? 4u : dtype_size(p.o_dtype);
+        const uint32_t ncols = GATE ? half : bn;
+        uint32_t iter = 0;
+        bool ok = true;
+        for (uint32_t w = cluster_id; w < num_work && ok; w += num_clusters, ++iter) {
+            const uint32_t tile = w / p.splits, z = w - tile * p.splits;
+            uint32_t ta, tb;
+            tile_coords(p, tile, ta, tb);
+            const uint32_t buf = iter & 1u, use = iter >> 1;
+            if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((q * 32u) << 16) + buf * acc_cols;
+            const uint32_t m = ta * 2u * TILE_ROWS + rank * TILE_ROWS + row_in_tile;
+            for (uint32_t c0 = 0; c0 < ncols; c0 += 16u) {
+                uint32_t r0[16], r1[16];
+                tmem_ld16(t_row + c0, r0);
+                if (GATE) tmem_ld16(t_row + c0 + half, r1);
+                tmem_ld_wait();
+                store_rows16<GATE>(p, r0, r1, m, tb, c0, z, out_cols, osz);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0u));
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) {
+        atomicExch(p.status, 1);
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    __syncthreads();
+    cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its tile
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, p.tmem_cols);
+    }
+}
+
+template <bool GATE>
+static cudaError_t launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, size_t smem,
+                                       cudaStream_t stream)
+{
+    auto kern = tc_gemm_pair_kernel<GATE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcMaxSmem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    kern<<<grid, kTcThreads, smem, stream>>>(ma, mb, p);
+    return cudaGetLastError();
+}
+
+// Number of CTA pairs that can be resident at once (pairs need two SMs of one TPC).
+cudaError_t tc_pair_max_clusters(size_t smem, int* clusters)
+{
+    auto kern = tc_gemm_pair_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcMaxSmem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(kTcThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    return cudaOccupancyMaxActiveClusters(clusters, kern, &cfg);
+}
+
 template <bool SWAP, bool GATE>
 static cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, size_t smem,
                                   cudaStream_t stream)
@@ -624,6 +889,8 @@ cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, c
                            size_t smem, cudaStream_t stream)
 {
     const bool gate = p.gate != 0;
+    if (p.pair) return gate ? launch_pair_variant<true>(map_a, map_b, p, grid, smem, stream)
+                            : launch_pair_variant<false>(map_a, map_b, p, grid, smem, stream);
     if (swap) return gate ? launch_variant<true, true>(map_a, map_b, p, grid, smem, stream)
                           : launch_variant<true, false>(map_a, map_b, p, grid, smem, stream);
     return gate ? launch_variant<false, true>(map_a, map_b, p, grid, smem, stream)

@@ -27,6 +27,7 @@ struct TcParams {
     uint32_t kblocks, kb_per_split, splits;
     uint32_t stages, tmem_cols;
     uint32_t wide;         // unswapped kernel only: 256-row tiles (two A boxes, two accumulators)
+    uint32_t pair;         // unswapped kernel only: two CTAs (a cluster of 2) share one 256-row tile through cta_group::2
     uint32_t acc_bufs;     // accumulator buffers in TMEM: 2, or 1 when one tile needs all 512 columns
     int32_t o_dtype, b_dtype, epilogue, residual_order, has_bias, has_res, gate;
     int32_t bias_mode, res_mode;
@@ -53,6 +54,7 @@ __host__ __device__ inline void tile_coords(const TcParams& p, uint32_t tile, ui
     tb = local / rows;
 }
 
+cudaError_t tc_pair_max_clusters(size_t smem, int* clusters);
 cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p, bool swap, int grid,
                            size_t smem, cudaStream_t stream);
 
