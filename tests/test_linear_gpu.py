@@ -237,11 +237,15 @@ def test_kernel_choice_by_shape(M, K, w_dtype, expect, device):
 
 @pytest.mark.parametrize("M,K,N", [(1300, 320, 520), (512, 1024, 256), (2048, 192, 1000)])
 @pytest.mark.parametrize("gate", [False, True])
-def test_wide_tiles(M, K, N, gate, device, monkeypatch):
-    """256-row tiles of the unswapped tensor-core kernel (two accumulators, one TMEM
-    buffer), forced on small shapes: ragged M, N and K tails, bias + residual, gate."""
-    monkeypatch.setenv("VAICU_TC_WIDE", "1")
-    monkeypatch.setenv("VAICU_TC_BN", "256")
+@pytest.mark.parametrize("mode,bn", [("wide", 256), ("pair", 256), ("pair", 128), ("pair", 64)])
+def test_256_row_tiles(M, K, N, gate, mode, bn, device, monkeypatch):
+    """256-row tiles of the unswapped tensor-core kernel, forced on small shapes with
+    ragged M, N and K tails, bias + residual, gate.  "wide": one CTA, two accumulators,
+    one TMEM buffer.  "pair": two CTAs of a cluster share the tile through
+    tcgen05.mma.cta_group::2, each staging half of the weights' rows."""
+    monkeypatch.setenv("VAICU_TC_PAIR", "1" if mode == "pair" else "0")
+    monkeypatch.setenv("VAICU_TC_WIDE", "1" if mode == "wide" else "0")
+    monkeypatch.setenv("VAICU_TC_BN", str(bn))
     rng = np.random.default_rng(M + N)
     rows = 2 * N if gate else N
     x = rng.standard_normal((M, K)).astype(np.float32)
@@ -250,8 +254,28 @@ def test_wide_tiles(M, K, N, gate, device, monkeypatch):
     r = None if gate else rng.standard_normal((M, N)).astype(np.float32)
     got, want, node = run_linear(x, w, b, r, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", b_dtype="f32",
                                  epilogue="SILU", gate_fuse=gate, kernel=nodes.KERNEL_TC_GEMM)
-    assert node.info.tile_m == 256
-    assert_close(got, want, (2e-4, 5e-5), f"wide {M}x{K}x{N} gate={gate}")
+    assert node.info.tile_m == 256 and node.info.tile_n == (bn // 2 if gate else bn)
+    assert_close(got, want, (2e-4, 5e-5), f"{mode} {M}x{K}x{N} gate={gate} bn={bn}")
+
+
+@pytest.mark.parametrize("M,K,N,splits", [(256, 4096, 256, 4), (520, 2048, 300, 3)])
+def test_pair_tiles_split_k_match_single_cta(M, K, N, splits, device, monkeypatch):
+    """Split-K on CTA pairs (raw partials + fold) against the float64 expectation, and the
+    unsplit pair kernel bit-identical to the single-CTA kernel (same order of K)."""
+    rng = np.random.default_rng(K + N)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    monkeypatch.setenv("VAICU_TC_PAIR", "1")
+    monkeypatch.setenv("VAICU_TC_SPLITS", str(splits))
+    got, want, node = run_linear(x, w, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", kernel=nodes.KERNEL_TC_GEMM)
+    assert node.info.split_count == splits and node.info.tile_m == 256
+    assert_close(got, want, (2e-4, 5e-5), f"pair split-K {M}x{K}x{N}")
+    monkeypatch.setenv("VAICU_TC_SPLITS", "1")
+    one, _, _ = run_linear(x, w, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", kernel=nodes.KERNEL_TC_GEMM)
+    monkeypatch.setenv("VAICU_TC_PAIR", "0")
+    single, _, node = run_linear(x, w, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", kernel=nodes.KERNEL_TC_GEMM)
+    assert node.info.tile_m == 128
+    np.testing.assert_array_equal(one, single)
 
 
 @pytest.mark.parametrize("M", [1, 3])

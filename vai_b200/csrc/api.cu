@@ -230,17 +230,24 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
         t.tiles_a = ceil_div(H, 128u);
         t.tiles_b = ceil_div(d.M, bn);
     } else {
+        // CTA pairs (cta_group::2): two neighbouring SMs share one 256-row tile and each
+        // stages half of the weights' tile; both accumulator buffers stay in use.
+        bool pair = d.M > 128u;
+        if (const char* e = getenv("VAICU_TC_PAIR")) pair = atoi(e) != 0;
         // output columns per tile: bn (bn / 2 with gate)
         const uint32_t cand[3] = {256u, 128u, 64u};
+        const uint32_t rows = pair ? 256u : 128u, units = pair ? sms / 2u : sms;
         double best = -1.0;
         bn = 256u;
         for (uint32_t c : cand) {
             const uint32_t out_cols = gate ? c / 2u : c;
-            const uint32_t tiles = ceil_div(d.M, 128u) * ceil_div(H, out_cols);
-            const uint32_t waves = ceil_div(tiles, sms);
-            double eff = (double)tiles / ((double)waves * sms);
+            const uint32_t tiles = ceil_div(d.M, rows) * ceil_div(H, out_cols);
+            const uint32_t waves = ceil_div(tiles, units);
+            double eff = (double)tiles / ((double)waves * units);
             // narrower tiles re-read the activations more often and issue shorter MMAs
-            eff *= (c == 256u) ? 1.0 : (c == 128u ? 0.88 : 0.70);
+            // (measured on 8192 x 3072 x 3072: 1256 / 888 TFLOP/s for 256 / 128 on pairs)
+            if (pair) eff *= (c == 256u) ? 1.0 : (c == 128u ? 0.70 : 0.45);
+            else eff *= (c == 256u) ? 1.0 : (c == 128u ? 0.88 : 0.70);
             // a tile wider than the whole output is wasted work
             if (out_cols > (uint32_t)align_up(H, 16u) && c != 64u) eff *= (double)H / out_cols;
             if (eff > best) { best = eff; bn = c; }
@@ -249,17 +256,11 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
             const uint32_t v = (uint32_t)atoi(e);
             if (v >= 16u && v <= 256u && v % 16u == 0u) bn = v;
         }
-        // 256-row tiles (two A boxes per stage) halve the re-reads of the weights' tile;
-        // they need all 512 TMEM columns at bn = 256, so the epilogue no longer overlaps
-        // the next tile.  Worth it when the problem is tensor-bound and has tiles to spare.
-        bool wide = bn == 256u && d.M >= 512u &&
+        // Single-CTA alternative for 256-row tiles: two A boxes per stage and two MMAs per
+        // k-step; needs all 512 TMEM columns at bn = 256 (no epilogue overlap).
+        bool wide = !pair && bn == 256u && d.M >= 512u &&
                     ceil_div(d.M, 256u) * ceil_div(H, gate ? bn / 2u : bn) * 100u >= 85u * sms;
-        if (const char* e = getenv("VAICU_TC_WIDE")) wide = atoi(e) != 0 && bn * 2u <= 512u;
-        // CTA pairs (cta_group::2): two neighbouring SMs share one 256-row tile and each
-        // stages half of the weights' tile; both accumulator buffers stay in use.
-        bool pair = d.M > 128u;
-        if (const char* e = getenv("VAICU_TC_PAIR")) pair = atoi(e) != 0;
-        if (pair) wide = false;
+        if (const char* e = getenv("VAICU_TC_WIDE")) wide = atoi(e) != 0 && bn * 2u <= 512u && !pair;
         t.pair = pair ? 1u : 0u;
         t.wide = wide ? 1u : 0u;
         t.tiles_a = ceil_div(d.M, (wide || pair) ? 256u : 128u);

@@ -20,6 +20,8 @@
 // the UMMA N axis (TMEM columns).  Large M: A = activations, B = weights.
 // Small M ("swap"): A = weights, B = activations, so a 128-row slab of W is
 // streamed once and the batch rides on N.
+// For M > 128 a second kernel (tc_gemm_pair_kernel, below) runs the same pipeline on
+// clusters of two CTAs with tcgen05.mma.cta_group::2.
 // Every wait is bounded; on expiry the kernel records a status word and leaves.
 #include <cuda.h>
 
@@ -642,7 +644,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load whose completion bytes are counted on an mbarrier of either CTA of the pair
-// (no multicast: every CTA fetches its own boxes).
+// (every CTA fetches its own boxes; nothing is shared between CTAs by the copy engine).
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int32_t x, int32_t y)
 {
     asm volatile(
