@@ -264,6 +264,16 @@ VAICU_API int vaicu_rms_norm_run(vaicu_device* dev, vaicu_stream_t stream, const
                                  const void* shift, const void* residual, void* out, uint32_t rows, uint32_t feat,
                                  int i_dtype, int w_dtype, int o_dtype, float eps);
 
+/* Layer normalisation over the last axis: vAi's LayerNorm node, the producer of a Linear's
+ * activations in the GPT-2 blocks (vai/nodes/layer-norm.h:9-31, 91-160;
+ * vai/shaders/layer-norm.comp):
+ *   O[i, j] = (I[i, j] - mean_i) * rsqrt(var_i + eps) * scale[j] (+ shift[j]) (+ R[i, j])
+ * with biased variance and fp32 statistics whatever the dtypes.  Arguments as for
+ * vaicu_rms_norm_run; `scale` is required, `shift` and `residual` may be NULL. */
+VAICU_API int vaicu_layer_norm_run(vaicu_device* dev, vaicu_stream_t stream, const void* in, const void* scale,
+                                 const void* shift, const void* residual, void* out, uint32_t rows, uint32_t feat,
+                                 int i_dtype, int w_dtype, int o_dtype, float eps);
+
 /* Row-wise argmax of logits [M, N] (fp32 / fp16 / bf16) into M raw uint32 indices:
  * vAi's Argmax node, the greedy-decode consumer of the lm_head Linear
  * (vai/nodes/argmax.h:9-18, 57-79; vai/shaders/argmax.comp).  Ties resolve to the

@@ -396,6 +396,54 @@ int vai_oracle_rms_norm(const void* in, const void* scale, const void* shift, co
     return 0;
 }
 
+/* LayerNorm (vai/shaders/layer-norm.comp:138-196): shifted one-pass statistics with
+ * s = I[row, 0]: wg_size threads accumulate strided partials of sum = S(x - s) and
+ * sumSq = S(x - s)^2 in fp32, subgroupAdd over 32 lanes (pairwise here), per-subgroup
+ * sums added in order; mean = s + sum / F, m2 = max(sumSq - sum^2 / F, 0),
+ * invStd = inversesqrt(m2 / F + eps); then
+ * O = (I - mean) * invStd * scale + shift + R left to right in fp32 (layer-norm.comp:132-135).
+ * wg_size follows lnTuning (vai/nodes/layer-norm.h:73-88): the power of two >= F / 4
+ * within [32, 512]; the caller passes it. */
+int vai_oracle_layer_norm(const void* in, const void* scale, const void* shift, const void* res, void* out,
+                          uint32_t rows, uint32_t feat, int i_dtype, int w_dtype, int o_dtype, float eps, uint32_t wg_size)
+{
+    if (wg_size == 0 || wg_size % 32u || wg_size > 1024u || !scale) return 1;
+    float* lane = (float*)malloc(sizeof(float) * wg_size * 2u);
+    if (!lane) return 2;
+    float* lane_sq = lane + wg_size;
+    for (uint32_t row = 0; row < rows; ++row) {
+        const size_t base = (size_t)row * feat;
+        const float sh = load_elem(in, i_dtype, base);
+        for (uint32_t t = 0; t < wg_size; ++t) { lane[t] = 0.0f; lane_sq[t] = 0.0f; }
+        for (uint32_t j = 0; j < feat; ++j) {
+            const float d = load_elem(in, i_dtype, base + j) - sh;
+            lane[j % wg_size] += d;
+            lane_sq[j % wg_size] += d * d;
+        }
+        float s = 0.0f, q = 0.0f;
+        for (uint32_t sg = 0; sg < wg_size / 32u; ++sg) {
+            float v[32], w[32];
+            for (int l = 0; l < 32; ++l) { v[l] = lane[sg * 32u + l]; w[l] = lane_sq[sg * 32u + l]; }
+            for (int off = 16; off > 0; off >>= 1)
+                for (int l = 0; l < off; ++l) { v[l] += v[l + off]; w[l] += w[l + off]; }
+            s += v[0];
+            q += w[0];
+        }
+        float m2 = q - s * s / (float)feat;
+        if (m2 < 0.0f) m2 = 0.0f;
+        const float mean = sh + s / (float)feat;
+        const float inv = 1.0f / sqrtf(m2 / (float)feat + eps);
+        for (uint32_t j = 0; j < feat; ++j) {
+            float v = (load_elem(in, i_dtype, base + j) - mean) * inv * load_elem(scale, w_dtype, j);
+            v = v + (shift ? load_elem(shift, w_dtype, j) : 0.0f);
+            v = v + (res ? load_elem(res, i_dtype, base + j) : 0.0f);
+            store_elem(out, o_dtype, base + j, v);
+        }
+    }
+    free(lane);
+    return 0;
+}
+
 int vai_oracle_num_threads(void)
 {
 #ifdef _OPENMP

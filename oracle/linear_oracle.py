@@ -199,3 +199,41 @@ def rms_norm_c(x, scale=None, shift=None, residual=None, eps=1e-5, i_dtype=F32, 
     if rc != 0:
         raise RuntimeError(f"oracle returned {rc}")
     return out
+
+
+def layer_norm_f64(x, scale, shift=None, residual=None, eps=1e-5):
+    """float64 layer norm, what torch.nn.functional.layer_norm computes in the reference's
+    tests (vAi python/tests/nodes/test_layer_norm.py): biased variance over the last axis."""
+    x = np.asarray(x, dtype=np.float64)
+    mean = x.mean(axis=-1, keepdims=True)
+    var = ((x - mean) ** 2).mean(axis=-1, keepdims=True)
+    out = (x - mean) / np.sqrt(var + eps) * np.asarray(scale, dtype=np.float64).reshape(-1)
+    if shift is not None:
+        out = out + np.asarray(shift, dtype=np.float64).reshape(-1)
+    if residual is not None:
+        out = out + np.asarray(residual, dtype=np.float64)
+    return out
+
+
+def layer_norm_wg_size(feat, subgroup=32):
+    """Threads per row the reference picks (vAi vai/nodes/layer-norm.h:73-88)."""
+    cap = min(16 * subgroup, 1024)
+    wg = subgroup
+    while wg * 4 < feat and wg < cap:
+        wg *= 2
+    return wg
+
+
+def layer_norm_c(x, scale, shift=None, residual=None, eps=1e-5, i_dtype=F32, w_dtype=F32, o_dtype=F32, wg_size=None):
+    """The C restatement of vAi's layer-norm shader; arrays in device representation."""
+    x = np.ascontiguousarray(x)
+    rows, feat = int(np.prod(x.shape[:-1])), x.shape[-1]
+    out = np.empty(x.shape, dtype=np.float32 if o_dtype == F32 else np.uint16)
+    keep = [None if a is None else np.ascontiguousarray(a) for a in (scale, shift, residual)]
+    wg = wg_size or layer_norm_wg_size(feat)
+    rc = lib().vai_oracle_layer_norm(_ptr(x), _ptr(keep[0]), _ptr(keep[1]), _ptr(keep[2]), _ptr(out), ctypes.c_uint32(rows),
+                                     ctypes.c_uint32(feat), ctypes.c_int(i_dtype), ctypes.c_int(w_dtype), ctypes.c_int(o_dtype),
+                                     ctypes.c_float(eps), ctypes.c_uint32(wg))
+    if rc != 0:
+        raise RuntimeError(f"oracle returned {rc}")
+    return out

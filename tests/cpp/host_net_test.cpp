@@ -4,9 +4,13 @@
 #include <cstdio>
 
 #include "../../vai_b200/host/net.h"
+#include "../../vai_b200/host/norm.h"
 
 using namespace vai;
+using vai::node::Argmax;
+using vai::node::LayerNorm;
 using vai::node::Linear;
+using vai::node::RmsNorm;
 
 static int fails = 0;
 #define EXPECT(cond)                                                                          \
@@ -90,12 +94,68 @@ static void mlp_on_gpu(bool useGraph)
     EXPECT(net.recordingCount() == (useGraph ? 2u : 1u));
 }
 
+// LayerNorm (or RmsNorm) -> Linear -> Argmax, the tail of a decoder: checked against double
+// precision on the host; the argmax must pick the same column.
+static void norm_head_on_gpu(bool layer)
+{
+    const uint32_t M = 3, D = 96, V = 200;
+    std::vector<float> x(M * D), g(D), b(D), w(V * D);
+    unsigned s = layer ? 99 : 4242;
+    auto rnd = [&] { s = s * 1664525u + 1013904223u; return ((s >> 8) & 0xFFFF) / 32768.0f - 1.0f; };
+    for (auto& v : x) v = 3.0f * rnd() + 0.5f;
+    for (auto& v : g) v = 1.0f + 0.2f * rnd();
+    for (auto& v : b) v = 0.2f * rnd();
+    for (auto& v : w) v = rnd() * 0.1f;
+    initVAIEngine(0);
+    NeuralNet net({.wDefaultDtype = Dtype::Fp32});
+    std::unique_ptr<Node> normNode;
+    if (layer) normNode = std::make_unique<LayerNorm>(LayerNorm::Config{.eps = 1e-5f});
+    else normNode = std::make_unique<RmsNorm>(RmsNorm::Config{.eps = 1e-6f});
+    Node& norm = *normNode;
+    Linear head({.inDim = D, .outDim = V});
+    Argmax pick;
+    net.input("x") - norm - head - pick - net.output("token");
+    head - net.output("logits");
+    net.finish();
+    norm["scale"] = Tensor({D}, Dtype::Fp32); norm["scale"].upload(g.data());
+    if (layer) { norm["shift"] = Tensor({D}, Dtype::Fp32); norm["shift"].upload(b.data()); }
+    head["weight"] = Tensor({V, D}, Dtype::Fp32); head["weight"].upload(w.data());
+    vaicu_device_synchronize(deviceHandle());
+    auto out = net({{"x", HostTensor::fromFloats({M, D}, x)}});
+    const std::vector<float> logits = out.at("logits").floats();
+    std::vector<uint32_t> token(M);
+    std::memcpy(token.data(), out.at("token").bytes.data(), M * 4);
+    double worst = 0;
+    for (uint32_t m = 0; m < M; ++m) {
+        double mean = 0, var = 0;
+        if (layer) {
+            for (uint32_t k = 0; k < D; ++k) mean += x[m * D + k];
+            mean /= D;
+        }
+        for (uint32_t k = 0; k < D; ++k) var += (x[m * D + k] - mean) * (x[m * D + k] - mean);
+        const double inv = 1.0 / std::sqrt(var / D + (layer ? 1e-5 : 1e-6));
+        uint32_t best = 0;
+        double bestv = -1e300;
+        for (uint32_t n = 0; n < V; ++n) {
+            double acc = 0;
+            for (uint32_t k = 0; k < D; ++k) acc += ((x[m * D + k] - mean) * inv * g[k] + (layer ? b[k] : 0.0)) * w[n * D + k];
+            worst = std::fmax(worst, std::fabs(acc - logits[m * V + n]));
+            if (acc > bestv) { bestv = acc; best = n; }
+        }
+        EXPECT(token[m] == best);
+    }
+    std::printf("%s -> Linear -> Argmax: worst abs err %.3g\n", layer ? "LayerNorm" : "RmsNorm", worst);
+    EXPECT(worst < 1e-4);
+}
+
 int main(int argc, char** argv)
 {
     wiring();
     if (argc > 1 && std::string(argv[1]) == "--gpu") {
         mlp_on_gpu(true);
         mlp_on_gpu(false);
+        norm_head_on_gpu(true);
+        norm_head_on_gpu(false);
     }
     std::printf(fails ? "FAILED (%d)\n" : "ok\n", fails);
     return fails ? 1 : 0;

@@ -39,6 +39,7 @@ def _stub_pyvai():
     nodes.LinearNode = lambda **kw: dict(kw)
     nodes.ArgmaxNode = lambda **kw: {"node": "argmax", **kw}
     nodes.RmsNormNode = lambda **kw: {"node": "rms_norm", **kw}
+    nodes.LayerNormNode = lambda **kw: {"node": "layer_norm", **kw}
     pyvai.nodes = nodes
     sys.modules["pyvai"] = pyvai
     sys.modules["pyvai.nodes"] = nodes
@@ -50,6 +51,7 @@ def main(ref_root):
     sys.path.insert(0, os.path.join(ref_root, "python", "tests", "nodes"))
     import node_check
     import test_argmax
+    import test_layer_norm
     import test_rms_norm
     import test_linear
 
@@ -125,6 +127,12 @@ def main(ref_root):
     # the producer of a Linear's activations: RmsNorm (python/tests/nodes/test_rms_norm.py)
     for fn in ("test_rms_norm", "test_rms_norm_scale_shift_residual", "test_rms_norm_coeffs_as_inputs"):
         getattr(test_rms_norm, fn)()
+        record(fn.replace("test_", ""))
+
+    # GPT-2's producer: LayerNorm (python/tests/nodes/test_layer_norm.py)
+    for fn in ("test_layer_norm_with_shift", "test_layer_norm_no_shift", "test_layer_norm_residual",
+               "test_layer_norm_coeffs_as_inputs"):
+        getattr(test_layer_norm, fn)()
         record(fn.replace("test_", ""))
 
     here = os.path.dirname(os.path.abspath(__file__))

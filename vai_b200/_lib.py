@@ -73,6 +73,8 @@ SIGNATURES = {
     "vaicu_linear_splitk_static": (ctypes.c_int, [ctypes.POINTER(LinearDesc)] + [ctypes.c_void_p] * 6),
     "vaicu_rms_norm_run": (ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, ctypes.c_int,
                                                                    ctypes.c_int, ctypes.c_float]),
+    "vaicu_layer_norm_run": (ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, ctypes.c_int,
+                                                                   ctypes.c_int, ctypes.c_float]),
     "vaicu_argmax_run": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]),
     "vaicu_linear_shard_desc": (ctypes.c_int, [ctypes.POINTER(LinearDesc), ctypes.c_int, ctypes.c_int,
                                                ctypes.POINTER(LinearDesc), ctypes.POINTER(ctypes.c_uint32),

@@ -855,6 +855,21 @@ int vaicu_rms_norm_run(vaicu_device* dev, vaicu_stream_t stream, const void* in,
     return VAICU_OK;
 }
 
+int vaicu_layer_norm_run(vaicu_device* dev, vaicu_stream_t stream, const void* in, const void* scale, const void* shift,
+                       const void* residual, void* out, uint32_t rows, uint32_t feat, int i_dtype, int w_dtype, int o_dtype,
+                       float eps)
+{
+    if (!dev || !in || !out || !scale || rows == 0 || feat == 0) return VAICU_ERR_INVALID_VALUE;
+    if (!valid_dtype(i_dtype) || !valid_dtype(o_dtype)) return VAICU_ERR_INVALID_VALUE;
+    if ((scale || shift) && !valid_dtype(w_dtype)) return VAICU_ERR_INVALID_VALUE;
+    if ((uint64_t)rows * feat >= (1ull << 32)) return VAICU_ERR_INVALID_VALUE;
+    if ((reinterpret_cast<uintptr_t>(in) & (dtype_size(i_dtype) - 1u)) || (reinterpret_cast<uintptr_t>(out) & (dtype_size(o_dtype) - 1u)))
+        return VAICU_ERR_ALIGNMENT;
+    VAICU_CUDA(launch_layer_norm(in, scale, shift, residual, out, rows, feat, i_dtype, w_dtype, o_dtype, eps, dev->sm_count,
+                               (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
 int vaicu_argmax_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, void* out_u32)
 {
     if (!logits || !out_u32 || M == 0 || N == 0) return VAICU_ERR_INVALID_VALUE;

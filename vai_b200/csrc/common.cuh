@@ -138,6 +138,8 @@ cudaError_t launch_argmax(const void* in, int dtype, uint32_t M, uint32_t N, uin
 
 cudaError_t launch_rms_norm(const void* in, const void* scale, const void* shift, const void* res, void* out, uint32_t rows,
                             uint32_t feat, int i_dtype, int w_dtype, int o_dtype, float eps, int sm_count, cudaStream_t stream);
+cudaError_t launch_layer_norm(const void* in, const void* scale, const void* shift, const void* res, void* out, uint32_t rows,
+                            uint32_t feat, int i_dtype, int w_dtype, int o_dtype, float eps, int sm_count, cudaStream_t stream);
 
 // Records "<where>: <what>" as the calling thread's last error text
 // (vaicu_last_cuda_error).

@@ -1,0 +1,120 @@
+// vai::node::RmsNorm, LayerNorm and Argmax on the CUDA backend: the nodes on either side
+// of a Linear (vAi vai/nodes/rms-norm.h:9-60, layer-norm.h:9-70, argmax.h:9-40), with the
+// reference's Config fields and slot names, over the C ABI.
+#ifndef VAI_B200_HOST_NORM_H
+#define VAI_B200_HOST_NORM_H
+
+#include "linear.h"
+
+namespace vai::node {
+
+namespace detail {
+
+// Shared body of the two row normalisations: same slots, same checks
+// (rms-norm.h:100-140, layer-norm.h:107-135), different kernel.
+class RowNorm : public vai::Node
+{
+public:
+    struct Config {
+        float eps = 1e-5f;
+        bool coeffsAsInputs = false;   // scale / shift are inputs, not parameters
+        bool acceptResidual = false;   // input "residual", added to the output
+    } config_;
+
+    bool hasScale() const { return (*this)["scale"].validShape(); }
+    bool hasShift() const { return (*this)["shift"].validShape(); }
+
+    void prepare() override
+    {
+        const Tensor& in = (*this)["in0"];
+        if (!in.validShape() || in.shape().size() < 2) throw std::invalid_argument("in0 must have at least two axes");
+        const uint32_t feat = in.shape().back();
+        if (needsScale_ && !hasScale()) throw std::invalid_argument("scale is required");
+        wDtype_ = Dtype::None;
+        for (const char* name : {"scale", "shift"}) {
+            const Tensor& t = (*this)[name];
+            if (!t.validShape()) continue;
+            if (t.shape().back() != feat || t.numElements() != feat) throw std::invalid_argument(std::string(name) + ": wrong size");
+            if (wDtype_ != Dtype::None && t.dtype() != wDtype_) throw std::invalid_argument("scale and shift must share a dtype");
+            wDtype_ = t.dtype();
+        }
+        if (config_.acceptResidual) {
+            const Tensor& r = (*this)["residual"];
+            if (r.shape() != in.shape() || r.dtype() != in.dtype())
+                throw std::invalid_argument("residual must match in0's shape and dtype");
+        }
+        (*this)["out0"] = Tensor(in.shape(), oDtype_ == Dtype::None ? oDefault_ : oDtype_);
+    }
+
+    void run(vaicu_stream_t stream) override
+    {
+        const Tensor& in = (*this)["in0"];
+        const Tensor& out = (*this)["out0"];
+        check(entry_(deviceHandle(), stream, in.devicePtr(), hasScale() ? (*this)["scale"].devicePtr() : nullptr,
+                     hasShift() ? (*this)["shift"].devicePtr() : nullptr,
+                     config_.acceptResidual ? (*this)["residual"].devicePtr() : nullptr, out.devicePtr(),
+                     outerSize(in.shape()), in.shape().back(), (int)in.dtype(), (int)wDtype_, (int)out.dtype(), config_.eps),
+              "row norm");
+    }
+
+protected:
+    using Entry = int (*)(vaicu_device*, vaicu_stream_t, const void*, const void*, const void*, const void*, void*, uint32_t,
+                          uint32_t, int, int, int, float);
+    RowNorm(Config config, Entry entry, bool needsScale) : config_(config), entry_(entry), needsScale_(needsScale)
+    {
+        addSlot("out0", NodeSlot::output);
+        addSlot("in0", NodeSlot::input);
+        const NodeSlot::Type w = config_.coeffsAsInputs ? NodeSlot::input : NodeSlot::persistent;
+        addSlot("scale", w);
+        addSlot("shift", w);
+        if (config_.acceptResidual) addSlot("residual", NodeSlot::input);
+    }
+
+private:
+    Entry entry_;
+    bool needsScale_;
+    Dtype wDtype_ = Dtype::None;
+};
+
+}   // namespace detail
+
+class RmsNorm : public detail::RowNorm
+{
+public:
+    explicit RmsNorm(Config config = {}) : RowNorm(config, &vaicu_rms_norm_run, false) {}
+};
+
+class LayerNorm : public detail::RowNorm
+{
+public:
+    explicit LayerNorm(Config config = {}) : RowNorm(config, &vaicu_layer_norm_run, true) {}
+};
+
+// Index of the largest value of each row, as uint32 bits in an Fp32-typed [M] tensor
+// (argmax.h:51-79); ties go to the lowest index.
+class Argmax : public vai::Node
+{
+public:
+    Argmax()
+    {
+        addSlot("out0", NodeSlot::output);
+        addSlot("in0", NodeSlot::input);
+    }
+    void prepare() override
+    {
+        const Tensor& in = (*this)["in0"];
+        if (!in.validShape() || in.shape().size() < 2) throw std::invalid_argument("in0 must have at least two axes");
+        (*this)["out0"] = Tensor({outerSize(in.shape())}, Dtype::Fp32);
+    }
+    void run(vaicu_stream_t stream) override
+    {
+        const Tensor& in = (*this)["in0"];
+        check(vaicu_argmax_run(stream, in.devicePtr(), (int)in.dtype(), outerSize(in.shape()), in.shape().back(),
+                               (*this)["out0"].devicePtr()),
+              "vaicu_argmax_run");
+    }
+};
+
+}   // namespace vai::node
+
+#endif   // VAI_B200_HOST_NORM_H

@@ -212,6 +212,8 @@ class RmsNormNode(Node):
     accept_residual opens the `residual` input (same shape and dtype as in0).  With
     set_o_dtype(F16 / BF16) the node hands 16-bit activations to the Linear after it."""
 
+    _entry = "vaicu_rms_norm_run"
+
     def __init__(self, eps=1e-5, coeffs_as_inputs=False, accept_residual=False):
         super().__init__()
         self.eps = float(eps)
@@ -262,10 +264,25 @@ class RmsNormNode(Node):
                 self["shift"].ptr if self.has_shift() else None,
                 self["residual"].ptr if self.accept_residual else None, o.ptr, rows, x.shape[-1],
                 int(x.dtype), int(self._w_dtype), int(o.dtype), self.eps)
-        run = dev.lib.vaicu_rms_norm_run
+        entry = self._entry
+        run = getattr(dev.lib, entry)
 
         def launch(stream):
-            _lib.check(run(args[0], stream, *args[1:]), "vaicu_rms_norm_run")
+            _lib.check(run(args[0], stream, *args[1:]), entry)
 
         launch.kernel_launches = 1
         return launch
+
+
+class LayerNormNode(RmsNormNode):
+    """Layer normalisation over the last axis (vAi vai/nodes/layer-norm.h:9-31):
+    out0 = (in0 - mean) * rsqrt(var + eps) * scale (+ shift) (+ residual), biased variance,
+    fp32 statistics.  Same slots and options as the reference node: `scale` is required,
+    `shift` applies when set; both are parameters, or inputs under coeffs_as_inputs."""
+
+    _entry = "vaicu_layer_norm_run"
+
+    def prepare(self):
+        if not self.has_scale():
+            raise ValueError("LayerNorm needs a scale")
+        super().prepare()

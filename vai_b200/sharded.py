@@ -291,7 +291,16 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5):
             dist.barrier()
             fused.close()
         w_bytes_all = n_rows * p["d"] * 2
+        flops_all = 2.0 * M * n_rows * p["d"]
+        best_ms = total_ms if fused_ms is None else min(total_ms, fused_ms)
         out["layers"][name] = {"rows": n_rows, "rows_per_gpu": rows_local, "kernel": int(lin.info.kernel),
+                               "tile": [int(lin.info.tile_m), int(lin.info.tile_n)],
+                               "aggregate_TFLOPs_local": flops_all / (local_ms * 1e-3) / 1e12,
+                               "aggregate_TFLOPs_with_allgather": flops_all / (total_ms * 1e-3) / 1e12,
+                               "aggregate_TFLOPs_fused_gather": None if fused_ms is None else flops_all / (fused_ms * 1e-3) / 1e12,
+                               # share of the step spent outside the local kernel (gather + re-layout)
+                               "collective_share_allgather": max(0.0, 1.0 - local_ms / total_ms),
+                               "collective_share_best": max(0.0, 1.0 - local_ms / best_ms),
                                "local_us": local_ms * 1e3, "with_allgather_us": total_ms * 1e3,
                                "aggregate_GBps_local": w_bytes_all / (local_ms * 1e-3) / 1e9,
                                "aggregate_GBps_with_allgather": w_bytes_all / (total_ms * 1e-3) / 1e9,
