@@ -89,6 +89,7 @@ public:
     bool gpuBufferBound() const { return buffer_ != nullptr || external_ != nullptr; }
     void allocate()
     {
+        initVAIEngine();
         vaicu_buffer* b = nullptr;
         check(vaicu_buffer_alloc(deviceHandle(), numBytes(), &b), "vaicu_buffer_alloc");
         buffer_.reset(b, [](vaicu_buffer* p) { vaicu_buffer_free(p); });
