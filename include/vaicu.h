@@ -281,6 +281,26 @@ VAICU_API int vaicu_layer_norm_run(vaicu_device* dev, vaicu_stream_t stream, con
  * kernel on `stream`; no allocation, no synchronisation. */
 VAICU_API int vaicu_argmax_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, void* out_u32);
 
+/* Argmax in two stages, for wide rows and for vocabulary-split heads.  Stage 1 scans
+ * column segments of 8192 in parallel blocks, stage 2 folds the per-segment candidates;
+ * the result is the same index vaicu_argmax_run returns (lowest index among equal maxima).
+ *   logits     [M, N] with a row stride of `ld` elements (ld >= N): a slab of wider rows works
+ *   index_base added to every column index: the first vocabulary entry of this GPU's slab
+ *   workspace  vaicu_argmax_workspace_bytes(M, N) bytes, 16-byte aligned
+ *   out_val    [M] fp32 row maxima, or NULL when only indices are wanted
+ *   out_u32    [M] uint32 indices
+ * vaicu_argmax_merge_run folds candidates of `groups` slabs: slab g's candidate for row m
+ * is vals[g * group_stride + m] / idx[g * group_stride + m] (group_stride >= M, in elements;
+ * an all-gather of one [2, M] buffer per GPU gives group_stride = 2 M), so a
+ * column-split lm_head exchanges 8 bytes per row and GPU instead of its logits.  This is
+ * the sharded form of vAi's Argmax node (vai/nodes/argmax.h:9-18); the reference has no
+ * multi-GPU counterpart. */
+VAICU_API int vaicu_argmax_workspace_bytes(uint32_t M, uint32_t N, size_t* out_bytes);
+VAICU_API int vaicu_argmax_pairs_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, size_t ld,
+                                     uint32_t index_base, void* workspace, float* out_val, void* out_u32);
+VAICU_API int vaicu_argmax_merge_run(vaicu_stream_t stream, const float* vals, const void* idx_u32, uint32_t groups,
+                                     size_t group_stride, uint32_t M, float* out_val, void* out_u32);
+
 /* Column-split helper for the multi-GPU layout: the desc of rank `rank` of
  * `world` when W's rows (output columns) are split evenly; for gate_fuse the
  * split is per half.  Fills row offsets into W / bias for that rank. No

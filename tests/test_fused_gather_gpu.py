@@ -1,7 +1,9 @@
 """GPU, 2 ranks on 2 GPUs (skipped on a one-GPU box): the column-split Linear whose
 tensor-core epilogue stores its slab into every rank's output over NVLink
 (vaicu_linear_run_scatter + CUDA IPC) gives bit-identical results to the NCCL all-gather
-of the same plan's dense output.  Runs vai_b200.sharded under torch.distributed.run."""
+of the same plan's dense output, and the vocabulary-split greedy head (per-GPU argmax
+candidates merged after an 8-byte-per-row exchange) picks the same tokens as the argmax over
+the gathered logits.  Runs vai_b200.sharded under torch.distributed.run."""
 import json
 import os
 import subprocess
@@ -28,3 +30,7 @@ def test_fused_gather_matches_nccl_on_two_gpus():
     for name, layer in res["layers"].items():
         assert layer["fused_gather_matches_nccl"] is True, name
         assert layer["fused_gather_us"] > 0
+    # vocabulary-split greedy head: candidates instead of logits cross the link
+    head = res["layers"]["lm_head"]
+    assert head["greedy_head_matches_argmax_of_gathered_logits"] is True
+    assert head["greedy_exchange_bytes_per_gpu"] == 8 * 64

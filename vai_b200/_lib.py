@@ -76,6 +76,11 @@ SIGNATURES = {
     "vaicu_layer_norm_run": (ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, ctypes.c_int,
                                                                    ctypes.c_int, ctypes.c_float]),
     "vaicu_argmax_run": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]),
+    "vaicu_argmax_workspace_bytes": (ctypes.c_int, [ctypes.c_uint32, ctypes.c_uint32, ctypes.POINTER(ctypes.c_size_t)]),
+    "vaicu_argmax_pairs_run": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
+                                              ctypes.c_size_t, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "vaicu_argmax_merge_run": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_size_t,
+                                              ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p]),
     "vaicu_linear_shard_desc": (ctypes.c_int, [ctypes.POINTER(LinearDesc), ctypes.c_int, ctypes.c_int,
                                                ctypes.POINTER(LinearDesc), ctypes.POINTER(ctypes.c_uint32),
                                                ctypes.POINTER(ctypes.c_uint32)]),

@@ -880,6 +880,39 @@ int vaicu_argmax_run(vaicu_stream_t stream, const void* logits, int dtype, uint3
     return VAICU_OK;
 }
 
+int vaicu_argmax_workspace_bytes(uint32_t M, uint32_t N, size_t* out_bytes)
+{
+    if (!out_bytes || M == 0 || N == 0) return VAICU_ERR_INVALID_VALUE;
+    *out_bytes = align_up((size_t)M * argmax_parts(N) * 8u, 256u);
+    return VAICU_OK;
+}
+
+int vaicu_argmax_pairs_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, size_t ld,
+                           uint32_t index_base, void* workspace, float* out_val, void* out_u32)
+{
+    if (!logits || !out_u32 || !workspace || M == 0 || N == 0 || ld < N) return VAICU_ERR_INVALID_VALUE;
+    if (!valid_dtype(dtype)) return VAICU_ERR_INVALID_VALUE;
+    if ((uint64_t)index_base + N > (1ull << 32)) return VAICU_ERR_INVALID_VALUE;
+    if ((reinterpret_cast<uintptr_t>(logits) & (dtype_size(dtype) - 1u)) || (reinterpret_cast<uintptr_t>(out_u32) & 3u) ||
+        (reinterpret_cast<uintptr_t>(out_val) & 3u) || (reinterpret_cast<uintptr_t>(workspace) & 15u))
+        return VAICU_ERR_ALIGNMENT;
+    VAICU_CUDA(launch_argmax_pairs(logits, dtype, M, N, ld, index_base, workspace, out_val, reinterpret_cast<uint32_t*>(out_u32),
+                                   (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
+int vaicu_argmax_merge_run(vaicu_stream_t stream, const float* vals, const void* idx_u32, uint32_t groups, size_t group_stride,
+                           uint32_t M, float* out_val, void* out_u32)
+{
+    if (!vals || !idx_u32 || !out_u32 || groups == 0 || M == 0 || group_stride < M) return VAICU_ERR_INVALID_VALUE;
+    if ((reinterpret_cast<uintptr_t>(vals) & 3u) || (reinterpret_cast<uintptr_t>(idx_u32) & 3u) ||
+        (reinterpret_cast<uintptr_t>(out_u32) & 3u) || (reinterpret_cast<uintptr_t>(out_val) & 3u))
+        return VAICU_ERR_ALIGNMENT;
+    VAICU_CUDA(launch_argmax_merge(vals, reinterpret_cast<const uint32_t*>(idx_u32), groups, group_stride, M, out_val,
+                                   reinterpret_cast<uint32_t*>(out_u32), (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
 int vaicu_linear_shard_desc(const vaicu_linear_desc* full, int rank, int world, vaicu_linear_desc* shard,
                             uint32_t* w_row_begin, uint32_t* w_row_count)
 {

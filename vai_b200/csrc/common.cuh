@@ -135,6 +135,11 @@ cudaError_t launch_splitk_reduce(const LinearArgs& a, const float* partial, uint
 cudaError_t launch_cast_f32_to_16(const float* src, void* dst, int dst_dtype, size_t n, int sm_count, cudaStream_t stream);
 
 cudaError_t launch_argmax(const void* in, int dtype, uint32_t M, uint32_t N, uint32_t* out, cudaStream_t stream);
+uint32_t argmax_parts(uint32_t N);
+cudaError_t launch_argmax_pairs(const void* in, int dtype, uint32_t M, uint32_t N, size_t ld, uint32_t index_base, void* workspace,
+                                float* out_val, uint32_t* out_idx, cudaStream_t stream);
+cudaError_t launch_argmax_merge(const float* vals, const uint32_t* idxs, uint32_t groups, size_t group_stride, uint32_t M,
+                                float* out_val, uint32_t* out_idx, cudaStream_t stream);
 
 cudaError_t launch_rms_norm(const void* in, const void* scale, const void* shift, const void* res, void* out, uint32_t rows,
                             uint32_t feat, int i_dtype, int w_dtype, int o_dtype, float eps, int sm_count, cudaStream_t stream);

@@ -518,7 +518,39 @@ class NeuralNet:
                 DeviceBuffer.end_capture()
             _lib.check(rc, "vaicu_graph_capture_end")
             rec.graph = g
+        # page-locked staging for the net's inputs and outputs, and a second recording that
+        # brackets the same launches with the host<->device copies: one submission per call
+        rec.stage_in, rec.stage_out = {}, {}
+        for name, t in rec.input_tensors.items():
+            rec.stage_in[name] = self._pinned(t.nbytes(), np.float32 if t.dtype == Dtype.F32 else np.uint16, t.shape)
+        for name, t in rec.outputs.items():
+            rec.stage_out[name] = self._pinned(t.nbytes(), np.float32 if t.dtype == Dtype.F32 else np.uint16, t.shape)
+        rec.graph_io = None
+        if self.use_graph:
+            _lib.check(lib.vaicu_graph_capture_begin(self.stream), "vaicu_graph_capture_begin")
+            DeviceBuffer._capturing += 1
+            try:
+                self._copies_in(rec)
+                self._play(ops)
+                self._copies_out(rec)
+            finally:
+                g = ctypes.c_void_p()
+                rc = lib.vaicu_graph_capture_end(self.stream, ctypes.byref(g))
+                DeviceBuffer.end_capture()
+            _lib.check(rc, "vaicu_graph_capture_end")
+            rec.graph_io = g
         return rec
+
+    def _copies_in(self, rec):
+        lib = self.device.lib
+        for name, (view, hp) in rec.stage_in.items():
+            _lib.check(lib.vaicu_memcpy_h2d(rec.input_tensors[name].ptr, hp, view.nbytes, self.stream), "vaicu_memcpy_h2d")
+
+    def _copies_out(self, rec):
+        lib = self.device.lib
+        for name, t in rec.outputs.items():
+            view, hp = rec.stage_out[name]
+            _lib.check(lib.vaicu_memcpy_d2h(hp, t.ptr, view.nbytes, self.stream), "vaicu_memcpy_d2h")
 
     def _play(self, ops):
         lib = self.device.lib
@@ -549,32 +581,24 @@ class NeuralNet:
         if set(fed) != set(names):
             raise ValueError(f"inputs {sorted(fed)} do not match the net's {sorted(names)}")
         lib = self.device.lib
-        self._upload_params()
         key = tuple((k, fed[k].shape, int(fed[k].dtype)) for k in sorted(fed))
-        if self._dirty:
-            self._recordings.clear()
+        if self._dirty:           # a parameter or a wire changed: every recording is stale
+            self._drop_recordings()
             self._dirty = False
         rec = self._recordings.get(key)
         if rec is None:
+            self._upload_params()
             rec = self._record(fed)
-            rec.stage_in, rec.stage_out = {}, {}
-            for name, t in rec.input_tensors.items():
-                rec.stage_in[name] = self._pinned(t.nbytes(), np.float32 if t.dtype == Dtype.F32 else np.uint16, t.shape)
-            for name, t in rec.outputs.items():
-                rec.stage_out[name] = self._pinned(t.nbytes(), np.float32 if t.dtype == Dtype.F32 else np.uint16, t.shape)
             rec.calls = 0
             self._recordings[key] = rec
         for name, t in fed.items():
-            view, hp = rec.stage_in[name]
-            np.copyto(view, t.host.reshape(view.shape))
-            _lib.check(lib.vaicu_memcpy_h2d(rec.input_tensors[name].ptr, hp, view.nbytes, self.stream), "vaicu_memcpy_h2d")
-        if rec.graph is not None:
-            _lib.check(lib.vaicu_graph_launch(rec.graph, self.stream), "vaicu_graph_launch")
+            np.copyto(rec.stage_in[name][0], t.host.reshape(rec.stage_in[name][0].shape))
+        if rec.graph_io is not None:
+            _lib.check(lib.vaicu_graph_launch(rec.graph_io, self.stream), "vaicu_graph_launch")
         else:
+            self._copies_in(rec)
             self._play(rec.ops)
-        for name, t in rec.outputs.items():
-            view, hp = rec.stage_out[name]
-            _lib.check(lib.vaicu_memcpy_d2h(hp, t.ptr, view.nbytes, self.stream), "vaicu_memcpy_d2h")
+            self._copies_out(rec)
         _lib.check(lib.vaicu_stream_sync(self.stream), "vaicu_stream_sync")
         # the kernels' bounded waits report through a device word: read it on the first
         # replay of a recording and then now and again, not on every step
@@ -590,8 +614,17 @@ class NeuralNet:
             outs[name] = host
         return outs[next(iter(outs))] if len(outs) == 1 else outs
 
+    def _drop_recordings(self):
+        for rec in self._recordings.values():
+            for g in (rec.graph, getattr(rec, "graph_io", None)):
+                if g is not None:
+                    self.device.lib.vaicu_graph_destroy(g)
+            rec.graph = rec.graph_io = None
+        self._recordings.clear()
+
     def __del__(self):
         try:
+            self._drop_recordings()
             for p in self._pinned_ptrs:
                 self.device.lib.vaicu_host_free_pinned(p)
         except Exception:

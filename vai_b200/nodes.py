@@ -176,12 +176,17 @@ class LinearNode(Node):
 class ArgmaxNode(Node):
     """Row-wise argmax (greedy decode) over logits: in0 [M, N] -> out0 [M] raw uint32
     indices in 4-byte slots (vAi vai/nodes/argmax.h:9-18; read them with
-    Tensor.to_u32()).  Ties go to the lowest index."""
+    Tensor.to_u32()).  Ties go to the lowest index.  Wide rows (a vocabulary) are scanned
+    by many blocks in column segments and folded in a second launch; the candidates live
+    in the `partial` temporary."""
+
+    WIDE = 16384        # from this row length on, one block per row is the slower form
 
     def __init__(self):
         super().__init__()
         self.add_slot("out0", OUTPUT)
         self.add_slot("in0", INPUT)
+        self.add_slot("partial", TEMPORARY)
 
     def prepare(self):
         x = self["in0"]
@@ -190,12 +195,28 @@ class ArgmaxNode(Node):
         # a [M] tensor of raw uint32; the dtype enum has no integer kind, so fp32 is the
         # 4-byte container, as in the reference (argmax.h:75-78)
         self.slots["out0"] = Tensor((x.shape[0],), Dtype.F32)
+        self.slots["partial"] = Tensor()
+        if x.shape[1] >= self.WIDE:
+            from .engine import Device
+            dev = self.net.device if self.net is not None else Device.default()
+            ws = ctypes.c_size_t()
+            _lib.check(dev.lib.vaicu_argmax_workspace_bytes(x.shape[0], x.shape[1], ctypes.byref(ws)), "vaicu_argmax_workspace_bytes")
+            self.slots["partial"] = Tensor((ws.value // 4,), Dtype.F32)
 
     def bind(self):
         from .engine import Device
         dev = self.net.device if self.net is not None else Device.default()
         x, o = self["in0"], self["out0"]
         xp, op, dt, M, N = x.ptr, o.ptr, int(x.dtype), x.shape[0], x.shape[1]
+        if self["partial"].valid_shape():
+            ws = self["partial"].ptr
+            pairs = dev.lib.vaicu_argmax_pairs_run
+
+            def launch(stream):
+                _lib.check(pairs(stream, xp, dt, M, N, N, 0, ws, None, op), "vaicu_argmax_pairs_run")
+
+            launch.kernel_launches = 2
+            return launch
         run = dev.lib.vaicu_argmax_run
 
         def launch(stream):

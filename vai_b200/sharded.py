@@ -204,6 +204,60 @@ class FusedGatherLinear(ShardedLinear):
         self._opened = []
 
 
+class ShardedGreedyHead:
+    """Vocabulary-split lm_head followed by greedy sampling without gathering logits: every
+    rank runs its slab of the head, reduces it to one (max, token) candidate per row with
+    the token's vocabulary offset (vaicu_argmax_pairs_run), the ranks exchange 8 bytes per
+    row, and each folds the candidates (vaicu_argmax_merge_run).  The same tokens as
+    Argmax over the gathered [M, vocab] logits, ties to the lowest token id."""
+
+    def __init__(self, device, dist, full_desc, w_local):
+        import torch
+        self.torch, self.dist, self.dev = torch, dist, device
+        self.rank = dist.get_rank() if dist is not None else 0
+        self.world = dist.get_world_size() if dist is not None else 1
+        self.desc, self.begin, self.count = shard_desc(full_desc, self.rank, self.world)
+        self.w = w_local
+        lib = device.lib
+        h = ctypes.c_void_p()
+        _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(self.desc), ctypes.byref(h)), "plan")
+        self.plan = h
+        self.info = _lib.LinearInfo()
+        _lib.check(lib.vaicu_linear_plan_info(h, ctypes.byref(self.info)), "info")
+        cuda = torch.device("cuda", device.ordinal)
+        M = self.desc.M
+        o_dt = {0: torch.float32, 1: torch.float16, 3: torch.bfloat16}[self.desc.o_dtype]
+        self.ws = torch.empty(max(self.info.workspace_bytes, 256), dtype=torch.uint8, device=cuda)
+        self.logits = torch.empty((M, self.count), dtype=o_dt, device=cuda)
+        n = ctypes.c_size_t()
+        _lib.check(lib.vaicu_argmax_workspace_bytes(M, self.count, ctypes.byref(n)), "vaicu_argmax_workspace_bytes")
+        self.arg_ws = torch.empty(n.value, dtype=torch.uint8, device=cuda)
+        # one buffer [2, M] per rank: row 0 the maxima (fp32), row 1 the token ids (uint32 bits)
+        self.mine = torch.empty((2, M), dtype=torch.float32, device=cuda)
+        self.all = torch.empty((self.world, 2, M), dtype=torch.float32, device=cuda)
+        self.tokens = torch.empty(M, dtype=torch.int32, device=cuda)
+
+    def forward(self, x):
+        lib, M = self.dev.lib, self.desc.M
+        stream = self.torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.vaicu_linear_run(self.plan, stream, x.data_ptr(), self.w.data_ptr(), None, None, self.logits.data_ptr(),
+                                        self.ws.data_ptr()), "vaicu_linear_run")
+        _lib.check(lib.vaicu_argmax_pairs_run(stream, self.logits.data_ptr(), self.desc.o_dtype, M, self.count, self.count,
+                                              self.begin, self.arg_ws.data_ptr(), self.mine[0].data_ptr(), self.mine[1].data_ptr()),
+                   "vaicu_argmax_pairs_run")
+        if self.world == 1:
+            return self.mine[1].view(self.torch.int32)
+        self.dist.all_gather_into_tensor(self.all, self.mine)
+        _lib.check(lib.vaicu_argmax_merge_run(stream, self.all.data_ptr(), self.all[0, 1].data_ptr(), self.world, 2 * M, M, None,
+                                              self.tokens.data_ptr()), "vaicu_argmax_merge_run")
+        return self.tokens
+
+    def close(self):
+        if self.plan:
+            self.dev.lib.vaicu_linear_plan_destroy(self.plan)
+            self.plan = None
+
+
 def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5):
     """Column-split lm_head and gate|value Linear of `preset` at batch M on this rank's
     GPU, with the NCCL all-gather of the output slabs; device-timed, max over ranks.
@@ -290,6 +344,19 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5):
             torch.cuda.synchronize()
             dist.barrier()
             fused.close()
+        greedy = {}
+        if name == "lm_head":
+            # greedy sampling without gathering logits: 8 bytes per row and GPU are exchanged
+            head = ShardedGreedyHead(device, dist, full, lin.w)
+            tok = head.forward(x).clone()
+            logits = lin.forward(x, assemble_output=True).float()
+            top = logits.max(dim=1, keepdim=True).values
+            want = (logits == top).int().argmax(dim=1)             # lowest token id among equal maxima
+            torch.cuda.synchronize()
+            greedy = {"greedy_head_us": timed(lambda: head.forward(x)) * 1e3,
+                      "greedy_head_matches_argmax_of_gathered_logits": bool(torch.equal(tok.long(), want)),
+                      "greedy_exchange_bytes_per_gpu": 8 * M}
+            head.close()
         w_bytes_all = n_rows * p["d"] * 2
         flops_all = 2.0 * M * n_rows * p["d"]
         best_ms = total_ms if fused_ms is None else min(total_ms, fused_ms)
@@ -307,7 +374,8 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5):
                                "allgather_bytes_per_gpu": M * cmax * 2,
                                "fused_gather_us": None if fused_ms is None else fused_ms * 1e3,
                                "fused_gather_matches_nccl": fused_equal,
-                               "aggregate_GBps_fused_gather": None if fused_ms is None else w_bytes_all / (fused_ms * 1e-3) / 1e9}
+                               "aggregate_GBps_fused_gather": None if fused_ms is None else w_bytes_all / (fused_ms * 1e-3) / 1e9,
+                               **greedy}
         device.lib.vaicu_linear_plan_destroy(h)
     return out
 
