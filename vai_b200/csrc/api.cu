@@ -772,11 +772,22 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
     t.n_dst = 1u;
     t.ldo = gate ? d.N / 2u : d.N;
     t.col0 = 0u;
+    size_t smem = pl->tc_smem;
     if (spec) {
         t.n_dst = spec->n_dst; t.ldo = spec->ldo; t.col0 = spec->col0;
         for (uint32_t i = 0; i < spec->n_dst; ++i) t.dst[i] = spec->dst[i];
+        if (t.pair && spec->n_dst > 1u) {
+            // stores to peers go out as whole 128-byte row segments: one ring stage less, 16 KB of staging
+            const uint32_t stage_bytes = 128u * 128u + (t.bn / 2u) * 128u;
+            const uint32_t staged_stages = (uint32_t)((kTcMaxSmem - 2048u - 16384u - 128u) / stage_bytes);
+            if (staged_stages >= 3u) {
+                t.staged = 1u;
+                t.stages = staged_stages < t.stages ? staged_stages : t.stages;
+                smem = (size_t)t.stages * stage_bytes + 1024u + 256u + 16384u + 128u;
+            }
+        }
     }
-    VAICU_CUDA(launch_tc_gemm(pl->map_a, pl->map_b, t, pl->tc_swap, pl->tc_grid, pl->tc_smem, s));
+    VAICU_CUDA(launch_tc_gemm(pl->map_a, pl->map_b, t, pl->tc_swap, pl->tc_grid, smem, s));
     if (partial) VAICU_CUDA(launch_splitk_reduce(a, partial, t.splits, s));
     return VAICU_OK;
 }

@@ -716,6 +716,8 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint64_t* acc_empty = acc_full + 2;           // [2], used in the leader
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    // 4 KB per epilogue warp for the staged stores (present when p.staged)
+    uint8_t* staging = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tmem_slot + 2) + 127u) & ~(uintptr_t)127u);
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -815,12 +817,74 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((q * 32u) << 16) + buf * acc_cols;
             const uint32_t m = ta * 2u * TILE_ROWS + rank * TILE_ROWS + row_in_tile;
-            for (uint32_t c0 = 0; c0 < ncols; c0 += 16u) {
-                uint32_t r0[16], r1[16];
-                tmem_ld16(t_row + c0, r0);
-                if (GATE) tmem_ld16(t_row + c0 + half, r1);
-                tmem_ld_wait();
-                store_rows16<GATE>(p, r0, r1, m, tb, c0, z, out_cols, osz);
+            // columns per 128-byte row segment of the output
+            const uint32_t seg_cols = 128u / osz;
+            for (uint32_t c0 = 0; c0 < ncols;) {
+                const uint32_t j_seg = (GATE ? tb * half : tb * bn) + c0;
+                const bool stage_it = p.staged && !p.partial && c0 + seg_cols <= ncols && j_seg + seg_cols <= out_cols &&
+                                      p.o_aligned16 && (((size_t)p.ldo * osz) % 16u == 0u) && (((size_t)(p.col0 + j_seg) * osz) % 16u == 0u);
+                if (!stage_it) {
+                    uint32_t r0[16], r1[16];
+                    tmem_ld16(t_row + c0, r0);
+                    if (GATE) tmem_ld16(t_row + c0 + half, r1);
+                    tmem_ld_wait();
+                    store_rows16<GATE>(p, r0, r1, m, tb, c0, z, out_cols, osz);
+                    c0 += 16u;
+                    continue;
+                }
+                // 1. this thread's row: seg_cols finished values -> its 128-byte line of the warp's staging
+                //    block, 16-byte chunks XOR-swizzled by the row so that the 32 lanes hit distinct banks
+                uint8_t* mine = staging + (size_t)q * 4096u + (size_t)lane * 128u;
+                for (uint32_t g = 0; g < seg_cols; g += 16u) {
+                    uint32_t r0[16], r1[16];
+                    tmem_ld16(t_row + c0 + g, r0);
+                    if (GATE) tmem_ld16(t_row + c0 + g + half, r1);
+                    tmem_ld_wait();
+                    float v[16], u[16];
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
+                    const uint32_t mm = m < p.M ? m : p.M - 1u;          // rows past M compute on a valid row and are not stored
+                    finish_row16<GATE>(p, v, u, mm, j_seg + g, out_cols, 16u);
+                    if (osz == 4u) {
+#pragma unroll
+                        for (uint32_t k4 = 0; k4 < 4u; ++k4) {
+                            const uint32_t chunk = (g / 4u + k4) ^ (lane & 7u);
+                            *reinterpret_cast<float4*>(mine + chunk * 16u) = make_float4(v[4 * k4], v[4 * k4 + 1], v[4 * k4 + 2], v[4 * k4 + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t k8 = 0; k8 < 2u; ++k8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                if (p.o_dtype == VAICU_DTYPE_F16) {
+                                    __half2 h = __floats2half2_rn(v[8 * k8 + 2 * e], v[8 * k8 + 2 * e + 1]);
+                                    w[e] = *reinterpret_cast<uint32_t*>(&h);
+                                } else {
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * k8 + 2 * e], v[8 * k8 + 2 * e + 1]);
+                                    w[e] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                            }
+                            const uint32_t chunk = (g / 8u + k8) ^ (lane & 7u);
+                            *reinterpret_cast<uint4*>(mine + chunk * 16u) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                }
+                __syncwarp();
+                // 2. eight lanes per row, four rows per store instruction: 4 x 128 contiguous bytes
+                const uint32_t m_base = ta * 2u * TILE_ROWS + rank * TILE_ROWS + q * 32u;
+#pragma unroll
+                for (uint32_t it = 0; it < 8u; ++it) {
+                    const uint32_t rr = it * 4u + (lane >> 3), chunk = lane & 7u;
+                    const uint4 val = *reinterpret_cast<const uint4*>(staging + (size_t)q * 4096u + (size_t)rr * 128u + ((chunk ^ (rr & 7u)) * 16u));
+                    if (m_base + rr < p.M) {
+                        const size_t byte_off = ((size_t)(m_base + rr) * p.ldo + p.col0 + j_seg) * osz + (size_t)chunk * 16u;
+                        for (uint32_t d = 0; d < p.n_dst; ++d)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.n_dst == 1u ? p.O : p.dst[d]) + byte_off) = val;
+                    }
+                }
+                __syncwarp();
+                c0 += seg_cols;
             }
             tc_fence_before();
             __syncwarp();

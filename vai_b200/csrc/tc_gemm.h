@@ -37,6 +37,8 @@ struct TcParams {
     // n_dst = 1, ldo = the output width, col0 = 0; a column-split run writes its slab into
     // up to 8 wider destinations at once (its own and its peers' over NVLink).
     uint32_t ldo, col0, n_dst;
+    uint32_t staged;       // CTA-pair kernel: finished tiles go through shared memory so that stores to the
+                           // destinations (peers over NVLink) are whole 128-byte row segments
     void* dst[8];
     float scale;
 };
