@@ -79,3 +79,47 @@ def test_shard_rows_agree_with_the_library():
         for rank in range(world):
             _, b, c = sharded.shard_desc(full, rank, world)
             assert (b, c) == sharded.shard_rows(50257, world, rank)
+
+
+def _row_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(5)
+        M, K, N = 4, 200, 24                     # 200 = 25 units of 8: uneven over 2 and 3 ranks
+        x = rng.standard_normal((M, K)).astype(np.float32)
+        w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+        r = rng.standard_normal((M, N)).astype(np.float32)
+        kb, kc = sharded.shard_k(K, world, rank)
+        ws = sharded.slice_weight_k(w, rank, world)
+        assert ws.shape == (N, kc) and ws.flags["C_CONTIGUOUS"]
+        d = orc.make_desc(M, N, kc)
+        partial = orc.linear_c(d, np.ascontiguousarray(x[:, kb:kb + kc]), ws)
+        t = torch.from_numpy(partial.copy())
+        dist.all_reduce(t)
+        np.save(os.path.join(out_dir, f"row{rank}.npy"), 0.25 * t.numpy() + r)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_row_parallel_split_matches_unsplit(world, tmp_path):
+    """K-split `down` (vai_b200.sharded.RowParallelLinear's host arithmetic): slices of the
+    reduction axis in 16-byte units, partial products per rank, one all-reduce, then scale and
+    residual: equals the unsplit Linear up to fp32 summation order."""
+    slices = [sharded.shard_k(200, world, r) for r in range(world)]
+    assert slices[0][0] == 0 and sum(c for _, c in slices) == 200
+    assert all(b % 8 == 0 for b, _ in slices) and all(slices[i][0] + slices[i][1] == slices[i + 1][0] for i in range(world - 1))
+    assert sharded.shard_k(203, 2, 1) == (104, 99)          # the ragged tail goes to the last rank
+    port = _free_port()
+    mp.spawn(_row_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    rng = np.random.default_rng(5)
+    M, K, N = 4, 200, 24
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    r = rng.standard_normal((M, N)).astype(np.float32)
+    want = orc.linear_f64(x, w, residual=r, scalar_scale=0.25)
+    for rank in range(world):
+        got = np.load(os.path.join(str(tmp_path), f"row{rank}.npy"))
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)

@@ -204,6 +204,82 @@ class FusedGatherLinear(ShardedLinear):
         self._opened = []
 
 
+def shard_k(k, world, rank, align=8):
+    """(begin, count) of rank's slice of the reduction axis K, in multiples of `align`
+    elements (16 bytes of a 16-bit weight row) so that every slice keeps the fast kernels."""
+    units = k // align
+    base, extra = divmod(units, world)
+    begin = (rank * base + min(rank, extra)) * align
+    count = (base + (1 if rank < extra else 0)) * align
+    if rank == world - 1:
+        count = k - begin          # a tail that is not a multiple of `align` goes to the last rank
+    return begin, count
+
+
+def slice_weight_k(w, rank, world):
+    """Rank's columns W[:, k0:k1] of W [N, K] as a contiguous array (row-parallel split)."""
+    b, c = shard_k(w.shape[1], world, rank)
+    part = w[:, b:b + c]
+    return part.contiguous() if hasattr(part, "contiguous") else np.ascontiguousarray(part)
+
+
+class RowParallelLinear:
+    """The second half of a tensor-parallel MLP: `down` split along K.  After a column-split
+    gate|value Linear every rank already holds columns [k0, k1) of the hidden state, which
+    are exactly the activations its K slice of `down` needs, so the hidden state is never
+    gathered: each rank multiplies its slice (fp32 partial output [M, N]) and one all-reduce
+    sums the partials (48 MiB at M = 8192, d = 3072, against 128 MiB for gathering the hidden
+    state).  Bias, residual, epilogue and scale apply after the sum, on every rank alike; only
+    the plain `O = sum + R` form that the models' down projections use is provided here."""
+
+    def __init__(self, device, dist, M, N, K, w_local, w_dtype, residual=False, scalar_scale=1.0):
+        import torch
+
+        from .engine import Dtype
+        self.torch, self.dist, self.dev = torch, dist, device
+        self.rank = dist.get_rank() if dist is not None else 0
+        self.world = dist.get_world_size() if dist is not None else 1
+        self.k_begin, self.k_count = shard_k(K, self.world, self.rank)
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = M, N, self.k_count
+        d.i_dtype = d.w_dtype = int(w_dtype)
+        d.o_dtype = int(Dtype.F32)               # partial sums stay fp32 until after the reduction
+        d.b_dtype = int(Dtype.NONE)
+        d.scalar_scale = 1.0
+        self.desc, self.scale, self.residual = d, float(scalar_scale), residual
+        self.w = w_local
+        h = ctypes.c_void_p()
+        _lib.check(device.lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
+        self.plan = h
+        self.info = _lib.LinearInfo()
+        _lib.check(device.lib.vaicu_linear_plan_info(h, ctypes.byref(self.info)), "info")
+        cuda = torch.device("cuda", device.ordinal)
+        self.ws = torch.empty(max(self.info.workspace_bytes, 256), dtype=torch.uint8, device=cuda)
+        self.partial = torch.empty((M, N), dtype=torch.float32, device=cuda)
+
+    def local_forward(self, x_slice):
+        stream = self.torch.cuda.current_stream().cuda_stream
+        _lib.check(self.dev.lib.vaicu_linear_run(self.plan, stream, x_slice.data_ptr(), self.w.data_ptr(), None, None,
+                                                 self.partial.data_ptr(), self.ws.data_ptr()), "vaicu_linear_run")
+        return self.partial
+
+    def forward(self, x_slice, residual=None):
+        """x_slice: this rank's columns [k0, k1) of the activations, contiguous [M, k_count]."""
+        out = self.local_forward(x_slice)
+        if self.world > 1:
+            self.dist.all_reduce(out)
+        if self.scale != 1.0:
+            out.mul_(self.scale)
+        if residual is not None:
+            out.add_(residual)
+        return out
+
+    def close(self):
+        if self.plan:
+            self.dev.lib.vaicu_linear_plan_destroy(self.plan)
+            self.plan = None
+
+
 class ShardedGreedyHead:
     """Vocabulary-split lm_head followed by greedy sampling without gathering logits: every
     rank runs its slab of the head, reduces it to one (max, token) candidate per row with
@@ -376,6 +452,26 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5):
                                "fused_gather_matches_nccl": fused_equal,
                                "aggregate_GBps_fused_gather": None if fused_ms is None else w_bytes_all / (fused_ms * 1e-3) / 1e9,
                                **greedy}
+        if name == "gate_up":
+            # the natural tensor-parallel MLP: this rank's hidden columns feed its K slice of `down`
+            # directly; one all-reduce of [M, d] replaces the all-gather of the hidden state
+            kb, kc = shard_k(p["ffn"], world, rank)
+            if kc == lin.count and kb == lin.begin:
+                w_down = (torch.randn(p["d"], kc, generator=gen) * 0.02).to(torch.bfloat16).to(cuda)
+                down = RowParallelLinear(device, dist, M, p["d"], p["ffn"], w_down, Dtype.BF16)
+
+                def mlp_local():
+                    lin.local_forward(x)
+                    down.local_forward(lin.slab)
+
+                def mlp():
+                    lin.local_forward(x)
+                    down.forward(lin.slab)
+
+                out["layers"]["mlp_column_then_row_parallel"] = {
+                    "down_K_per_gpu": kc, "allreduce_bytes": M * p["d"] * 4,
+                    "gate_up_plus_down_local_us": timed(mlp_local) * 1e3, "with_allreduce_us": timed(mlp) * 1e3}
+                down.close()
         device.lib.vaicu_linear_plan_destroy(h)
     return out
 
