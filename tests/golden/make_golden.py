@@ -40,6 +40,7 @@ def _stub_pyvai():
     nodes.ArgmaxNode = lambda **kw: {"node": "argmax", **kw}
     nodes.RmsNormNode = lambda **kw: {"node": "rms_norm", **kw}
     nodes.LayerNormNode = lambda **kw: {"node": "layer_norm", **kw}
+    nodes.GatedMulNode = lambda **kw: {"node": "gated_mul", **kw}
     pyvai.nodes = nodes
     sys.modules["pyvai"] = pyvai
     sys.modules["pyvai.nodes"] = nodes
@@ -51,6 +52,7 @@ def main(ref_root):
     sys.path.insert(0, os.path.join(ref_root, "python", "tests", "nodes"))
     import node_check
     import test_argmax
+    import test_gated_mul
     import test_layer_norm
     import test_rms_norm
     import test_linear
@@ -134,6 +136,15 @@ def main(ref_root):
                "test_layer_norm_coeffs_as_inputs"):
         getattr(test_layer_norm, fn)()
         record(fn.replace("test_", ""))
+
+    # the consumer of a gate|value Linear: GatedMul (python/tests/nodes/test_gated_mul.py); this
+    # repository folds it into the Linear's epilogue (gate_fuse), so the cases pin that epilogue
+    for mark in test_gated_mul.test_gated_mul.pytestmark:
+        if mark.name != "parametrize":
+            continue
+        for activation in mark.args[1]:
+            test_gated_mul.test_gated_mul(activation)
+            record(f"gated_mul_{activation}")
 
     here = os.path.dirname(os.path.abspath(__file__))
     np.savez_compressed(os.path.join(here, "linear_golden.npz"), **arrays)
