@@ -301,6 +301,19 @@ VAICU_API int vaicu_argmax_pairs_run(vaicu_stream_t stream, const void* logits, 
 VAICU_API int vaicu_argmax_merge_run(vaicu_stream_t stream, const float* vals, const void* idx_u32, uint32_t groups,
                                      size_t group_stride, uint32_t M, float* out_val, void* out_u32);
 
+/* Top-k sampling over logits [M, N]: vAi's TopKSampling node (vai/nodes/topk-sampling.h:9-31,
+ * vai/shaders/topk-sampling.comp): keep the k largest logits of each row ranked by (value
+ * descending, index ascending), softmax over them at `temperature` (floored at 1e-6), sample by
+ * inverse CDF with the uniform *u_device in [0, 1) — device memory, so that a recorded launch
+ * reads each step's value, as the reference reads its host-visible uniform buffer.
+ *   k          1 .. 128 (TopKSampling::maxK); k > N uses N
+ *   workspace  vaicu_topk_workspace_bytes(M, N, k) bytes (0 for rows of at most 8192 columns)
+ *   out_u32    [M] sampled indices
+ * VAICU_ERR_TOO_LARGE when ceil(N / 2048) * k exceeds 8192 candidates per row. */
+VAICU_API int vaicu_topk_workspace_bytes(uint32_t M, uint32_t N, uint32_t k, size_t* out_bytes);
+VAICU_API int vaicu_topk_sample_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, uint32_t k,
+                                    float temperature, const float* u_device, void* workspace, void* out_u32);
+
 /* Column-split helper for the multi-GPU layout: the desc of rank `rank` of
  * `world` when W's rows (output columns) are split evenly; for gate_fuse the
  * split is per half.  Fills row offsets into W / bias for that rank. No

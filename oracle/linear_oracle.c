@@ -444,6 +444,50 @@ int vai_oracle_layer_norm(const void* in, const void* scale, const void* shift, 
     return 0;
 }
 
+/* TopKSampling — parity unpinned: the reference holds no test, fixture or golden vector for this
+ * node, so this restatement is checked only against a float64 formulation of the same rules.
+ * (vai/shaders/topk-sampling.comp:76-79, 237-258): the k best of each row in
+ * strict (value descending, index ascending) order, found here by k selection sweeps; then
+ * invT = 1 / max(temperature, 1e-6), Z = sum exp((v_r - v_0) * invT) in rank order, and the
+ * first rank whose running sum reaches u * Z (rank 0 if none does).  fp32 throughout, expf
+ * as the shader's exp.  `in` is fp32 (the caller widens 16-bit logits). */
+int vai_oracle_topk_sample(const float* in, uint32_t M, uint32_t N, uint32_t K, float temperature, float u, uint32_t* out)
+{
+    const uint32_t k = K < N ? K : N;
+    if (k == 0 || k > 128u) return 1;
+    float top_v[128];
+    uint32_t top_i[128];
+    for (uint32_t row = 0; row < M; ++row) {
+        const float* x = in + (size_t)row * N;
+        for (uint32_t r = 0; r < k; ++r) {
+            float bv = -3.4028235e38f;
+            uint32_t bi = 0xFFFFFFFFu;
+            for (uint32_t i = 0; i < N; ++i) {
+                const float v = x[i];
+                /* ranked strictly below the previous winner ... */
+                if (r > 0 && !(v < top_v[r - 1] || (v == top_v[r - 1] && i > top_i[r - 1]))) continue;
+                /* ... and the best of those */
+                if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+            }
+            top_v[r] = bv;
+            top_i[r] = bi;
+        }
+        const float inv_t = 1.0f / (temperature > 1e-6f ? temperature : 1e-6f);
+        const float m = top_v[0];
+        float z = 0.0f;
+        for (uint32_t r = 0; r < k; ++r) z += expf((top_v[r] - m) * inv_t);
+        const float target = u * z;
+        float cum = 0.0f;
+        uint32_t chosen = top_i[0];
+        for (uint32_t r = 0; r < k; ++r) {
+            cum += expf((top_v[r] - m) * inv_t);
+            if (cum >= target) { chosen = top_i[r]; break; }
+        }
+        out[row] = chosen;
+    }
+    return 0;
+}
+
 int vai_oracle_num_threads(void)
 {
 #ifdef _OPENMP

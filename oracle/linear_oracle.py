@@ -237,3 +237,25 @@ def layer_norm_c(x, scale, shift=None, residual=None, eps=1e-5, i_dtype=F32, w_d
     if rc != 0:
         raise RuntimeError(f"oracle returned {rc}")
     return out
+
+
+def topk_sample_c(logits, k, temperature, u):
+    """The C restatement of vAi's top-k sampling shader on fp32 logits [M, N]; returns uint32 [M]."""
+    a = np.ascontiguousarray(logits, dtype=np.float32)
+    out = np.empty(a.shape[0], dtype=np.uint32)
+    rc = lib().vai_oracle_topk_sample(_ptr(a), ctypes.c_uint32(a.shape[0]), ctypes.c_uint32(a.shape[1]), ctypes.c_uint32(k),
+                                      ctypes.c_float(temperature), ctypes.c_float(u), _ptr(out))
+    if rc != 0:
+        raise RuntimeError(f"oracle returned {rc}")
+    return out
+
+
+def topk_probabilities_f64(logits, k, temperature):
+    """float64 view of the same distribution: (indices [M, k] in rank order, probabilities
+    [M, k]); ties rank the lower index first."""
+    a = np.asarray(logits, dtype=np.float64)
+    k = min(k, a.shape[1])
+    order = np.lexsort((np.arange(a.shape[1])[None, :].repeat(a.shape[0], 0), -a), axis=1)[:, :k]
+    top = np.take_along_axis(a, order, axis=1)
+    e = np.exp((top - top[:, :1]) / max(temperature, 1e-6))
+    return order.astype(np.uint32), e / e.sum(axis=1, keepdims=True)

@@ -1,0 +1,104 @@
+"""TopKSampling, the sampling consumer of the lm_head Linear (vAi vai/nodes/topk-sampling.h,
+vai/shaders/topk-sampling.comp).  The reference ships no test or golden vector for this node,
+so the C restatement of the shader is checked against an independent float64 formulation of
+the same distribution (parity unpinned), and the CUDA node against the restatement, exactly:
+the sample is an index."""
+import numpy as np
+import pytest
+
+from oracle import linear_oracle as orc
+
+US = [0.0, 0.013, 0.25, 0.5, 0.77, 0.93, 0.9990234]
+
+
+def _expected_from_f64(x, k, temperature, u):
+    """Index by float64 CDF lookup, or None where u * Z falls within rounding of a CDF step."""
+    idx, p = orc.topk_probabilities_f64(x, k, temperature)
+    cdf = np.cumsum(p, axis=1)
+    out = []
+    for r in range(x.shape[0]):
+        j = int(np.searchsorted(cdf[r], u, side="left"))
+        j = min(j, idx.shape[1] - 1)
+        near = np.abs(cdf[r] - u).min() < 1e-5
+        out.append(None if near else int(idx[r, j]))
+    return out
+
+
+@pytest.mark.parametrize("k,temperature", [(40, 1.0), (5, 0.7), (128, 1.5), (1, 1.0)])
+def test_oracle_samples_the_float64_distribution(k, temperature):
+    rng = np.random.default_rng(k)
+    x = (rng.standard_normal((4, 3000)) * 2).astype(np.float32)
+    for u in US:
+        got = orc.topk_sample_c(x, k, temperature, u)
+        for r, want in enumerate(_expected_from_f64(x, k, temperature, u)):
+            if want is not None:
+                assert int(got[r]) == want, (k, temperature, u, r)
+
+
+def test_oracle_edge_rules():
+    x = np.zeros((2, 20), dtype=np.float32)
+    x[0, [3, 11, 7]] = 5.0                          # equal logits rank by index: 3, 7, 11
+    x[1, 4] = 1.0
+    assert list(orc.topk_sample_c(x, 3, 1.0, 0.0)) == [3, 4]
+    assert int(orc.topk_sample_c(x, 3, 1.0, 0.5)[0]) == 7          # three equal thirds: 0.5 lands in the second
+    assert int(orc.topk_sample_c(x, 3, 1.0, 0.9)[0]) == 11
+    assert int(orc.topk_sample_c(x, 40, 1e-9, 0.99)[1]) == 4        # temperature floor (1e-6): all mass on the maximum
+    assert int(orc.topk_sample_c(x, 40, 1e-9, 0.99)[0]) == 11       # ... shared equally by equal maxima
+    rng = np.random.default_rng(1)
+    y = rng.standard_normal((3, 7)).astype(np.float32)
+    np.testing.assert_array_equal(orc.topk_sample_c(y, 128, 1.0, 0.0), y.argmax(axis=1))   # k > N uses N
+    np.testing.assert_array_equal(orc.topk_sample_c(y, 1, 1.0, 0.999), y.argmax(axis=1))
+
+
+def _net(k, temperature):
+    import vai_b200
+    from vai_b200 import nodes
+
+    class Net(vai_b200.NeuralNet):
+        def __init__(self):
+            super().__init__()
+            self.s = nodes.TopKSamplingNode(k=k, temperature=temperature)
+            self.input("in0") - self.s - self.output("out0")
+
+    return Net()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N", [(1, 128256), (3, 50257), (4, 50), (2, 8192), (2, 8200)])
+@pytest.mark.parametrize("k,temperature", [(40, 1.0), (128, 0.8), (1, 1.0)])
+def test_topk_node_matches_restatement(M, N, k, temperature, device):
+    """Single-launch rows (N <= 8192) and two-stage rows, several uniforms through ONE
+    recording: set_uniform between replays changes the sample as the restatement says."""
+    from vai_b200 import Tensor
+    rng = np.random.default_rng(M + N + k)
+    x = (rng.standard_normal((M, N)) * 2).astype(np.float32)
+    x[0, N // 3] = x[0, N // 2] = x[0].max() + 1.0          # a tie at the top, in different slices
+    net = _net(k, temperature)
+    t = Tensor.from_numpy(x)
+    for u in US:
+        net.s.set_uniform(u)
+        got = net(t).to_u32()
+        np.testing.assert_array_equal(got, orc.topk_sample_c(x, k, temperature, u), err_msg=f"u={u}")
+    assert len(net._recordings) == 1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_topk_node_16bit_logits(dtype, device):
+    from gpu_util import DT, seen
+    from vai_b200 import Tensor
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal((2, 20000)) * 3).astype(np.float32)
+    vals = seen(x, DT[dtype])            # many ties after rounding: the index rule decides
+    net = _net(40, 1.0)
+    for u in (0.1, 0.6, 0.95):
+        net.s.set_uniform(u)
+        np.testing.assert_array_equal(net(Tensor.from_numpy(x, dtype=DT[dtype])).to_u32(), orc.topk_sample_c(vals, 40, 1.0, u))
+
+
+def test_topk_node_rejects_bad_k():
+    from vai_b200 import nodes
+    with pytest.raises(ValueError):
+        nodes.TopKSamplingNode(k=0)
+    with pytest.raises(ValueError):
+        nodes.TopKSamplingNode(k=129)

@@ -924,6 +924,31 @@ int vaicu_argmax_merge_run(vaicu_stream_t stream, const float* vals, const void*
     return VAICU_OK;
 }
 
+int vaicu_topk_workspace_bytes(uint32_t M, uint32_t N, uint32_t k, size_t* out_bytes)
+{
+    if (!out_bytes || M == 0 || N == 0 || k == 0 || k > 128u) return VAICU_ERR_INVALID_VALUE;
+    const uint32_t G = topk_groups(N);
+    *out_bytes = G == 1u ? 0 : align_up((size_t)M * G * (k < N ? k : N) * 8u, 256u);
+    return VAICU_OK;
+}
+
+int vaicu_topk_sample_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, uint32_t k,
+                          float temperature, const float* u_device, void* workspace, void* out_u32)
+{
+    if (!logits || !out_u32 || !u_device || M == 0 || N == 0 || k == 0 || k > 128u) return VAICU_ERR_INVALID_VALUE;
+    if (!valid_dtype(dtype)) return VAICU_ERR_INVALID_VALUE;
+    const uint32_t G = topk_groups(N);
+    if (G > 1u && !workspace) return VAICU_ERR_WORKSPACE;
+    // stage 2 holds G * k candidates in 1024 lists of 8
+    if (G > 1u && (uint64_t)G * (k < N ? k : N) > 8192u) return VAICU_ERR_TOO_LARGE;
+    if ((reinterpret_cast<uintptr_t>(logits) & (dtype_size(dtype) - 1u)) || (reinterpret_cast<uintptr_t>(out_u32) & 3u) ||
+        (reinterpret_cast<uintptr_t>(u_device) & 3u) || (reinterpret_cast<uintptr_t>(workspace) & 7u))
+        return VAICU_ERR_ALIGNMENT;
+    VAICU_CUDA(launch_topk_sample(logits, dtype, M, N, k, temperature, u_device, workspace, reinterpret_cast<uint32_t*>(out_u32),
+                                  (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
 int vaicu_linear_shard_desc(const vaicu_linear_desc* full, int rank, int world, vaicu_linear_desc* shard,
                             uint32_t* w_row_begin, uint32_t* w_row_count)
 {

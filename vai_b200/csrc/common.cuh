@@ -136,6 +136,9 @@ cudaError_t launch_cast_f32_to_16(const float* src, void* dst, int dst_dtype, si
 
 cudaError_t launch_argmax(const void* in, int dtype, uint32_t M, uint32_t N, uint32_t* out, cudaStream_t stream);
 uint32_t argmax_parts(uint32_t N);
+uint32_t topk_groups(uint32_t N);
+cudaError_t launch_topk_sample(const void* logits, int dtype, uint32_t M, uint32_t N, uint32_t K, float temperature,
+                               const float* u, void* workspace, uint32_t* out, cudaStream_t stream);
 cudaError_t launch_argmax_pairs(const void* in, int dtype, uint32_t M, uint32_t N, size_t ld, uint32_t index_base, void* workspace,
                                 float* out_val, uint32_t* out_idx, cudaStream_t stream);
 cudaError_t launch_argmax_merge(const float* vals, const uint32_t* idxs, uint32_t groups, size_t group_stride, uint32_t M,

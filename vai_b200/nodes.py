@@ -5,6 +5,8 @@ kernels through the C ABI.  Python-facing signature as in the reference's bindin
 """
 import ctypes
 
+import numpy as np
+
 from . import _lib
 from .engine import (INPUT, OUTPUT, PERSISTENT, TEMPORARY, Dtype, Epilogue, Node, ResidualOrder, Tensor)
 
@@ -223,6 +225,67 @@ class ArgmaxNode(Node):
             _lib.check(run(stream, xp, dt, M, N, op), "vaicu_argmax_run")
 
         launch.kernel_launches = 1
+        return launch
+
+
+class TopKSamplingNode(Node):
+    """Row-wise top-k sampling (vAi vai/nodes/topk-sampling.h:9-31): in0 [..., N] logits ->
+    out0 [...] raw uint32 indices in 4-byte slots.  Keeps the k largest logits of each row,
+    softmax over them at `temperature`, inverse-CDF sample with the uniform given by
+    set_uniform(u) before each forward (the reference's setUniform).  The uniform lives in a
+    4-byte device buffer that the recorded launch reads, so replays see the new value."""
+
+    MAX_K = 128
+
+    def __init__(self, k=40, temperature=1.0):
+        super().__init__()
+        if not 1 <= int(k) <= self.MAX_K:
+            raise ValueError(f"k must be in 1..{self.MAX_K}")
+        self.k, self.temperature = int(k), float(temperature)
+        self.add_slot("out0", OUTPUT)
+        self.add_slot("in0", INPUT)
+        self.add_slot("partial", TEMPORARY)
+        self._uniform = None          # DeviceBuffer of one float
+        self._u_host = 0.0
+
+    def _device(self):
+        from .engine import Device
+        return self.net.device if self.net is not None else Device.default()
+
+    def set_uniform(self, u):
+        """The uniform in [0, 1) used by the next forward."""
+        self._u_host = float(u)
+        if self._uniform is not None:
+            self._uniform.upload(np.array([self._u_host], dtype=np.float32))
+
+    def prepare(self):
+        x = self["in0"]
+        if not x.valid_shape() or len(x.shape) < 2:
+            raise ValueError("in0 must have at least two axes")
+        rows = x.num_elements() // x.shape[-1]
+        self.slots["out0"] = Tensor(tuple(x.shape[:-1]), Dtype.F32)
+        dev = self._device()
+        ws = ctypes.c_size_t()
+        _lib.check(dev.lib.vaicu_topk_workspace_bytes(rows, x.shape[-1], self.k, ctypes.byref(ws)), "vaicu_topk_workspace_bytes")
+        self.slots["partial"] = Tensor((ws.value // 4,), Dtype.F32) if ws.value else Tensor()
+
+    def bind(self):
+        from .engine import DeviceBuffer
+        dev = self._device()
+        if self._uniform is None:
+            self._uniform = DeviceBuffer(dev, 4)
+        self._uniform.upload(np.array([self._u_host], dtype=np.float32))
+        x, o = self["in0"], self["out0"]
+        rows, n = x.num_elements() // x.shape[-1], x.shape[-1]
+        xp, op, up, dt = x.ptr, o.ptr, self._uniform.ptr, int(x.dtype)
+        ws = self["partial"].ptr if self["partial"].valid_shape() else None
+        k, temp = self.k, self.temperature
+        run = dev.lib.vaicu_topk_sample_run
+
+        def launch(stream):
+            _lib.check(run(stream, xp, dt, rows, n, k, temp, up, ws, op), "vaicu_topk_sample_run")
+
+        launch.kernel_launches = 2 if ws else 1
         return launch
 
 
