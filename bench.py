@@ -301,14 +301,16 @@ def main():
     e2e_ms = max_over_ranks(dist, e2e_ms)
     e2e_tok_s = world * args.steps / (e2e_ms / 1e3)
 
-    # Column split of the large-N layers over the GPUs (Gemma-3-4B-shaped lm_head and
-    # gate|value Linear at batch 64, NCCL all-gather of the output slabs): reported beside
-    # the headline, never part of it.
+    # Column split of the large-N layers over the GPUs (Gemma-3-4B-shaped lm_head and gate|value
+    # Linear at batch 64; Llama-3.2-3B-shaped ones at M = 8192): local slab, NCCL all-gather,
+    # gather fused into the GEMM epilogue, greedy head, column-then-row-parallel MLP.  Reported
+    # beside the headline, never part of it.
     sharded = None
     if world > 1:
         try:
             from vai_b200 import sharded as sharded_mod
-            sharded = sharded_mod.bench_sharded(dev, dist, "gemma-3-4b", 64, iters=10, warmup=3)
+            sharded = {"decode_gemma3_4b_m64": sharded_mod.bench_sharded(dev, dist, "gemma-3-4b", 64, iters=10, warmup=3),
+                       "prefill_llama32_3b_m8192": sharded_mod.bench_sharded(dev, dist, "llama-3.2-3b", 8192, iters=5, warmup=2)}
         except Exception as e:   # a report only
             sharded = {"error": str(e)[:200]}
 

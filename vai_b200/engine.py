@@ -399,6 +399,7 @@ class NeuralNet:
         self._recordings = {}
         self._dirty = False
         self._pinned_ptrs = []
+        self._input_names = self._input_order = None
         self.h2d_bytes = self.d2h_bytes = 0
         NeuralNet._tls.net = self
 
@@ -575,13 +576,17 @@ class NeuralNet:
         return np.frombuffer(buf, dtype=np_dtype, count=int(np.prod(shape))).reshape(shape), p
 
     def __call__(self, *args, **kwargs):
-        names = list(self._inputs)
-        fed = dict(zip(names, args))
-        fed.update(kwargs)
-        if set(fed) != set(names):
-            raise ValueError(f"inputs {sorted(fed)} do not match the net's {sorted(names)}")
+        names = self._input_names
+        if names is None or len(names) != len(self._inputs):
+            names = self._input_names = sorted(self._inputs)
+            self._input_order = list(self._inputs)
+        fed = dict(zip(self._input_order, args))
+        if kwargs:
+            fed.update(kwargs)
+        if len(fed) != len(names) or any(k not in fed for k in names):
+            raise ValueError(f"inputs {sorted(fed)} do not match the net's {names}")
         lib = self.device.lib
-        key = tuple((k, fed[k].shape, int(fed[k].dtype)) for k in sorted(fed))
+        key = tuple([(k, fed[k].shape, fed[k].dtype) for k in names])
         if self._dirty:           # a parameter or a wire changed: every recording is stale
             self._drop_recordings()
             self._dirty = False
@@ -590,6 +595,8 @@ class NeuralNet:
             self._upload_params()
             rec = self._record(fed)
             rec.calls = 0
+            rec.h2d_bytes = sum(v.nbytes for v, _ in rec.stage_in.values())
+            rec.d2h_bytes = sum(v.nbytes for v, _ in rec.stage_out.values())
             self._recordings[key] = rec
         for name, t in fed.items():
             np.copyto(rec.stage_in[name][0], t.host.reshape(rec.stage_in[name][0].shape))
@@ -605,8 +612,7 @@ class NeuralNet:
         if rec.calls % 256 == 0:
             self.device.check_status()
         rec.calls += 1
-        self.h2d_bytes = sum(v.nbytes for v, _ in rec.stage_in.values())
-        self.d2h_bytes = sum(v.nbytes for v, _ in rec.stage_out.values())
+        self.h2d_bytes, self.d2h_bytes = rec.h2d_bytes, rec.d2h_bytes
         outs = {}
         for name, t in rec.outputs.items():
             host = Tensor(t.shape, t.dtype)
