@@ -11,6 +11,7 @@ using vai::node::Argmax;
 using vai::node::LayerNorm;
 using vai::node::Linear;
 using vai::node::RmsNorm;
+using vai::node::TopKSampling;
 
 static int fails = 0;
 #define EXPECT(cond)                                                                          \
@@ -148,6 +149,35 @@ static void norm_head_on_gpu(bool layer)
     EXPECT(worst < 1e-4);
 }
 
+// Linear -> TopKSampling with k = 1 is greedy decoding whatever the uniform; with k = 3 and three
+// equal top logits the uniform picks among them in index order.
+static void topk_on_gpu()
+{
+    const uint32_t M = 2, D = 8, V = 64;
+    std::vector<float> x(M * D, 0.0f), w(V * D, 0.0f);
+    for (uint32_t m = 0; m < M; ++m) x[m * D + m] = 1.0f;      // row m of x selects column m of W^T
+    for (uint32_t n = 0; n < V; ++n) { w[n * D + 0] = 0.01f * n; w[n * D + 1] = (n == 5 || n == 9 || n == 40) ? 3.0f : 0.0f; }
+    initVAIEngine(0);
+    NeuralNet net({.wDefaultDtype = Dtype::Fp32});
+    Linear head({.inDim = D, .outDim = V});
+    TopKSampling pick({.k = 3, .temperature = 1.0f});
+    net.input("x") - head - pick - net.output("token");
+    net.finish();
+    head["weight"] = Tensor({V, D}, Dtype::Fp32); head["weight"].upload(w.data());
+    vaicu_device_synchronize(deviceHandle());
+    const float us[3] = {0.1f, 0.5f, 0.9f};
+    const uint32_t want1[3] = {5, 9, 40};
+    for (int i = 0; i < 3; ++i) {
+        pick.setUniform(us[i]);
+        auto out = net({{"x", HostTensor::fromFloats({M, D}, x)}});
+        uint32_t token[M];
+        std::memcpy(token, out.at("token").bytes.data(), sizeof(token));
+        EXPECT(token[1] == want1[i]);                         // three equal logits: thirds of the unit interval
+        EXPECT(token[0] >= V - 3);                            // row 0: logits rise with n, the sample is one of the top 3
+    }
+    EXPECT(net.recordingCount() == 1);
+}
+
 int main(int argc, char** argv)
 {
     wiring();
@@ -156,6 +186,7 @@ int main(int argc, char** argv)
         mlp_on_gpu(false);
         norm_head_on_gpu(true);
         norm_head_on_gpu(false);
+        topk_on_gpu();
     }
     std::printf(fails ? "FAILED (%d)\n" : "ok\n", fails);
     return fails ? 1 : 0;

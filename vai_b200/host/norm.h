@@ -1,5 +1,6 @@
-// vai::node::RmsNorm, LayerNorm and Argmax on the CUDA backend: the nodes on either side
-// of a Linear (vAi vai/nodes/rms-norm.h:9-60, layer-norm.h:9-70, argmax.h:9-40), with the
+// vai::node::RmsNorm, LayerNorm, Argmax and TopKSampling on the CUDA backend: the nodes on either
+// side of a Linear (vAi vai/nodes/rms-norm.h:9-60, layer-norm.h:9-70, argmax.h:9-40,
+// topk-sampling.h:9-60), with the
 // reference's Config fields and slot names, over the C ABI.
 #ifndef VAI_B200_HOST_NORM_H
 #define VAI_B200_HOST_NORM_H
@@ -113,6 +114,57 @@ public:
                                (*this)["out0"].devicePtr()),
               "vaicu_argmax_run");
     }
+};
+
+// Top-k sampling (topk-sampling.h:33-57): out0 = one raw uint32 index per row; the uniform is
+// refreshed with setUniform() before each forward and lives in a 4-byte device buffer that the
+// recorded launch reads.
+class TopKSampling : public vai::Node
+{
+public:
+    struct Config {
+        uint32_t k = 40;
+        float temperature = 1.0f;
+    } config_;
+    static constexpr uint32_t maxK = 128;
+
+    TopKSampling() : TopKSampling(Config()) {}
+    explicit TopKSampling(Config config) : config_(config)
+    {
+        if (config_.k == 0 || config_.k > maxK) throw std::invalid_argument("k must be in 1..128");
+        addSlot("out0", NodeSlot::output);
+        addSlot("in0", NodeSlot::input);
+        addSlot("partial", NodeSlot::temporary);
+    }
+    void setUniform(float u)
+    {
+        if (!uniform_.gpuBufferBound()) uniform_ = Tensor({1}, Dtype::Fp32);
+        uniform_.upload(&u);
+        vaicu_device_synchronize(deviceHandle());      // the 4 bytes come from the caller's stack
+    }
+    void prepare() override
+    {
+        const Tensor& in = (*this)["in0"];
+        if (!in.validShape() || in.shape().size() < 2) throw std::invalid_argument("in0 must have at least two axes");
+        std::vector<uint32_t> rows(in.shape().begin(), in.shape().end() - 1);
+        (*this)["out0"] = Tensor(rows, Dtype::Fp32);
+        size_t ws = 0;
+        check(vaicu_topk_workspace_bytes(outerSize(in.shape()), in.shape().back(), config_.k, &ws), "vaicu_topk_workspace_bytes");
+        (*this)["partial"] = ws ? Tensor({(uint32_t)(ws / 4)}, Dtype::Fp32) : Tensor();
+        if (!uniform_.gpuBufferBound()) setUniform(0.0f);
+    }
+    void run(vaicu_stream_t stream) override
+    {
+        const Tensor& in = (*this)["in0"];
+        const Tensor& partial = (*this)["partial"];
+        check(vaicu_topk_sample_run(stream, in.devicePtr(), (int)in.dtype(), outerSize(in.shape()), in.shape().back(), config_.k,
+                                    config_.temperature, static_cast<const float*>(uniform_.devicePtr()),
+                                    partial.validShape() ? partial.devicePtr() : nullptr, (*this)["out0"].devicePtr()),
+              "vaicu_topk_sample_run");
+    }
+
+private:
+    Tensor uniform_;
 };
 
 }   // namespace vai::node
