@@ -275,7 +275,8 @@ class Node:
     def __init__(self):
         self.slots = {}
         self.slot_types = {}
-        self.links = {}          # input slot -> (producer node, producer slot)
+        self.links = {}          # input slot -> (producer node, producer slot): the first producer wired
+        self.producers = {}      # input slot -> every producer wired (two only where a gate's branches merge)
         self.o_dtype = Dtype.NONE
         self.net = NeuralNet._current()
         if self.net is not None:
@@ -331,7 +332,14 @@ class Flow:
 
     def __sub__(self, other):
         nxt = other if isinstance(other, Flow) else Flow(other)
-        nxt.node.links[nxt.in_slot] = (self.node, self.out_slot)
+        if nxt.in_slot not in nxt.node.slots or self.out_slot not in self.node.slots:
+            raise KeyError(f"no such slot: {self.out_slot} -> {nxt.in_slot}")
+        srcs = nxt.node.producers.setdefault(nxt.in_slot, [])
+        if (self.node, self.out_slot) not in srcs:
+            srcs.append((self.node, self.out_slot))
+        nxt.node.links[nxt.in_slot] = srcs[0]
+        if nxt.node.net is not None:
+            nxt.node.net._dirty = True
         return nxt
 
 
@@ -356,6 +364,37 @@ class OutputNode(Node):
 
     def prepare(self):
         pass
+
+    def bind(self):
+        return lambda stream: None
+
+
+class GateNode(Node):
+    """Conditional branch without computation (vAi vai/nodes/gate.h:9-60): `then` and `else`
+    both alias in0; one branch is recorded per recording, the engine leaves out every node that
+    only the closed branch reaches, and a node both branches reach (the merge point, where two
+    producers may share an input slot, and everything past it) is kept.  The condition is host
+    state: set_open() invalidates the recordings."""
+
+    def __init__(self):
+        super().__init__()
+        self.add_slot("in0", INPUT)
+        self.add_slot("then", OUTPUT)
+        self.add_slot("else", OUTPUT)
+        self._open = True
+
+    def is_open(self):
+        return self._open
+
+    def set_open(self, is_open):
+        if bool(is_open) != self._open:
+            self._open = bool(is_open)
+            if self.net is not None:
+                self.net._dirty = True
+
+    def prepare(self):
+        self.slots["then"] = self.slots["in0"]
+        self.slots["else"] = self.slots["in0"]
 
     def bind(self):
         return lambda stream: None
@@ -418,9 +457,10 @@ class NeuralNet:
         indeg = {n: 0 for n in self._nodes}
         users = {n: [] for n in self._nodes}
         for n in self._nodes:
-            for src, _ in n.links.values():
-                indeg[n] += 1
-                users[src].append(n)
+            for srcs in n.producers.values():
+                for src, _ in srcs:
+                    indeg[n] += 1
+                    users[src].append(n)
         ready = [n for n in self._nodes if indeg[n] == 0]
         order = []
         while ready:
@@ -432,7 +472,75 @@ class NeuralNet:
                     ready.append(u)
         if len(order) != len(self._nodes):
             raise RuntimeError("the graph has a cycle")
+        self._check_fan_in(order)
         return order
+
+    def _check_fan_in(self, order):
+        """Two producers may share an input slot only where one gate's two branches meet
+        (vAi vai/engine/graph-controller.h:66-70): per node, which gate branches reach it."""
+        gates = [n for n in order if isinstance(n, GateNode)]
+        bit = {g: 1 << i for i, g in enumerate(gates)}
+        then_bits, else_bits = {}, {}
+        for n in order:
+            t = e = 0
+            for srcs in n.producers.values():
+                for src, src_slot in srcs:
+                    t |= then_bits[src]
+                    e |= else_bits[src]
+                    if isinstance(src, GateNode):
+                        if src_slot == "then":
+                            t |= bit[src]
+                        elif src_slot == "else":
+                            e |= bit[src]
+            then_bits[n], else_bits[n] = t, e
+        for n in order:
+            for slot, srcs in n.producers.items():
+                if len(srcs) == 1:
+                    continue
+
+                def side(src, src_slot):
+                    t, e = then_bits[src], else_bits[src]
+                    if isinstance(src, GateNode):
+                        t |= bit[src] if src_slot == "then" else 0
+                        e |= bit[src] if src_slot == "else" else 0
+                    return t, e
+
+                ok = False
+                if len(srcs) == 2:
+                    (t0, e0), (t1, e1) = side(*srcs[0]), side(*srcs[1])
+                    ok = bool((t0 & ~e0) & (e1 & ~t1)) or bool((t1 & ~e1) & (e0 & ~t0))
+                if not ok:
+                    raise RuntimeError(f"slot {slot} has {len(srcs)} producers that are not the two branches of one gate")
+
+    def _live(self, order, fed_names):
+        """What this recording keeps (vAi graph-controller.h:13-32): an input node is live when
+        it is fed, a gate's branch when the gate is live and set that way, any other node when
+        every wired input slot has a live producer.  Returns {node: {slot: live producer}}."""
+        chosen = {}
+
+        def out_live(src, src_slot):
+            if src not in chosen:
+                return False
+            if isinstance(src, GateNode):
+                return (src_slot == "then") == src.is_open() if src_slot in ("then", "else") else True
+            return True
+
+        for n in order:
+            if isinstance(n, InputNode):
+                if n.name in fed_names:
+                    chosen[n] = {}
+                continue
+            picks = {}
+            alive = True
+            for slot, srcs in n.producers.items():
+                live = [p for p in srcs if out_live(*p)]
+                if not live:
+                    alive = False
+                    break
+                picks[slot] = live[0]
+            if alive:
+                chosen[n] = picks
+        return chosen
 
     def _upload_params(self):
         # persistent slots -> device in the dtype their tensor carries; a slot the
@@ -452,11 +560,13 @@ class NeuralNet:
             dev_t.buffer = self.pool.request(dev_t.nbytes())
             rec.input_tensors[name] = dev_t
             self._inputs[name].slots["out0"] = dev_t
-        order = self._sorted()
+        live = self._live(self._sorted(), set(fed))
+        order = [n for n in self._sorted() if n in live]
         # prepare() fixes shapes and plans, then outputs / temporaries get buffers
         bound = {}
         level = {}
         for n in order:
+            n.links = dict(live[n]) if n.producers else n.links      # this recording's producer of every slot
             for slot, (src, src_slot) in n.links.items():
                 n.slots[slot] = src.slots[src_slot]
             n.prepare()
@@ -468,7 +578,11 @@ class NeuralNet:
             bound[n] = n.bind()
             level[n] = 1 + max((level[src] for src, _ in n.links.values()), default=-1)
         for name, out in self._outputs.items():
+            if out not in live:
+                continue            # nothing this recording keeps feeds it
             rec.outputs[name] = out.slots["in0"] if "in0" not in out.links else out.links["in0"][0].slots[out.links["in0"][1]]
+        if not rec.outputs:
+            raise RuntimeError("no output is reachable from the inputs given")
         # Nodes of one level do not depend on each other (q / k / v of a block): they go to
         # side streams between a fork and a join, so their launch latencies overlap.
         by_level = {}
@@ -583,10 +697,12 @@ class NeuralNet:
         fed = dict(zip(self._input_order, args))
         if kwargs:
             fed.update(kwargs)
-        if len(fed) != len(names) or any(k not in fed for k in names):
+        if not fed or any(k not in self._inputs for k in fed):
             raise ValueError(f"inputs {sorted(fed)} do not match the net's {names}")
         lib = self.device.lib
-        key = tuple([(k, fed[k].shape, fed[k].dtype) for k in names])
+        # a recording is made for the inputs that came (and the gates as they stand): nodes
+        # that need an input left out are not part of it
+        key = tuple([(k, fed[k].shape, fed[k].dtype) for k in names if k in fed])
         if self._dirty:           # a parameter or a wire changed: every recording is stale
             self._drop_recordings()
             self._dirty = False

@@ -8,7 +8,7 @@ import ctypes
 import numpy as np
 
 from . import _lib
-from .engine import (INPUT, OUTPUT, PERSISTENT, TEMPORARY, Dtype, Epilogue, Node, ResidualOrder, Tensor)
+from .engine import (INPUT, OUTPUT, PERSISTENT, TEMPORARY, Dtype, Epilogue, GateNode, Node, ResidualOrder, Tensor)  # noqa: F401 (GateNode re-exported)
 
 KERNEL_AUTO, KERNEL_GEMV, KERNEL_FMA_TILE, KERNEL_TC_GEMM, KERNEL_TC_SKINNY = 0, 1, 2, 3, 4
 
