@@ -8,6 +8,7 @@
 
 using namespace vai;
 using vai::node::Argmax;
+using vai::node::Gate;
 using vai::node::LayerNorm;
 using vai::node::Linear;
 using vai::node::RmsNorm;
@@ -93,6 +94,95 @@ static void mlp_on_gpu(bool useGraph)
         EXPECT(worst < 1e-4);
     }
     EXPECT(net.recordingCount() == (useGraph ? 2u : 1u));
+}
+
+// x -> gate; then: a (relu); else: b; both -> c -> "main"; a second input y -> d -> "side".
+struct GatedNet {
+    NeuralNet net{{.wDefaultDtype = Dtype::Fp32}};
+    Gate gate;
+    Linear a{{.inDim = 8, .outDim = 8, .epilogue = Epilogue::Relu}};
+    Linear b{{.inDim = 8, .outDim = 8, .scalarScale = -1.0f}};
+    Linear c{{.inDim = 8, .outDim = 4}};
+    Linear d{{.inDim = 6, .outDim = 4}};
+    GatedNet()
+    {
+        net.input("x") - gate;
+        gate / "then" - a - c;
+        gate / "else" - b - c;               // the merge: two producers of c.in0
+        c - net.output("main");
+        net.input("y") - d - net.output("side");
+        net.finish();
+    }
+};
+
+static void gates_wiring()
+{
+    GatedNet g;
+    auto order = g.net.sortedNodes();
+    auto has = [](auto& live, Node& n) { return live.count(&n) != 0; };
+    auto live = g.net.liveNodes(order, {"x", "y"});
+    EXPECT(has(live, g.a) && !has(live, g.b) && has(live, g.c) && has(live, g.d));
+    g.gate.setOpen(false);
+    live = g.net.liveNodes(order, {"x", "y"});
+    EXPECT(!has(live, g.a) && has(live, g.b) && has(live, g.c));
+    EXPECT(live[&g.c].at("in0").first == &g.b);                    // the merge point reads the surviving branch
+    live = g.net.liveNodes(order, {"y"});
+    EXPECT(!has(live, g.gate) && !has(live, g.c) && has(live, g.d));   // x left out: nothing that needs it is kept
+    // fan-in anywhere else is rejected
+    NeuralNet bad;
+    Linear p({.inDim = 4, .outDim = 4}), q({.inDim = 4, .outDim = 4}), r({.inDim = 4, .outDim = 4});
+    bad.input("x") - p - r;
+    bad.input("x") - q - r;
+    bad.finish();
+    bool threw = false;
+    try { bad.sortedNodes(); } catch (const std::runtime_error&) { threw = true; }
+    EXPECT(threw);
+}
+
+static void gates_on_gpu()
+{
+    GatedNet g;
+    std::vector<float> wa(64), wb(64), wc(32), wd(24), x(3 * 8), y(3 * 6);
+    unsigned s = 31;
+    auto rnd = [&] { s = s * 1664525u + 1013904223u; return ((s >> 8) & 0xFFFF) / 32768.0f - 1.0f; };
+    for (auto* v : {&wa, &wb, &wc, &wd, &x, &y})
+        for (auto& e : *v) e = rnd();
+    initVAIEngine(0);
+    g.a["weight"] = Tensor({8, 8}, Dtype::Fp32); g.a["weight"].upload(wa.data());
+    g.b["weight"] = Tensor({8, 8}, Dtype::Fp32); g.b["weight"].upload(wb.data());
+    g.c["weight"] = Tensor({4, 8}, Dtype::Fp32); g.c["weight"].upload(wc.data());
+    g.d["weight"] = Tensor({4, 6}, Dtype::Fp32); g.d["weight"].upload(wd.data());
+    vaicu_device_synchronize(deviceHandle());
+    auto expect_main = [&](bool open) {
+        std::vector<double> out(3 * 4);
+        for (int m = 0; m < 3; ++m) {
+            double h[8];
+            for (int j = 0; j < 8; ++j) {
+                double acc = 0;
+                for (int k = 0; k < 8; ++k) acc += double(x[m * 8 + k]) * (open ? wa : wb)[j * 8 + k];
+                h[j] = open ? (acc > 0 ? acc : 0) : -acc;
+            }
+            for (int n = 0; n < 4; ++n) {
+                double acc = 0;
+                for (int j = 0; j < 8; ++j) acc += h[j] * wc[n * 8 + j];
+                out[m * 4 + n] = acc;
+            }
+        }
+        return out;
+    };
+    for (bool open : {true, false, true}) {
+        g.gate.setOpen(open);
+        auto out = g.net({{"x", HostTensor::fromFloats({3, 8}, x)}, {"y", HostTensor::fromFloats({3, 6}, y)}});
+        EXPECT(out.count("main") == 1 && out.count("side") == 1);
+        const std::vector<float> got = out.at("main").floats();
+        const std::vector<double> want = expect_main(open);
+        double worst = 0;
+        for (size_t i = 0; i < want.size(); ++i) worst = std::fmax(worst, std::fabs(want[i] - got[i]));
+        EXPECT(worst < 1e-4);
+    }
+    EXPECT(g.net.recordingCount() == 2);                           // one recording per gate state, both kept
+    auto only = g.net({{"y", HostTensor::fromFloats({3, 6}, y)}});
+    EXPECT(only.size() == 1 && only.count("side") == 1);
 }
 
 // LayerNorm (or RmsNorm) -> Linear -> Argmax, the tail of a decoder: checked against double
@@ -181,12 +271,14 @@ static void topk_on_gpu()
 int main(int argc, char** argv)
 {
     wiring();
+    gates_wiring();
     if (argc > 1 && std::string(argv[1]) == "--gpu") {
         mlp_on_gpu(true);
         mlp_on_gpu(false);
         norm_head_on_gpu(true);
         norm_head_on_gpu(false);
         topk_on_gpu();
+        gates_on_gpu();
     }
     std::printf(fails ? "FAILED (%d)\n" : "ok\n", fails);
     return fails ? 1 : 0;

@@ -146,8 +146,11 @@ inline NodeOwner*& currentOwner()
 class Node
 {
     std::map<std::string, NodeSlot> slots_;
-    // input slot -> (producer, its output slot); written by the wiring operators
+    // input slot -> (producer, its output slot): the producer this recording reads; written by
+    // the wiring operators (first producer wired) and by the engine when it records
     std::map<std::string, std::pair<Node*, std::string>> links_;
+    // input slot -> every producer wired (two only where a gate's branches merge)
+    std::map<std::string, std::vector<std::pair<Node*, std::string>>> producers_;
 
 protected:
     Dtype oDtype_ = Dtype::None;
@@ -164,6 +167,11 @@ public:
     virtual ~Node() = default;
     std::map<std::string, std::pair<Node*, std::string>>& links() { return links_; }
     const std::map<std::string, std::pair<Node*, std::string>>& links() const { return links_; }
+    std::map<std::string, std::vector<std::pair<Node*, std::string>>>& producers() { return producers_; }
+    const std::map<std::string, std::vector<std::pair<Node*, std::string>>>& producers() const { return producers_; }
+    // a conditional branch (vai::node::Gate): the engine reads its two outputs through this
+    virtual bool isGate() const { return false; }
+    virtual bool gateOpen() const { return true; }
     bool hasSlot(const std::string& name) const { return slots_.count(name) != 0; }
     Tensor& operator[](const std::string& name) { return slots_.at(name).getValueRef(); }
     const Tensor& operator[](const std::string& name) const { return slots_.at(name).getValueRef(); }

@@ -14,6 +14,7 @@
 
 #include <algorithm>
 #include <deque>
+#include <set>
 
 #include "linear.h"
 
@@ -53,7 +54,10 @@ inline Flow operator/(Node& n, const char* slot) { return Flow{&n, "in0", slot};
 inline Flow operator-(Flow a, Flow b)
 {
     if (!a.node->hasSlot(a.out) || !b.node->hasSlot(b.in)) throw std::invalid_argument("no such slot: " + a.out + " -> " + b.in);
-    b.node->links()[b.in] = {a.node, a.out};
+    auto& srcs = b.node->producers()[b.in];
+    const std::pair<Node*, std::string> src{a.node, a.out};
+    if (std::find(srcs.begin(), srcs.end(), src) == srcs.end()) srcs.push_back(src);
+    b.node->links()[b.in] = srcs.front();
     return b;
 }
 inline Flow operator-(Flow a, Node& b) { return a - Flow{&b}; }
@@ -74,6 +78,35 @@ public:
     void prepare() override {}
     void run(vaicu_stream_t) override {}
 };
+
+namespace node {
+// Conditional branch without computation (vai/nodes/gate.h:9-60): "then" and "else" both alias
+// in0; a recording keeps one branch, leaves out every node only the closed branch reaches, and
+// keeps what both reach (the merge point and everything past it).  Flipping re-records.
+class Gate : public vai::Node
+{
+    bool open_ = true;
+
+public:
+    Gate()
+    {
+        addSlot("in0", NodeSlot::input);
+        addSlot("then", NodeSlot::output);
+        addSlot("else", NodeSlot::output);
+    }
+    bool isGate() const override { return true; }
+    bool gateOpen() const override { return open_; }
+    bool isOpen() const { return open_; }
+    // The net keys its recordings by the gates' states: a flip selects (or makes) another recording.
+    void setOpen(bool open) { open_ = open; }
+    void prepare() override
+    {
+        (*this)["then"] = (*this)["in0"];
+        (*this)["else"] = (*this)["in0"];
+    }
+    void run(vaicu_stream_t) override {}
+};
+}   // namespace node
 
 // Size-keyed reuse of device buffers (vai/engine/buffer-pool.h:77-153).
 class BufferPool
@@ -147,17 +180,19 @@ public:
     }
     const std::vector<Node*>& nodes() const { return nodes_; }
 
-    // Kahn's algorithm over the links (vai/engine/neural-net.cpp:282-354); throws on a cycle.
+    // Kahn's algorithm over the links (vai/engine/neural-net.cpp:282-354); throws on a cycle and on
+    // a slot with two producers that are not the two branches of one gate (graph-controller.h:66-70).
     std::vector<Node*> sortedNodes() const
     {
         std::map<Node*, int> indeg;
         std::map<Node*, std::vector<Node*>> users;
         for (Node* n : nodes_) indeg[n] = 0;
         for (Node* n : nodes_)
-            for (auto& [slot, src] : n->links()) {
-                ++indeg[n];
-                users[src.first].push_back(n);
-            }
+            for (auto& [slot, srcs] : n->producers())
+                for (auto& src : srcs) {
+                    ++indeg[n];
+                    users[src.first].push_back(n);
+                }
         std::deque<Node*> ready;
         for (Node* n : nodes_)
             if (indeg[n] == 0) ready.push_back(n);
@@ -170,12 +205,77 @@ public:
                 if (--indeg[u] == 0) ready.push_back(u);
         }
         if (order.size() != nodes_.size()) throw std::runtime_error("the graph has a cycle");
+        // which gate branches reach each node, one bit per gate
+        std::map<const Node*, uint64_t> bit, thenBits, elseBits;
+        uint64_t next = 1;
+        for (Node* n : order)
+            if (n->isGate()) { bit[n] = next; next <<= 1; }
+        auto side = [&](const std::pair<Node*, std::string>& src) {
+            uint64_t t = thenBits[src.first], e = elseBits[src.first];
+            if (src.first->isGate()) {
+                if (src.second == "then") t |= bit[src.first];
+                if (src.second == "else") e |= bit[src.first];
+            }
+            return std::pair<uint64_t, uint64_t>{t, e};
+        };
+        for (Node* n : order) {
+            uint64_t t = 0, e = 0;
+            for (auto& [slot, srcs] : n->producers())
+                for (auto& src : srcs) {
+                    auto [st, se] = side(src);
+                    t |= st; e |= se;
+                }
+            thenBits[n] = t; elseBits[n] = e;
+        }
+        for (Node* n : order)
+            for (auto& [slot, srcs] : n->producers()) {
+                if (srcs.size() == 1) continue;
+                bool ok = false;
+                if (srcs.size() == 2) {
+                    auto [t0, e0] = side(srcs[0]);
+                    auto [t1, e1] = side(srcs[1]);
+                    ok = ((t0 & ~e0) & (e1 & ~t1)) || ((t1 & ~e1) & (e0 & ~t0));
+                }
+                if (!ok) throw std::runtime_error("slot " + slot + " has producers that are not the two branches of one gate");
+            }
         return order;
+    }
+
+    // What a recording keeps (graph-controller.h:13-32): an input node when it is fed, a gate's
+    // branch when the gate is live and set that way, any other node when every wired slot has
+    // a live producer.  node -> (slot -> the live producer).
+    std::map<Node*, std::map<std::string, std::pair<Node*, std::string>>> liveNodes(const std::vector<Node*>& order,
+                                                                                    const std::set<std::string>& fed) const
+    {
+        std::map<Node*, std::map<std::string, std::pair<Node*, std::string>>> chosen;
+        std::map<const Node*, std::string> inputName;
+        for (auto& [name, node] : inputs_) inputName[node.get()] = name;
+        auto outLive = [&](const std::pair<Node*, std::string>& src) {
+            if (!chosen.count(src.first)) return false;
+            if (src.first->isGate() && (src.second == "then" || src.second == "else")) return (src.second == "then") == src.first->gateOpen();
+            return true;
+        };
+        for (Node* n : order) {
+            auto in = inputName.find(n);
+            if (in != inputName.end()) {
+                if (fed.count(in->second)) chosen[n];
+                continue;
+            }
+            std::map<std::string, std::pair<Node*, std::string>> picks;
+            bool alive = true;
+            for (auto& [slot, srcs] : n->producers()) {
+                auto it = std::find_if(srcs.begin(), srcs.end(), outLive);
+                if (it == srcs.end()) { alive = false; break; }
+                picks[slot] = *it;
+            }
+            if (alive) chosen[n] = std::move(picks);
+        }
+        return chosen;
     }
 
     HostDict operator()(const HostDict& fed)
     {
-        if (fed.size() != inputs_.size()) throw std::invalid_argument("inputs do not match the net's");
+        if (fed.empty()) throw std::invalid_argument("inputs do not match the net's");
         initVAIEngine(config_.deviceOrdinal);
         if (!stream_) check(vaicu_stream_create(deviceHandle(), &stream_), "vaicu_stream_create");
         std::string key;
@@ -185,6 +285,8 @@ public:
             for (uint32_t s : t.shape) key += "," + std::to_string(s);
             key += ";";
         }
+        for (Node* n : nodes_)
+            if (n->isGate()) key += n->gateOpen() ? 'T' : 'E';       // a recording bakes in one branch per gate
         auto it = recordings_.find(key);
         if (it == recordings_.end()) {
             // without a graph the launches are re-issued from the nodes' current slots, which
@@ -232,8 +334,14 @@ private:
             rec.inputs[name] = dev;
             (*inputs_.at(name))["out0"] = dev;
         }
-        rec.order = sortedNodes();
+        const std::vector<Node*> sorted = sortedNodes();
+        std::set<std::string> names;
+        for (auto& [name, t] : fed) names.insert(name);
+        auto live = liveNodes(sorted, names);
+        for (Node* n : sorted)
+            if (live.count(n)) rec.order.push_back(n);
         for (Node* n : rec.order) {
+            if (!n->producers().empty()) n->links() = live[n];       // this recording's producer of every slot
             for (auto& [slot, src] : n->links()) (*n)[slot] = (*src.first)[src.second];
             n->setODefaultDtype(config_.oDefaultDtype);
             n->prepare();
@@ -247,10 +355,12 @@ private:
             }
         }
         for (auto& [name, node] : outputs_) {
-            auto link = node->links().find("in0");
-            if (link == node->links().end()) throw std::runtime_error("output " + name + " is not connected");
-            rec.outputs[name] = (*link->second.first)[link->second.second];
+            if (node->producers().find("in0") == node->producers().end()) throw std::runtime_error("output " + name + " is not connected");
+            if (!live.count(node.get())) continue;                 // nothing this recording keeps feeds it
+            auto& link = node->links().at("in0");
+            rec.outputs[name] = (*link.first)[link.second];
         }
+        if (rec.outputs.empty()) throw std::runtime_error("no output is reachable from the inputs given");
         if (config_.useGraph) {
             check(vaicu_graph_capture_begin(stream_), "vaicu_graph_capture_begin");
             try {
