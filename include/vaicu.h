@@ -307,9 +307,9 @@ VAICU_API int vaicu_argmax_merge_run(vaicu_stream_t stream, const float* vals, c
  * inverse CDF with the uniform *u_device in [0, 1) — device memory, so that a recorded launch
  * reads each step's value, as the reference reads its host-visible uniform buffer.
  *   k          1 .. 128 (TopKSampling::maxK); k > N uses N
- *   workspace  vaicu_topk_workspace_bytes(M, N, k) bytes (0 for rows of at most 8192 columns)
+ *   workspace  vaicu_topk_workspace_bytes(M, N, k) bytes (0 for rows of at most 2048 columns)
  *   out_u32    [M] sampled indices
- * VAICU_ERR_TOO_LARGE when ceil(N / 2048) * k exceeds 8192 candidates per row. */
+ * VAICU_ERR_TOO_LARGE for rows of more than 256 * 2048 columns. */
 VAICU_API int vaicu_topk_workspace_bytes(uint32_t M, uint32_t N, uint32_t k, size_t* out_bytes);
 VAICU_API int vaicu_topk_sample_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, uint32_t k,
                                     float temperature, const float* u_device, void* workspace, void* out_u32);

@@ -939,8 +939,8 @@ int vaicu_topk_sample_run(vaicu_stream_t stream, const void* logits, int dtype, 
     if (!valid_dtype(dtype)) return VAICU_ERR_INVALID_VALUE;
     const uint32_t G = topk_groups(N);
     if (G > 1u && !workspace) return VAICU_ERR_WORKSPACE;
-    // stage 2 holds G * k candidates in 1024 lists of 8
-    if (G > 1u && (uint64_t)G * (k < N ? k : N) > 8192u) return VAICU_ERR_TOO_LARGE;
+    // stage 2 walks the G slice lists with one warp, at most 8 per lane
+    if (G > 256u) return VAICU_ERR_TOO_LARGE;
     if ((reinterpret_cast<uintptr_t>(logits) & (dtype_size(dtype) - 1u)) || (reinterpret_cast<uintptr_t>(out_u32) & 3u) ||
         (reinterpret_cast<uintptr_t>(u_device) & 3u) || (reinterpret_cast<uintptr_t>(workspace) & 7u))
         return VAICU_ERR_ALIGNMENT;

@@ -5,11 +5,15 @@
 // ascending); Z and the running sum accumulated in that order in fp32 with the row maximum
 // subtracted; the first rank whose running sum reaches u * Z is the sample (rank 0 if none).
 //
-// Two launches, as in the reference.  Stage 1: block (g, row) keeps its 2048-column slice in
-// registers (8 per thread, each thread's list sorted descending), then k rounds of a block-wide
-// "best head" reduction pop the slice's top-k in order.  Stage 2: one block per row does the
-// same over the G * k candidates and thread 0 samples.  Rows of at most 8192 columns need
-// stage 2 only.  u lives in device memory so that a recorded launch sees each step's value.
+// Two launches, as in the reference; the selection itself is organised for warps instead of
+// workgroup-wide rounds.  Stage 1: block (g, row) owns a 2048-column slice; each of its 8 warps
+// keeps 256 columns in registers (8 per lane, each lane's list sorted descending) and pops its
+// own top-k in k rounds of a warp-shuffle "best head" reduction (no block barrier), leaving a
+// sorted list in shared memory; warp 0 then merges the 8 sorted lists into the slice's top-k.
+// Stage 2: one warp merges the G sorted candidate lists (heads in registers, lists in shared
+// memory) and lane 0 samples.  Rows of at most 2048 columns need stage 1's block only.  Both
+// merges are exact: the top-k of a union is within the union of the parts' top-k.  u lives in
+// device memory so that a recorded launch sees each step's value.
 #include "common.cuh"
 
 namespace vaicu {
@@ -28,24 +32,92 @@ __device__ __forceinline__ bool outranks(float av, uint32_t ai, float bv, uint32
 }
 
 struct TopkParams {
-    const void* logits;       // stage 1 / single stage: [M, N] of dtype
-    const uint2* cand_in;     // stage 2: [M, n_in] (value bits, index)
-    uint2* cand_out;          // stage 1: [M, G * k]
-    uint32_t* out;            // final stage: [M]
+    const void* logits;       // stage 1: [M, N] of dtype
+    const uint2* cand_in;     // stage 2: [M, G * k] (value bits, index), G sorted lists of k
+    uint2* cand_out;          // stage 1 with G > 1: [M, G * k]
+    uint32_t* out;            // sampling launch: [M]
     const float* u;           // device scalar in [0, 1)
-    uint32_t N;               // elements per row this launch reads
+    uint32_t N;               // stage 1: row width; stage 2: lists per row (G)
     uint32_t k;               // min(K, row width of the logits)
     int32_t dtype;
     float temperature;
 };
 
-// FINAL: this launch samples (reads logits when cand_in is null, else candidates).
-template <bool FINAL>
-__global__ void topk_kernel(const TopkParams p)
+// One warp merges `nlists` descending lists of `len` (value, index) entries each, stored
+// back to back at `lists`, into the best `k` of their union, in order, at top_v / top_i.
+// Lane l walks lists l, l + 32, ...: their heads live in registers, SLOTS lists per lane at most.
+template <uint32_t SLOTS>
+__device__ __forceinline__ void merge_lists(const uint2* lists, uint32_t nlists, uint32_t len, uint32_t k, float* top_v,
+                                            uint32_t* top_i, uint32_t lane)
 {
-    const uint32_t row = blockIdx.y, g = blockIdx.x, G = gridDim.x, tid = threadIdx.x, nthreads = blockDim.x;
-    __shared__ float s_val[32];
-    __shared__ uint32_t s_idx[32];
+    float hv[SLOTS];
+    uint32_t hi[SLOTS], pos[SLOTS];
+#pragma unroll
+    for (uint32_t j = 0; j < SLOTS; ++j) {
+        const uint32_t l = lane + 32u * j;
+        pos[j] = 0u;
+        if (l < nlists && len > 0u) {
+            const uint2 c = lists[(size_t)l * len];
+            hv[j] = __uint_as_float(c.x); hi[j] = c.y;
+        } else {
+            hv[j] = kLowest; hi[j] = 0xFFFFFFFFu;
+        }
+    }
+    for (uint32_t r = 0; r < k; ++r) {
+        // this lane's best head, then the warp's
+        float bv = hv[0];
+        uint32_t bi = hi[0];
+#pragma unroll
+        for (uint32_t j = 1; j < SLOTS; ++j)
+            if (outranks(hv[j], hi[j], bv, bi)) { bv = hv[j]; bi = hi[j]; }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off);
+            const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, off);
+            if (outranks(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0u) { top_v[r] = bv; top_i[r] = bi; }
+        // the list whose head won advances (indices are unique, sentinels aside)
+#pragma unroll
+        for (uint32_t j = 0; j < SLOTS; ++j) {
+            if (hi[j] == bi && hv[j] == bv && bi != 0xFFFFFFFFu) {
+                const uint32_t l = lane + 32u * j;
+                if (++pos[j] < len) {
+                    const uint2 c = lists[(size_t)l * len + pos[j]];
+                    hv[j] = __uint_as_float(c.x); hi[j] = c.y;
+                } else {
+                    hv[j] = kLowest; hi[j] = 0xFFFFFFFFu;
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
+// Temperature softmax over the k winners and the inverse-CDF sample (topk-sampling.comp:237-258).
+__device__ __forceinline__ uint32_t sample(const float* top_v, const uint32_t* top_i, uint32_t k, float temperature, float u)
+{
+    const float inv_t = 1.0f / fmaxf(temperature, 1e-6f);
+    const float m = top_v[0];
+    float z = 0.0f;
+    for (uint32_t r = 0; r < k; ++r) z += expf((top_v[r] - m) * inv_t);
+    const float target = u * z;
+    float cum = 0.0f;
+    for (uint32_t r = 0; r < k; ++r) {
+        cum += expf((top_v[r] - m) * inv_t);
+        if (cum >= target) return top_i[r];
+    }
+    return top_i[0];
+}
+
+// Stage 1.  SAMPLE: the row fits one block, which also samples.
+template <bool SAMPLE>
+__global__ void __launch_bounds__(kPartThreads) topk_slice_kernel(const TopkParams p)
+{
+    const uint32_t row = blockIdx.y, g = blockIdx.x, G = gridDim.x, tid = threadIdx.x;
+    const uint32_t warp = tid >> 5, lane = tid & 31u;
+    constexpr uint32_t kWarps = kPartThreads / 32u;
+    __shared__ uint2 warp_list[kWarps * kMaxK];          // each warp's top-k, descending
     __shared__ float top_v[kMaxK];
     __shared__ uint32_t top_i[kMaxK];
 
@@ -53,23 +125,13 @@ __global__ void topk_kernel(const TopkParams p)
     uint32_t li[kList];
 #pragma unroll
     for (uint32_t j = 0; j < kList; ++j) { lv[j] = kLowest; li[j] = 0xFFFFFFFFu; }
-
     const uint32_t slice = (p.N + G - 1u) / G;
     const uint32_t s0 = g * slice, s1 = (s0 + slice < p.N) ? s0 + slice : p.N;
-    for (uint32_t i = s0 + tid; i < s1; i += nthreads) {
-        float v;
-        uint32_t idx;
-        if (p.cand_in) {
-            const uint2 c = p.cand_in[(size_t)row * p.N + i];
-            v = __uint_as_float(c.x);
-            idx = c.y;
-        } else {
-            v = load_as_f32(p.logits, p.dtype, (size_t)row * p.N + i);
-            idx = i;
-        }
+    for (uint32_t i = s0 + tid; i < s1; i += kPartThreads) {
+        const float v = load_as_f32(p.logits, p.dtype, (size_t)row * p.N + i);
         // insertion into the descending list (fully unrolled: the list stays in registers)
-        if (outranks(v, idx, lv[kList - 1], li[kList - 1])) {
-            lv[kList - 1] = v; li[kList - 1] = idx;
+        if (outranks(v, i, lv[kList - 1], li[kList - 1])) {
+            lv[kList - 1] = v; li[kList - 1] = i;
 #pragma unroll
             for (int q = kList - 1; q > 0; --q) {
                 if (outranks(lv[q], li[q], lv[q - 1], li[q - 1])) {
@@ -79,9 +141,8 @@ __global__ void topk_kernel(const TopkParams p)
             }
         }
     }
-
-    // k rounds: the best list head of the block wins the round and its thread pops
-    const uint32_t nwarps = nthreads >> 5;
+    // k rounds inside the warp: the best list head wins and its lane pops
+    uint2* mine = warp_list + warp * p.k;
     for (uint32_t r = 0; r < p.k; ++r) {
         float bv = lv[0];
         uint32_t bi = li[0];
@@ -91,76 +152,76 @@ __global__ void topk_kernel(const TopkParams p)
             const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, off);
             if (outranks(ov, oi, bv, bi)) { bv = ov; bi = oi; }
         }
-        if ((tid & 31u) == 0u) { s_val[tid >> 5] = bv; s_idx[tid >> 5] = bi; }
-        __syncthreads();
-        bv = s_val[0]; bi = s_idx[0];
-        for (uint32_t w = 1; w < nwarps; ++w)
-            if (outranks(s_val[w], s_idx[w], bv, bi)) { bv = s_val[w]; bi = s_idx[w]; }
-        if (tid == 0u) { top_v[r] = bv; top_i[r] = bi; }
-        if (lv[0] == bv && li[0] == bi) {          // this thread's head won: advance its list
+        if (lane == 0u) mine[r] = make_uint2(__float_as_uint(bv), bi);
+        if (li[0] == bi && lv[0] == bv && bi != 0xFFFFFFFFu) {
 #pragma unroll
             for (uint32_t q = 0; q + 1u < kList; ++q) { lv[q] = lv[q + 1]; li[q] = li[q + 1]; }
             lv[kList - 1] = kLowest; li[kList - 1] = 0xFFFFFFFFu;
         }
-        __syncthreads();
     }
-
-    if (!FINAL) {
-        if (tid < p.k) p.cand_out[((size_t)row * G + g) * p.k + tid] = make_uint2(__float_as_uint(top_v[tid]), top_i[tid]);
-        return;
-    }
-    if (tid == 0u) {
-        // temperature softmax over the k winners and the inverse-CDF sample (topk-sampling.comp:237-258)
-        const float inv_t = 1.0f / fmaxf(p.temperature, 1e-6f);
-        const float m = top_v[0];
-        float z = 0.0f;
-        for (uint32_t r = 0; r < p.k; ++r) z += expf((top_v[r] - m) * inv_t);
-        const float target = *p.u * z;
-        float cum = 0.0f;
-        uint32_t chosen = top_i[0];
-        for (uint32_t r = 0; r < p.k; ++r) {
-            cum += expf((top_v[r] - m) * inv_t);
-            if (cum >= target) { chosen = top_i[r]; break; }
-        }
-        p.out[row] = chosen;
+    __syncthreads();
+    if (warp != 0u) return;
+    merge_lists<1>(warp_list, kWarps, p.k, p.k, top_v, top_i, lane);
+    if (SAMPLE) {
+        if (lane == 0u) p.out[row] = sample(top_v, top_i, p.k, p.temperature, *p.u);
+    } else {
+        for (uint32_t r = lane; r < p.k; r += 32u)
+            p.cand_out[((size_t)row * G + g) * p.k + r] = make_uint2(__float_as_uint(top_v[r]), top_i[r]);
     }
 }
 
-uint32_t final_threads(uint32_t n)
+// Stage 2: one warp per row merges the G sorted lists (copied to shared memory when they fit).
+__global__ void __launch_bounds__(32) topk_merge_kernel(const TopkParams p, uint32_t lists_in_smem)
 {
-    uint32_t t = ((n + kList - 1u) / kList + 31u) / 32u * 32u;
-    if (t < 32u) t = 32u;
-    return t > 1024u ? 1024u : t;
+    extern __shared__ uint2 staged[];
+    __shared__ float top_v[kMaxK];
+    __shared__ uint32_t top_i[kMaxK];
+    const uint32_t row = blockIdx.x, lane = threadIdx.x, G = p.N;
+    const uint2* lists = p.cand_in + (size_t)row * G * p.k;
+    if (lists_in_smem) {
+        for (uint32_t i = lane; i < G * p.k; i += 32u) staged[i] = lists[i];
+        __syncwarp();
+        lists = staged;
+    }
+    if (G <= 64u) merge_lists<2>(lists, G, p.k, p.k, top_v, top_i, lane);
+    else if (G <= 128u) merge_lists<4>(lists, G, p.k, p.k, top_v, top_i, lane);
+    else merge_lists<8>(lists, G, p.k, p.k, top_v, top_i, lane);
+    if (lane == 0u) p.out[row] = sample(top_v, top_i, p.k, p.temperature, *p.u);
 }
 
 }  // namespace
 
 // Blocks per row in stage 1 (1: single launch).
-uint32_t topk_groups(uint32_t N) { return N <= 1024u * kList ? 1u : (N + kSlice - 1u) / kSlice; }
+uint32_t topk_groups(uint32_t N) { return (N + kSlice - 1u) / kSlice; }
 
 cudaError_t launch_topk_sample(const void* logits, int dtype, uint32_t M, uint32_t N, uint32_t K, float temperature,
                                const float* u, void* workspace, uint32_t* out, cudaStream_t stream)
 {
     TopkParams p{};
     p.logits = logits; p.dtype = dtype; p.temperature = temperature; p.u = u; p.out = out;
+    p.N = N;
     p.k = K < N ? K : N;
     const uint32_t G = topk_groups(N);
     if (G == 1u) {
-        p.N = N;
-        topk_kernel<true><<<dim3(1, M), final_threads(N), 0, stream>>>(p);
+        topk_slice_kernel<true><<<dim3(1, M), kPartThreads, 0, stream>>>(p);
         return cudaGetLastError();
     }
-    p.N = N;
     p.cand_out = reinterpret_cast<uint2*>(workspace);
-    topk_kernel<false><<<dim3(G, M), kPartThreads, 0, stream>>>(p);
+    topk_slice_kernel<false><<<dim3(G, M), kPartThreads, 0, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     TopkParams q = p;
     q.logits = nullptr;
     q.cand_in = reinterpret_cast<const uint2*>(workspace);
     q.cand_out = nullptr;
-    q.N = G * p.k;
-    topk_kernel<true><<<dim3(1, M), final_threads(q.N), 0, stream>>>(q);
+    q.N = G;
+    const size_t bytes = (size_t)G * p.k * sizeof(uint2);
+    const bool in_smem = bytes <= 200u * 1024u;
+    if (in_smem && bytes > 48u * 1024u) {
+        e = cudaFuncSetAttribute(topk_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200u * 1024u));
+        if (e != cudaSuccess) return e;
+    }
+    topk_merge_kernel<<<M, 32, in_smem ? bytes : 0, stream>>>(q, in_smem ? 1u : 0u);
     return cudaGetLastError();
 }
 
