@@ -330,7 +330,7 @@ def main():
         "config": workload_config(),
         "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": net_e2e.h2d_bytes, "d2h_bytes_per_step": net_e2e.d2h_bytes,
                 "ms_per_step": e2e_ms / args.steps,
-                "path": "NeuralNet call: pinned H2D of x, replay of 97 Linear nodes + Argmax, D2H of the token, sync"},
+                "path": "NeuralNet call: one graph submission (H2D of x from pinned memory, 97 Linear nodes + Argmax, the token stored by its kernel into page-locked host memory), then a sync"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "gemv_kernel<bf16, M=1, R> (every launch of the step)",

@@ -187,6 +187,25 @@ class BufferPool:
         self.free.setdefault(buf.nbytes, []).append(buf)
 
 
+class HostMappedBuffer:
+    """Page-locked host memory used as a kernel's output: with unified addressing the device
+    stores to it directly, so a small result (a sampled token) reaches the host without a
+    copy command of its own.  Same surface as DeviceBuffer where the engine needs it."""
+
+    def __init__(self, net, nbytes):
+        self.device = net.device
+        self.view, p = net._pinned(nbytes, np.uint8, (max(nbytes, 4),))
+        self.ptr = p.value
+        self.nbytes = nbytes
+
+    def download(self, array, stream=None):
+        np.copyto(array.reshape(-1).view(np.uint8), self.view[:array.nbytes])
+        return array
+
+    def free(self):
+        pass
+
+
 class Tensor:
     """Shape + dtype + host array and/or device buffer (vAi vai/engine/tensor.h:111-332).
     Copies share storage, as the reference's handle does."""
@@ -431,6 +450,9 @@ class NeuralNet:
         self.parallel_branches = parallel_branches
         self.group_siblings = group_siblings
         self.max_side_streams = 3
+        # outputs up to this size that nothing else reads are stored by their kernel directly into
+        # page-locked host memory (0: always a device buffer and a device-to-host copy)
+        self.direct_output_bytes = 4096
         self.use_graph = use_graph
         self._nodes = []
         self._inputs = {}
@@ -562,6 +584,16 @@ class NeuralNet:
             self._inputs[name].slots["out0"] = dev_t
         live = self._live(self._sorted(), set(fed))
         order = [n for n in self._sorted() if n in live]
+        # A small result that only the net's output reads (a sampled token) is written by its
+        # kernel straight into page-locked host memory: no copy command after the launches.
+        uses = {}
+        for n in order:
+            for src in (live[n].values() if n.producers else n.links.values()):
+                uses[src] = uses.get(src, 0) + 1
+        direct = set()
+        for out in self._outputs.values():
+            if out in live and "in0" in live[out] and uses.get(live[out]["in0"], 0) == 1:
+                direct.add(live[out]["in0"])
         # prepare() fixes shapes and plans, then outputs / temporaries get buffers
         bound = {}
         level = {}
@@ -573,7 +605,10 @@ class NeuralNet:
             for name, kind in n.slot_types.items():
                 t = n.slots[name]
                 if kind in (OUTPUT, TEMPORARY) and t.valid_shape() and t.buffer is None and t.nbytes() > 0:
-                    t.buffer = self.pool.request(t.nbytes())
+                    if kind == OUTPUT and (n, name) in direct and t.nbytes() <= self.direct_output_bytes:
+                        t.buffer = HostMappedBuffer(self, t.nbytes())
+                    else:
+                        t.buffer = self.pool.request(t.nbytes())
                     rec.keep.append(t)
             bound[n] = n.bind()
             level[n] = 1 + max((level[src] for src, _ in n.links.values()), default=-1)
@@ -639,7 +674,11 @@ class NeuralNet:
         for name, t in rec.input_tensors.items():
             rec.stage_in[name] = self._pinned(t.nbytes(), np.float32 if t.dtype == Dtype.F32 else np.uint16, t.shape)
         for name, t in rec.outputs.items():
-            rec.stage_out[name] = self._pinned(t.nbytes(), np.float32 if t.dtype == Dtype.F32 else np.uint16, t.shape)
+            np_dtype = np.float32 if t.dtype == Dtype.F32 else np.uint16
+            if isinstance(t.buffer, HostMappedBuffer):
+                rec.stage_out[name] = (t.buffer.view[:t.nbytes()].view(np_dtype).reshape(t.shape), None)
+            else:
+                rec.stage_out[name] = self._pinned(t.nbytes(), np_dtype, t.shape)
         rec.graph_io = None
         if self.use_graph:
             _lib.check(lib.vaicu_graph_capture_begin(self.stream), "vaicu_graph_capture_begin")
@@ -665,7 +704,8 @@ class NeuralNet:
         lib = self.device.lib
         for name, t in rec.outputs.items():
             view, hp = rec.stage_out[name]
-            _lib.check(lib.vaicu_memcpy_d2h(hp, t.ptr, view.nbytes, self.stream), "vaicu_memcpy_d2h")
+            if hp is not None:          # else the kernel wrote the host memory itself
+                _lib.check(lib.vaicu_memcpy_d2h(hp, t.ptr, view.nbytes, self.stream), "vaicu_memcpy_d2h")
 
     def _play(self, ops):
         lib = self.device.lib
