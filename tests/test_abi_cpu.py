@@ -114,3 +114,34 @@ def test_shard_desc_splits_rows_evenly():
         sizes.append(c.value)
     assert sum(sizes) == 50257 and max(sizes) - min(sizes) == 1
     assert lib.vaicu_linear_shard_desc(ctypes.byref(full), 8, 8, ctypes.byref(shard), ctypes.byref(b), ctypes.byref(c)) == 1
+
+
+def test_static_split_k_rejects_misaligned_operands_before_any_launch():
+    """vaicu_linear_splitk_static applies vaicu_linear_run's rule (every operand aligned to
+    its element size) before it touches the GPU: an odd pointer is a status code, never a
+    kernel argument.  The pointers here are made-up addresses; the call returns before
+    anything could read them, which is why this runs without a GPU."""
+    lib = _lib.load()
+    d = _lib.LinearDesc()
+    d.M, d.N, d.K = 4, 8, 64
+    d.i_dtype = d.w_dtype = d.o_dtype = 0
+    d.b_dtype = 0
+    d.has_bias, d.bias_elems = 1, 8
+    d.has_residual = 1
+    d.scalar_scale = 1.0
+    good = 0x10000
+    args = dict(I=good, W=good, bias=good, residual=good, O=good)
+    for name in args:
+        for off in (1, 2, 3):
+            a = dict(args)
+            a[name] = good + off
+            rc = lib.vaicu_linear_splitk_static(ctypes.byref(d), None, a["I"], a["W"], a["bias"], a["residual"], a["O"])
+            assert rc == 6, (name, off, rc)
+    # 16-bit operands need 2-byte alignment only
+    d.w_dtype, d.b_dtype = 3, 1
+    assert lib.vaicu_linear_splitk_static(ctypes.byref(d), None, good, good + 1, good, good, good) == 6
+    assert lib.vaicu_linear_splitk_static(ctypes.byref(d), None, good, good, good + 1, good, good) == 6
+    # an absent operand is not checked
+    d.has_bias = d.has_residual = 0
+    d.b_dtype = 2
+    assert lib.vaicu_linear_splitk_static(ctypes.byref(d), None, good + 2, good, None, None, good) == 6

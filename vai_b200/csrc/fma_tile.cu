@@ -258,6 +258,13 @@ extern "C" int vaicu_linear_splitk_static(const vaicu_linear_desc* d, vaicu_stre
     if (d->has_bias && d->bias_elems && (d->bias_elems % d->N || ((uint64_t)d->M * d->N) % d->bias_elems)) return VAICU_ERR_INVALID_VALUE;
     if (d->has_residual && d->residual_elems && (d->residual_elems % d->N || ((uint64_t)d->M * d->N) % d->residual_elems))
         return VAICU_ERR_INVALID_VALUE;
+    // Same rule as vaicu_linear_run: every operand aligned to its element size.  Checked before
+    // anything touches the GPU, so a bad pointer comes back as a status instead of a
+    // misaligned-address fault inside the kernel.
+    auto elem_aligned = [](const void* p, int dt) { return (reinterpret_cast<uintptr_t>(p) & (dtype_size(dt) - 1u)) == 0; };
+    if (!elem_aligned(I, d->i_dtype) || !elem_aligned(W, d->w_dtype) || !elem_aligned(O, d->o_dtype)) return VAICU_ERR_ALIGNMENT;
+    if (d->has_bias && !elem_aligned(bias, d->b_dtype)) return VAICU_ERR_ALIGNMENT;
+    if (d->has_residual && !elem_aligned(residual, d->o_dtype)) return VAICU_ERR_ALIGNMENT;
 
     float* scratch = nullptr;
     int sms = 0;
