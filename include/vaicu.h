@@ -274,6 +274,16 @@ VAICU_API int vaicu_layer_norm_run(vaicu_device* dev, vaicu_stream_t stream, con
                                  const void* shift, const void* residual, void* out, uint32_t rows, uint32_t feat,
                                  int i_dtype, int w_dtype, int o_dtype, float eps);
 
+/* vAi's GatedMul node as a launch of its own (vai/nodes/gated-mul.h:9-20, 56-84;
+ * vai/shaders/gated-mul.comp:38-49):
+ *   O[r, j] = activation(I[r, j]) * I[r, H + j]      I [rows, 2H] -> O [rows, H]
+ * `activation` is a VAICU_EPILOGUE_* code (silu: SwiGLU, gelu: GEGLU, relu: ReGLU, none:
+ * bilinear), evaluated in fp32 with the reference's constants.  A host engine records a
+ * gate|value Linear followed by this node as one vaicu_linear_run with desc.gate_fuse set;
+ * this entry is what it records when the pair cannot be merged.  Enqueues one kernel. */
+VAICU_API int vaicu_gated_mul_run(vaicu_device* dev, vaicu_stream_t stream, const void* in, void* out, uint32_t rows,
+                                  uint32_t H, int i_dtype, int o_dtype, int activation);
+
 /* Row-wise argmax of logits [M, N] (fp32 / fp16 / bf16) into M raw uint32 indices:
  * vAi's Argmax node, the greedy-decode consumer of the lm_head Linear
  * (vai/nodes/argmax.h:9-18, 57-79; vai/shaders/argmax.comp).  Ties resolve to the

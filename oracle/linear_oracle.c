@@ -488,6 +488,21 @@ int vai_oracle_topk_sample(const float* in, uint32_t M, uint32_t N, uint32_t K, 
     return 0;
 }
 
+/* GatedMul as a node of its own (vai/shaders/gated-mul.comp:38-49): one output element
+ * per thread, row = e / H, src = row * 2H + (e - row * H); O[e] = epilogue(I[src]) * I[src + H]
+ * in fp32, I and O in their own dtypes. */
+int vai_oracle_gated_mul(const void* in, void* out, uint32_t rows, uint32_t H, int i_dtype, int o_dtype, int epilogue)
+{
+    if (!in || !out || rows == 0 || H == 0) return 1;
+    const size_t total = (size_t)rows * H;
+    for (size_t e = 0; e < total; ++e) {
+        const size_t row = e / H, src = row * 2u * H + (e - row * H);
+        const float g = load_elem(in, i_dtype, src), u = load_elem(in, i_dtype, src + H);
+        store_elem(out, o_dtype, e, vai_oracle_epilogue(epilogue, g) * u);
+    }
+    return 0;
+}
+
 int vai_oracle_num_threads(void)
 {
 #ifdef _OPENMP

@@ -162,6 +162,27 @@ def linear_c(desc, I, W, bias=None, residual=None, path="auto", wg_size=128, sta
     return O
 
 
+def gated_mul_f64(x, epilogue):
+    """float64 GLU gating as the reference's test states it (vAi
+    python/tests/nodes/test_gated_mul.py:10-13): activation(first half) * second half."""
+    x = np.asarray(x, dtype=np.float64)
+    h = x.shape[-1] // 2
+    return epilogue_f64(epilogue, x[..., :h]) * x[..., h:]
+
+
+def gated_mul_c(x, epilogue, i_dtype=F32, o_dtype=F32):
+    """The C restatement of vAi's gated-mul shader; x [..., 2H] in device representation."""
+    x = np.ascontiguousarray(x)
+    h = x.shape[-1] // 2
+    rows = int(np.prod(x.shape[:-1])) if x.ndim > 1 else 1
+    out = np.empty(tuple(x.shape[:-1]) + (h,), dtype=np.float32 if o_dtype == F32 else np.uint16)
+    rc = lib().vai_oracle_gated_mul(_ptr(x), _ptr(out), ctypes.c_uint32(rows), ctypes.c_uint32(h), ctypes.c_int(i_dtype),
+                                    ctypes.c_int(o_dtype), ctypes.c_int(epilogue))
+    if rc != 0:
+        raise RuntimeError(f"oracle returned {rc}")
+    return out
+
+
 def argmax_c(logits, dtype=F32):
     """The C restatement of vAi's argmax shader on a [M, N] array in device representation."""
     a = np.ascontiguousarray(logits)

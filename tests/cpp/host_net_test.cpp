@@ -4,11 +4,13 @@
 #include <cstdio>
 
 #include "../../vai_b200/host/net.h"
+#include "../../vai_b200/host/gated_mul.h"
 #include "../../vai_b200/host/norm.h"
 
 using namespace vai;
 using vai::node::Argmax;
 using vai::node::Gate;
+using vai::node::GatedMul;
 using vai::node::LayerNorm;
 using vai::node::Linear;
 using vai::node::RmsNorm;
@@ -45,6 +47,95 @@ static void wiring()
     threw = false;
     try { loop.sortedNodes(); } catch (const std::runtime_error&) { threw = true; }
     EXPECT(threw);
+}
+
+// GatedMul: the reference's slots and shape rule (vai/nodes/gated-mul.h:50-84); no device needed.
+static void gated_mul_host_logic()
+{
+    GatedMul g({.activation = Epilogue::Gelu});
+    EXPECT(g.slots().count("in0") && g.slots().count("out0") && g.slots().size() == 2);
+    EXPECT(GatedMul().config_.activation == Epilogue::Silu);            // the reference's default
+    g["in0"] = Tensor({3, 5, 48}, Dtype::Fp16);
+    g.prepare();
+    EXPECT(g["out0"].shape() == (std::vector<uint32_t>{3, 5, 24}) && g["out0"].dtype() == Dtype::Fp32);
+    g.setODtype(Dtype::Fp16);
+    g.prepare();
+    EXPECT(g["out0"].dtype() == Dtype::Fp16);
+    g["in0"] = Tensor({3, 7}, Dtype::Fp32);
+    bool threw = false;
+    try { g.prepare(); } catch (const std::invalid_argument&) { threw = true; }
+    EXPECT(threw);
+    // which Linears may carry the gate in their epilogue
+    Linear plain({.inDim = 8, .outDim = 16});
+    Linear odd({.inDim = 8, .outDim = 15});
+    Linear act({.inDim = 8, .outDim = 16, .epilogue = Epilogue::Relu});
+    Linear res({.inDim = 8, .outDim = 16, .acceptResidual = true});
+    Linear scaled({.inDim = 8, .outDim = 16, .scalarScale = 2.0f});
+    EXPECT(plain.canAbsorbGate() && !odd.canAbsorbGate() && !act.canAbsorbGate() && !res.canAbsorbGate() && !scaled.canAbsorbGate());
+    plain["bias"] = Tensor({2, 16}, Dtype::Fp32);                      // a bias table over rows is not one entry per weight row
+    EXPECT(!plain.canAbsorbGate());
+    plain["bias"] = Tensor({16}, Dtype::Fp32);
+    EXPECT(plain.canAbsorbGate());
+    GatedMul h;
+    EXPECT(!h.absorbIntoProducer(act, "out0") && !h.fused());
+    EXPECT(h.absorbIntoProducer(plain, "out0") && h.fused() && plain.gateFused());
+    h.resetFusion();
+    plain.resetFusion();
+    EXPECT(!h.fused() && !plain.gateFused());
+}
+
+// The gated MLP of the Llama / Gemma blocks wired exactly as vAi's GatedFeedForward wires it
+// (vai/groups/gated-feed-forward.h:38-46): gateValue - gatedMul - out (+ residual).  Recorded
+// with the pair merged into one launch and, for comparison, as separate launches.
+static void gated_mlp_on_gpu(bool fuse, bool secondReader)
+{
+    const uint32_t M = 6, D = 64, H = 80;
+    std::vector<float> x(M * D), wg(2 * H * D), wo(D * H);
+    unsigned s = 2024;
+    auto rnd = [&] { s = s * 1664525u + 1013904223u; return ((s >> 8) & 0xFFFF) / 32768.0f - 1.0f; };
+    for (auto& v : x) v = rnd();
+    for (auto& v : wg) v = rnd() * 0.2f;
+    for (auto& v : wo) v = rnd() * 0.2f;
+    initVAIEngine(0);
+    NeuralNet net({.wDefaultDtype = Dtype::Fp32, .fuseGatedMul = fuse});
+    Linear gateValue({.inDim = D, .outDim = 2 * H});
+    GatedMul gatedMul({.activation = Epilogue::Silu});
+    Linear out({.inDim = H, .outDim = D, .acceptResidual = true});
+    gateValue - gatedMul - out;
+    net.input("x") - gateValue;
+    net.input("x") - "residual" / out;
+    out - net.output("y");
+    if (secondReader) gateValue - net.output("hidden2");
+    net.finish();
+    gateValue["weight"] = Tensor({2 * H, D}, Dtype::Fp32); gateValue["weight"].upload(wg.data());
+    out["weight"] = Tensor({D, H}, Dtype::Fp32); out["weight"].upload(wo.data());
+    vaicu_device_synchronize(deviceHandle());
+    auto res = net({{"x", HostTensor::fromFloats({M, D}, x)}});
+    const bool merged = fuse && !secondReader;
+    EXPECT(gatedMul.fused() == merged && gateValue.gateFused() == merged);
+    EXPECT(gateValue["out0"].shape().back() == (merged ? H : 2 * H));
+    const std::vector<float> y = res.at("y").floats();
+    double worst = 0;
+    for (uint32_t m = 0; m < M; ++m) {
+        std::vector<double> h(H);
+        for (uint32_t j = 0; j < H; ++j) {
+            double g = 0, u = 0;
+            for (uint32_t k = 0; k < D; ++k) {
+                g += double(x[m * D + k]) * wg[j * D + k];
+                u += double(x[m * D + k]) * wg[(H + j) * D + k];
+            }
+            h[j] = g / (1.0 + std::exp(-g)) * u;
+        }
+        for (uint32_t n = 0; n < D; ++n) {
+            double acc = 0;
+            for (uint32_t j = 0; j < H; ++j) acc += h[j] * wo[n * H + j];
+            const double want = acc + x[m * D + n];
+            worst = std::fmax(worst, std::fabs(want - y[m * D + n]) / std::fmax(1.0, std::fabs(want)));
+        }
+    }
+    std::printf("gated MLP fuse=%d second reader=%d merged=%d worst rel err %.3g\n", (int)fuse, (int)secondReader, (int)merged, worst);
+    EXPECT(worst < 1e-4);
+    if (secondReader) EXPECT(res.at("hidden2").shape == (std::vector<uint32_t>{M, 2 * H}));
 }
 
 static void mlp_on_gpu(bool useGraph)
@@ -272,6 +363,7 @@ int main(int argc, char** argv)
 {
     wiring();
     gates_wiring();
+    gated_mul_host_logic();
     if (argc > 1 && std::string(argv[1]) == "--gpu") {
         mlp_on_gpu(true);
         mlp_on_gpu(false);
@@ -279,6 +371,9 @@ int main(int argc, char** argv)
         norm_head_on_gpu(false);
         topk_on_gpu();
         gates_on_gpu();
+        gated_mlp_on_gpu(true, false);
+        gated_mlp_on_gpu(false, false);
+        gated_mlp_on_gpu(true, true);
     }
     std::printf(fails ? "FAILED (%d)\n" : "ok\n", fails);
     return fails ? 1 : 0;

@@ -20,20 +20,31 @@ def seen(a, dt):
 
 
 class OneLinear(vai_b200.NeuralNet):
-    """The one-node net of the reference's node tests (node_check.py:103-118)."""
+    """The one-node net of the reference's node tests (node_check.py:103-118); with `gated`
+    (an Epilogue) a GatedMul node follows the Linear, wired as vAi's gated feed-forward
+    wires gateValue - gatedMul (vai/groups/gated-feed-forward.h:46)."""
 
-    def __init__(self, make, slots, w_dtype=Dtype.F32, use_graph=True):
-        super().__init__(w_default_dtype=w_dtype, use_graph=use_graph)
+    def __init__(self, make, slots, w_dtype=Dtype.F32, use_graph=True, gated=None, o_dtype=None, fuse=True):
+        super().__init__(w_default_dtype=w_dtype, use_graph=use_graph, fuse_gated_mul=fuse)
         self.node = make()
-        self.input(slots[0]) - slots[0] / self.node - self.output("out0")
+        self.gm = None
+        if gated is None:
+            self.input(slots[0]) - slots[0] / self.node - self.output("out0")
+        else:
+            self.gm = nodes.GatedMulNode(activation=gated)
+            if o_dtype is not None:
+                self.gm.set_o_dtype(o_dtype)
+            self.input(slots[0]) - slots[0] / self.node - self.gm - self.output("out0")
         for slot in slots[1:]:
             self.input(slot) - slot / self.node
 
 
 def run_linear(x, w, bias=None, residual=None, *, i_dtype="f32", w_dtype="f32", o_dtype="f32", b_dtype=None,
                epilogue="NONE", residual_order="AFTER_EPILOGUE", scalar_scale=1.0, split_size=0, gate_fuse=False,
-               kernel=0, use_graph=True):
-    """Returns (out float32 array, expected float64 array, node)."""
+               kernel=0, use_graph=True, fuse=True):
+    """Returns (out float32 array, expected float64 array, node).  gate_fuse=True builds
+    Linear -> GatedMul(epilogue) and expects the net to record the pair as one launch
+    (fuse=False keeps the two launches and the [M, 2H] intermediate in o_dtype)."""
     i_dt, w_dt, o_dt = DT[i_dtype], DT[w_dtype], DT[o_dtype]
     b_dt = DT[b_dtype] if b_dtype else w_dt
     N, K = w.shape
@@ -41,12 +52,14 @@ def run_linear(x, w, bias=None, residual=None, *, i_dtype="f32", w_dtype="f32", 
 
     def make():
         n = nodes.LinearNode(in_dim=K, out_dim=N, accept_residual=residual is not None,
-                             residual_order=getattr(ResidualOrder, residual_order), epilogue=getattr(Epilogue, epilogue),
-                             scalar_scale=scalar_scale, split_size=split_size, gate_fuse=gate_fuse, kernel=kernel)
+                             residual_order=getattr(ResidualOrder, residual_order),
+                             epilogue=Epilogue.NONE if gate_fuse else getattr(Epilogue, epilogue),
+                             scalar_scale=scalar_scale, split_size=split_size, kernel=kernel)
         n.set_o_dtype(o_dt)
         return n
 
-    net = OneLinear(make, slots, w_dtype=w_dt, use_graph=use_graph)
+    net = OneLinear(make, slots, w_dtype=w_dt, use_graph=use_graph, gated=getattr(Epilogue, epilogue) if gate_fuse else None,
+                    o_dtype=o_dt, fuse=fuse)
     net.node["weight"] = Tensor.from_numpy(w, dtype=w_dt)
     if bias is not None:
         net.node["bias"] = Tensor.from_numpy(bias, dtype=b_dt)
@@ -55,6 +68,8 @@ def run_linear(x, w, bias=None, residual=None, *, i_dtype="f32", w_dtype="f32", 
         fed["residual"] = Tensor.from_numpy(residual, dtype=o_dt)
     out = net(**fed)
     got = out.to_numpy().astype(np.float32)
+    if gate_fuse:
+        assert net.node.gate_fuse == fuse and net.gm.fused == fuse, "the Linear -> GatedMul pair was not recorded as asked"
     again = net(**fed).to_numpy().astype(np.float32)
     np.testing.assert_array_equal(again, got, err_msg="the replayed forward differs from the first")
     # the expectation: float64 over the values the kernels read

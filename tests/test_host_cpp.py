@@ -16,7 +16,7 @@ def _build(name):
     lib_dir = os.path.dirname(_lib.LIB_PATH)
     src = os.path.join(CPP, name + ".cpp")
     exe = os.path.join(CPP, name)
-    headers = [os.path.join(ROOT, "vai_b200", "host", h) for h in ("linear.h", "net.h", "norm.h", "safetensors.h")]
+    headers = [os.path.join(ROOT, "vai_b200", "host", h) for h in ("linear.h", "net.h", "norm.h", "gated_mul.h", "safetensors.h")]
     newest = max(os.path.getmtime(f) for f in [src, _lib.LIB_PATH] + headers)
     if not os.path.exists(exe) or os.path.getmtime(exe) < newest:
         subprocess.run(["g++", "-std=c++20", "-O1", "-Wall", "-o", exe, src, "-L", lib_dir, "-lvaicu",

@@ -49,8 +49,8 @@ def test_linear_node_argument_checks():
         nodes.LinearNode(in_dim=8, out_dim=8, split_size=16)      # must be 0 or >= 32 (vAi linear.cpp:27)
     with pytest.raises(ValueError):
         nodes.LinearNode(in_dim=0, out_dim=8)
-    with pytest.raises(ValueError):
-        nodes.LinearNode(in_dim=8, out_dim=7, gate_fuse=True)
+    with pytest.raises(TypeError):
+        nodes.LinearNode(in_dim=8, out_dim=8, gate_fuse=True)     # not part of the reference's Config (linear.h:270-280)
     n = nodes.LinearNode(in_dim=8, out_dim=4, accept_residual=True)
     assert set(n.slots) == {"out0", "in0", "weight", "partial", "bias", "residual"}   # vAi linear.h:2134-2144
     assert not n.has_bias()
@@ -77,8 +77,49 @@ def test_chain_builder_shapes():
     nodes_ = presets.build_linear_chain(net, "llama-3.2-1b", layers=2, vocab_rows=1024)
     assert len(nodes_) == 2 * 6 + 1
     assert [(n.in_dim, n.out_dim) for n in nodes_[:6]] == [(2048, 2048), (2048, 512), (2048, 512), (2048, 2048), (2048, 16384), (8192, 2048)]
-    assert nodes_[4].gate_fuse and nodes_[3].accept_residual and nodes_[5].accept_residual
+    assert nodes_[4].can_absorb_gate() and nodes_[3].accept_residual and nodes_[5].accept_residual
+    # gateValue - gatedMul - out, as vAi's gated feed-forward wires it (gated-feed-forward.h:46)
+    gm, gm_slot = nodes_[5].links["in0"]
+    from vai_b200.nodes import GatedMulNode
+    assert isinstance(gm, GatedMulNode) and gm.links["in0"] == (nodes_[4], "out0") and gm.activation == engine.Epilogue.SILU
     assert nodes_[0]["weight"].shape == (2048, 2048) and nodes_[0]["weight"].dtype == Dtype.BF16
     w = engine.bits_to_f32(nodes_[0]["weight"].host, Dtype.BF16)
     assert abs(float(w.std()) - 0.02) < 1e-3
     net._sorted()
+
+
+def test_gated_mul_node_and_the_merge_rule():
+    """GatedMulNode has the reference's single option and slots (vAi vai/nodes/gated-mul.h:34-54);
+    a Linear may carry it in its epilogue only when it ends at acc + bias[row]."""
+    from vai_b200 import Epilogue, nodes
+    _net()
+    g = nodes.GatedMulNode()
+    assert g.activation == Epilogue.SILU and set(g.slots) == {"out0", "in0"}
+    g = nodes.GatedMulNode(activation=Epilogue.GELU_TANH)
+    g.slots["in0"] = engine.Tensor((3, 5, 48), Dtype.F16)
+    g.prepare()
+    assert g["out0"].shape == (3, 5, 24) and g["out0"].dtype == Dtype.F32      # the net's default output dtype
+    g.set_o_dtype(Dtype.F16)
+    g.prepare()
+    assert g["out0"].dtype == Dtype.F16
+    g.slots["in0"] = engine.Tensor((3, 7), Dtype.F32)
+    with pytest.raises(ValueError):
+        g.prepare()
+
+    plain = nodes.LinearNode(in_dim=8, out_dim=16)
+    assert plain.can_absorb_gate() and not plain.gate_fuse
+    assert not nodes.LinearNode(in_dim=8, out_dim=15).can_absorb_gate()
+    assert not nodes.LinearNode(in_dim=8, out_dim=16, epilogue=Epilogue.RELU).can_absorb_gate()
+    assert not nodes.LinearNode(in_dim=8, out_dim=16, accept_residual=True).can_absorb_gate()
+    assert not nodes.LinearNode(in_dim=8, out_dim=16, scalar_scale=2.0).can_absorb_gate()
+    plain["bias"] = engine.Tensor((2, 16), Dtype.F32)      # a table over rows is not one entry per weight row
+    assert not plain.can_absorb_gate()
+    plain["bias"] = engine.Tensor((16,), Dtype.F32)
+    assert plain.can_absorb_gate()
+    g.set_o_dtype(Dtype.BF16)
+    assert g.absorb_into_producer(plain, "out0") and g.fused and plain.gate_fuse
+    assert plain._gate == Epilogue.GELU_TANH and plain._gate_o_dtype == Dtype.BF16
+    g.reset_fusion()
+    plain.reset_fusion()
+    assert not g.fused and not plain.gate_fuse
+    assert not g.absorb_into_producer(nodes.RmsNormNode(), "out0")

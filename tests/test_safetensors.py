@@ -242,8 +242,8 @@ def test_cpp_large_tensor_crosses_staging_parts(tmp_path, device):
 
 @pytest.mark.gpu
 def test_checkpoint_weights_drive_a_linear(tmp_path, device):
-    """gate_proj | up_proj of a synthetic checkpoint -> gateValue Linear with the SiLU gate
-    fused, against float64 over the stored bf16 values."""
+    """gate_proj | up_proj of a synthetic checkpoint -> gateValue Linear - GatedMul(SiLU), recorded
+    as one launch, against float64 over the stored bf16 values."""
     import vai_b200
     from vai_b200 import Epilogue, Tensor, nodes
     values = _tiny_llama(tmp_path, blocks=1, d=64, kv=32, ffn=96, vocab=40, shards=1)
@@ -253,13 +253,14 @@ def test_checkpoint_weights_drive_a_linear(tmp_path, device):
     class Net(vai_b200.NeuralNet):
         def __init__(self):
             super().__init__(w_default_dtype=Dtype.BF16)
-            self.lin = nodes.LinearNode(in_dim=64, out_dim=192, epilogue=Epilogue.SILU, gate_fuse=True)
-            self.input("in0") - self.lin - self.output("out0")
+            self.lin = nodes.LinearNode(in_dim=64, out_dim=192)
+            self.input("in0") - self.lin - nodes.GatedMulNode(activation=Epilogue.SILU) - self.output("out0")
 
     net = Net()
     net.lin["weight"] = w["blocks"][0]["gateValue"]
     x = np.random.default_rng(1).standard_normal((3, 64)).astype(np.float32)
     got = net(Tensor.from_numpy(x)).to_numpy()
+    assert net.lin.gate_fuse
     gate = orc.to_f32(orc.to_dtype(values["model.layers.0.mlp.gate_proj.weight"], orc.BF16), orc.BF16)
     up = orc.to_f32(orc.to_dtype(values["model.layers.0.mlp.up_proj.weight"], orc.BF16), orc.BF16)
     want = orc.linear_f64(x, np.concatenate([gate, up]), epilogue=orc.EPILOGUES["SILU"], gate_fuse=True)

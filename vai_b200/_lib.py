@@ -75,6 +75,7 @@ SIGNATURES = {
                                                                    ctypes.c_int, ctypes.c_float]),
     "vaicu_layer_norm_run": (ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, ctypes.c_int,
                                                                    ctypes.c_int, ctypes.c_float]),
+    "vaicu_gated_mul_run": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "vaicu_argmax_run": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]),
     "vaicu_argmax_workspace_bytes": (ctypes.c_int, [ctypes.c_uint32, ctypes.c_uint32, ctypes.POINTER(ctypes.c_size_t)]),
     "vaicu_argmax_pairs_run": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,

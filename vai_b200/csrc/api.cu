@@ -881,6 +881,19 @@ int vaicu_layer_norm_run(vaicu_device* dev, vaicu_stream_t stream, const void* i
     return VAICU_OK;
 }
 
+int vaicu_gated_mul_run(vaicu_device* dev, vaicu_stream_t stream, const void* in, void* out, uint32_t rows, uint32_t H,
+                        int i_dtype, int o_dtype, int activation)
+{
+    if (!dev || !in || !out || rows == 0 || H == 0) return VAICU_ERR_INVALID_VALUE;
+    if (!valid_dtype(i_dtype) || !valid_dtype(o_dtype)) return VAICU_ERR_INVALID_VALUE;
+    if (activation < 0 || activation > VAICU_EPILOGUE_SIGMOID) return VAICU_ERR_INVALID_VALUE;
+    if ((uint64_t)rows * H * 2u >= (1ull << 32)) return VAICU_ERR_INVALID_VALUE;      // vAi indexes with uint32
+    if ((reinterpret_cast<uintptr_t>(in) & (dtype_size(i_dtype) - 1u)) || (reinterpret_cast<uintptr_t>(out) & (dtype_size(o_dtype) - 1u)))
+        return VAICU_ERR_ALIGNMENT;
+    VAICU_CUDA(launch_gated_mul(in, out, rows, H, i_dtype, o_dtype, activation, dev->sm_count, (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
 int vaicu_argmax_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, void* out_u32)
 {
     if (!logits || !out_u32 || M == 0 || N == 0) return VAICU_ERR_INVALID_VALUE;

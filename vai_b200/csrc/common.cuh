@@ -149,6 +149,9 @@ cudaError_t launch_rms_norm(const void* in, const void* scale, const void* shift
 cudaError_t launch_layer_norm(const void* in, const void* scale, const void* shift, const void* res, void* out, uint32_t rows,
                             uint32_t feat, int i_dtype, int w_dtype, int o_dtype, float eps, int sm_count, cudaStream_t stream);
 
+cudaError_t launch_gated_mul(const void* in, void* out, uint32_t rows, uint32_t H, int i_dtype, int o_dtype, int act,
+                             int sm_count, cudaStream_t stream);
+
 // Records "<where>: <what>" as the calling thread's last error text
 // (vaicu_last_cuda_error).
 void set_last_error(const char* where, const char* what);

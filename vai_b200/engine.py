@@ -438,7 +438,7 @@ class NeuralNet:
         return getattr(cls._tls, "net", None)
 
     def __init__(self, w_default_dtype=Dtype.F16, o_default_dtype=Dtype.F32, device=None, use_graph=True,
-                 parallel_branches=True, group_siblings=True):
+                 parallel_branches=True, group_siblings=True, fuse_gated_mul=True):
         if Dtype(w_default_dtype) == Dtype.NONE or Dtype(o_default_dtype) == Dtype.NONE:
             raise ValueError("default dtypes may not be NONE")
         self.w_default_dtype = Dtype(w_default_dtype)
@@ -449,6 +449,9 @@ class NeuralNet:
         self._streams = [self.stream]
         self.parallel_branches = parallel_branches
         self.group_siblings = group_siblings
+        # a GatedMul that is the only reader of a gate|value Linear is recorded into that
+        # Linear's launch (False: always two launches and the [.., 2H] intermediate)
+        self.fuse_gated_mul = fuse_gated_mul
         self.max_side_streams = 3
         # outputs up to this size that nothing else reads are stored by their kernel directly into
         # page-locked host memory (0: always a device buffer and a device-to-host copy)
@@ -590,6 +593,17 @@ class NeuralNet:
         for n in order:
             for src in (live[n].values() if n.producers else n.links.values()):
                 uses[src] = uses.get(src, 0) + 1
+        # Linear -> GatedMul becomes one launch when nothing else reads the Linear's output
+        for n in self._nodes:
+            if hasattr(n, "reset_fusion"):
+                n.reset_fusion()
+        if self.fuse_gated_mul:
+            for n in order:
+                absorb = getattr(n, "absorb_into_producer", None)
+                if absorb is not None:
+                    src = (live[n] if n.producers else n.links).get("in0")
+                    if src is not None and uses.get(src, 0) == 1:
+                        absorb(*src)
         direct = set()
         for out in self._outputs.values():
             if out in live and "in0" in live[out] and uses.get(live[out]["in0"], 0) == 1:

@@ -178,6 +178,12 @@ public:
     const std::map<std::string, NodeSlot>& slots() const { return slots_; }
     void setODtype(Dtype dt) { oDtype_ = dt; }
     void setODefaultDtype(Dtype dt) { oDefault_ = dt; }
+    Dtype resolvedODtype() const { return oDtype_ == Dtype::None ? oDefault_ : oDtype_; }
+    // Record-time merging of neighbouring nodes into one launch.  The engine clears every
+    // node's state before it records, then offers each node the producer of its "in0" when
+    // this node is that output's only reader; true = the producer now does this node's work.
+    virtual void resetFusion() {}
+    virtual bool absorbIntoProducer(Node& /*producer*/, const std::string& /*slot*/) { return false; }
     virtual void prepare() = 0;
     virtual void run(vaicu_stream_t stream) = 0;
 };
@@ -221,6 +227,19 @@ public:
     bool hasBias() const { return (*this)["bias"].validShape(); }   // linear.h:287
     const vaicu_linear_info& info() const { return info_; }
 
+    // The GatedMul behind a gate|value Linear (vai/groups/gated-feed-forward.h:38-46) can ride
+    // in this node's epilogue when the node itself ends at acc + bias[row]: no epilogue,
+    // residual or scale of its own, an even outDim, a bias (if any) of outDim entries.  The
+    // kernel then writes [.., outDim / 2] = activation(gate) * value from its accumulators.
+    bool canAbsorbGate() const
+    {
+        return config_.epilogue == vai::Epilogue::None && !config_.acceptResidual && config_.scalarScale == 1.0f &&
+               config_.outDim % 2 == 0 && (!hasBias() || (*this)["bias"].numElements() == config_.outDim);
+    }
+    void absorbGate(vai::Epilogue activation, Dtype oDtype) { gate_ = true; gateActivation_ = activation; gateODtype_ = oDtype; }
+    bool gateFused() const { return gate_; }
+    void resetFusion() override { gate_ = false; }
+
     // linear.h:2291-2704 without the vendor tables: dtype resolution, M, the repeat
     // lengths of bias / residual, then the library's plan (kernel + split choice).
     void prepare() override
@@ -232,7 +251,7 @@ public:
         const uint32_t N = config_.outDim, K = config_.inDim;
         if (!in.validShape() || in.shape().back() != K) throw std::invalid_argument("in0: last axis must equal inDim");
         if (!w.isShapeOf(N, K)) throw std::invalid_argument("weight must be [outDim, inDim]");
-        const Dtype oDtype = oDtype_ == Dtype::None ? oDefault_ : oDtype_;
+        const Dtype oDtype = gate_ ? gateODtype_ : resolvedODtype();   // a merged launch writes the GatedMul's output
         const uint32_t M = outerSize(in.shape());
         auto repeatOf = [&](const Tensor& t) {   // linear.h:2333-2338
             const uint32_t outElems = M * N, elems = t.numElements();
@@ -247,7 +266,7 @@ public:
         if (hasBias()) {
             d.has_bias = 1;
             d.b_dtype = (int)(*this)["bias"].dtype();
-            d.bias_elems = repeatOf((*this)["bias"]);
+            d.bias_elems = gate_ ? N : repeatOf((*this)["bias"]);
         }
         if (config_.acceptResidual) {
             const Tensor& r = (*this)["residual"];
@@ -256,9 +275,10 @@ public:
             d.residual_elems = repeatOf(r);
         }
         d.residual_order = (int)config_.residualOrder;
-        d.epilogue = (int)config_.epilogue;
+        d.epilogue = (int)(gate_ ? gateActivation_ : config_.epilogue);
         d.scalar_scale = config_.scalarScale;
         d.split_size = config_.splitSize;
+        d.gate_fuse = gate_ ? 1 : 0;
         if (!plan_ || std::memcmp(&d, &desc_, sizeof(d)) != 0) {   // parameters changed: new plan (linear.h:2365)
             if (plan_) { vaicu_linear_plan_destroy(plan_); plan_ = nullptr; }
             initVAIEngine();
@@ -269,7 +289,7 @@ public:
         // "partial" carries the plan's workspace (linear.h:2697-2698); empty when none is needed
         (*this)["partial"] = info_.workspace_bytes ? Tensor({(uint32_t)((info_.workspace_bytes + 3) / 4)}, Dtype::Fp32) : Tensor();
         auto outShape = in.shape();
-        outShape.back() = N;
+        outShape.back() = gate_ ? N / 2 : N;
         (*this)["out0"] = Tensor(outShape, oDtype);
     }
 
@@ -289,6 +309,9 @@ private:
     vaicu_linear_plan* plan_ = nullptr;
     vaicu_linear_desc desc_{};
     vaicu_linear_info info_{};
+    bool gate_ = false;
+    vai::Epilogue gateActivation_ = vai::Epilogue::None;
+    Dtype gateODtype_ = Dtype::Fp32;
 };
 
 }   // namespace node

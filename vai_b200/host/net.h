@@ -135,6 +135,7 @@ struct NeuralNetConfig {
     Dtype wDefaultDtype = Dtype::Fp16;   // vai/engine/neural-net.h:279
     Dtype oDefaultDtype = Dtype::Fp32;   // vai/engine/neural-net.h:283
     bool useGraph = true;                // replay a recorded CUDA graph (else re-enqueue the launches)
+    bool fuseGatedMul = true;            // record Linear -> GatedMul as one launch where the wiring allows it
 };
 
 class NeuralNet : public NodeOwner
@@ -340,6 +341,26 @@ private:
         auto live = liveNodes(sorted, names);
         for (Node* n : sorted)
             if (live.count(n)) rec.order.push_back(n);
+        // Neighbours that one kernel can serve (a gate|value Linear and the GatedMul behind it)
+        // are merged before anything is prepared: a node is offered the producer of its in0
+        // when it is that output's only reader in this recording.
+        for (Node* n : nodes_) {
+            n->resetFusion();
+            n->setODefaultDtype(config_.oDefaultDtype);
+        }
+        if (config_.fuseGatedMul) {
+            auto linksOf = [&](Node* n) -> const std::map<std::string, std::pair<Node*, std::string>>& {
+                return n->producers().empty() ? n->links() : live[n];
+            };
+            std::map<std::pair<Node*, std::string>, int> readers;
+            for (Node* n : rec.order)
+                for (auto& [slot, src] : linksOf(n)) ++readers[src];
+            for (Node* n : rec.order) {
+                auto& links = linksOf(n);
+                auto it = links.find("in0");
+                if (it != links.end() && readers[it->second] == 1) n->absorbIntoProducer(*it->second.first, it->second.second);
+            }
+        }
         for (Node* n : rec.order) {
             if (!n->producers().empty()) n->links() = live[n];       // this recording's producer of every slot
             for (auto& [slot, src] : n->links()) (*n)[slot] = (*src.first)[src.second];

@@ -21,29 +21,30 @@ class LinearNode(Node):
     split_size is the K length per split-K span (0 = the kernel's heuristic, otherwise
     >= 32) and only matters past 8 input rows.
 
-    gate_fuse (extension): `weight` holds [2H, K] with gate rows first (the layout of
-    vAi's gateValue Linear, vai/groups/gated-feed-forward.h:38) and out0 is
-    [..., H] = epilogue(gate) * value, i.e. the Linear and the GatedMul node that
-    follows it (vai/nodes/gated-mul.h:9-20) in one pass; out_dim stays 2H.
+    When the only reader of out0 is a GatedMulNode (the gateValue - gatedMul wiring of
+    vAi's gated feed-forward, vai/groups/gated-feed-forward.h:38-46) and this node does
+    nothing after the dot product but add a per-row bias, the net records the pair as one
+    launch: `weight` [2H, K] holds the gate rows first, and the kernel writes
+    [..., H] = activation(gate) * value straight from its accumulators.  Nothing in the
+    node's signature asks for that; `gate_fuse` reports whether the current recording did it.
     """
 
     def __init__(self, in_dim, out_dim, accept_residual=False, residual_order=ResidualOrder.AFTER_EPILOGUE,
-                 epilogue=Epilogue.NONE, scalar_scale=1.0, split_size=0, gate_fuse=False, kernel=KERNEL_AUTO):
+                 epilogue=Epilogue.NONE, scalar_scale=1.0, split_size=0, kernel=KERNEL_AUTO):
         super().__init__()
         if not (split_size == 0 or split_size >= 32):
             raise ValueError("split_size: must be 0 or >= 32")
         if in_dim <= 0 or out_dim <= 0:
             raise ValueError("in_dim and out_dim must be positive")
-        if gate_fuse and (out_dim % 2 or accept_residual):
-            raise ValueError("gate_fuse needs an even out_dim and takes no residual")
         self.in_dim, self.out_dim = int(in_dim), int(out_dim)
         self.accept_residual = bool(accept_residual)
         self.residual_order = ResidualOrder(residual_order)
         self.epilogue = Epilogue(epilogue)
         self.scalar_scale = float(scalar_scale)
         self.split_size = int(split_size)
-        self.gate_fuse = bool(gate_fuse)
         self.kernel = int(kernel)
+        self._gate = None           # activation of the GatedMul recorded into this node's launch
+        self._gate_o_dtype = None   # ... and that node's output dtype
         # slot set of Linear::Linear (linear.h:2134-2144)
         self.add_slot("out0", OUTPUT)
         self.add_slot("in0", INPUT)
@@ -59,6 +60,24 @@ class LinearNode(Node):
     def has_bias(self):
         return self["bias"].valid_shape()
 
+    @property
+    def gate_fuse(self):
+        """True while a GatedMul is recorded into this node's launch."""
+        return self._gate is not None
+
+    def reset_fusion(self):
+        self._gate = self._gate_o_dtype = None
+
+    def can_absorb_gate(self):
+        """A GatedMul may ride in this node's epilogue when the node itself ends at
+        `acc + bias[row]`: no epilogue, residual or scale of its own, an even out_dim,
+        and a bias (if any) with one entry per weight row."""
+        return (self.epilogue == Epilogue.NONE and not self.accept_residual and self.scalar_scale == 1.0
+                and self.out_dim % 2 == 0 and (not self.has_bias() or self["bias"].num_elements() == self.out_dim))
+
+    def absorb_gate(self, activation, o_dtype):
+        self._gate, self._gate_o_dtype = Epilogue(activation), Dtype(o_dtype)
+
     def _device(self):
         from .engine import Device
         return self.net.device if self.net is not None else Device.default()
@@ -73,6 +92,8 @@ class LinearNode(Node):
         if tuple(w.shape) != (self.out_dim, self.in_dim):
             raise ValueError(f"weight shape {w.shape} != {(self.out_dim, self.in_dim)}")
         o_dtype = self.o_dtype if self.o_dtype != Dtype.NONE else (self.net.o_default_dtype if self.net else Dtype.F32)
+        if self.gate_fuse:
+            o_dtype = self._gate_o_dtype          # the fused launch writes the GatedMul's output
         M = 1
         for s in x.shape[:-1]:
             M *= s
@@ -100,7 +121,7 @@ class LinearNode(Node):
             d.has_residual = 1
             d.residual_elems = repeat_of(r, out_cols, M * out_cols)
         d.residual_order = int(self.residual_order)
-        d.epilogue = int(self.epilogue)
+        d.epilogue = int(self._gate if self.gate_fuse else self.epilogue)
         d.scalar_scale = self.scalar_scale
         d.split_size = self.split_size
         d.gate_fuse = 1 if self.gate_fuse else 0
@@ -173,6 +194,68 @@ class LinearNode(Node):
                 lib.vaicu_linear_plan_destroy(h)
         except Exception:
             pass
+
+
+class GatedMulNode(Node):
+    """GLU gating (vAi vai/nodes/gated-mul.h:9-20): in0 [..., 2H] -> out0 [..., H] =
+    activation(in0[..., j]) * in0[..., H + j]; the leading half is the activated one.
+    activation names the variant (SILU: SwiGLU, GELU / GELU_TANH: GEGLU, RELU: ReGLU,
+    NONE: bilinear).  Python-facing signature as in the reference's binding
+    (python/bindings/nodes/gated-mul.cpp).
+
+    Placed right after a gate|value LinearNode whose output nothing else reads, the node
+    launches nothing: the net records it into that Linear's epilogue (see LinearNode) and
+    out0 is the Linear's output.  Otherwise it is one streaming kernel."""
+
+    def __init__(self, activation=Epilogue.SILU):
+        super().__init__()
+        self.activation = Epilogue(activation)
+        self.add_slot("out0", OUTPUT)
+        self.add_slot("in0", INPUT)
+        self.fused = False
+
+    def reset_fusion(self):
+        self.fused = False
+
+    def _resolved_o_dtype(self):
+        return self.o_dtype if self.o_dtype != Dtype.NONE else (self.net.o_default_dtype if self.net else Dtype.F32)
+
+    def absorb_into_producer(self, src, src_slot):
+        """Called by the net while it records, when this node is the only reader of
+        src's `src_slot`: merge into a Linear that can carry the gate in its epilogue."""
+        if isinstance(src, LinearNode) and src_slot == "out0" and src.can_absorb_gate():
+            src.absorb_gate(self.activation, self._resolved_o_dtype())
+            self.fused = True
+        return self.fused
+
+    def prepare(self):
+        x = self["in0"]
+        if self.fused:
+            self.slots["out0"] = x          # the Linear already wrote activation(gate) * value
+            return
+        if not x.valid_shape() or len(x.shape) < 1 or x.shape[-1] % 2:
+            raise ValueError("in0 needs an even last axis")
+        self.slots["out0"] = Tensor(tuple(x.shape[:-1]) + (x.shape[-1] // 2,), self._resolved_o_dtype())
+
+    def bind(self):
+        if self.fused:
+            def nothing(stream):
+                pass
+            nothing.kernel_launches = 0
+            return nothing
+        from .engine import Device
+        dev = self.net.device if self.net is not None else Device.default()
+        x, o = self["in0"], self["out0"]
+        h = o.shape[-1]
+        rows = o.num_elements() // h
+        args = (dev.handle, x.ptr, o.ptr, rows, h, int(x.dtype), int(o.dtype), int(self.activation))
+        run = dev.lib.vaicu_gated_mul_run
+
+        def launch(stream):
+            _lib.check(run(args[0], stream, *args[1:]), "vaicu_gated_mul_run")
+
+        launch.kernel_launches = 1
+        return launch
 
 
 class ArgmaxNode(Node):

@@ -4,9 +4,9 @@ builder that wires one decode/prefill step's Linear nodes as a chain.
 Shapes follow the reference's nets: Llama 3.2 (models/production/llama3/net.h:34-35,
 50-62), GPT-2 small (models/production/gpt2/net.h:34,42-53), Gemma 3 4B
 (models/production/gemma3/net.h:54).  Per block the reference has separate Linear
-nodes for q, k, v, the attention output (+residual), one gate|value Linear
-(vai/groups/gated-feed-forward.h:38) and the down projection (+residual); the lm_head
-follows the last block.  Only the Linear nodes are built here: attention, norms and
+nodes for q, k, v, the attention output (+residual), one gate|value Linear, the GatedMul
+behind it (vai/groups/gated-feed-forward.h:38-46) and the down projection (+residual); the
+lm_head follows the last block.  Only those nodes are built here: attention, norms and
 rope are other operators.  The stand-in wiring keeps every Linear's shape, dtype and
 epilogue: `o` reads q's output in place of the attention result, the residual inputs
 read the net input (unit variance) and the o / down projections carry a scalar_scale,
@@ -16,7 +16,7 @@ number of blocks with N(0, 0.02) weights.
 import numpy as np
 
 from .engine import Dtype, Epilogue, Tensor
-from .nodes import LinearNode
+from .nodes import GatedMulNode, LinearNode
 
 PRESETS = {
     # name: layers, d_model, q_dim, kv_dim, ffn (H), vocab, gate activation, biases
@@ -97,13 +97,17 @@ class _BitsSource:
 
 def build_linear_chain(net, name, *, w_dtype=Dtype.BF16, fuse_gate=True, seed=0, layers=None, lm_head=True,
                        vocab_rows=None, argmax=False, share_weights=None):
-    """Adds one step's Linear nodes to `net` and wires them; returns the list of nodes.
+    """Adds one step's Linear nodes to `net` and wires them; returns the list of Linear nodes.
+    The gated MLP is wired as the reference's group does, gateValue - gatedMul - out;
+    fuse_gate=False makes the net record the GatedMul as a launch of its own instead of
+    folding it into the gate|value Linear.
     Input slot "x" [M, d]; output "logits" [M, vocab] (or the last hidden state when
     lm_head is False).  With argmax=True an Argmax node follows the lm_head and the
     output is "token" [M] (raw uint32), the greedy-decode step of the reference's nets.
     Weights ~ N(0, 0.02) in `w_dtype`; share_weights = the node list of another chain of
     the same preset makes this chain use those nodes' weight tensors (same storage)."""
     p = PRESETS[name]
+    net.fuse_gated_mul = bool(fuse_gate)
     src = _BitsSource(w_dtype, 0.02, seed) if share_weights is None else None
     shared = iter(share_weights) if share_weights is not None else None
 
@@ -123,9 +127,8 @@ def build_linear_chain(net, name, *, w_dtype=Dtype.BF16, fuse_gate=True, seed=0,
         specs = block_linears(p)
         made = {}
         for lname, k, n, ex in specs:
-            gate = bool(ex.get("gate")) and fuse_gate
             node = LinearNode(in_dim=k, out_dim=n, accept_residual=bool(ex.get("residual")),
-                              epilogue=act if (gate or ex.get("act")) else Epilogue.NONE, gate_fuse=gate,
+                              epilogue=act if ex.get("act") else Epilogue.NONE,
                               scalar_scale={"o": 0.5, "down": 0.25, "fc2": 0.25}.get(lname, 1.0))
             node["weight"] = weight_for(node, (n, k))
             if ex.get("bias") and shared is None:
@@ -138,11 +141,7 @@ def build_linear_chain(net, name, *, w_dtype=Dtype.BF16, fuse_gate=True, seed=0,
             x - made["v"]
             h = made["q"] - made["o"]
             x0 - "residual" / made["o"]
-            h - made["gate_up"]
-            if fuse_gate:
-                made["gate_up"] - made["down"]
-            else:
-                raise NotImplementedError("the unfused chain needs a GatedMul node between gate_up and down")
+            h - made["gate_up"] - GatedMulNode(activation=act) - made["down"]
             x0 - "residual" / made["down"]
             x = Flow_of(made["down"])
         else:
