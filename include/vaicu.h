@@ -130,6 +130,15 @@ VAICU_API int  vaicu_device_synchronize(vaicu_device* dev);
  * (vai/engine/neural-net.cpp:206-217). */
 VAICU_API int  vaicu_device_status(vaicu_device* dev, int* out);
 
+/* Self-test of that report: enqueues one single-warp kernel that waits, with a limit of 1024
+ * probes, on a barrier nothing ever arrives on, gives up, and sets the status word exactly as
+ * the GEMM kernels do when one of their waits runs out; it holds no memory in flight and
+ * returns normally, so the context stays usable.  The next vaicu_device_status() reports
+ * VAICU_ERR_TIMEOUT once and clears the word.  For hosts that want to verify their handling of
+ * a lost step (the reference's counterpart is the device-lost branch of NeuralNet::sync(),
+ * vai/engine/neural-net.cpp:206-217) without anything actually going wrong. */
+VAICU_API int  vaicu_device_selftest_wait_expiry(vaicu_device* dev, vaicu_stream_t stream);
+
 /* ---- buffers (replace eva::Buffer / BufferPool::requestBuffer,
  *      vai/engine/buffer-pool.h:77-134) ---------------------------------- */
 VAICU_API int   vaicu_buffer_alloc(vaicu_device* dev, size_t bytes, vaicu_buffer** out);
@@ -188,8 +197,35 @@ VAICU_API int vaicu_linear_plan_create(vaicu_device* dev, const vaicu_linear_des
  * Linear::setAccDtype (linear.h:291); used by the parity tests to drive every
  * kernel over the same shapes. */
 VAICU_API int vaicu_linear_plan_create_forced(vaicu_device* dev, const vaicu_linear_desc* desc, int kernel, vaicu_linear_plan** out);
+/* Same again with every choice the library would make from the shape open to the caller: a
+ * field left at 0 (tc_pair / tc_wide: at -1) keeps the library's choice.  This is how the
+ * parity tests reach each tile form on small shapes and how a host pins a geometry it has
+ * measured; nothing is read from the environment.  The reference's counterpart is the set of
+ * per-node overrides and vendor tables in Linear::prepare (linear.h:2395-2666).
+ * VAICU_ERR_INVALID_VALUE for a value outside the ranges given here. */
+typedef struct vaicu_linear_tuning {
+    int32_t  kernel;        /* VAICU_KERNEL_*; 0: by shape                                      */
+    int32_t  tc_pair;       /* 1: CTA pairs (cta_group::2, 256-row tiles); 0: single CTAs; -1   */
+    int32_t  tc_wide;       /* 1: single CTA with two 128-row accumulators; 0: off; -1          */
+    uint32_t tc_bn;         /* UMMA N of the unswapped kernel: multiple of 16 in 16..256; 0     */
+    uint32_t tc_splits;     /* number of K splits of the tensor-core kernels; 0                 */
+    int32_t  gemv_rows;     /* weight rows per warp step: 2 or 4; 0                             */
+    int32_t  gemv_k_warps;  /* warps of a block that split K: 1, 2, 4 or 8; 0                   */
+    int32_t  gemv_unroll;   /* k-steps in flight per lane at M = 1: 2 or 4; 0                   */
+    int32_t  gemv_grid;     /* blocks of the weight-streaming kernel; 0                         */
+    int32_t  gemv_plain_launch; /* 1: no programmatic dependent launch (plain stream order)     */
+} vaicu_linear_tuning;
+VAICU_API int vaicu_linear_plan_create_tuned(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_linear_tuning* tuning,
+                                             vaicu_linear_plan** out);
 VAICU_API int vaicu_linear_plan_destroy(vaicu_linear_plan* plan);
 VAICU_API int vaicu_linear_plan_info(const vaicu_linear_plan* plan, vaicu_linear_info* out);
+/* What the most recent vaicu_linear_run on this plan enqueued: *kernel = VAICU_KERNEL_* (0 before
+ * the first run), *vectorized = 1 for the 16-byte-vector / TMA form of that kernel.  A tensor may be
+ * a view at an element offset into a larger buffer (vai/engine/tensor.h:228-242); operands that
+ * are not 16-byte aligned make a run take the element-wise weight-streaming kernel or the FMA
+ * tile kernel instead of the one the plan names, with the same results.  The reference has no
+ * such query: its shaders index by element and never need the distinction. */
+VAICU_API int vaicu_linear_plan_last_run(const vaicu_linear_plan* plan, int* kernel, int* vectorized);
 /* Size of the "partial" temporary slot (linear.h:2697-2698) plus any private
  * staging the chosen kernel needs; 0 when the kernel needs none. */
 VAICU_API int vaicu_linear_workspace_bytes(const vaicu_linear_plan* plan, size_t* out);

@@ -25,7 +25,8 @@ class OneLinear(vai_b200.NeuralNet):
     wires gateValue - gatedMul (vai/groups/gated-feed-forward.h:46)."""
 
     def __init__(self, make, slots, w_dtype=Dtype.F32, use_graph=True, gated=None, o_dtype=None, fuse=True):
-        super().__init__(w_default_dtype=w_dtype, use_graph=use_graph, fuse_gated_mul=fuse)
+        # every activation, output and workspace range sits between 512-byte canary zones
+        super().__init__(w_default_dtype=w_dtype, use_graph=use_graph, fuse_gated_mul=fuse, guard_bytes=512)
         self.node = make()
         self.gm = None
         if gated is None:
@@ -41,7 +42,7 @@ class OneLinear(vai_b200.NeuralNet):
 
 def run_linear(x, w, bias=None, residual=None, *, i_dtype="f32", w_dtype="f32", o_dtype="f32", b_dtype=None,
                epilogue="NONE", residual_order="AFTER_EPILOGUE", scalar_scale=1.0, split_size=0, gate_fuse=False,
-               kernel=0, use_graph=True, fuse=True):
+               kernel=0, use_graph=True, fuse=True, tuning=None):
     """Returns (out float32 array, expected float64 array, node).  gate_fuse=True builds
     Linear -> GatedMul(epilogue) and expects the net to record the pair as one launch
     (fuse=False keeps the two launches and the [M, 2H] intermediate in o_dtype)."""
@@ -54,7 +55,7 @@ def run_linear(x, w, bias=None, residual=None, *, i_dtype="f32", w_dtype="f32", 
         n = nodes.LinearNode(in_dim=K, out_dim=N, accept_residual=residual is not None,
                              residual_order=getattr(ResidualOrder, residual_order),
                              epilogue=Epilogue.NONE if gate_fuse else getattr(Epilogue, epilogue),
-                             scalar_scale=scalar_scale, split_size=split_size, kernel=kernel)
+                             scalar_scale=scalar_scale, split_size=split_size, kernel=kernel, tuning=tuning)
         n.set_o_dtype(o_dt)
         return n
 
@@ -72,6 +73,7 @@ def run_linear(x, w, bias=None, residual=None, *, i_dtype="f32", w_dtype="f32", 
         assert net.node.gate_fuse == fuse and net.gm.fused == fuse, "the Linear -> GatedMul pair was not recorded as asked"
     again = net(**fed).to_numpy().astype(np.float32)
     np.testing.assert_array_equal(again, got, err_msg="the replayed forward differs from the first")
+    assert net.pool.check_guards() >= 1      # the input, and every output or workspace larger than a host-mapped token
     # the expectation: float64 over the values the kernels read
     xs = seen(x, i_dt)
     if net.node.info.kernel in (nodes.KERNEL_TC_GEMM, nodes.KERNEL_TC_SKINNY) and i_dt == Dtype.F32:

@@ -101,12 +101,40 @@ def test_gate_branches_and_optional_input_on_gpu(device):
     out = net(x=Tensor.from_numpy(x), y=Tensor.from_numpy(y))
     np.testing.assert_allclose(out["main"].to_numpy(), np.maximum(x @ w["a"].T, 0) @ w["c"].T, rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(out["side"].to_numpy(), y @ w["d"].T, rtol=1e-5, atol=1e-5)
-    net.gate.set_open(False)                                      # flips the branch: the next call re-records
+    net.gate.set_open(False)                                      # flips the branch: the next call records that state
     out = net(x=Tensor.from_numpy(x), y=Tensor.from_numpy(y))
     np.testing.assert_allclose(out["main"].to_numpy(), -(x @ w["b"].T) @ w["c"].T, rtol=1e-5, atol=1e-5)
     only_side = net(y=Tensor.from_numpy(y))                       # x left out: one output, one Linear recorded
     np.testing.assert_allclose(only_side.to_numpy(), y @ w["d"].T, rtol=1e-5, atol=1e-5)
-    rec = net._recordings[next(k for k in net._recordings if len(k) == 1)]
-    assert rec.kernel_launches == 1
+    assert sorted(r.kernel_launches for r in net._recordings.values()) == [1, 3, 3]
     with pytest.raises(ValueError):
         net(z=Tensor.from_numpy(y))
+
+
+@pytest.mark.gpu
+def test_flipping_a_gate_keeps_one_recording_per_state(device):
+    """A decode loop that flips a gate every step: two recordings in all, and the page-locked
+    staging stays what those two recordings need.  Changing a weight drops the recordings
+    together with their staging and returns their device ranges to the pool."""
+    rng = np.random.default_rng(4)
+    net = _net()
+    w = {k: rng.standard_normal(s).astype(np.float32) for k, s in {"a": (8, 8), "b": (8, 8), "c": (4, 8), "d": (4, 6)}.items()}
+    for k in w:
+        getattr(net, k)["weight"] = Tensor.from_numpy(w[k])
+    x = rng.standard_normal((3, 8)).astype(np.float32)
+    want = {True: np.maximum(x @ w["a"].T, 0) @ w["c"].T, False: -(x @ w["b"].T) @ w["c"].T}
+    pinned = []
+    for step in range(12):
+        is_open = step % 2 == 0
+        net.gate.set_open(is_open)
+        got = net(x=Tensor.from_numpy(x)).to_numpy()
+        np.testing.assert_allclose(got, want[is_open], rtol=1e-5, atol=1e-5)
+        pinned.append(sum(len(r.pinned) for r in net._recordings.values()) + len(net._pinned_ptrs))
+    assert len(net._recordings) == 2
+    assert pinned[1] == pinned[-1] and pinned[1] <= 2 * pinned[0]
+    net.a["weight"] = Tensor.from_numpy(w["a"] * 2)               # a parameter changed: recordings are stale
+    got = net(x=Tensor.from_numpy(x)).to_numpy()                  # gate is closed: branch b, unchanged
+    np.testing.assert_allclose(got, want[False], rtol=1e-5, atol=1e-5)
+    assert len(net._recordings) == 1
+    assert sum(len(r.pinned) for r in net._recordings.values()) + len(net._pinned_ptrs) == pinned[0]
+    assert sum(len(v) for v in net.pool.free.values()) > 0         # the dropped recordings' ranges are reusable

@@ -237,15 +237,13 @@ def test_kernel_choice_by_shape(M, K, w_dtype, expect, device):
 
 @pytest.mark.parametrize("M,K,N", [(1300, 320, 520), (512, 1024, 256), (2048, 192, 1000)])
 @pytest.mark.parametrize("gate", [False, True])
-@pytest.mark.parametrize("mode,bn", [("wide", 256), ("pair", 256), ("pair", 128), ("pair", 64)])
-def test_256_row_tiles(M, K, N, gate, mode, bn, device, monkeypatch):
+@pytest.mark.parametrize("mode,bn", [("wide", 256), ("pair", 256), ("pair", 192), ("pair", 128), ("pair", 64)])
+def test_256_row_tiles(M, K, N, gate, mode, bn, device):
     """256-row tiles of the unswapped tensor-core kernel, forced on small shapes with
     ragged M, N and K tails, bias + residual, gate.  "wide": one CTA, two accumulators,
     one TMEM buffer.  "pair": two CTAs of a cluster share the tile through
     tcgen05.mma.cta_group::2, each staging half of the weights' rows."""
-    monkeypatch.setenv("VAICU_TC_PAIR", "1" if mode == "pair" else "0")
-    monkeypatch.setenv("VAICU_TC_WIDE", "1" if mode == "wide" else "0")
-    monkeypatch.setenv("VAICU_TC_BN", str(bn))
+    tuning = dict(tc_pair=int(mode == "pair"), tc_wide=int(mode == "wide"), tc_bn=bn)
     rng = np.random.default_rng(M + N)
     rows = 2 * N if gate else N
     x = rng.standard_normal((M, K)).astype(np.float32)
@@ -253,27 +251,26 @@ def test_256_row_tiles(M, K, N, gate, mode, bn, device, monkeypatch):
     b = rng.standard_normal(rows).astype(np.float32)
     r = None if gate else rng.standard_normal((M, N)).astype(np.float32)
     got, want, node = run_linear(x, w, b, r, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", b_dtype="f32",
-                                 epilogue="SILU", gate_fuse=gate, kernel=nodes.KERNEL_TC_GEMM)
+                                 epilogue="SILU", gate_fuse=gate, kernel=nodes.KERNEL_TC_GEMM, tuning=tuning)
     assert node.info.tile_m == 256 and node.info.tile_n == (bn // 2 if gate else bn)
     assert_close(got, want, (2e-4, 5e-5), f"{mode} {M}x{K}x{N} gate={gate} bn={bn}")
 
 
 @pytest.mark.parametrize("M,K,N,splits", [(256, 4096, 256, 4), (520, 2048, 300, 3)])
-def test_pair_tiles_split_k_match_single_cta(M, K, N, splits, device, monkeypatch):
+def test_pair_tiles_split_k_match_single_cta(M, K, N, splits, device):
     """Split-K on CTA pairs (raw partials + fold) against the float64 expectation, and the
     unsplit pair kernel bit-identical to the single-CTA kernel (same order of K)."""
     rng = np.random.default_rng(K + N)
     x = rng.standard_normal((M, K)).astype(np.float32)
     w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
-    monkeypatch.setenv("VAICU_TC_PAIR", "1")
-    monkeypatch.setenv("VAICU_TC_SPLITS", str(splits))
-    got, want, node = run_linear(x, w, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", kernel=nodes.KERNEL_TC_GEMM)
+    got, want, node = run_linear(x, w, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", kernel=nodes.KERNEL_TC_GEMM,
+                                 tuning=dict(tc_pair=1, tc_splits=splits))
     assert node.info.split_count == splits and node.info.tile_m == 256
     assert_close(got, want, (2e-4, 5e-5), f"pair split-K {M}x{K}x{N}")
-    monkeypatch.setenv("VAICU_TC_SPLITS", "1")
-    one, _, _ = run_linear(x, w, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", kernel=nodes.KERNEL_TC_GEMM)
-    monkeypatch.setenv("VAICU_TC_PAIR", "0")
-    single, _, node = run_linear(x, w, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", kernel=nodes.KERNEL_TC_GEMM)
+    one, _, _ = run_linear(x, w, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", kernel=nodes.KERNEL_TC_GEMM,
+                           tuning=dict(tc_pair=1, tc_splits=1))
+    single, _, node = run_linear(x, w, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", kernel=nodes.KERNEL_TC_GEMM,
+                                 tuning=dict(tc_pair=0, tc_splits=1))
     assert node.info.tile_m == 128
     np.testing.assert_array_equal(one, single)
 
@@ -377,3 +374,22 @@ def test_scatter_run_writes_slabs_into_wider_outputs(M, K, N, gate, device):
         np.testing.assert_array_equal(got[:, col0:col0 + N], want)
         np.testing.assert_array_equal(got[:, :col0], canary[:, :col0])
         np.testing.assert_array_equal(got[:, col0 + N:], canary[:, col0 + N:])
+
+
+def test_config_1_gpt2_mlp_linear_fp32(device):
+    """The single-node configuration of the benchmark list at its exact size: X [128, 768] fp32
+    ~N(0, 1) seed 0, W [3072, 768] fp32 ~N(0, 0.02), bias ~N(0, 0.02), fused GELU(tanh), output
+    [128, 3072] fp32 (GPT-2 small's fc1, vAi models/production/gpt2/net.h:51).  fp32 operands keep
+    the exact fp32 kernel; bound: |got - ref| <= 1e-4 * max(|ref|, 0.1) against float64."""
+    import torch
+    def draw(seed, shape, std):
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        return (torch.randn(shape, generator=g, dtype=torch.float32) * std).numpy()
+    x, w, b = draw(0, (128, 768), 1.0), draw(1, (3072, 768), 0.02), draw(2, (3072,), 0.02)
+    got, want, node = run_linear(x, w, b, epilogue="GELU_TANH")
+    assert node.info.kernel == nodes.KERNEL_FMA_TILE and got.shape == (128, 3072)
+    rel = np.abs(got - want) / np.maximum(np.abs(want), 0.1)
+    assert rel.max() <= 1e-4, f"worst relative error {rel.max():.3g}"
+    # the C restatement of the reference's scalar tile shader on the same operands
+    d = orc.make_desc(128, 3072, 768, b_dtype=orc.F32, bias_elems=3072, epilogue=3)
+    assert_close(got, orc.linear_c(d, x, w, b), BOUND_FP32, "config 1 vs the shader restatement")

@@ -266,3 +266,96 @@ def test_checkpoint_weights_drive_a_linear(tmp_path, device):
     want = orc.linear_f64(x, np.concatenate([gate, up]), epilogue=orc.EPILOGUES["SILU"], gate_fuse=True)
     np.testing.assert_allclose(got, want, rtol=2e-4, atol=2e-5)
     ckpt.close()
+
+
+# ---- the one real checkpoint the reference ships -------------------------------------------
+# tests/golden/mnist_jroot_model.safetensors is a byte-for-byte copy of the reference's
+# data/ckpts/mnist/jroot/model.safetensors (201 KB, fp32; the weights of its MNIST example,
+# examples/mnist/main.cpp:167-169).  Not written by this repository's save_file, so it pins
+# the two readers to a file produced elsewhere; the `safetensors` wheel is the referee.
+
+MNIST = os.path.join(ROOT, "tests", "golden", "mnist_jroot_model.safetensors")
+MNIST_SHAPES = {"conv1.bias": (32,), "conv1.weight": (32, 1, 3, 3), "conv2.bias": (64,), "conv2.weight": (64, 32, 3, 3),
+                "fc.bias": (10,), "fc.weight": (10, 3136)}
+
+
+def test_reference_checkpoint_python_reader_equals_the_safetensors_wheel():
+    from safetensors.numpy import load_file
+    theirs = load_file(MNIST)
+    p = st.SafetensorsParser(MNIST)
+    assert sorted(p.get_tensor_names()) == sorted(MNIST_SHAPES) == sorted(theirs)
+    for name, shape in MNIST_SHAPES.items():
+        assert p.get_shape(name) == shape and p.get_data_type(name) == "F32"
+        mine = st.tensor(p[name], Dtype.F32).host
+        assert mine.shape == shape
+        assert mine.tobytes() == np.ascontiguousarray(theirs[name]).tobytes(), name
+        # and the conversions of the real values follow the loader's rules
+        for target in (Dtype.F16, Dtype.BF16):
+            np.testing.assert_array_equal(st.tensor(p[name], target).host, orc.to_dtype(theirs[name], ORC_DT[target]))
+    p.close()
+
+
+def test_reference_checkpoint_cpp_reader_equals_python():
+    from safetensors.numpy import load_file
+    theirs = load_file(MNIST)
+    r = subprocess.run([_cpp_exe(), MNIST], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    _check_cpp_listing(r.stdout, MNIST, {k: (v, "F32") for k, v in theirs.items()})
+    # the F32 column of the listing is the checksum of the raw bytes the wheel returns
+    for ln in r.stdout.splitlines():
+        if " | " in ln:
+            name = ln.split()[0]
+            assert int(ln.split(" | ")[1].split()[1], 16) == _fnv(np.ascontiguousarray(theirs[name]).tobytes())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [1, 5, 16, 130])
+def test_reference_checkpoint_fc_layer_on_gpu(rows, device):
+    """The checkpoint's fc Linear ([10, 3136] + bias, fp32 as the MNIST example loads it) driven by
+    both readers' tensors: weight-streaming kernel for up to 8 rows, exact fp32 tile kernel above."""
+    from linear_check import BOUND_FP32, FP32, assert_close
+    from safetensors.numpy import load_file
+
+    import vai_b200
+    from vai_b200 import Tensor, nodes
+    theirs = load_file(MNIST)
+    p = st.SafetensorsParser(MNIST)
+
+    class Net(vai_b200.NeuralNet):
+        def __init__(self):
+            super().__init__(w_default_dtype=Dtype.F32)
+            self.fc = nodes.LinearNode(in_dim=3136, out_dim=10)
+            self.input("in0") - self.fc - self.output("out0")
+
+    net = Net()
+    net.fc["weight"] = st.tensor(p["fc.weight"], Dtype.F32)
+    net.fc["bias"] = st.tensor(p["fc.bias"], Dtype.F32)
+    x = np.random.default_rng(rows).standard_normal((rows, 3136)).astype(np.float32)
+    got = net(Tensor.from_numpy(x)).to_numpy()
+    want = orc.linear_f64(x, theirs["fc.weight"], theirs["fc.bias"])
+    assert net.fc.info.kernel == (nodes.KERNEL_GEMV if rows <= 8 else nodes.KERNEL_FMA_TILE)
+    assert_close(got, want, FP32 if rows <= 8 else BOUND_FP32, f"mnist fc, {rows} rows")
+    p.close()
+
+
+def test_hostile_headers_are_rejected(tmp_path):
+    """Offsets and shapes chosen so that a sum or a product would wrap: both readers refuse the
+    file instead of reading outside the mapping (the reference reads through fread and cannot)."""
+    path = str(tmp_path / "hostile.safetensors")
+    big = 2 ** 64
+    cases = [
+        {"t": {"dtype": "F32", "shape": [1], "data_offsets": [big - 100, big - 96]}},          # start_of_data + end wraps
+        {"t": {"dtype": "F32", "shape": [1], "data_offsets": [-8, -4]}},                        # negative offsets
+        {"t": {"dtype": "F32", "shape": [1], "data_offsets": [-8, 0]}},
+        {"t": {"dtype": "F32", "shape": [2 ** 31, 2 ** 31, 4], "data_offsets": [0, 16]}},       # 2^64 elements "= 0"
+        {"t": {"dtype": "F32", "shape": [2 ** 40], "data_offsets": [0, 16]}},                   # axis beyond 32 bits
+        {"t": {"dtype": "F32", "shape": [4], "data_offsets": [0, 18446744073709551632]}},       # 2^64 + 16: beyond uint64
+    ]
+    for i, header in enumerate(cases):
+        _raw_file(path, header, b"\0" * 16)
+        with pytest.raises(ValueError):
+            parser = st.SafetensorsParser(path)
+            parser.byte_size("t")
+            parser.view("t")
+        r = subprocess.run([_cpp_exe(), path], capture_output=True, text=True)
+        assert r.returncode == 3 and "error:" in r.stdout, (i, r.stdout)

@@ -102,3 +102,63 @@ def test_topk_node_rejects_bad_k():
         nodes.TopKSamplingNode(k=0)
     with pytest.raises(ValueError):
         nodes.TopKSamplingNode(k=129)
+
+
+# ---- the two anchors the reference does give -------------------------------------------
+# (1) With k = 1 the node is greedy decoding whatever the uniform, so it must return the golden
+#     output of the reference's Argmax test (python/tests/nodes/test_argmax.py) on that test's
+#     seeded input.  (2) topk-sampling.h:33-57 ranks by value descending, then index ascending,
+#     and samples by inverse CDF: on a row with three equal maxima and k = 3 the unit interval
+#     splits into thirds in index order.  Expected values below are written out by hand; the
+#     restatement is not consulted.
+
+def _argmax_case():
+    from linear_check import draw_case, load_golden
+    meta, arrays = load_golden()
+    _, _, fed = draw_case(meta, "argmax")
+    return fed["in0"], arrays["argmax"].astype(np.uint32)
+
+
+def test_restatement_with_k1_returns_the_reference_argmax_case():
+    x, want = _argmax_case()
+    for u in US:
+        np.testing.assert_array_equal(orc.topk_sample_c(x, 1, 1.0, u), want)
+        np.testing.assert_array_equal(orc.topk_sample_c(x, 1, 0.3, u), want)
+
+
+@pytest.mark.gpu
+def test_topk_node_with_k1_returns_the_reference_argmax_case(device):
+    from vai_b200 import Tensor
+    x, want = _argmax_case()
+    net = _net(1, 1.0)
+    for u in US:
+        net.s.set_uniform(u)
+        np.testing.assert_array_equal(net(Tensor.from_numpy(x)).to_u32(), want, err_msg=f"u={u}")
+
+
+TIE_ROWS = [
+    # (row length, positions of the equal maxima, k, u, expected index)
+    (20, [3, 11, 7], 3, 0.0, 3), (20, [3, 11, 7], 3, 0.2, 3), (20, [3, 11, 7], 3, 0.5, 7), (20, [3, 11, 7], 3, 0.9, 11),
+    # ties across the 2048-column slices of the two-stage form
+    (9000, [8100, 17, 4000], 3, 0.1, 17), (9000, [8100, 17, 4000], 3, 0.5, 4000), (9000, [8100, 17, 4000], 3, 0.95, 8100),
+    # k smaller than the number of equal maxima keeps the lowest indices
+    (9000, [8100, 17, 4000, 6000], 2, 0.25, 17), (9000, [8100, 17, 4000, 6000], 2, 0.75, 4000),
+]
+
+
+@pytest.mark.parametrize("n,pos,k,u,want", TIE_ROWS)
+def test_restatement_ranks_ties_by_index(n, pos, k, u, want):
+    x = np.zeros((1, n), dtype=np.float32)
+    x[0, pos] = 5.0
+    assert int(orc.topk_sample_c(x, k, 1e-3, u)[0]) == want       # low temperature: all the mass on the maxima
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,pos,k,u,want", TIE_ROWS)
+def test_topk_node_ranks_ties_by_index(n, pos, k, u, want, device):
+    from vai_b200 import Tensor
+    x = np.zeros((1, n), dtype=np.float32)
+    x[0, pos] = 5.0
+    net = _net(k, 1e-3)
+    net.s.set_uniform(u)
+    assert int(net(Tensor.from_numpy(x)).to_u32()[0]) == want

@@ -28,6 +28,22 @@ class LinearInfo(ctypes.Structure):
                 ("tile_n", ctypes.c_uint32), ("launches", ctypes.c_uint32), ("workspace_bytes", ctypes.c_size_t)]
 
 
+class LinearTuning(ctypes.Structure):
+    """struct vaicu_linear_tuning; a fresh instance means "the library's choice" everywhere."""
+    _fields_ = [("kernel", ctypes.c_int32), ("tc_pair", ctypes.c_int32), ("tc_wide", ctypes.c_int32),
+                ("tc_bn", ctypes.c_uint32), ("tc_splits", ctypes.c_uint32), ("gemv_rows", ctypes.c_int32),
+                ("gemv_k_warps", ctypes.c_int32), ("gemv_unroll", ctypes.c_int32), ("gemv_grid", ctypes.c_int32),
+                ("gemv_plain_launch", ctypes.c_int32)]
+
+    def __init__(self, **kw):
+        super().__init__()
+        self.tc_pair = self.tc_wide = -1
+        for k, v in kw.items():
+            if k not in dict(self._fields_):
+                raise TypeError(f"no tuning field {k}")
+            setattr(self, k, int(v))
+
+
 # name -> (restype, argtypes); every function include/vaicu.h declares
 SIGNATURES = {
     "vaicu_device_open": (ctypes.c_int, [ctypes.c_int, c_void_pp]),
@@ -35,6 +51,7 @@ SIGNATURES = {
     "vaicu_device_sm_count": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
     "vaicu_device_synchronize": (ctypes.c_int, [ctypes.c_void_p]),
     "vaicu_device_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
+    "vaicu_device_selftest_wait_expiry": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "vaicu_buffer_alloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_size_t, c_void_pp]),
     "vaicu_buffer_free": (ctypes.c_int, [ctypes.c_void_p]),
     "vaicu_buffer_ptr": (ctypes.c_void_p, [ctypes.c_void_p]),
@@ -59,8 +76,10 @@ SIGNATURES = {
     "vaicu_graph_destroy": (ctypes.c_int, [ctypes.c_void_p]),
     "vaicu_linear_plan_create": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(LinearDesc), c_void_pp]),
     "vaicu_linear_plan_create_forced": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(LinearDesc), ctypes.c_int, c_void_pp]),
+    "vaicu_linear_plan_create_tuned": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(LinearDesc), ctypes.POINTER(LinearTuning), c_void_pp]),
     "vaicu_linear_plan_destroy": (ctypes.c_int, [ctypes.c_void_p]),
     "vaicu_linear_plan_info": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(LinearInfo)]),
+    "vaicu_linear_plan_last_run": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]),
     "vaicu_linear_workspace_bytes": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
     "vaicu_linear_run": (ctypes.c_int, [ctypes.c_void_p] * 8),
     "vaicu_linear_run_group": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,

@@ -6,7 +6,6 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -108,6 +107,7 @@ void set_last_error(const char* where, const char* what)
 struct vaicu_linear_plan {
     vaicu_device* dev;
     vaicu_linear_desc d;
+    vaicu_linear_tuning tune;   // the caller's overrides (all "library's choice" for a plain plan)
     int kernel;               // VAICU_KERNEL_*
     // GEMV
     GemvConfig gemv_vec, gemv_any;
@@ -126,6 +126,10 @@ struct vaicu_linear_plan {
     const void* map_b_base;
     size_t workspace_bytes;
     uint32_t launches;
+    // what the most recent run on this plan enqueued (VAICU_KERNEL_*), and whether it was the
+    // 16-byte-vector form of that kernel: differs from `kernel` when a view's alignment sent
+    // the call to a fallback
+    int last_kernel, last_vectorized;
 };
 
 namespace {
@@ -233,7 +237,7 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
         // CTA pairs (cta_group::2): two neighbouring SMs share one 256-row tile and each
         // stages half of the weights' tile; both accumulator buffers stay in use.
         bool pair = d.M > 128u;
-        if (const char* e = getenv("VAICU_TC_PAIR")) pair = atoi(e) != 0;
+        if (pl->tune.tc_pair >= 0) pair = pl->tune.tc_pair != 0;
         // output columns per tile: bn (bn / 2 with gate)
         const uint32_t cand[3] = {256u, 128u, 64u};
         const uint32_t rows = pair ? 256u : 128u, units = pair ? sms / 2u : sms;
@@ -252,15 +256,12 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
             if (out_cols > (uint32_t)align_up(H, 16u) && c != 64u) eff *= (double)H / out_cols;
             if (eff > best) { best = eff; bn = c; }
         }
-        if (const char* e = getenv("VAICU_TC_BN")) {   // tuning override: UMMA N of the unswapped kernel
-            const uint32_t v = (uint32_t)atoi(e);
-            if (v >= 16u && v <= 256u && v % 16u == 0u) bn = v;
-        }
+        if (pl->tune.tc_bn) bn = pl->tune.tc_bn;   // validated when the plan was created
         // Single-CTA alternative for 256-row tiles: two A boxes per stage and two MMAs per
         // k-step; needs all 512 TMEM columns at bn = 256 (no epilogue overlap).
         bool wide = !pair && bn == 256u && d.M >= 512u &&
                     ceil_div(d.M, 256u) * ceil_div(H, gate ? bn / 2u : bn) * 100u >= 85u * sms;
-        if (const char* e = getenv("VAICU_TC_WIDE")) wide = atoi(e) != 0 && bn * 2u <= 512u && !pair;
+        if (pl->tune.tc_wide >= 0) wide = pl->tune.tc_wide != 0 && bn * 2u <= 512u && !pair;
         t.pair = pair ? 1u : 0u;
         t.wide = wide ? 1u : 0u;
         t.tiles_a = ceil_div(d.M, (wide || pair) ? 256u : 128u);
@@ -281,10 +282,7 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
         if (want > 32u) want = 32u;
         if (want >= 2u) kb_per_split = ceil_div(t.kblocks, want);
     }
-    if (const char* e = getenv("VAICU_TC_SPLITS")) {   // tuning override: number of K splits
-        const uint32_t v = (uint32_t)atoi(e);
-        if (v >= 1u && !d.split_size) kb_per_split = ceil_div(t.kblocks, v);
-    }
+    if (pl->tune.tc_splits && !d.split_size) kb_per_split = ceil_div(t.kblocks, pl->tune.tc_splits);
     if (kb_per_split == 0u) kb_per_split = 1u;
     if (kb_per_split > t.kblocks) kb_per_split = t.kblocks;
     t.kb_per_split = kb_per_split;
@@ -328,23 +326,49 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
     pl->ws_partial_bytes = t.splits > 1u ? (size_t)t.splits * d.M * d.N * sizeof(float) : 0;
 }
 
-int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, int force_kernel, vaicu_linear_plan** out)
+vaicu_linear_tuning default_tuning()
+{
+    vaicu_linear_tuning t;
+    memset(&t, 0, sizeof(t));
+    t.tc_pair = t.tc_wide = -1;
+    return t;
+}
+
+int validate_tuning(const vaicu_linear_tuning& t)
+{
+    if (t.kernel != 0 && (t.kernel < VAICU_KERNEL_GEMV || t.kernel > VAICU_KERNEL_TC_SKINNY)) return VAICU_ERR_INVALID_VALUE;
+    if (t.tc_pair < -1 || t.tc_pair > 1 || t.tc_wide < -1 || t.tc_wide > 1) return VAICU_ERR_INVALID_VALUE;
+    if (t.tc_bn && (t.tc_bn < 16u || t.tc_bn > 256u || t.tc_bn % 16u)) return VAICU_ERR_INVALID_VALUE;
+    if (t.tc_splits > 1024u) return VAICU_ERR_INVALID_VALUE;
+    if (t.gemv_rows != 0 && t.gemv_rows != 2 && t.gemv_rows != 4) return VAICU_ERR_INVALID_VALUE;
+    const int k = t.gemv_k_warps;
+    if (k != 0 && k != 1 && k != 2 && k != 4 && k != 8) return VAICU_ERR_INVALID_VALUE;
+    if (t.gemv_unroll != 0 && t.gemv_unroll != 2 && t.gemv_unroll != 4) return VAICU_ERR_INVALID_VALUE;
+    if (t.gemv_grid < 0) return VAICU_ERR_INVALID_VALUE;
+    return VAICU_OK;
+}
+
+int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_linear_tuning& tuning, vaicu_linear_plan** out)
 {
     if (!dev || !out) return VAICU_ERR_INVALID_VALUE;
     int rc = validate_desc(desc);
     if (rc != VAICU_OK) return rc;
+    rc = validate_tuning(tuning);
+    if (rc != VAICU_OK) return rc;
+    const int force_kernel = tuning.kernel;
     vaicu_linear_plan* pl = new (std::nothrow) vaicu_linear_plan();
     if (!pl) return VAICU_ERR_INVALID_VALUE;
     pl->dev = dev;
     pl->d = *desc;
+    pl->tune = tuning;
     if (!pl->d.has_bias) { pl->d.bias_elems = 0; pl->d.b_dtype = VAICU_DTYPE_NONE; }
     if (!pl->d.has_residual) pl->d.residual_elems = 0;
     // a [N] bias under M == 1 "covers O" (elems 0); name it per-row so every kernel takes the cheap index
     if (pl->d.has_bias && pl->d.bias_elems == 0 && pl->d.M == 1u) pl->d.bias_elems = pl->d.N;
     const vaicu_linear_desc& d = pl->d;
     LinearArgs a = make_args(d, nullptr, nullptr, nullptr, nullptr, nullptr);
-    pl->gemv_vec = choose_gemv(a, dev->sm_count, true);
-    pl->gemv_any = choose_gemv(a, dev->sm_count, false);
+    pl->gemv_vec = choose_gemv(a, dev->sm_count, true, &pl->tune);
+    pl->gemv_any = choose_gemv(a, dev->sm_count, false, &pl->tune);
     plan_fma(pl);
     pl->tc = false;
     int kernel = force_kernel;
@@ -383,6 +407,8 @@ int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, int force_kerne
         return VAICU_ERR_INVALID_VALUE;
     }
     pl->kernel = kernel;
+    pl->last_kernel = 0;
+    pl->last_vectorized = 0;
     pl->map_a_base = pl->map_b_base = nullptr;
     *out = pl;
     return VAICU_OK;
@@ -467,6 +493,14 @@ int vaicu_device_status(vaicu_device* dev, int* out)
         VAICU_CUDA(cudaMemset(dev->status_word, 0, sizeof(int)));
         return VAICU_ERR_TIMEOUT;
     }
+    return VAICU_OK;
+}
+
+int vaicu_device_selftest_wait_expiry(vaicu_device* dev, vaicu_stream_t stream)
+{
+    if (!dev) return VAICU_ERR_INVALID_VALUE;
+    VAICU_CUDA(cudaSetDevice(dev->ordinal));
+    VAICU_CUDA(launch_wait_expiry_selftest(dev->status_word, (cudaStream_t)stream));
     return VAICU_OK;
 }
 
@@ -638,12 +672,20 @@ int vaicu_graph_destroy(vaicu_graph* graph)
 
 int vaicu_linear_plan_create(vaicu_device* dev, const vaicu_linear_desc* desc, vaicu_linear_plan** out)
 {
-    return build_plan(dev, desc, 0, out);
+    return build_plan(dev, desc, default_tuning(), out);
 }
 int vaicu_linear_plan_create_forced(vaicu_device* dev, const vaicu_linear_desc* desc, int kernel, vaicu_linear_plan** out)
 {
     if (kernel < VAICU_KERNEL_GEMV || kernel > VAICU_KERNEL_TC_SKINNY) return VAICU_ERR_INVALID_VALUE;
-    return build_plan(dev, desc, kernel, out);
+    vaicu_linear_tuning t = default_tuning();
+    t.kernel = kernel;
+    return build_plan(dev, desc, t, out);
+}
+int vaicu_linear_plan_create_tuned(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_linear_tuning* tuning,
+                                   vaicu_linear_plan** out)
+{
+    if (!tuning) return VAICU_ERR_INVALID_VALUE;
+    return build_plan(dev, desc, *tuning, out);
 }
 int vaicu_linear_plan_destroy(vaicu_linear_plan* plan)
 {
@@ -667,6 +709,13 @@ int vaicu_linear_plan_info(const vaicu_linear_plan* plan, vaicu_linear_info* out
         out->tile_m = plan->tc_swap ? outc : ((plan->tcp.wide || plan->tcp.pair) ? 256u : 128u);
         out->tile_n = plan->tc_swap ? 128u : outc;
     }
+    return VAICU_OK;
+}
+int vaicu_linear_plan_last_run(const vaicu_linear_plan* plan, int* kernel, int* vectorized)
+{
+    if (!plan || !kernel || !vectorized) return VAICU_ERR_INVALID_VALUE;
+    *kernel = plan->last_kernel;
+    *vectorized = plan->last_vectorized;
     return VAICU_OK;
 }
 int vaicu_linear_workspace_bytes(const vaicu_linear_plan* plan, size_t* out)
@@ -732,10 +781,14 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
     const LinearArgs a = make_args(d, I, W, d.has_bias ? bias : nullptr, d.has_residual ? residual : nullptr, O);
 
     if (pl->kernel == VAICU_KERNEL_GEMV) {
-        const bool vec = aligned16(I) && aligned16(W);
-        VAICU_CUDA(launch_gemv(a, (vec && pl->gemv_vec.vectorized) ? pl->gemv_vec : pl->gemv_any, s));
+        const bool vec = aligned16(I) && aligned16(W) && pl->gemv_vec.vectorized;
+        pl->last_kernel = VAICU_KERNEL_GEMV;
+        pl->last_vectorized = vec ? 1 : 0;
+        VAICU_CUDA(launch_gemv(a, vec ? pl->gemv_vec : pl->gemv_any, s));
         return VAICU_OK;
     }
+    pl->last_kernel = VAICU_KERNEL_FMA_TILE;
+    pl->last_vectorized = 0;
     if (pl->kernel == VAICU_KERNEL_FMA_TILE) return run_fma(pl, a, workspace, s);
 
     // tensor-core path; operands TMA cannot address go to the FMA tile kernel
@@ -743,6 +796,8 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
         if (spec) return VAICU_ERR_ALIGNMENT;      // the fallback kernel writes dense outputs only
         return run_fma(pl, a, workspace, s);
     }
+    pl->last_kernel = pl->kernel;
+    pl->last_vectorized = 1;
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
     const void* act = I;
     if (pl->tc_cast) {
@@ -845,7 +900,7 @@ int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_str
     vaicu_linear_desc all = p0->d;
     all.N = (uint32_t)total;
     LinearArgs a = make_args(all, I, W[0], nullptr, nullptr, O[0]);
-    const GemvConfig cfg = choose_gemv(a, p0->dev->sm_count, true);
+    const GemvConfig cfg = choose_gemv(a, p0->dev->sm_count, true, &p0->tune);
     if (!cfg.vectorized) return VAICU_ERR_UNSUPPORTED;
     VAICU_CUDA(launch_gemv_group(a, cfg, (uint32_t)count, rows, W, O, (cudaStream_t)stream));
     return VAICU_OK;

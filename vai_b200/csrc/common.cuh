@@ -121,10 +121,11 @@ __device__ __forceinline__ float finish_gated(const EpilogueArgs& e, float acc_g
 }
 
 // Launchers implemented in the .cu files; each returns a cudaError_t.
-struct GemvConfig { int rows_per_warp; int k_warps; int grid; size_t smem; int vectorized; int unroll; };
+struct GemvConfig { int rows_per_warp; int k_warps; int grid; size_t smem; int vectorized; int unroll; int plain_launch; };
 
 cudaError_t launch_gemv(const LinearArgs& a, const GemvConfig& cfg, cudaStream_t stream);
-GemvConfig  choose_gemv(const LinearArgs& a, int sm_count, bool w_aligned16);
+// `tuning` (may be null) carries a caller's overrides of the geometry; see vaicu_linear_tuning.
+GemvConfig  choose_gemv(const LinearArgs& a, int sm_count, bool w_aligned16, const vaicu_linear_tuning* tuning = nullptr);
 // `a` describes the concatenation (a.N = sum of rows); plain Linears only.
 cudaError_t launch_gemv_group(const LinearArgs& a, const GemvConfig& cfg, uint32_t nseg, const uint32_t* rows,
                               const void* const* w, void* const* o, cudaStream_t stream);
@@ -151,6 +152,26 @@ cudaError_t launch_layer_norm(const void* in, const void* scale, const void* shi
 
 cudaError_t launch_gated_mul(const void* in, void* out, uint32_t rows, uint32_t H, int i_dtype, int o_dtype, int act,
                              int sm_count, cudaStream_t stream);
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device property of a kernel: a process
+// that drives several GPUs has to opt in on each of them.  One flag per device ordinal and
+// kernel instantiation; the attribute call itself is idempotent, so a race between two threads
+// on the first launch only repeats it.
+struct SmemOptIn {
+    static constexpr int kMaxDevices = 64;
+    unsigned char done[kMaxDevices] = {};
+    template <typename Kernel> cudaError_t ensure(Kernel kern, int bytes)
+    {
+        int dev = -1;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        const bool tracked = dev >= 0 && dev < kMaxDevices;
+        if (tracked && done[dev]) return cudaSuccess;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e == cudaSuccess && tracked) done[dev] = 1;
+        return e;
+    }
+};
 
 // Records "<where>: <what>" as the calling thread's last error text
 // (vaicu_last_cuda_error).

@@ -12,8 +12,6 @@
 //   * K is split over `k_warps` warps of a block when N alone cannot fill
 //     148 SMs; the fold goes through shared memory, no global scratch;
 //   * blocks are persistent over row groups (grid sized to the SM count).
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace vaicu {
@@ -401,12 +399,8 @@ template <typename TW, int M, int R, int U = 2>
 cudaError_t launch_one(const GemvParams& p, const GemvConfig& cfg, cudaStream_t stream)
 {
     auto kern = gemv_kernel<TW, M, R, U>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static SmemOptIn optin;
+    if (cudaError_t e = optin.ensure(kern, 100 * 1024); e != cudaSuccess) return e;
     // Programmatic stream serialization: this launch may begin while the kernel ahead
     // of it in the stream drains; gemv_kernel itself waits (dependency_wait) before it
     // reads anything that kernel produced.
@@ -419,8 +413,7 @@ cudaError_t launch_one(const GemvParams& p, const GemvConfig& cfg, cudaStream_t 
     lc.dynamicSmemBytes = cfg.smem;
     lc.stream = stream;
     lc.attrs = attr;
-    static const bool no_pdl = getenv("VAICU_NO_PDL") != nullptr;   // diagnostic: plain stream order
-    lc.numAttrs = no_pdl ? 0 : 1;
+    lc.numAttrs = cfg.plain_launch ? 0 : 1;
     return cudaLaunchKernelEx(&lc, kern, p);
 }
 
@@ -447,9 +440,10 @@ cudaError_t launch_typed(const GemvParams& p, const GemvConfig& cfg, cudaStream_
 
 // Shape -> launch geometry (the analogue of ggmlSlabWgSize, vAi linear.h:655-663:
 // deep-K layers with few rows get their K split over several warps).
-GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
+GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16, const vaicu_linear_tuning* tuning)
 {
     GemvConfig c{};
+    c.plain_launch = (tuning && tuning->gemv_plain_launch) ? 1 : 0;
     const int vec = a.w_dtype == VAICU_DTYPE_F32 ? 4 : 8;
     const uint32_t H = a.gate_fuse ? a.N / 2u : a.N;
     c.vectorized = ptrs_aligned16 && (a.K % (uint32_t)vec == 0u) && a.M >= 1u && a.M <= 8u;
@@ -464,8 +458,7 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
     // resident slots used; so few rows get a smaller R and a deeper K split, while
     // every warp keeps two 16-byte steps.
     // M = 1 comes in two depths: U = 2 k-steps in flight at 3 blocks per SM, or U = 4 at 2
-    static const int m1_unroll = getenv("VAICU_GEMV_U") ? atoi(getenv("VAICU_GEMV_U")) : 2;
-    c.unroll = (a.M == 1u && m1_unroll == 4) ? 4 : 2;
+    c.unroll = (a.M == 1u && tuning && tuning->gemv_unroll == 4) ? 4 : 2;
     const uint32_t capacity = (uint32_t)sm_count * ((a.M == 1u && c.unroll == 2) ? 3u : 2u);
     // Measured: a deeper K split than needed is costly (lm_head 76 -> 108 us with ks = 2:
     // every pass then ends in a block-wide fold), so K is split only until about half
@@ -500,8 +493,11 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
             resident(2 * ks) > resident(ks))
             ks *= 2;
     }
-    if (const char* e = getenv("VAICU_GEMV_R")) { const int v = atoi(e); if ((v == 2 || v == 4) && (v == 2 || a.M <= 4u)) R = v; }   // tuning overrides
-    if (const char* e = getenv("VAICU_GEMV_KS")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8) ks = v; }
+    if (tuning) {   // a caller's overrides
+        if (tuning->gemv_rows == 2 || (tuning->gemv_rows == 4 && a.M <= 4u)) R = tuning->gemv_rows;
+        const int v = tuning->gemv_k_warps;
+        if (v == 1 || v == 2 || v == 4 || v == 8) ks = v;
+    }
     const uint32_t cols = a.gate_fuse ? (uint32_t)R / 2u : (uint32_t)R;
     const uint32_t groups = (H + cols - 1u) / cols;
     c.rows_per_warp = R;
@@ -518,7 +514,7 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16)
     // that every block runs the same number of passes instead of leaving a short tail
     const uint32_t rounds = (nblocks + capacity - 1u) / capacity;
     c.grid = (int)((nblocks + rounds - 1u) / rounds);
-    if (const char* e = getenv("VAICU_GEMV_GRID")) { const int v = atoi(e); if (v > 0) c.grid = v < (int)nblocks ? v : (int)nblocks; }
+    if (tuning && tuning->gemv_grid > 0) c.grid = tuning->gemv_grid < (int)nblocks ? tuning->gemv_grid : (int)nblocks;
     return c;
 }
 

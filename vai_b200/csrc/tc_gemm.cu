@@ -913,12 +913,8 @@ static cudaError_t launch_pair_variant(const CUtensorMap& ma, const CUtensorMap&
                                        cudaStream_t stream)
 {
     auto kern = tc_gemm_pair_kernel<GATE>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcMaxSmem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static SmemOptIn optin;
+    if (cudaError_t e = optin.ensure(kern, (int)kTcMaxSmem); e != cudaSuccess) return e;
     kern<<<grid, kTcThreads, smem, stream>>>(ma, mb, p);
     return cudaGetLastError();
 }
@@ -936,17 +932,40 @@ cudaError_t tc_pair_max_clusters(size_t smem, int* clusters)
     return cudaOccupancyMaxActiveClusters(clusters, kern, &cfg);
 }
 
+// Self-test of the time-out path: one thread waits on an mbarrier that nothing will ever
+// arrive on, with a limit of 1024 probes instead of kSpinLimit, and then does exactly what the
+// GEMM kernels do when a wait gives up: it records the status word and returns.  No copy is in
+// flight, no tensor memory is held, nothing else waits on this thread.
+__global__ void __launch_bounds__(32) wait_expiry_selftest_kernel(int* status)
+{
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_word;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_word = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        bool arrived = false;
+        for (uint32_t spin = 0; spin < 1024u && !arrived; ++spin) arrived = mbar_try_wait(&bar, 0u);
+        if (!arrived) {
+            abort_word = 1u;
+            atomicExch(status, 1);
+        }
+    }
+}
+
+cudaError_t launch_wait_expiry_selftest(int* status, cudaStream_t stream)
+{
+    wait_expiry_selftest_kernel<<<1, 32, 0, stream>>>(status);
+    return cudaGetLastError();
+}
+
 template <bool SWAP, bool GATE>
 static cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, size_t smem,
                                   cudaStream_t stream)
 {
     auto kern = tc_gemm_kernel<SWAP, GATE>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcMaxSmem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static SmemOptIn optin;
+    if (cudaError_t e = optin.ensure(kern, (int)kTcMaxSmem); e != cudaSuccess) return e;
     kern<<<grid, kTcThreads, smem, stream>>>(ma, mb, p);
     return cudaGetLastError();
 }

@@ -57,6 +57,8 @@ __host__ __device__ inline void tile_coords(const TcParams& p, uint32_t tile, ui
 }
 
 cudaError_t tc_pair_max_clusters(size_t smem, int* clusters);
+// One tiny launch whose bounded mbarrier wait is made to run out; sets *status as the GEMM kernels do.
+cudaError_t launch_wait_expiry_selftest(int* status, cudaStream_t stream);
 cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p, bool swap, int grid,
                            size_t smem, cudaStream_t stream);
 

@@ -171,17 +171,73 @@ class DeviceBuffer:
         return array
 
 
-class BufferPool:
-    """Size-keyed reuse of device buffers (vAi vai/engine/buffer-pool.h:77-153)."""
+class GuardedBuffer:
+    """A pooled range with `guard` canary bytes on either side (debugging aid: with
+    compute-sanitizer unavailable, this is how the tests see a kernel that writes outside
+    its output or workspace).  Same surface as DeviceBuffer; `ptr` is the inner range."""
+    CANARY = 0xA5
 
-    def __init__(self, device):
+    def __init__(self, device, nbytes, guard):
+        self.device, self.guard, self.nbytes = device, guard, nbytes
+        self.outer = DeviceBuffer(device, nbytes + 2 * guard)
+        _lib.check(device.lib.vaicu_memset(self.outer.ptr, self.CANARY, self.outer.nbytes, None), "vaicu_memset")
+        device.synchronize()
+        self.ptr = self.outer.ptr + guard
+
+    def upload(self, array, stream=None):
+        a = np.ascontiguousarray(array)
+        assert a.nbytes <= self.nbytes
+        _lib.check(self.device.lib.vaicu_memcpy_h2d(self.ptr, a.ctypes.data, a.nbytes, stream), "vaicu_memcpy_h2d")
+
+    def download(self, array, stream=None):
+        assert array.flags["C_CONTIGUOUS"] and array.nbytes <= self.nbytes
+        _lib.check(self.device.lib.vaicu_memcpy_d2h(array.ctypes.data, self.ptr, array.nbytes, stream), "vaicu_memcpy_d2h")
+        if stream is not None:
+            _lib.check(self.device.lib.vaicu_stream_sync(stream), "vaicu_stream_sync")
+        return array
+
+    def intact(self):
+        """True while both guard zones still hold the canary."""
+        self.device.synchronize()
+        lo = np.empty(self.guard, dtype=np.uint8)
+        hi = np.empty(self.guard, dtype=np.uint8)
+        lib = self.device.lib
+        _lib.check(lib.vaicu_memcpy_d2h(lo.ctypes.data, self.outer.ptr, self.guard, None), "vaicu_memcpy_d2h")
+        _lib.check(lib.vaicu_memcpy_d2h(hi.ctypes.data, self.ptr + self.nbytes, self.guard, None), "vaicu_memcpy_d2h")
+        return bool((lo == self.CANARY).all() and (hi == self.CANARY).all())
+
+    def free(self):
+        self.outer.free()
+
+
+class BufferPool:
+    """Size-keyed reuse of device buffers (vAi vai/engine/buffer-pool.h:77-153).  With
+    guard > 0 every range it hands out sits between canary zones of that many bytes
+    (a multiple of 256, so the inner range keeps its alignment); check_guards() reports
+    ranges whose zones were written."""
+
+    def __init__(self, device, guard=0):
         self.device = device
         self.free = {}
+        self.guard = (guard + 255) // 256 * 256 if guard else 0
+        self.handed_out = []
 
     def request(self, nbytes):
         nbytes = max(256, (nbytes + 255) // 256 * 256)
         lst = self.free.get(nbytes)
-        return lst.pop() if lst else DeviceBuffer(self.device, nbytes)
+        if lst:
+            return lst.pop()
+        if self.guard:
+            buf = GuardedBuffer(self.device, nbytes, self.guard)
+            self.handed_out.append(buf)
+            return buf
+        return DeviceBuffer(self.device, nbytes)
+
+    def check_guards(self):
+        bad = [b for b in self.handed_out if not b.intact()]
+        if bad:
+            raise AssertionError(f"{len(bad)} of {len(self.handed_out)} pooled ranges were written outside their bounds")
+        return len(self.handed_out)
 
     def release(self, buf):
         self.free.setdefault(buf.nbytes, []).append(buf)
@@ -393,7 +449,8 @@ class GateNode(Node):
     both alias in0; one branch is recorded per recording, the engine leaves out every node that
     only the closed branch reaches, and a node both branches reach (the merge point, where two
     producers may share an input slot, and everything past it) is kept.  The condition is host
-    state: set_open() invalidates the recordings."""
+    state: the net keeps one recording per combination of gate states, so a decode loop that
+    flips a gate back and forth records each state once and replays from then on."""
 
     def __init__(self):
         super().__init__()
@@ -406,10 +463,7 @@ class GateNode(Node):
         return self._open
 
     def set_open(self, is_open):
-        if bool(is_open) != self._open:
-            self._open = bool(is_open)
-            if self.net is not None:
-                self.net._dirty = True
+        self._open = bool(is_open)
 
     def prepare(self):
         self.slots["then"] = self.slots["in0"]
@@ -425,6 +479,7 @@ class _Recording:
         self.outputs = {}
         self.graph = None
         self.keep = []
+        self.pinned = []        # page-locked host allocations made for this recording
 
 
 class NeuralNet:
@@ -438,13 +493,13 @@ class NeuralNet:
         return getattr(cls._tls, "net", None)
 
     def __init__(self, w_default_dtype=Dtype.F16, o_default_dtype=Dtype.F32, device=None, use_graph=True,
-                 parallel_branches=True, group_siblings=True, fuse_gated_mul=True):
+                 parallel_branches=True, group_siblings=True, fuse_gated_mul=True, guard_bytes=0):
         if Dtype(w_default_dtype) == Dtype.NONE or Dtype(o_default_dtype) == Dtype.NONE:
             raise ValueError("default dtypes may not be NONE")
         self.w_default_dtype = Dtype(w_default_dtype)
         self.o_default_dtype = Dtype(o_default_dtype)
         self.device = device or Device.default()
-        self.pool = BufferPool(self.device)
+        self.pool = BufferPool(self.device, guard_bytes)      # guard_bytes > 0: canary zones round every pooled range
         self.stream = self.device.create_stream()
         self._streams = [self.stream]
         self.parallel_branches = parallel_branches
@@ -463,6 +518,7 @@ class NeuralNet:
         self._recordings = {}
         self._dirty = False
         self._pinned_ptrs = []
+        self._pin_sink = self._pinned_ptrs
         self._input_names = self._input_order = None
         self.h2d_bytes = self.d2h_bytes = 0
         NeuralNet._tls.net = self
@@ -578,8 +634,15 @@ class NeuralNet:
                     t.host = None      # the device copy is the parameter from here on
 
     def _record(self, fed):
-        lib = self.device.lib
         rec = _Recording()
+        self._pin_sink = rec.pinned
+        try:
+            return self._record_into(rec, fed)
+        finally:
+            self._pin_sink = self._pinned_ptrs
+
+    def _record_into(self, rec, fed):
+        lib = self.device.lib
         for name, t in fed.items():
             dev_t = Tensor(t.shape, t.dtype)
             dev_t.buffer = self.pool.request(dev_t.nbytes())
@@ -739,7 +802,7 @@ class NeuralNet:
         way, vai/engine/neural-net.cpp:219-280)."""
         p = ctypes.c_void_p()
         _lib.check(self.device.lib.vaicu_host_alloc_pinned(max(nbytes, 4), ctypes.byref(p)), "vaicu_host_alloc_pinned")
-        self._pinned_ptrs.append(p)
+        self._pin_sink.append(p)
         buf = (ctypes.c_uint8 * max(nbytes, 4)).from_address(p.value)
         return np.frombuffer(buf, dtype=np_dtype, count=int(np.prod(shape))).reshape(shape), p
 
@@ -757,6 +820,9 @@ class NeuralNet:
         # a recording is made for the inputs that came (and the gates as they stand): nodes
         # that need an input left out are not part of it
         key = tuple([(k, fed[k].shape, fed[k].dtype) for k in names if k in fed])
+        gates = tuple(n.is_open() for n in self._nodes if isinstance(n, GateNode))
+        if gates:
+            key += (("gates",) + gates,)
         if self._dirty:           # a parameter or a wire changed: every recording is stale
             self._drop_recordings()
             self._dirty = False
@@ -791,11 +857,28 @@ class NeuralNet:
         return outs[next(iter(outs))] if len(outs) == 1 else outs
 
     def _drop_recordings(self):
+        """Recordings go with everything made for them: the graphs, the page-locked staging
+        (freed) and the pooled device ranges (back to the pool)."""
+        if not self._recordings:
+            return
+        lib = self.device.lib
+        if lib is not None and self.stream is not None:
+            lib.vaicu_stream_sync(self.stream)           # nothing recorded is still running
         for rec in self._recordings.values():
             for g in (rec.graph, getattr(rec, "graph_io", None)):
                 if g is not None:
-                    self.device.lib.vaicu_graph_destroy(g)
+                    lib.vaicu_graph_destroy(g)
             rec.graph = rec.graph_io = None
+            for p in rec.pinned:
+                lib.vaicu_host_free_pinned(p)
+            rec.pinned = []
+            seen_buffers = set()
+            for t in list(rec.input_tensors.values()) + rec.keep:
+                b = t.buffer
+                if isinstance(b, (DeviceBuffer, GuardedBuffer)) and id(b) not in seen_buffers and b.ptr is not None:
+                    seen_buffers.add(id(b))
+                    self.pool.release(b)
+                t.buffer = None
         self._recordings.clear()
 
     def __del__(self):

@@ -37,27 +37,34 @@ inline float halfToFloat(uint16_t h)
     }
     return std::bit_cast<float>(sign | ((exp + 112u) << 23) | (mant << 13));
 }
-// Round to nearest even; results below the smallest normal flush to zero, overflow goes
-// to infinity, NaN stays NaN.
+// fp32 -> fp16 with the loader's rules (the bit rule of vai/engine/tensor.cpp:46-69, which a
+// reader of vAi checkpoints has to reproduce exactly): round to nearest even, anything below
+// the smallest normal half (2^-14) flushes to a signed zero, overflow saturates to infinity,
+// NaN becomes the quiet NaN 0x7E00.  Done on the magnitude bits: adding 0xFFF plus the
+// keep-bit rounds at bit 13, and the shifted result minus the bias difference (112 << 10) is
+// the half's exponent and mantissa, carry included.
 inline uint16_t floatToHalf(float f)
 {
-    const uint32_t b = std::bit_cast<uint32_t>(f);
-    const uint32_t sign = (b >> 16) & 0x8000u, expRaw = (b >> 23) & 0xFFu, mant = b & 0x7FFFFFu;
-    if (expRaw == 0xFFu) return uint16_t(sign | 0x7C00u | (mant ? 0x0200u : 0u));
-    const int32_t exp = int32_t(expRaw) - 112;
-    if (exp <= 0) return uint16_t(sign);
-    const uint32_t rest = mant & 0x1FFFu;
-    uint32_t mant10 = mant >> 13;
-    mant10 += (rest > 0x1000u) || (rest == 0x1000u && (mant10 & 1u));
-    const uint32_t normal = uint32_t(exp) * 0x400u + mant10;
-    return uint16_t(sign | (normal >= 0x7C00u ? 0x7C00u : normal));
+    const uint32_t bits = std::bit_cast<uint32_t>(f);
+    const uint16_t sgn = uint16_t((bits >> 16) & 0x8000u);
+    const uint32_t mag = bits & 0x7FFFFFFFu;
+    if (mag > 0x7F800000u) return uint16_t(sgn | 0x7E00u);
+    if (mag == 0x7F800000u) return uint16_t(sgn | 0x7C00u);
+    if (mag < 0x38800000u) return sgn;                                   // |f| < 2^-14
+    const uint32_t rounded = mag + 0xFFFu + ((mag >> 13) & 1u);
+    const uint32_t half = (rounded >> 13) - (112u << 10);
+    return uint16_t(sgn | (half < 0x7C00u ? half : 0x7C00u));
 }
 inline float bfloatToFloat(uint16_t b) { return std::bit_cast<float>(uint32_t(b) << 16); }
+// fp32 -> bf16, round to nearest even on the upper 16 bits; a NaN keeps its upper payload and
+// gets the quiet bit (vai/engine/tensor.cpp:73-85).
 inline uint16_t floatToBfloat(float f)
 {
-    const uint32_t b = std::bit_cast<uint32_t>(f);
-    if (((b >> 23) & 0xFFu) == 0xFFu && (b & 0x7FFFFFu)) return uint16_t((b >> 16) | 0x40u);
-    return uint16_t((b + 0x7FFFu + ((b >> 16) & 1u)) >> 16);
+    const uint32_t bits = std::bit_cast<uint32_t>(f);
+    const bool nan = (bits & 0x7FFFFFFFu) > 0x7F800000u;
+    if (nan) return uint16_t((bits >> 16) | 0x0040u);
+    const uint32_t keep = (bits >> 16) & 1u;
+    return uint16_t((bits + 0x7FFFu + keep) >> 16);
 }
 
 class SafetensorsParser;
@@ -124,7 +131,11 @@ class SafetensorsParser
             ws();
             const char* s = p;
             uint64_t v = 0;
-            while (p < end && *p >= '0' && *p <= '9') v = v * 10u + uint64_t(*p++ - '0');
+            while (p < end && *p >= '0' && *p <= '9') {
+                const uint64_t digit = uint64_t(*p++ - '0');
+                if (v > (UINT64_MAX - digit) / 10u) throw std::runtime_error("JSON parse error: integer out of range");
+                v = v * 10u + digit;
+            }
             if (p == s) throw std::runtime_error("JSON parse error: expected a non-negative integer");
             return v;
         }
@@ -181,7 +192,10 @@ class SafetensorsParser
                                 }
                             c.expect(']');
                             if (field == "shape") {
-                                for (uint64_t d : v) m.shape.push_back((uint32_t)d);
+                                for (uint64_t d : v) {
+                                    if (d > UINT32_MAX) throw std::runtime_error("Invalid tensor entry (axis too long): " + key);
+                                    m.shape.push_back((uint32_t)d);
+                                }
                             } else {
                                 if (v.size() != 2) throw std::runtime_error("Invalid tensor entry: " + key);
                                 m.begin = v[0]; m.end = v[1];
@@ -194,7 +208,8 @@ class SafetensorsParser
                         break;
                     }
                 c.expect('}');
-                if (!haveOffsets || m.begin > m.end || startOfData_ + m.end > fileSize_)
+                // compared against the size of the data section, so that no sum can wrap
+                if (!haveOffsets || m.begin > m.end || m.end > fileSize_ - startOfData_)
                     throw std::runtime_error("Tensor data runs past the end of the file: " + key);
                 if (tensors_.emplace(key, std::move(m)).second) order_.push_back(key);
             }
@@ -257,16 +272,18 @@ public:
     size_t byteSize(std::string_view key) const
     {
         const Meta& m = meta(key);
-        size_t n = 1;
-        for (uint32_t s : m.shape) n *= s;
         const size_t bytes = m.end - m.begin;
-        if (m.dtype == "F32") {
-            if (bytes != n * 4) throw std::runtime_error("Data size mismatch for F32 tensor.");
-        } else if (m.dtype == "F16" || m.dtype == "BF16") {
-            if (bytes != n * 2) throw std::runtime_error("Data size mismatch for F16/BF16 tensor.");
-        } else {
-            throw std::runtime_error("Unsupported dtype: " + m.dtype);
+        size_t esz = 0;
+        if (m.dtype == "F32") esz = 4;
+        else if (m.dtype == "F16" || m.dtype == "BF16") esz = 2;
+        else throw std::runtime_error("Unsupported dtype: " + m.dtype);
+        // element count with the product checked: it can never exceed the bytes the file holds
+        size_t n = 1;
+        for (uint32_t s : m.shape) {
+            if (s != 0 && n > fileSize_ / s) throw std::runtime_error("Data size mismatch for " + m.dtype + " tensor.");
+            n *= s;
         }
+        if (n > fileSize_ / esz || bytes != n * esz) throw std::runtime_error("Data size mismatch for " + m.dtype + " tensor.");
         return bytes;
     }
     const void* data(std::string_view key) const { return map_ + startOfData_ + meta(key).begin; }
@@ -274,7 +291,8 @@ public:
     void readInto(std::string_view key, void* dst, size_t byteOffset, size_t byteCount) const
     {
         const Meta& m = meta(key);
-        if (byteOffset + byteCount > m.end - m.begin) throw std::runtime_error("Tensor read runs past the end of the tensor.");
+        const size_t total = m.end - m.begin;
+        if (byteOffset > total || byteCount > total - byteOffset) throw std::runtime_error("Tensor read runs past the end of the tensor.");
         std::memcpy(dst, map_ + startOfData_ + m.begin + byteOffset, byteCount);
     }
 };

@@ -30,7 +30,8 @@ def algorithmic_bytes(M, N, K, i_dt, w_dt, o_dt, bias, residual, gate):
 
 
 def run(M, K, N, i_dtype="f32", w_dtype="bf16", o_dtype="f32", epilogue="NONE", gate=False, bias=False,
-        residual=False, kernel=0, copies=0, iters=50, warmup=5, split_size=0, device=None, graph=False, clocks=False):
+        residual=False, kernel=0, copies=0, iters=50, warmup=5, split_size=0, device=None, graph=False, clocks=False,
+        tuning=None):
     dev = device or Device.default()
     lib = dev.lib
     i_dt, w_dt, o_dt = DT[i_dtype], DT[w_dtype], DT[o_dtype]
@@ -70,7 +71,10 @@ def run(M, K, N, i_dtype="f32", w_dtype="bf16", o_dtype="f32", epilogue="NONE", 
     info = _lib.LinearInfo()
     for _ in range(copies):   # one plan per weight copy: each keeps its own tensor maps
         h = ctypes.c_void_p()
-        if kernel:
+        if tuning:
+            t = _lib.LinearTuning(kernel=kernel, **tuning)
+            _lib.check(lib.vaicu_linear_plan_create_tuned(dev.handle, ctypes.byref(d), ctypes.byref(t), ctypes.byref(h)), "plan")
+        elif kernel:
             _lib.check(lib.vaicu_linear_plan_create_forced(dev.handle, ctypes.byref(d), kernel, ctypes.byref(h)), "plan")
         else:
             _lib.check(lib.vaicu_linear_plan_create(dev.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
@@ -165,9 +169,11 @@ def main():
     ap.add_argument("--split-size", type=int, default=0)
     ap.add_argument("--graph", action="store_true", help="time a replayed recording of the launches")
     ap.add_argument("--clocks", action="store_true", help="sample nvidia-smi SM clock and power during the timed loop")
+    ap.add_argument("--tune", default="", help="vaicu_linear_tuning fields, e.g. tc_bn=192,tc_pair=1")
     a = ap.parse_args()
+    tuning = {k: int(v) for k, v in (kv.split("=") for kv in a.tune.split(",") if kv)} or None
     print(json.dumps(run(a.M, a.K, a.N, a.i_dtype, a.w_dtype, a.o_dtype, a.epilogue, a.gate, a.bias, a.residual,
-                         a.kernel, a.copies, a.iters, a.warmup, a.split_size, graph=a.graph, clocks=a.clocks)))
+                         a.kernel, a.copies, a.iters, a.warmup, a.split_size, graph=a.graph, clocks=a.clocks, tuning=tuning)))
 
 
 if __name__ == "__main__":

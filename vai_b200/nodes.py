@@ -30,7 +30,7 @@ class LinearNode(Node):
     """
 
     def __init__(self, in_dim, out_dim, accept_residual=False, residual_order=ResidualOrder.AFTER_EPILOGUE,
-                 epilogue=Epilogue.NONE, scalar_scale=1.0, split_size=0, kernel=KERNEL_AUTO):
+                 epilogue=Epilogue.NONE, scalar_scale=1.0, split_size=0, kernel=KERNEL_AUTO, tuning=None):
         super().__init__()
         if not (split_size == 0 or split_size >= 32):
             raise ValueError("split_size: must be 0 or >= 32")
@@ -43,6 +43,9 @@ class LinearNode(Node):
         self.scalar_scale = float(scalar_scale)
         self.split_size = int(split_size)
         self.kernel = int(kernel)
+        # Not in the reference's signature: `kernel` fixes the kernel family, `tuning` (a dict of
+        # vaicu_linear_tuning fields) fixes tile and launch geometry; both default to the library's choice.
+        self.tuning = dict(tuning) if tuning else None
         self._gate = None           # activation of the GatedMul recorded into this node's launch
         self._gate_o_dtype = None   # ... and that node's output dtype
         # slot set of Linear::Linear (linear.h:2134-2144)
@@ -130,7 +133,10 @@ class LinearNode(Node):
         plan = self._plans.get(key)
         if plan is None:
             h = ctypes.c_void_p()
-            if self.kernel == KERNEL_AUTO:
+            if self.tuning:
+                t = _lib.LinearTuning(kernel=self.kernel, **self.tuning)
+                rc = dev.lib.vaicu_linear_plan_create_tuned(dev.handle, ctypes.byref(d), ctypes.byref(t), ctypes.byref(h))
+            elif self.kernel == KERNEL_AUTO:
                 rc = dev.lib.vaicu_linear_plan_create(dev.handle, ctypes.byref(d), ctypes.byref(h))
             else:
                 rc = dev.lib.vaicu_linear_plan_create_forced(dev.handle, ctypes.byref(d), self.kernel, ctypes.byref(h))

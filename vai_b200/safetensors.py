@@ -70,10 +70,16 @@ class SafetensorsParser:
                 continue
             if not isinstance(meta, dict):
                 raise ValueError(f"Invalid tensor entry: {key}")
-            begin, end = (int(v) for v in meta["data_offsets"])
-            if begin > end or self.start_of_data + end > size:
+            try:
+                begin, end = (int(v) for v in meta["data_offsets"])
+                shape = tuple(int(s) for s in meta["shape"])
+            except (KeyError, TypeError, ValueError):
+                raise ValueError(f"Invalid tensor entry: {key}") from None
+            if not 0 <= begin <= end or end > size - self.start_of_data:
                 raise ValueError(f"Tensor data runs past the end of the file: {key}")
-            self.tensors[key] = (str(meta["dtype"]), tuple(int(s) for s in meta["shape"]), begin, end)
+            if any(s < 0 or s > 0xFFFFFFFF for s in shape):
+                raise ValueError(f"Invalid tensor entry (axis out of range): {key}")
+            self.tensors[key] = (str(meta["dtype"]), shape, begin, end)
         self._map = mmap.mmap(self._file.fileno(), 0, access=mmap.ACCESS_READ) if size else None
 
     def close(self):
@@ -107,7 +113,10 @@ class SafetensorsParser:
         dtype, shape, begin, end = self._meta(key)
         if dtype not in _FILE_DTYPES:
             raise ValueError(f"Unsupported dtype: {dtype}")
-        if end - begin != int(np.prod(shape, dtype=np.int64)) * _FILE_DTYPES[dtype][1]:
+        elems = 1
+        for axis in shape:          # Python integers: the product cannot wrap
+            elems *= axis
+        if end - begin != elems * _FILE_DTYPES[dtype][1]:
             raise ValueError(f"Data size mismatch for {dtype} tensor.")
         return end - begin
 
@@ -115,7 +124,7 @@ class SafetensorsParser:
         total = self.byte_size(key)
         dtype, _, begin, _ = self._meta(key)
         count = total - byte_offset if byte_count is None else byte_count
-        if byte_offset + count > total:
+        if byte_offset < 0 or count < 0 or byte_offset + count > total:
             raise ValueError("Tensor read runs past the end of the tensor.")
         np_dtype, esz = _FILE_DTYPES[dtype]
         if byte_offset % esz or count % esz:
