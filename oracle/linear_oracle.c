@@ -503,6 +503,17 @@ int vai_oracle_gated_mul(const void* in, void* out, uint32_t rows, uint32_t H, i
     return 0;
 }
 
+/* Threads the parallel loops use from now on.  A launcher may export OMP_NUM_THREADS=1 to its
+ * children (torch.distributed.run does); the timed CPU baseline sets the count it reports. */
+void vai_oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int vai_oracle_num_threads(void)
 {
 #ifdef _OPENMP

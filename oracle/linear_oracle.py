@@ -99,6 +99,12 @@ def num_threads():
     return int(lib().vai_oracle_num_threads())
 
 
+def set_num_threads(n):
+    """Use n OpenMP threads whatever OMP_NUM_THREADS said when the process started."""
+    lib().vai_oracle_set_num_threads(ctypes.c_int(int(n)))
+    return num_threads()
+
+
 def to_dtype(a, dtype):
     """fp32 array -> device representation (np.float32, or uint16 bit patterns for
     fp16/bf16) using the loader's conversions (vAi vai/engine/tensor.cpp:46-85)."""

@@ -103,7 +103,10 @@ def test_node_alone_shapes_and_dtypes(shape, dt, activation, device):
     assert_close(got, orc.gated_mul_f64(xs, code), out_tol(dt[1], 1e-5, 1e-6), f"{shape} {dt} {activation}")
     i_c, o_c = {"f32": orc.F32, "f16": orc.F16, "bf16": orc.BF16}[dt[0]], {"f32": orc.F32, "f16": orc.F16, "bf16": orc.BF16}[dt[1]]
     c = orc.to_f32(orc.gated_mul_c(orc.to_dtype(x, i_c), code, i_c, o_c), o_c)
-    assert_close(got, c, out_tol(dt[1], 1e-5, 1e-6), f"{shape} {dt} {activation} vs restatement")
+    # the device's expf / tanhf and the host's differ in the last fp32 bit now and then, which can move
+    # a 16-bit output to the neighbouring value: one unit in the last place of the output dtype is allowed
+    ulp = {"f32": 0.0, "f16": 2.0 ** -10, "bf16": 2.0 ** -7}[dt[1]]
+    assert_close(got, c, (1e-5 + ulp, 1e-6), f"{shape} {dt} {activation} vs restatement")
 
 
 @pytest.mark.gpu

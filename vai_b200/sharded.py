@@ -130,6 +130,12 @@ class ShardedLinear:
         return assemble(self.gathered, self.n_out) if assemble_output else self.gathered
 
 
+def destination_order(rank, world):
+    """Ranks in the order rank `rank` stores to them: its right-hand neighbour first, itself
+    last, so that at any moment the `world` ranks write to `world` different GPUs."""
+    return [(rank + 1 + i) % world for i in range(world)]
+
+
 class _CudaView:
     """A [rows, cols] view of a device range for torch.as_tensor (CUDA array interface)."""
 
@@ -144,7 +150,16 @@ class FusedGatherLinear(ShardedLinear):
     stream-ordered all-reduce that tells every rank that all slabs have landed.
 
     The outputs are cudaMalloc'ed ranges shared through CUDA IPC handles; no TMA descriptor
-    and no multicast load touches peer memory — peers are only ever stored to."""
+    and no multicast load touches peer memory — peers are only ever stored to.
+
+    Two hazards of writing into other ranks' memory are handled here.  (1) Every rank would
+    otherwise walk the destinations in the same order and all of them would store to rank 0
+    at once, then to rank 1, ...: each rank's destination list starts with its right-hand
+    neighbour and ends with itself.  (2) A fast rank may start call n + 1 while a slow rank's
+    consumers of call n still read its output; two outputs alternate by call parity, so a
+    store of call n + 1 lands in the buffer nobody has read since call n - 1, and the flag
+    all-reduce of call n (which every rank passes only after its readers of call n - 1 were
+    enqueued ahead of it on the same stream) orders that reuse."""
 
     def __init__(self, device, dist, full_desc, w_local, bias_local=None):
         import torch
@@ -166,37 +181,44 @@ class FusedGatherLinear(ShardedLinear):
         self.ws = torch.empty(max(self.info.workspace_bytes, 256), dtype=torch.uint8, device=cuda)
         from .engine import DeviceBuffer
         esz = 4 if self.desc.o_dtype == 0 else 2
-        self.out = DeviceBuffer(device, self.desc.M * self.n_out * esz)      # the gathered [M, n_out] of this rank
-        handle = (ctypes.c_uint8 * 64)()
-        _lib.check(lib.vaicu_ipc_export(self.out.ptr, handle), "vaicu_ipc_export")
-        handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle))
         self._opened = []
-        ptrs = []
-        for r, raw in enumerate(handles):
-            if r == self.rank:
-                ptrs.append(self.out.ptr)
-                continue
-            p = ctypes.c_void_p()
-            _lib.check(lib.vaicu_ipc_open((ctypes.c_uint8 * 64).from_buffer_copy(raw), ctypes.byref(p)), "vaicu_ipc_open")
-            self._opened.append(p)
-            ptrs.append(p.value)
-        self.ptrs = (ctypes.c_void_p * self.world)(*ptrs)
-        self.flag = torch.zeros(1, dtype=torch.float32, device=cuda)
+        self.outs, self.ptrs, self.results = [], [], []
         typestr = {0: "<f4", 1: "<f2", 3: "<u2"}[self.desc.o_dtype]
-        view = torch.as_tensor(_CudaView(self.out.ptr, (self.desc.M, self.n_out), typestr), device=cuda)
-        self.result = view.view(torch.bfloat16) if self.desc.o_dtype == 3 else view
+        for parity in range(2):
+            out = DeviceBuffer(device, self.desc.M * self.n_out * esz)      # a gathered [M, n_out] of this rank
+            handle = (ctypes.c_uint8 * 64)()
+            _lib.check(lib.vaicu_ipc_export(out.ptr, handle), "vaicu_ipc_export")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle))
+            by_rank = []
+            for r, raw in enumerate(handles):
+                if r == self.rank:
+                    by_rank.append(out.ptr)
+                    continue
+                p = ctypes.c_void_p()
+                _lib.check(lib.vaicu_ipc_open((ctypes.c_uint8 * 64).from_buffer_copy(raw), ctypes.byref(p)), "vaicu_ipc_open")
+                self._opened.append(p)
+                by_rank.append(p.value)
+            order = destination_order(self.rank, self.world)
+            self.outs.append(out)
+            self.ptrs.append((ctypes.c_void_p * self.world)(*[by_rank[r] for r in order]))
+            view = torch.as_tensor(_CudaView(out.ptr, (self.desc.M, self.n_out), typestr), device=cuda)
+            self.results.append(view.view(torch.bfloat16) if self.desc.o_dtype == 3 else view)
+        self.calls = 0
+        self.flag = torch.zeros(1, dtype=torch.float32, device=cuda)
 
     def forward(self, x):
         stream = self.torch.cuda.current_stream().cuda_stream
+        parity = self.calls & 1
+        self.calls += 1
         _lib.check(self.dev.lib.vaicu_linear_run_scatter(self.plan, stream, x.data_ptr(), self.w.data_ptr(),
                                                          self.b.data_ptr() if self.b is not None else None,
-                                                         self.ptrs, self.world, self.n_out, self.begin,
+                                                         self.ptrs[parity], self.world, self.n_out, self.begin,
                                                          self.ws.data_ptr()), "vaicu_linear_run_scatter")
         # every rank's kernel precedes its contribution on the stream: when the reduction
         # returns, all slabs are in this rank's output
         self.dist.all_reduce(self.flag)
-        return self.result
+        return self.results[parity]
 
     def close(self):
         for p in self._opened:
@@ -334,10 +356,80 @@ class ShardedGreedyHead:
             self.plan = None
 
 
-def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5):
-    """Column-split lm_head and gate|value Linear of `preset` at batch M on this rank's
-    GPU, with the NCCL all-gather of the output slabs; device-timed, max over ranks.
-    Returns a dict (rank 0 reports it)."""
+def _tiled_weight(torch, rows, k, seed):
+    """[rows, k] bf16 ~N(0, 0.02) on the host, the same on every rank: one seeded pool of 2^24 + 977
+    values repeated (the odd length keeps rows from lining up), so that a 1.3 GB matrix takes a
+    second to make."""
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    pool = (torch.randn((1 << 24) + 977, generator=gen) * 0.02).to(torch.bfloat16)
+    total = rows * k
+    reps = (total + pool.numel() - 1) // pool.numel()
+    return pool.repeat(reps)[:total].view(rows, k)
+
+
+def _timed(torch, dist, cuda, fn, iters, warmup):
+    """Device-timed milliseconds per call of fn, max over ranks."""
+    for _ in range(warmup):
+        fn()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    if dist is not None:
+        t = torch.tensor([ms], dtype=torch.float64, device=cuda)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def _act_f64(code, v):
+    """The gate activations of the presets in float64 (4: SiLU, 3: GELU-tanh)."""
+    v = np.asarray(v, dtype=np.float64)
+    if code == 4:
+        return v / (1.0 + np.exp(-v))
+    if code == 3:
+        return 0.5 * v * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (v + 0.044715 * v ** 3)))
+    if code == 0:
+        return v
+    raise ValueError(code)
+
+
+def _sampled_error(torch, got, x_host, w_host, gate, epilogue, samples=4096, seed=99):
+    """Largest |got - float64| / max(|float64|, 0.05) over `samples` random outputs: float64 dot
+    products of the bf16 values both sides hold, the gate applied as the node pair does."""
+    rng = np.random.default_rng(seed)
+    M, n_out = got.shape
+    ms = rng.integers(0, M, samples)
+    ns = rng.integers(0, n_out, samples)
+    xs = x_host[ms].double().numpy()
+    if gate:
+        g = (xs * w_host[ns].double().numpy()).sum(axis=1)
+        u = (xs * w_host[ns + n_out].double().numpy()).sum(axis=1)
+        want = _act_f64(epilogue, g) * u
+    else:
+        want = (xs * w_host[ns].double().numpy()).sum(axis=1)
+    have = got[torch.as_tensor(ms), torch.as_tensor(ns)].double().cpu().numpy()
+    return float(np.max(np.abs(have - want) / np.maximum(np.abs(want), 0.05)))
+
+
+def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5, peaks=None):
+    """The large-N layers of `preset` at batch M split over the ranks' GPUs, each beside the same
+    layer on ONE GPU measured in the same run (every rank holds the full weight for that):
+
+      lm_head, gate|value   column split; the slab alone, then gathered three ways — NCCL all-gather
+                            + re-layout, the gather fused into the GEMM epilogue (peer stores), and
+                            for the lm_head the greedy head that exchanges candidates, not logits;
+      mlp                   gate|value column split feeding `down` split along K (row parallel),
+                            summed by one all-reduce.
+
+    Device-timed, max over ranks.  Gathered outputs are compared with float64 on sampled elements
+    (rank 0's copy) and, bit for bit, with the NCCL path.  Returns a dict; rank 0 reports it."""
     import torch
 
     from . import presets
@@ -346,134 +438,217 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5):
     world = dist.get_world_size() if dist is not None else 1
     rank = dist.get_rank() if dist is not None else 0
     cuda = torch.device("cuda", device.ordinal)
+    peaks = peaks or {}
+    hbm, burst = peaks.get("hbm_gbs", 6650.0), peaks.get("bf16_tflops", 1590.0)
+    compute_bound = M >= 1024
+    lib = device.lib
     gen = torch.Generator(device="cpu").manual_seed(1234)
+    x_host = torch.randn(M, p["d"], generator=gen).to(torch.bfloat16)
+    x = x_host.to(cuda)
+    act = int(getattr(Epilogue, p["act"]))
     out = {"preset": preset, "M": M, "world": world, "layers": {}}
-    x = (torch.randn(M, p["d"], generator=gen)).to(torch.bfloat16).to(cuda)
+
+    def desc_of(n_rows, k, gate, o_dtype=Dtype.BF16):
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = M, n_rows, k
+        d.i_dtype = d.w_dtype = int(Dtype.BF16)
+        d.o_dtype = int(o_dtype)
+        d.b_dtype = int(Dtype.NONE)
+        d.scalar_scale = 1.0
+        d.gate_fuse = 1 if gate else 0
+        d.epilogue = act if gate else 0
+        return d
+
+    def plan_of(d):
+        h = ctypes.c_void_p()
+        _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
+        info = _lib.LinearInfo()
+        _lib.check(lib.vaicu_linear_plan_info(h, ctypes.byref(info)), "info")
+        return h, info
+
+    def one_gpu_us(d, w_dev, x_dev):
+        """The whole layer on this GPU alone."""
+        h, info = plan_of(d)
+        ws = torch.empty(max(info.workspace_bytes, 256), dtype=torch.uint8, device=cuda)
+        n_out = d.N // 2 if d.gate_fuse else d.N
+        o = torch.empty((M, n_out), dtype=torch.bfloat16 if d.o_dtype == 3 else torch.float32, device=cuda)
+
+        def run():
+            stream = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.vaicu_linear_run(h, stream, x_dev.data_ptr(), w_dev.data_ptr(), None, None, o.data_ptr(), ws.data_ptr()), "run")
+
+        ms = _timed(torch, dist, cuda, run, iters, warmup)
+        lib.vaicu_linear_plan_destroy(h)
+        return ms * 1e3, o
+
+    def figures(name, flops_all, bytes_all, t1_us, tn_us, local_us, collective):
+        """Speed-up over one GPU, efficiency, and the fraction of world x the roofline of one GPU."""
+        agg = flops_all / (tn_us * 1e-6) / 1e12 if compute_bound else bytes_all / (tn_us * 1e-6) / 1e9
+        one = burst if compute_bound else hbm
+        return {"layer": name, "bound": "tensor" if compute_bound else "hbm", "t1_us": round(t1_us, 1), "tN_us": round(tn_us, 1),
+                "local_us": round(local_us, 1), "speedup": round(t1_us / tn_us, 2), "efficiency": round(t1_us / tn_us / world, 3),
+                ("aggregate_TFLOPs" if compute_bound else "aggregate_GBps"): round(agg, 1),
+                "frac_of_N_x_roofline": round(agg / (world * one), 3), "collective": collective,
+                "collective_share": round(max(0.0, 1.0 - local_us / tn_us), 3)}
+
     cases = [("lm_head", p["vocab"], False), ("gate_up", 2 * p["ffn"], True)]
+    kept = {}
     for name, n_rows, gate in cases:
-        full = _lib.LinearDesc()
-        full.M, full.N, full.K = M, n_rows, p["d"]
-        full.i_dtype = full.w_dtype = full.o_dtype = int(Dtype.BF16)
-        full.b_dtype = int(Dtype.NONE)
-        full.scalar_scale = 1.0
-        full.gate_fuse = 1 if gate else 0
-        full.epilogue = int(getattr(Epilogue, p["act"])) if gate else 0
-        # only this rank's rows are ever materialised: draw them directly
+        full = desc_of(n_rows, p["d"], gate)
         n_out = n_rows // 2 if gate else n_rows
-        _, cnt = shard_rows(n_out, world, rank)
-        rows_local = 2 * cnt if gate else cnt
-        w_local = (torch.randn(rows_local, p["d"], generator=gen) * 0.02).to(torch.bfloat16)
+        w_host = _tiled_weight(torch, n_rows, p["d"], 7 + len(name))
+        w_full = w_host.to(cuda)
+        t1_us, o_full = one_gpu_us(full, w_full, x)
+        err_one = _sampled_error(torch, o_full.float(), x_host, w_host, gate, act) if rank == 0 else 0.0
+        del w_full, o_full
+        w_local = slice_weight(w_host, rank, world, gate).contiguous().to(cuda)
 
         lin = ShardedLinear.__new__(ShardedLinear)
         lin.torch, lin.dist, lin.dev, lin.rank, lin.world = torch, dist, device, rank, world
         lin.full, lin.gate, lin.n_out = full, gate, n_out
         lin.desc, lin.begin, lin.count = shard_desc(full, rank, world)
-        lin.w, lin.b = w_local.to(cuda), None
-        h = ctypes.c_void_p()
-        _lib.check(device.lib.vaicu_linear_plan_create(device.handle, ctypes.byref(lin.desc), ctypes.byref(h)), "plan")
-        lin.plan = h
-        lin.info = _lib.LinearInfo()
-        _lib.check(device.lib.vaicu_linear_plan_info(h, ctypes.byref(lin.info)), "info")
+        lin.w, lin.b = w_local, None
+        lin.plan, lin.info = plan_of(lin.desc)
         lin.ws = torch.empty(max(lin.info.workspace_bytes, 256), dtype=torch.uint8, device=cuda)
         cmax = gathered_shape(M, n_out, world)[2]
         lin.local = torch.zeros((M, cmax), dtype=torch.bfloat16, device=cuda)
         lin.slab = lin.local if cmax == lin.count else torch.empty((M, lin.count), dtype=torch.bfloat16, device=cuda)
         lin.gathered = torch.empty((world, M, cmax), dtype=torch.bfloat16, device=cuda)
 
-        def timed(fn):
-            for _ in range(warmup):
-                fn()
-            if dist is not None:
-                dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(iters):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / iters
-            if dist is not None:
-                t = torch.tensor([ms], dtype=torch.float64, device=cuda)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                ms = float(t.item())
-            return ms
-
-        local_ms = timed(lambda: lin.local_forward(x))
-        total_ms = timed(lambda: lin.forward(x, assemble_output=True))
-        fused_ms, fused_equal = None, None
+        local_ms = _timed(torch, dist, cuda, lambda: lin.local_forward(x), iters, warmup)
+        nccl_ms = _timed(torch, dist, cuda, lambda: lin.forward(x, assemble_output=True), iters, warmup)
+        ref = lin.forward(x, assemble_output=True)
+        err_nccl = _sampled_error(torch, ref.float(), x_host, w_host, gate, act) if rank == 0 else 0.0
+        fused_ms, fused_equal, err_fused = None, None, None
         if dist is not None and world > 1:
             fused = FusedGatherLinear(device, dist, full, lin.w, None)
             got = fused.forward(x)
-            # the same plan run densely on this rank, gathered by NCCL: must be bit-identical
+            # the same plan run densely on this rank and gathered by NCCL: must be bit-identical
             stream = torch.cuda.current_stream().cuda_stream
-            _lib.check(device.lib.vaicu_linear_run(fused.plan, stream, x.data_ptr(), lin.w.data_ptr(), None, None,
-                                                   lin.slab.data_ptr(), fused.ws.data_ptr()), "vaicu_linear_run")
+            _lib.check(lib.vaicu_linear_run(fused.plan, stream, x.data_ptr(), lin.w.data_ptr(), None, None,
+                                            lin.slab.data_ptr(), fused.ws.data_ptr()), "vaicu_linear_run")
             if lin.slab is not lin.local:
                 lin.local[:, :lin.count].copy_(lin.slab)
             dist.all_gather_into_tensor(lin.gathered, lin.local)
-            ref = assemble(lin.gathered, n_out)
+            same_plan = assemble(lin.gathered, n_out)
             torch.cuda.synchronize()
             dist.barrier()
-            fused_equal = bool(torch.equal(got.view(torch.int16), ref.view(torch.int16)))
-            fused_ms = timed(lambda: fused.forward(x))
+            fused_equal = bool(torch.equal(got.view(torch.int16), same_plan.view(torch.int16)))
+            err_fused = _sampled_error(torch, got.float(), x_host, w_host, gate, act) if rank == 0 else 0.0
+            fused_ms = _timed(torch, dist, cuda, lambda: fused.forward(x), iters, warmup)
             torch.cuda.synchronize()
             dist.barrier()
             fused.close()
-        greedy = {}
+        flops_all = 2.0 * M * n_rows * p["d"]
+        bytes_all = n_rows * p["d"] * 2 + M * p["d"] * 2 + M * n_out * 2
+        best_ms, how = nccl_ms, "NCCL all-gather + re-layout"
+        if fused_ms is not None and fused_ms < nccl_ms:
+            best_ms, how = fused_ms, "all-gather fused into the GEMM epilogue (peer stores) + a 4-byte all-reduce"
+        entry = figures(name, flops_all, bytes_all, t1_us, best_ms * 1e3, local_ms * 1e3, how)
+        entry.update({"rows": n_rows, "rows_per_gpu": int(w_local.shape[0]), "kernel": int(lin.info.kernel),
+                      "tile": [int(lin.info.tile_m), int(lin.info.tile_n)], "nccl_allgather_us": round(nccl_ms * 1e3, 1),
+                      "fused_gather_us": None if fused_ms is None else round(fused_ms * 1e3, 1),
+                      "fused_gather_matches_nccl": fused_equal, "allgather_bytes_per_gpu": M * cmax * 2,
+                      "max_rel_err_vs_float64": {"one_gpu": err_one, "nccl": err_nccl, "fused": err_fused}})
         if name == "lm_head":
             # greedy sampling without gathering logits: 8 bytes per row and GPU are exchanged
             head = ShardedGreedyHead(device, dist, full, lin.w)
             tok = head.forward(x).clone()
-            logits = lin.forward(x, assemble_output=True).float()
+            logits = ref.float()
             top = logits.max(dim=1, keepdim=True).values
             want = (logits == top).int().argmax(dim=1)             # lowest token id among equal maxima
             torch.cuda.synchronize()
-            greedy = {"greedy_head_us": timed(lambda: head.forward(x)) * 1e3,
+            greedy_ms = _timed(torch, dist, cuda, lambda: head.forward(x), iters, warmup)
+            g = figures("lm_head + greedy sampling", flops_all, bytes_all, t1_us, greedy_ms * 1e3, local_ms * 1e3,
+                        "all-gather of one (max, token) candidate per row and GPU (8 bytes), then a merge kernel")
+            g.update({"greedy_head_us": round(greedy_ms * 1e3, 1), "greedy_exchange_bytes_per_gpu": 8 * M,
                       "greedy_head_matches_argmax_of_gathered_logits": bool(torch.equal(tok.long(), want)),
-                      "greedy_exchange_bytes_per_gpu": 8 * M}
+                      "note": "t1_us is the one-GPU lm_head without its argmax pass"})
+            out["layers"]["lm_head_greedy"] = g
+            entry["greedy_head_us"] = g["greedy_head_us"]
+            entry["greedy_head_matches_argmax_of_gathered_logits"] = g["greedy_head_matches_argmax_of_gathered_logits"]
+            entry["greedy_exchange_bytes_per_gpu"] = 8 * M
             head.close()
-        w_bytes_all = n_rows * p["d"] * 2
-        flops_all = 2.0 * M * n_rows * p["d"]
-        best_ms = total_ms if fused_ms is None else min(total_ms, fused_ms)
-        out["layers"][name] = {"rows": n_rows, "rows_per_gpu": rows_local, "kernel": int(lin.info.kernel),
-                               "tile": [int(lin.info.tile_m), int(lin.info.tile_n)],
-                               "aggregate_TFLOPs_local": flops_all / (local_ms * 1e-3) / 1e12,
-                               "aggregate_TFLOPs_with_allgather": flops_all / (total_ms * 1e-3) / 1e12,
-                               "aggregate_TFLOPs_fused_gather": None if fused_ms is None else flops_all / (fused_ms * 1e-3) / 1e12,
-                               # share of the step spent outside the local kernel (gather + re-layout)
-                               "collective_share_allgather": max(0.0, 1.0 - local_ms / total_ms),
-                               "collective_share_best": max(0.0, 1.0 - local_ms / best_ms),
-                               "local_us": local_ms * 1e3, "with_allgather_us": total_ms * 1e3,
-                               "aggregate_GBps_local": w_bytes_all / (local_ms * 1e-3) / 1e9,
-                               "aggregate_GBps_with_allgather": w_bytes_all / (total_ms * 1e-3) / 1e9,
-                               "allgather_bytes_per_gpu": M * cmax * 2,
-                               "fused_gather_us": None if fused_ms is None else fused_ms * 1e3,
-                               "fused_gather_matches_nccl": fused_equal,
-                               "aggregate_GBps_fused_gather": None if fused_ms is None else w_bytes_all / (fused_ms * 1e-3) / 1e9,
-                               **greedy}
+        out["layers"][name] = entry
         if name == "gate_up":
-            # the natural tensor-parallel MLP: this rank's hidden columns feed its K slice of `down`
-            # directly; one all-reduce of [M, d] replaces the all-gather of the hidden state
-            kb, kc = shard_k(p["ffn"], world, rank)
-            if kc == lin.count and kb == lin.begin:
-                w_down = (torch.randn(p["d"], kc, generator=gen) * 0.02).to(torch.bfloat16).to(cuda)
-                down = RowParallelLinear(device, dist, M, p["d"], p["ffn"], w_down, Dtype.BF16)
+            kept = {"lin": lin, "w_host": w_host, "t1_us": t1_us}
+        else:
+            lib.vaicu_linear_plan_destroy(lin.plan)
+            del lin, w_host
 
-                def mlp_local():
-                    lin.local_forward(x)
-                    down.local_forward(lin.slab)
+    # the natural tensor-parallel MLP: this rank's hidden columns feed its K slice of `down`
+    # directly; one all-reduce of [M, d] replaces the all-gather of the hidden state
+    lin = kept["lin"]
+    kb, kc = shard_k(p["ffn"], world, rank)
+    if kc == lin.count and kb == lin.begin:
+        wd_host = _tiled_weight(torch, p["d"], p["ffn"], 31)
+        wd_full = wd_host.to(cuda)
+        h_full = torch.empty((M, p["ffn"]), dtype=torch.bfloat16, device=cuda).normal_(0, 0.5)
+        down_t1_us, _ = one_gpu_us(desc_of(p["d"], p["ffn"], False), wd_full, h_full)
+        del wd_full, h_full
+        w_down = wd_host[:, kb:kb + kc].contiguous().to(cuda)
+        down = RowParallelLinear(device, dist, M, p["d"], p["ffn"], w_down, Dtype.BF16)
 
-                def mlp():
-                    lin.local_forward(x)
-                    down.forward(lin.slab)
+        def mlp_local():
+            lin.local_forward(x)
+            down.local_forward(lin.slab)
 
-                out["layers"]["mlp_column_then_row_parallel"] = {
-                    "down_K_per_gpu": kc, "allreduce_bytes": M * p["d"] * 4,
-                    "gate_up_plus_down_local_us": timed(mlp_local) * 1e3, "with_allreduce_us": timed(mlp) * 1e3}
-                down.close()
-        device.lib.vaicu_linear_plan_destroy(h)
+        def mlp():
+            lin.local_forward(x)
+            down.forward(lin.slab)
+
+        local_ms = _timed(torch, dist, cuda, mlp_local, iters, warmup)
+        total_ms = _timed(torch, dist, cuda, mlp, iters, warmup)
+        # float64 on sampled outputs: hidden = act(gate) * value in bf16 (as the column-split Linear stores it), then down
+        lin.local_forward(x)
+        y = down.forward(lin.slab).clone()
+        err = None
+        if rank == 0:
+            rng = np.random.default_rng(5)
+            rows = rng.integers(0, M, 8)
+            wg = kept["w_host"].double().numpy()
+            xs = x_host[rows].double().numpy()
+            acc = xs @ wg.T
+            hid = _act_f64(act, acc[:, :p["ffn"]]) * acc[:, p["ffn"]:]
+            hid = torch.as_tensor(hid).to(torch.bfloat16).double().numpy()
+            want = hid @ wd_host.double().numpy().T
+            have = y[torch.as_tensor(rows)].double().cpu().numpy()
+            err = float(np.max(np.abs(have - want) / np.maximum(np.abs(want), 0.05)))
+        t1 = kept["t1_us"] + down_t1_us
+        flops_all = 2.0 * M * (2 * p["ffn"]) * p["d"] + 2.0 * M * p["d"] * p["ffn"]
+        bytes_all = (2 * p["ffn"] * p["d"] + p["d"] * p["ffn"]) * 2 + M * p["d"] * 2 * 2 + M * p["ffn"] * 2 * 2
+        e = figures("mlp: gate|value column split -> down split along K", flops_all, bytes_all, t1, total_ms * 1e3, local_ms * 1e3,
+                    f"one NCCL all-reduce of the fp32 partial outputs [{M}, {p['d']}] ({M * p['d'] * 4} bytes)")
+        e.update({"down_K_per_gpu": kc, "allreduce_bytes": M * p["d"] * 4, "gate_up_plus_down_local_us": round(local_ms * 1e3, 1),
+                  "with_allreduce_us": round(total_ms * 1e3, 1), "max_rel_err_vs_float64": err})
+        out["layers"]["mlp_column_then_row_parallel"] = e
+        down.close()
+    lib.vaicu_linear_plan_destroy(lin.plan)
     return out
+
+
+def sharded_report(device, dist, peaks):
+    """What bench.py prints under roofline.sharded at N > 1: both sharded configurations, each layer
+    with its one-GPU time, N-GPU time, speed-up, efficiency, fraction of N x roofline, the
+    collective and its share, and the float64 check.  Raises if a check fails."""
+    decode = bench_sharded(device, dist, "gemma-3-4b", 64, iters=10, warmup=3, peaks=peaks)
+    prefill = bench_sharded(device, dist, "llama-3.2-3b", 8192, iters=5, warmup=2, peaks=peaks)
+    keep = ("layer", "bound", "t1_us", "tN_us", "local_us", "speedup", "efficiency", "aggregate_TFLOPs", "aggregate_GBps",
+            "frac_of_N_x_roofline", "collective", "collective_share", "nccl_allgather_us", "fused_gather_us",
+            "fused_gather_matches_nccl", "greedy_head_matches_argmax_of_gathered_logits", "max_rel_err_vs_float64")
+    report = {"world": decode["world"], "bound_checked": "sampled outputs within 2e-2 of float64 (bf16 operands, fp32 accumulate)"}
+    for key, res in (("gemma3_4b_decode_M64", decode), ("llama32_3b_prefill_M8192", prefill)):
+        rows = []
+        for layer in res["layers"].values():
+            rows.append({k: layer[k] for k in keep if k in layer})
+            errs = layer.get("max_rel_err_vs_float64")
+            for v in (errs.values() if isinstance(errs, dict) else [errs]):
+                if v is not None and not v <= 2e-2:
+                    raise RuntimeError(f"{key} / {layer['layer']}: relative error {v} against float64 exceeds 2e-2")
+            if layer.get("fused_gather_matches_nccl") is False or layer.get("greedy_head_matches_argmax_of_gathered_logits") is False:
+                raise RuntimeError(f"{key} / {layer['layer']}: sharded result differs from the gathered reference")
+        report[key] = rows
+    return report
 
 
 def main():
