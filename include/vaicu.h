@@ -214,6 +214,8 @@ typedef struct vaicu_linear_tuning {
     int32_t  gemv_unroll;   /* k-steps in flight per lane at M = 1: 2 or 4; 0                   */
     int32_t  gemv_grid;     /* blocks of the weight-streaming kernel; 0                         */
     int32_t  gemv_plain_launch; /* 1: no programmatic dependent launch (plain stream order)     */
+    int32_t  tc_separate_fold;  /* 1: split-K partials of the single-CTA tensor-core kernel are
+                                   folded by a second launch instead of by the tile's last CTA  */
 } vaicu_linear_tuning;
 VAICU_API int vaicu_linear_plan_create_tuned(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_linear_tuning* tuning,
                                              vaicu_linear_plan** out);
@@ -237,6 +239,28 @@ VAICU_API int vaicu_linear_workspace_bytes(const vaicu_linear_plan* plan, size_t
 VAICU_API int vaicu_linear_run(vaicu_linear_plan* plan, vaicu_stream_t stream,
                      const void* I, const void* W, const void* bias, const void* residual,
                      void* O, void* workspace);
+
+/* A Linear and the Argmax node that reads its output (the lm_head and the greedy-decode node,
+ * vai/nodes/argmax.h:9-18) as ONE launch of the weight-streaming kernel: every block keeps the best
+ * (value, column) of the outputs it produces and the last block to finish folds the blocks'
+ * candidates, so the logits are never read back.  Same result as vaicu_linear_run followed by
+ * vaicu_argmax_run over O: values compared as stored in o_dtype, lowest index among equal maxima.
+ *   O                 the logits [M, N], or NULL to skip storing them
+ *   argmax_workspace  vaicu_linear_argmax_workspace_bytes(plan) bytes, 256-byte aligned; its first
+ *                     256 bytes must be zero before the FIRST call (vaicu_memset) and are zero again
+ *                     after every call, so a recorded launch replays without a clear
+ *   index_base        added to every column index: the first vocabulary entry of this GPU's slab
+ *   out_val           [M] fp32 maxima, or NULL; out_u32 [M] indices.  A column-split head passes both and
+ *                     folds the ranks' candidates with vaicu_argmax_merge_run.
+ * workspace_bytes reports 0 and run returns VAICU_ERR_UNSUPPORTED for plans that are not on the
+ * weight-streaming kernel (M > 8, or M = 5..8 with 16-bit weights), for gated plans, and for I / W
+ * views that are not 16-byte aligned; the caller then records the two nodes separately.  Two calls that
+ * share a workspace must not overlap on the GPU.  No counterpart in the reference, which records one
+ * dispatch per node. */
+VAICU_API int vaicu_linear_argmax_workspace_bytes(const vaicu_linear_plan* plan, size_t* out_bytes);
+VAICU_API int vaicu_linear_run_argmax(vaicu_linear_plan* plan, vaicu_stream_t stream, const void* I, const void* W,
+                                      const void* bias, const void* residual, void* O, void* argmax_workspace,
+                                      uint32_t index_base, float* out_val, void* out_u32);
 
 /* Two or three Linears that read the same activations (q / k / v of a block) as ONE
  * launch over the concatenation of their weight rows: plans[i] was created for

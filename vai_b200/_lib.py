@@ -33,7 +33,7 @@ class LinearTuning(ctypes.Structure):
     _fields_ = [("kernel", ctypes.c_int32), ("tc_pair", ctypes.c_int32), ("tc_wide", ctypes.c_int32),
                 ("tc_bn", ctypes.c_uint32), ("tc_splits", ctypes.c_uint32), ("gemv_rows", ctypes.c_int32),
                 ("gemv_k_warps", ctypes.c_int32), ("gemv_unroll", ctypes.c_int32), ("gemv_grid", ctypes.c_int32),
-                ("gemv_plain_launch", ctypes.c_int32)]
+                ("gemv_plain_launch", ctypes.c_int32), ("tc_separate_fold", ctypes.c_int32)]
 
     def __init__(self, **kw):
         super().__init__()
@@ -82,6 +82,8 @@ SIGNATURES = {
     "vaicu_linear_plan_last_run": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]),
     "vaicu_linear_workspace_bytes": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
     "vaicu_linear_run": (ctypes.c_int, [ctypes.c_void_p] * 8),
+    "vaicu_linear_argmax_workspace_bytes": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
+    "vaicu_linear_run_argmax": (ctypes.c_int, [ctypes.c_void_p] * 8 + [ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p]),
     "vaicu_linear_run_group": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
                                               ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p)]),
     "vaicu_linear_run_scatter": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,

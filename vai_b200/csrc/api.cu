@@ -126,6 +126,9 @@ struct vaicu_linear_plan {
     const void* map_b_base;
     size_t workspace_bytes;
     uint32_t launches;
+    // split-K on the single-CTA tensor-core kernel: finished-splits count per tile, owned by the plan
+    // (all zero between launches), so that the fold needs no launch of its own
+    unsigned int* tile_done;
     // what the most recent run on this plan enqueued (VAICU_KERNEL_*), and whether it was the
     // 16-byte-vector form of that kernel: differs from `kernel` when a view's alignment sent
     // the call to a fallback
@@ -345,6 +348,7 @@ int validate_tuning(const vaicu_linear_tuning& t)
     if (k != 0 && k != 1 && k != 2 && k != 4 && k != 8) return VAICU_ERR_INVALID_VALUE;
     if (t.gemv_unroll != 0 && t.gemv_unroll != 2 && t.gemv_unroll != 4) return VAICU_ERR_INVALID_VALUE;
     if (t.gemv_grid < 0) return VAICU_ERR_INVALID_VALUE;
+    if (t.tc_separate_fold != 0 && t.tc_separate_fold != 1) return VAICU_ERR_INVALID_VALUE;
     return VAICU_OK;
 }
 
@@ -361,6 +365,7 @@ int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_lin
     pl->dev = dev;
     pl->d = *desc;
     pl->tune = tuning;
+    pl->tile_done = nullptr;
     if (!pl->d.has_bias) { pl->d.bias_elems = 0; pl->d.b_dtype = VAICU_DTYPE_NONE; }
     if (!pl->d.has_residual) pl->d.residual_elems = 0;
     // a [N] bias under M == 1 "covers O" (elems 0); name it per-row so every kernel takes the cheap index
@@ -400,7 +405,19 @@ int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_lin
         pl->workspace_bytes = pl->ws_cast_bytes + pl->ws_partial_bytes;
         // unaligned operands fall back to the FMA tile kernel at run time
         if (pl->fma_ws_bytes > pl->workspace_bytes) pl->workspace_bytes = pl->fma_ws_bytes;
-        pl->launches = 1u + (pl->tc_cast ? 1u : 0u) + (pl->tcp.splits > 1u ? 1u : 0u);
+        if (pl->tcp.splits > 1u && !pl->tcp.pair && !pl->tune.tc_separate_fold) {
+            // the last CTA of a tile folds its splits: a few bytes of device state that live with the plan
+            const size_t bytes = align_up((size_t)pl->tcp.num_tiles * sizeof(unsigned int), 256u);
+            cudaError_t e = cudaSetDevice(dev->ordinal);
+            if (e == cudaSuccess) e = cudaMalloc(&pl->tile_done, bytes);
+            if (e == cudaSuccess) e = cudaMemset(pl->tile_done, 0, bytes);
+            if (e != cudaSuccess) {
+                if (pl->tile_done) cudaFree(pl->tile_done);
+                delete pl;
+                return cuda_fail(e, "split-K tile counters");
+            }
+        }
+        pl->launches = 1u + (pl->tc_cast ? 1u : 0u) + ((pl->tcp.splits > 1u && !pl->tile_done) ? 1u : 0u);
         break;
     default:
         delete pl;
@@ -690,6 +707,10 @@ int vaicu_linear_plan_create_tuned(vaicu_device* dev, const vaicu_linear_desc* d
 int vaicu_linear_plan_destroy(vaicu_linear_plan* plan)
 {
     if (!plan) return VAICU_ERR_INVALID_VALUE;
+    if (plan->tile_done) {
+        cudaSetDevice(plan->dev->ordinal);
+        cudaFree(plan->tile_done);
+    }
     delete plan;
     return VAICU_OK;
 }
@@ -740,6 +761,56 @@ int vaicu_linear_run(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I
                      const void* residual, void* O, void* workspace)
 {
     return run_impl(pl, stream, I, W, bias, residual, O, workspace, nullptr);
+}
+
+namespace {
+size_t argmax_ws_bytes(const vaicu_linear_plan* pl)
+{
+    if (pl->kernel != VAICU_KERNEL_GEMV || !pl->gemv_vec.vectorized || pl->d.gate_fuse) return 0;
+    return 256u + align_up((size_t)pl->gemv_vec.grid * pl->d.M * 8u, 256u);
+}
+}  // namespace
+
+int vaicu_linear_argmax_workspace_bytes(const vaicu_linear_plan* plan, size_t* out)
+{
+    if (!plan || !out) return VAICU_ERR_INVALID_VALUE;
+    *out = argmax_ws_bytes(plan);
+    return VAICU_OK;
+}
+
+int vaicu_linear_run_argmax(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W, const void* bias,
+                            const void* residual, void* O, void* argmax_workspace, uint32_t index_base, float* out_val, void* out_u32)
+{
+    if (!pl || !I || !W || !argmax_workspace || !out_u32) return VAICU_ERR_INVALID_VALUE;
+    const vaicu_linear_desc& d = pl->d;
+    const size_t need = argmax_ws_bytes(pl);
+    if (need == 0) return VAICU_ERR_UNSUPPORTED;             // not the weight-streaming kernel, or a gated Linear
+    if (d.has_bias && !bias) return VAICU_ERR_INVALID_VALUE;
+    if (d.has_residual && !residual) return VAICU_ERR_INVALID_VALUE;
+    if ((uint64_t)index_base + d.N > (1ull << 32)) return VAICU_ERR_INVALID_VALUE;
+    auto elem_aligned = [](const void* p, int dt) { return (reinterpret_cast<uintptr_t>(p) & (dtype_size(dt) - 1u)) == 0; };
+    if (O && !elem_aligned(O, d.o_dtype)) return VAICU_ERR_ALIGNMENT;
+    if (d.has_bias && !elem_aligned(bias, d.b_dtype)) return VAICU_ERR_ALIGNMENT;
+    if (d.has_residual && !elem_aligned(residual, d.o_dtype)) return VAICU_ERR_ALIGNMENT;
+    if ((reinterpret_cast<uintptr_t>(argmax_workspace) & 255u) || (reinterpret_cast<uintptr_t>(out_u32) & 3u) ||
+        (reinterpret_cast<uintptr_t>(out_val) & 3u))
+        return VAICU_ERR_ALIGNMENT;
+    // the fused form exists for the 16-byte-vector kernel only; other views take the two-node path
+    if (!aligned16(I) || !aligned16(W)) return VAICU_ERR_UNSUPPORTED;
+    const LinearArgs a = make_args(d, I, W, d.has_bias ? bias : nullptr, d.has_residual ? residual : nullptr, O);
+    uint8_t* ws = reinterpret_cast<uint8_t*>(argmax_workspace);
+    GemvArgmax am{};
+    am.count = reinterpret_cast<unsigned int*>(ws);
+    am.block_val = reinterpret_cast<float*>(ws + 256u);
+    am.block_idx = reinterpret_cast<uint32_t*>(am.block_val + (size_t)pl->gemv_vec.grid * d.M);
+    am.out_val = out_val;
+    am.out_idx = reinterpret_cast<uint32_t*>(out_u32);
+    am.index_base = index_base;
+    am.write_logits = O ? 1 : 0;
+    pl->last_kernel = VAICU_KERNEL_GEMV;
+    pl->last_vectorized = 1;
+    VAICU_CUDA(launch_gemv(a, pl->gemv_vec, (cudaStream_t)stream, &am));
+    return VAICU_OK;
 }
 
 int vaicu_linear_run_scatter(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W, const void* bias,
@@ -823,6 +894,7 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
     }
     TcParams t = pl->tcp;
     t.O = O; t.bias = a.bias; t.res = a.res; t.partial = partial;
+    t.tile_done = partial ? pl->tile_done : nullptr;
     t.o_aligned16 = aligned16(O) ? 1u : 0u;
     t.n_dst = 1u;
     t.ldo = gate ? d.N / 2u : d.N;
@@ -843,7 +915,7 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
         }
     }
     VAICU_CUDA(launch_tc_gemm(pl->map_a, pl->map_b, t, pl->tc_swap, pl->tc_grid, smem, s));
-    if (partial) VAICU_CUDA(launch_splitk_reduce(a, partial, t.splits, s));
+    if (partial && !t.tile_done) VAICU_CUDA(launch_splitk_reduce(a, partial, t.splits, s));
     return VAICU_OK;
 }
 }  // namespace

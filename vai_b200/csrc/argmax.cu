@@ -11,10 +11,7 @@ namespace {
 
 constexpr int kArgmaxThreads = 1024;
 
-__device__ __forceinline__ void take(float v, uint32_t i, float& best, uint32_t& idx)
-{
-    if (v > best || (v == best && i < idx)) { best = v; idx = i; }
-}
+__device__ __forceinline__ void take(float v, uint32_t i, float& best, uint32_t& idx) { argmax_take(v, i, best, idx); }
 
 __global__ void __launch_bounds__(kArgmaxThreads) argmax_kernel(const void* __restrict__ in, int dtype, uint32_t N,
                                                                 uint32_t* __restrict__ out)

@@ -120,10 +120,40 @@ __device__ __forceinline__ float finish_gated(const EpilogueArgs& e, float acc_g
     return e.scale * (apply_epilogue(e.epilogue, g) * u) + read_res(e, flat);
 }
 
+// Argmax bookkeeping shared by the Argmax kernels and the weight-streaming kernel's fused form:
+// the larger value wins, the LOWER index among equal values (what torch.argmax, the reference's
+// test oracle, returns); a NaN never wins.  kArgmaxLowest is the shader's start value
+// (vAi vai/shaders/argmax.comp:58).
+constexpr float kArgmaxLowest = -3.4028235e38f;
+__device__ __forceinline__ void argmax_take(float v, uint32_t i, float& best, uint32_t& idx)
+{
+    if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+}
+// v as it reads back after being stored in dtype dt.
+__device__ __forceinline__ float round_through(int dt, float v)
+{
+    if (dt == VAICU_DTYPE_F16) return __half2float(__float2half_rn(v));
+    if (dt == VAICU_DTYPE_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+    return v;
+}
+
+// The Argmax node folded into the weight-streaming Linear that feeds it: every block keeps the
+// best (value, column) of the outputs it produces, the last block to finish folds the blocks'
+// candidates.  `count` must be zero when the kernel starts and is zero again when it ends.
+struct GemvArgmax {
+    float* block_val;          // [grid][M]
+    uint32_t* block_idx;       // [grid][M]
+    unsigned int* count;       // blocks done
+    float* out_val;            // [M] or null
+    uint32_t* out_idx;         // [M]
+    uint32_t index_base;       // added to every column index (first vocabulary entry of a slab)
+    int write_logits;          // also store O
+};
+
 // Launchers implemented in the .cu files; each returns a cudaError_t.
 struct GemvConfig { int rows_per_warp; int k_warps; int grid; size_t smem; int vectorized; int unroll; int plain_launch; };
 
-cudaError_t launch_gemv(const LinearArgs& a, const GemvConfig& cfg, cudaStream_t stream);
+cudaError_t launch_gemv(const LinearArgs& a, const GemvConfig& cfg, cudaStream_t stream, const GemvArgmax* argmax = nullptr);
 // `tuning` (may be null) carries a caller's overrides of the geometry; see vaicu_linear_tuning.
 GemvConfig  choose_gemv(const LinearArgs& a, int sm_count, bool w_aligned16, const vaicu_linear_tuning* tuning = nullptr);
 // `a` describes the concatenation (a.N = sum of rows); plain Linears only.

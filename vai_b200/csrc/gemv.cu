@@ -90,6 +90,8 @@ struct GemvParams {
     uint32_t seg_begin[4];   // first virtual row of each segment; [nseg] = total rows
     const void* seg_w[3];
     void* seg_o[3];
+    // Argmax folded into the launch (am.out_idx != null): plain Linears only, no gate, no group.
+    GemvArgmax am;
 };
 
 // Four consecutive activations (chunk-relative kk, kk % 4 == 0) of row m -> fp32 in
@@ -179,6 +181,9 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
     bool staged = false;
     uint4 wv[U][R];           // one trip of weights: U k-steps of R rows per lane
     bool preloaded = false;   // wv already holds the first trip (loaded ahead of the dependency wait)
+    const bool with_argmax = p.am.out_idx != nullptr;
+    float am_best = kArgmaxLowest;          // this lane's best output so far (its batch row m = lane % M)
+    uint32_t am_at = 0xFFFFFFFFu;
 
     for (uint32_t pb = blockIdx.x; pb < nblocks; pb += gridDim.x) {
         const uint32_t g = pb * RG + rg;              // may be >= ngroups: rows clamp, stores skip
@@ -332,7 +337,10 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
                             store_from_f32(p.seg_o[sg], a.o_dtype, (size_t)m * width + (n - p.seg_begin[sg]), mine);
                         } else {
                             const size_t flat = (size_t)m * a.N + n;
-                            store_from_f32(a.O, a.o_dtype, flat, finish_output(ep, mine, flat));
+                            const float v = finish_output(ep, mine, flat);
+                            if (!with_argmax || p.am.write_logits) store_from_f32(a.O, a.o_dtype, flat, v);
+                            // the Argmax node reads the stored logits: compare what the store would hold
+                            if (with_argmax) argmax_take(round_through(a.o_dtype, v), p.am.index_base + n, am_best, am_at);
                         }
                     }
                 }
@@ -350,6 +358,50 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
             }
         }
         if (KS > 1u) __syncthreads();   // red is reused by the next row group
+    }
+
+    if (with_argmax) {
+        // 1. the block's candidate per batch row: lanes r * M + m of the store warps hold results
+        __shared__ float s_val[kThreads];
+        __shared__ uint32_t s_at[kThreads];
+        __shared__ bool s_last;
+        s_val[threadIdx.x] = am_best;
+        s_at[threadIdx.x] = am_at;
+        __syncthreads();
+        if (threadIdx.x < (uint32_t)M) {
+            float best = kArgmaxLowest;
+            uint32_t at = 0xFFFFFFFFu;
+            for (uint32_t w = 0; w < (uint32_t)kWarps; ++w)
+#pragma unroll
+                for (int r = 0; r < R; ++r) argmax_take(s_val[w * 32u + r * M + threadIdx.x], s_at[w * 32u + r * M + threadIdx.x], best, at);
+            p.am.block_val[(size_t)blockIdx.x * M + threadIdx.x] = best;
+            p.am.block_idx[(size_t)blockIdx.x * M + threadIdx.x] = at;
+            __threadfence();                           // candidates visible before the ticket below
+        }
+        __syncthreads();
+        // 2. the last block to take a ticket folds all blocks' candidates; nobody waits for anybody
+        if (threadIdx.x == 0) s_last = atomicAdd(p.am.count, 1u) == gridDim.x - 1u;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            if (warp < (uint32_t)M) {                  // one warp per batch row
+                float best = kArgmaxLowest;
+                uint32_t at = 0xFFFFFFFFu;
+                for (uint32_t b = lane; b < gridDim.x; b += 32u)
+                    argmax_take(__ldcg(p.am.block_val + (size_t)b * M + warp), __ldcg(p.am.block_idx + (size_t)b * M + warp), best, at);
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) {
+                    const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+                    const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, at, off);
+                    argmax_take(ov, oi, best, at);
+                }
+                if (lane == 0u) {
+                    p.am.out_idx[warp] = at == 0xFFFFFFFFu ? p.am.index_base : at;   // a row of NaNs: its first column
+                    if (p.am.out_val) p.am.out_val[warp] = best;
+                }
+            }
+            if (threadIdx.x == 0) *p.am.count = 0u;    // ready for the next launch
+        }
     }
 }
 
@@ -552,11 +604,15 @@ cudaError_t launch_gemv_group(const LinearArgs& a, const GemvConfig& cfg, uint32
     }
 }
 
-cudaError_t launch_gemv(const LinearArgs& a, const GemvConfig& cfg, cudaStream_t stream)
+cudaError_t launch_gemv(const LinearArgs& a, const GemvConfig& cfg, cudaStream_t stream, const GemvArgmax* argmax)
 {
     GemvParams p{};
     p.a = a;
     p.H = a.gate_fuse ? a.N / 2u : a.N;
+    if (argmax) {
+        if (!cfg.vectorized || a.gate_fuse) return cudaErrorInvalidValue;
+        p.am = *argmax;
+    }
     if (!cfg.vectorized) {
         gemv_generic_kernel<<<cfg.grid, kThreads, 0, stream>>>(p);
         return cudaGetLastError();

@@ -344,6 +344,53 @@ __device__ __forceinline__ void finish_col16(const TcParams& p, float* v, float*
     }
 }
 
+// Unswapped kernel: 16 finished dot products (v; u = the value half with GATE) of activation row m,
+// output columns [j0, j0 + 16): bias / epilogue / residual / scale, then the stores.
+template <bool GATE>
+__device__ __forceinline__ void emit_rows16(const TcParams& p, float* v, float* u, uint32_t m, uint32_t j0, uint32_t out_cols,
+                                            uint32_t osz)
+{
+    const uint32_t n_valid = out_cols - j0 < 16u ? out_cols - j0 : 16u;
+    finish_row16<GATE>(p, v, u, m, j0, out_cols, n_valid);
+    // O may be a column slab of wider destinations (ldo, col0), one per GPU
+    const size_t flat0 = (size_t)m * p.ldo + p.col0 + j0;
+    const bool vec_ok = n_valid == 16u && (((size_t)flat0 * osz) % 16u == 0u) && p.o_aligned16;
+    for (uint32_t d = 0; d < p.n_dst; ++d) {
+        void* dst = p.n_dst == 1u ? p.O : p.dst[d];
+        if (vec_ok) store16(dst, p.o_dtype, flat0, v, true);
+        else
+            for (uint32_t c = 0; c < n_valid; ++c) store_from_f32(dst, p.o_dtype, flat0 + c, v[c]);
+    }
+}
+
+// Swapped kernel: this thread owns output column n; v holds its dot products with activation rows
+// m0 .. m0 + 15: bias / epilogue / residual / scale, then the (column-strided) stores.
+template <bool GATE>
+__device__ __forceinline__ void emit_cols16(const TcParams& p, float* v, float* u, uint32_t n, uint32_t m0, uint32_t out_cols,
+                                            float bias_n, float bias_up)
+{
+    finish_col16<GATE>(p, v, u, n, m0, out_cols, bias_n, bias_up);
+    for (uint32_t d = 0; d < p.n_dst; ++d) {
+        void* dst = p.n_dst == 1u ? p.O : p.dst[d];
+        if (p.o_dtype == VAICU_DTYPE_F32) {
+            float* O = reinterpret_cast<float*>(dst);
+#pragma unroll
+            for (uint32_t c = 0; c < 16u; ++c)
+                if (m0 + c < p.M) O[(size_t)(m0 + c) * p.ldo + p.col0 + n] = v[c];
+        } else if (p.o_dtype == VAICU_DTYPE_F16) {
+            __half* O = reinterpret_cast<__half*>(dst);
+#pragma unroll
+            for (uint32_t c = 0; c < 16u; ++c)
+                if (m0 + c < p.M) O[(size_t)(m0 + c) * p.ldo + p.col0 + n] = __float2half_rn(v[c]);
+        } else {
+            __nv_bfloat16* O = reinterpret_cast<__nv_bfloat16*>(dst);
+#pragma unroll
+            for (uint32_t c = 0; c < 16u; ++c)
+                if (m0 + c < p.M) O[(size_t)(m0 + c) * p.ldo + p.col0 + n] = __float2bfloat16_rn(v[c]);
+        }
+    }
+}
+
 // Unswapped epilogue for 16 accumulator columns starting at c0 of one 128-row block:
 // this thread owns activation row m.  r0 / r1 hold the raw accumulators (r1: the value
 // half with GATE).  Either raw split-K partials or the finished outputs are stored.
@@ -378,17 +425,7 @@ __device__ __forceinline__ void store_rows16(const TcParams& p, const uint32_t* 
         float v[16], u[16];
 #pragma unroll
         for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
-        const uint32_t n_valid = out_cols - j0 < 16u ? out_cols - j0 : 16u;
-        finish_row16<GATE>(p, v, u, m, j0, out_cols, n_valid);
-        // O may be a column slab of wider destinations (ldo, col0), one per GPU
-        const size_t flat0 = (size_t)m * p.ldo + p.col0 + j0;
-        const bool vec_ok = n_valid == 16u && (((size_t)flat0 * osz) % 16u == 0u) && p.o_aligned16;
-        for (uint32_t d = 0; d < p.n_dst; ++d) {
-            void* dst = p.n_dst == 1u ? p.O : p.dst[d];
-            if (vec_ok) store16(dst, p.o_dtype, flat0, v, true);
-            else
-                for (uint32_t c = 0; c < n_valid; ++c) store_from_f32(dst, p.o_dtype, flat0 + c, v[c]);
-        }
+        emit_rows16<GATE>(p, v, u, m, j0, out_cols, osz);
     }
 }
 
@@ -425,12 +462,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint64_t* empty_bar = full_bar + stages;
     uint64_t* acc_full = empty_bar + stages;      // [2]
     uint64_t* acc_empty = acc_full + 2;           // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* fold_in = acc_empty + 2;            // split-K fold: the four epilogue warps have written their partials
+    uint64_t* fold_out = fold_in + 1;             // ... and the ticket for this tile has been drawn
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fold_out + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* fold_flag = tmem_slot + 2;     // epilogue warps: "this CTA folds the tile's splits"
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (uint32_t b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        mbar_init(fold_in, 4);
+        mbar_init(fold_out, 1);
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -533,7 +575,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tc_fence_after();
             const uint32_t t_buf = tmem_base + ((q * 32u) << 16) + buf * acc_cols;
             float bias_n = 0.0f, bias_up = 0.0f;
-            if (SWAP && !p.partial && p.bias_mode == OPERAND_PER_COLUMN) {
+            if (SWAP && (!p.partial || p.tile_done) && p.bias_mode == OPERAND_PER_COLUMN) {
                 const uint32_t n = ta * TILE_ROWS + row_in_tile;
                 if (n < out_cols) {
                     bias_n = load_as_f32(p.bias, p.b_dtype, n);
@@ -570,27 +612,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         float v[16], u[16];
 #pragma unroll
                         for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
-                        const uint32_t m0 = tb * bn + c0;
-                        finish_col16<GATE>(p, v, u, n, m0, out_cols, bias_n, bias_up);
-                        for (uint32_t d = 0; d < p.n_dst; ++d) {
-                            void* dst = p.n_dst == 1u ? p.O : p.dst[d];
-                            if (p.o_dtype == VAICU_DTYPE_F32) {
-                                float* O = reinterpret_cast<float*>(dst);
-#pragma unroll
-                                for (uint32_t c = 0; c < 16u; ++c)
-                                    if (m0 + c < p.M) O[(size_t)(m0 + c) * p.ldo + p.col0 + n] = v[c];
-                            } else if (p.o_dtype == VAICU_DTYPE_F16) {
-                                __half* O = reinterpret_cast<__half*>(dst);
-#pragma unroll
-                                for (uint32_t c = 0; c < 16u; ++c)
-                                    if (m0 + c < p.M) O[(size_t)(m0 + c) * p.ldo + p.col0 + n] = __float2half_rn(v[c]);
-                            } else {
-                                __nv_bfloat16* O = reinterpret_cast<__nv_bfloat16*>(dst);
-#pragma unroll
-                                for (uint32_t c = 0; c < 16u; ++c)
-                                    if (m0 + c < p.M) O[(size_t)(m0 + c) * p.ldo + p.col0 + n] = __float2bfloat16_rn(v[c]);
-                            }
-                        }
+                        emit_cols16<GATE>(p, v, u, n, tb * bn + c0, out_cols, bias_n, bias_up);
                     }
                 }
             }
@@ -598,6 +620,65 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
+
+            if (p.partial && p.tile_done) {
+                // Split-K without a second launch: the CTA that finishes the LAST split of this tile
+                // folds all splits' partial sums (in split order, whoever comes last) and stores the
+                // outputs.  Nobody waits for anybody: a ticket per tile decides.
+                // The rendezvous of the four epilogue warps goes through mbarriers, like every other
+                // wait of this kernel, so that it is bounded too.
+                const uint32_t fold_parity = iter & 1u;
+                __threadfence();                                         // this thread's partials, device-wide
+                __syncwarp();
+                if (lane == 0) mbar_arrive(fold_in);
+                if (threadIdx.x == 64u) {
+                    uint32_t mine = 0u;
+                    if (mbar_wait(fold_in, fold_parity, abort_flag)) mine = atomicAdd(p.tile_done + tile, 1u) == p.splits - 1u ? 1u : 0u;
+                    *fold_flag = mine;
+                    mbar_arrive(fold_out);
+                }
+                if (!mbar_wait(fold_out, fold_parity, abort_flag)) { ok = false; break; }
+                if (*fold_flag) {
+                    __threadfence();
+                    const size_t MN = (size_t)p.M * p.N;
+                    for (uint32_t sub = 0; sub < (wide ? 2u : 1u); ++sub) {
+                        const uint32_t row = ta * a_rows + sub * TILE_ROWS + row_in_tile;   // SWAP: output column n; else activation row m
+                        for (uint32_t c0 = 0; c0 < ncols; c0 += 16u) {
+                            float v[16], u[16];
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) { v[c] = 0.0f; u[c] = 0.0f; }
+                            if (SWAP) {
+                                if (row >= out_cols) continue;
+                                const uint32_t m0 = tb * bn + c0;
+                                for (uint32_t zz = 0; zz < p.splits; ++zz) {
+                                    const float* P = p.partial + zz * MN;
+#pragma unroll
+                                    for (uint32_t c = 0; c < 16u; ++c)
+                                        if (m0 + c < p.M) {
+                                            v[c] += __ldcg(P + (size_t)(m0 + c) * p.N + row);
+                                            if (GATE) u[c] += __ldcg(P + (size_t)(m0 + c) * p.N + p.H + row);
+                                        }
+                                }
+                                emit_cols16<GATE>(p, v, u, row, m0, out_cols, bias_n, bias_up);
+                            } else {
+                                const uint32_t j0 = (GATE ? tb * (bn / 2u) : tb * bn) + c0;
+                                if (row >= p.M || j0 >= out_cols) continue;
+                                for (uint32_t zz = 0; zz < p.splits; ++zz) {
+                                    const float* P = p.partial + zz * MN + (size_t)row * p.N;
+#pragma unroll
+                                    for (uint32_t c = 0; c < 16u; ++c)
+                                        if (j0 + c < out_cols) {
+                                            v[c] += __ldcg(P + j0 + c);
+                                            if (GATE) u[c] += __ldcg(P + p.H + j0 + c);
+                                        }
+                                }
+                                emit_rows16<GATE>(p, v, u, row, j0, out_cols, dtype_size(p.o_dtype));
+                            }
+                        }
+                    }
+                    if (threadIdx.x == 64u) p.tile_done[tile] = 0u;      // ready for the next launch
+                }
+            }
         }
     }
 

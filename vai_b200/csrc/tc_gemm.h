@@ -18,6 +18,9 @@ struct TcParams {
     const void* bias;
     const void* res;
     float* partial;        // non-null: split-K, raw fp32 partials [splits][M][N]
+    unsigned int* tile_done;  // non-null (single-CTA kernel, split-K): per-tile count of finished splits; the CTA that
+                              // finishes a tile's last split folds the partials and writes O itself.  All zero
+                              // between launches.
     int* status;           // device word set to 1 when a bounded wait expired
     uint32_t M, N, K;      // Linear dims; N counts weight rows (2H with gate)
     uint32_t H;            // output columns when gate (N / 2), else N

@@ -493,7 +493,7 @@ class NeuralNet:
         return getattr(cls._tls, "net", None)
 
     def __init__(self, w_default_dtype=Dtype.F16, o_default_dtype=Dtype.F32, device=None, use_graph=True,
-                 parallel_branches=True, group_siblings=True, fuse_gated_mul=True, guard_bytes=0):
+                 parallel_branches=True, group_siblings=True, fuse_gated_mul=True, fuse_argmax=True, guard_bytes=0):
         if Dtype(w_default_dtype) == Dtype.NONE or Dtype(o_default_dtype) == Dtype.NONE:
             raise ValueError("default dtypes may not be NONE")
         self.w_default_dtype = Dtype(w_default_dtype)
@@ -507,6 +507,8 @@ class NeuralNet:
         # a GatedMul that is the only reader of a gate|value Linear is recorded into that
         # Linear's launch (False: always two launches and the [.., 2H] intermediate)
         self.fuse_gated_mul = fuse_gated_mul
+        # an Argmax that is the only reader of a weight-streaming Linear shares that Linear's launch
+        self.fuse_argmax = fuse_argmax
         self.max_side_streams = 3
         # outputs up to this size that nothing else reads are stored by their kernel directly into
         # page-locked host memory (0: always a device buffer and a device-to-host copy)
@@ -660,13 +662,12 @@ class NeuralNet:
         for n in self._nodes:
             if hasattr(n, "reset_fusion"):
                 n.reset_fusion()
-        if self.fuse_gated_mul:
-            for n in order:
-                absorb = getattr(n, "absorb_into_producer", None)
-                if absorb is not None:
-                    src = (live[n] if n.producers else n.links).get("in0")
-                    if src is not None and uses.get(src, 0) == 1:
-                        absorb(*src)
+        for n in order:
+            absorb = getattr(n, "absorb_into_producer", None)
+            if absorb is not None and getattr(self, "fuse_" + n.fusion_kind):
+                src = (live[n] if n.producers else n.links).get("in0")
+                if src is not None and uses.get(src, 0) == 1:
+                    absorb(*src)
         direct = set()
         for out in self._outputs.values():
             if out in live and "in0" in live[out] and uses.get(live[out]["in0"], 0) == 1:

@@ -29,6 +29,7 @@ public:
     }
 
     bool fused() const { return fused_; }
+    bool isGatedMul() const override { return true; }
     void resetFusion() override { fused_ = false; }
     bool absorbIntoProducer(Node& producer, const std::string& slot) override
     {

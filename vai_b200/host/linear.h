@@ -171,6 +171,7 @@ public:
     const std::map<std::string, std::vector<std::pair<Node*, std::string>>>& producers() const { return producers_; }
     // a conditional branch (vai::node::Gate): the engine reads its two outputs through this
     virtual bool isGate() const { return false; }
+    virtual bool isGatedMul() const { return false; }
     virtual bool gateOpen() const { return true; }
     bool hasSlot(const std::string& name) const { return slots_.count(name) != 0; }
     Tensor& operator[](const std::string& name) { return slots_.at(name).getValueRef(); }
@@ -184,6 +185,9 @@ public:
     // this node is that output's only reader; true = the producer now does this node's work.
     virtual void resetFusion() {}
     virtual bool absorbIntoProducer(Node& /*producer*/, const std::string& /*slot*/) { return false; }
+    // Called once per recording after every node is prepared and its buffers are bound, before any
+    // run() is recorded: the place for one-time device work that must not be part of the recording.
+    virtual void bound(vaicu_stream_t /*stream*/) {}
     virtual void prepare() = 0;
     virtual void run(vaicu_stream_t stream) = 0;
 };
@@ -238,7 +242,16 @@ public:
     }
     void absorbGate(vai::Epilogue activation, Dtype oDtype) { gate_ = true; gateActivation_ = activation; gateODtype_ = oDtype; }
     bool gateFused() const { return gate_; }
-    void resetFusion() override { gate_ = false; }
+    void resetFusion() override { gate_ = false; argmaxReader_ = nullptr; launchTaken_ = false; }
+
+    // An Argmax that is this node's only reader may share its launch (vaicu_linear_run_argmax)
+    // when the plan turns out to be on the weight-streaming kernel; that node then issues the
+    // launch and this node's run() enqueues nothing.
+    bool canFeedArgmax() const { return !gate_; }
+    void setArgmaxReader(Node* reader) { argmaxReader_ = reader; }
+    void takeLaunch() { launchTaken_ = true; }
+    bool launchTaken() const { return launchTaken_; }
+    vaicu_linear_plan* plan() const { return plan_; }
 
     // linear.h:2291-2704 without the vendor tables: dtype resolution, M, the repeat
     // lengths of bias / residual, then the library's plan (kernel + split choice).
@@ -297,6 +310,7 @@ public:
     void run(vaicu_stream_t stream) override
     {
         if (!plan_) throw std::logic_error("Linear::run before prepare");
+        if (launchTaken_) return;      // the Argmax behind this node launches the fused kernel
         const Tensor& partial = (*this)["partial"];
         check(vaicu_linear_run(plan_, stream, (*this)["in0"].devicePtr(), (*this)["weight"].devicePtr(),
                                hasBias() ? (*this)["bias"].devicePtr() : nullptr,
@@ -309,6 +323,8 @@ private:
     vaicu_linear_plan* plan_ = nullptr;
     vaicu_linear_desc desc_{};
     vaicu_linear_info info_{};
+    Node* argmaxReader_ = nullptr;
+    bool launchTaken_ = false;
     bool gate_ = false;
     vai::Epilogue gateActivation_ = vai::Epilogue::None;
     Dtype gateODtype_ = Dtype::Fp32;

@@ -136,6 +136,7 @@ struct NeuralNetConfig {
     Dtype oDefaultDtype = Dtype::Fp32;   // vai/engine/neural-net.h:283
     bool useGraph = true;                // replay a recorded CUDA graph (else re-enqueue the launches)
     bool fuseGatedMul = true;            // record Linear -> GatedMul as one launch where the wiring allows it
+    bool fuseArgmax = true;              // record a weight-streaming Linear -> Argmax as one launch
 };
 
 class NeuralNet : public NodeOwner
@@ -348,7 +349,7 @@ private:
             n->resetFusion();
             n->setODefaultDtype(config_.oDefaultDtype);
         }
-        if (config_.fuseGatedMul) {
+        if (config_.fuseGatedMul || config_.fuseArgmax) {
             auto linksOf = [&](Node* n) -> const std::map<std::string, std::pair<Node*, std::string>>& {
                 return n->producers().empty() ? n->links() : live[n];
             };
@@ -358,7 +359,8 @@ private:
             for (Node* n : rec.order) {
                 auto& links = linksOf(n);
                 auto it = links.find("in0");
-                if (it != links.end() && readers[it->second] == 1) n->absorbIntoProducer(*it->second.first, it->second.second);
+                const bool wanted = n->isGatedMul() ? config_.fuseGatedMul : config_.fuseArgmax;
+                if (wanted && it != links.end() && readers[it->second] == 1) n->absorbIntoProducer(*it->second.first, it->second.second);
             }
         }
         for (Node* n : rec.order) {
@@ -382,6 +384,7 @@ private:
             rec.outputs[name] = (*link.first)[link.second];
         }
         if (rec.outputs.empty()) throw std::runtime_error("no output is reachable from the inputs given");
+        for (Node* n : rec.order) n->bound(stream_);        // one-time device work, ahead of the recording
         if (config_.useGraph) {
             check(vaicu_graph_capture_begin(stream_), "vaicu_graph_capture_begin");
             try {

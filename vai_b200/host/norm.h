@@ -92,7 +92,11 @@ public:
 };
 
 // Index of the largest value of each row, as uint32 bits in an Fp32-typed [M] tensor
-// (argmax.h:51-79); ties go to the lowest index.
+// (argmax.h:51-79); ties go to the lowest index.  Directly behind a Linear whose output nothing
+// else reads and whose plan is on the weight-streaming kernel (the lm_head of a greedy decoder),
+// the node shares that Linear's launch: the kernel's blocks keep their best logit and the last
+// block folds the candidates (vaicu_linear_run_argmax); the logits are then neither stored nor
+// read back.
 class Argmax : public vai::Node
 {
 public:
@@ -100,20 +104,62 @@ public:
     {
         addSlot("out0", NodeSlot::output);
         addSlot("in0", NodeSlot::input);
+        addSlot("partial", NodeSlot::temporary);
+    }
+    bool fused() const { return fused_; }
+    void resetFusion() override { producer_ = nullptr; fused_ = false; }
+    bool absorbIntoProducer(Node& producer, const std::string& slot) override
+    {
+        auto* lin = dynamic_cast<Linear*>(&producer);
+        if (lin && slot == "out0" && lin->canFeedArgmax()) {
+            producer_ = lin;
+            lin->setArgmaxReader(this);
+        }
+        return producer_ != nullptr;
     }
     void prepare() override
     {
         const Tensor& in = (*this)["in0"];
         if (!in.validShape() || in.shape().size() < 2) throw std::invalid_argument("in0 must have at least two axes");
         (*this)["out0"] = Tensor({outerSize(in.shape())}, Dtype::Fp32);
+        (*this)["partial"] = Tensor();
+        fused_ = false;
+        if (producer_ && producer_->plan() && !producer_->gateFused()) {
+            size_t ws = 0;
+            check(vaicu_linear_argmax_workspace_bytes(producer_->plan(), &ws), "vaicu_linear_argmax_workspace_bytes");
+            const auto aligned16 = [](const void* p) { return p && (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+            if (ws && aligned16((*producer_)["in0"].devicePtr()) && aligned16((*producer_)["weight"].devicePtr())) {
+                fused_ = true;
+                producer_->takeLaunch();
+                (*this)["partial"] = Tensor({(uint32_t)(ws / 4)}, Dtype::Fp32);
+            }
+        }
+    }
+    void bound(vaicu_stream_t stream) override
+    {
+        // the ticket counter at the head of the workspace starts at zero; the kernel leaves it at zero
+        if (fused_) check(vaicu_memset((*this)["partial"].devicePtr(), 0, 256, stream), "vaicu_memset");
     }
     void run(vaicu_stream_t stream) override
     {
+        if (fused_) {
+            Linear& lin = *producer_;
+            check(vaicu_linear_run_argmax(lin.plan(), stream, lin["in0"].devicePtr(), lin["weight"].devicePtr(),
+                                          lin.hasBias() ? lin["bias"].devicePtr() : nullptr,
+                                          lin.config_.acceptResidual ? lin["residual"].devicePtr() : nullptr, nullptr,
+                                          (*this)["partial"].devicePtr(), 0, nullptr, (*this)["out0"].devicePtr()),
+                  "vaicu_linear_run_argmax");
+            return;
+        }
         const Tensor& in = (*this)["in0"];
         check(vaicu_argmax_run(stream, in.devicePtr(), (int)in.dtype(), outerSize(in.shape()), in.shape().back(),
                                (*this)["out0"].devicePtr()),
               "vaicu_argmax_run");
     }
+
+private:
+    Linear* producer_ = nullptr;
+    bool fused_ = false;
 };
 
 // Top-k sampling (topk-sampling.h:33-57): out0 = one raw uint32 index per row; the uniform is

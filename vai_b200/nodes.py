@@ -48,6 +48,8 @@ class LinearNode(Node):
         self.tuning = dict(tuning) if tuning else None
         self._gate = None           # activation of the GatedMul recorded into this node's launch
         self._gate_o_dtype = None   # ... and that node's output dtype
+        self._argmax_reader = None  # the ArgmaxNode that asked to share this node's launch, if any
+        self._launch_taken = False  # that node issues the (fused) launch; this node's own is skipped
         # slot set of Linear::Linear (linear.h:2134-2144)
         self.add_slot("out0", OUTPUT)
         self.add_slot("in0", INPUT)
@@ -70,6 +72,13 @@ class LinearNode(Node):
 
     def reset_fusion(self):
         self._gate = self._gate_o_dtype = None
+        self._argmax_reader = None
+        self._launch_taken = False
+
+    def can_feed_argmax(self):
+        """An Argmax that is this node's only reader may be folded into the launch when the node is
+        not gated; whether the plan is on the weight-streaming kernel is known after prepare()."""
+        return not self.gate_fuse
 
     def can_absorb_gate(self):
         """A GatedMul may ride in this node's epilogue when the node itself ends at
@@ -162,10 +171,15 @@ class LinearNode(Node):
         ws = self["partial"].ptr if self["partial"].valid_shape() else None
         run = dev.lib.vaicu_linear_run
 
+        node = self
+
         def launch(stream):
+            if node._launch_taken:        # the Argmax behind this node launches the fused kernel
+                return
             _lib.check(run(plan, stream, x, w, b, r, o, ws), "vaicu_linear_run")
 
         launch.kernel_launches = int(self.info.launches)
+        self._launch = launch
         return launch
 
     def groupable(self):
@@ -173,7 +187,7 @@ class LinearNode(Node):
         share one launch with sibling Linears that read the same activations."""
         return (self.info is not None and self.info.kernel == KERNEL_GEMV and not self.has_bias()
                 and not self.accept_residual and self.epilogue == Epilogue.NONE and not self.gate_fuse
-                and self.scalar_scale == 1.0)
+                and self.scalar_scale == 1.0 and self._argmax_reader is None)
 
     @staticmethod
     def bind_group(group):
@@ -212,6 +226,8 @@ class GatedMulNode(Node):
     Placed right after a gate|value LinearNode whose output nothing else reads, the node
     launches nothing: the net records it into that Linear's epilogue (see LinearNode) and
     out0 is the Linear's output.  Otherwise it is one streaming kernel."""
+
+    fusion_kind = "gated_mul"       # NeuralNet(fuse_gated_mul=...) switches the merge
 
     def __init__(self, activation=Epilogue.SILU):
         super().__init__()
@@ -269,15 +285,47 @@ class ArgmaxNode(Node):
     indices in 4-byte slots (vAi vai/nodes/argmax.h:9-18; read them with
     Tensor.to_u32()).  Ties go to the lowest index.  Wide rows (a vocabulary) are scanned
     by many blocks in column segments and folded in a second launch; the candidates live
-    in the `partial` temporary."""
+    in the `partial` temporary.
+
+    Behind a LinearNode whose output nothing else reads (the lm_head of a greedy decoder) and
+    whose plan is on the weight-streaming kernel, the node shares that Linear's launch: the
+    kernel's blocks keep the best logit they produce and the last one folds the candidates
+    (vaicu_linear_run_argmax), so the logits are not read a second time and the step is two
+    launches shorter."""
 
     WIDE = 16384        # from this row length on, one block per row is the slower form
+    fusion_kind = "argmax"          # NeuralNet(fuse_argmax=...) switches the merge
 
     def __init__(self):
         super().__init__()
         self.add_slot("out0", OUTPUT)
         self.add_slot("in0", INPUT)
         self.add_slot("partial", TEMPORARY)
+        self._producer = None
+        self.fused = False
+
+    def reset_fusion(self):
+        self._producer = None
+        self.fused = False
+
+    def absorb_into_producer(self, src, src_slot):
+        """Called by the net while it records, when this node is the only reader of src's output:
+        remember a Linear that may carry the argmax; prepare() decides once its plan is known."""
+        if isinstance(src, LinearNode) and src_slot == "out0" and src.can_feed_argmax():
+            self._producer = src
+            src._argmax_reader = self
+        return self._producer is not None
+
+    def _fused_workspace_bytes(self, dev):
+        lin = self._producer
+        if lin is None or lin._plan is None or lin.gate_fuse:
+            return 0
+        ws = ctypes.c_size_t()
+        _lib.check(dev.lib.vaicu_linear_argmax_workspace_bytes(lin._plan, ctypes.byref(ws)), "vaicu_linear_argmax_workspace_bytes")
+        ptrs = (lin["in0"].ptr, lin["weight"].ptr)
+        if any(p is None or p % 16 for p in ptrs):
+            return 0                      # views the vector kernel cannot address: two nodes, two launches
+        return ws.value
 
     def prepare(self):
         x = self["in0"]
@@ -287,6 +335,16 @@ class ArgmaxNode(Node):
         # 4-byte container, as in the reference (argmax.h:75-78)
         self.slots["out0"] = Tensor((x.shape[0],), Dtype.F32)
         self.slots["partial"] = Tensor()
+        self.fused = False
+        if self._producer is not None:
+            from .engine import Device
+            dev = self.net.device if self.net is not None else Device.default()
+            ws = self._fused_workspace_bytes(dev)
+            if ws:
+                self.fused = True
+                self._producer._launch_taken = True
+                self.slots["partial"] = Tensor((ws // 4,), Dtype.F32)
+                return
         if x.shape[1] >= self.WIDE:
             from .engine import Device
             dev = self.net.device if self.net is not None else Device.default()
@@ -299,6 +357,23 @@ class ArgmaxNode(Node):
         dev = self.net.device if self.net is not None else Device.default()
         x, o = self["in0"], self["out0"]
         xp, op, dt, M, N = x.ptr, o.ptr, int(x.dtype), x.shape[0], x.shape[1]
+        if self.fused:
+            lin = self._producer
+            plan, ws = lin._plan, self["partial"].ptr
+            li, lw = lin["in0"].ptr, lin["weight"].ptr
+            lb = lin["bias"].ptr if lin.has_bias() else None
+            lr = lin["residual"].ptr if lin.accept_residual else None
+            # the ticket counter at the head of the workspace starts at zero; the kernel leaves it at zero
+            _lib.check(dev.lib.vaicu_memset(ws, 0, 256, self.net.stream if self.net is not None else None), "vaicu_memset")
+            fused_run = dev.lib.vaicu_linear_run_argmax
+            lin._launch.kernel_launches = 0
+
+            def launch(stream):
+                # nobody else reads the logits (that is why the nodes merged): they are not stored
+                _lib.check(fused_run(plan, stream, li, lw, lb, lr, None, ws, 0, None, op), "vaicu_linear_run_argmax")
+
+            launch.kernel_launches = 1
+            return launch
         if self["partial"].valid_shape():
             ws = self["partial"].ptr
             pairs = dev.lib.vaicu_argmax_pairs_run

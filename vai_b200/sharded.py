@@ -330,6 +330,11 @@ class ShardedGreedyHead:
         n = ctypes.c_size_t()
         _lib.check(lib.vaicu_argmax_workspace_bytes(M, self.count, ctypes.byref(n)), "vaicu_argmax_workspace_bytes")
         self.arg_ws = torch.empty(n.value, dtype=torch.uint8, device=cuda)
+        # up to 4 rows the slab runs on the weight-streaming kernel, whose blocks can keep the best
+        # logit themselves: slab and candidates in one launch, the logits never stored
+        n = ctypes.c_size_t()
+        _lib.check(lib.vaicu_linear_argmax_workspace_bytes(h, ctypes.byref(n)), "vaicu_linear_argmax_workspace_bytes")
+        self.fused_ws = torch.zeros(n.value, dtype=torch.uint8, device=cuda) if n.value else None
         # one buffer [2, M] per rank: row 0 the maxima (fp32), row 1 the token ids (uint32 bits)
         self.mine = torch.empty((2, M), dtype=torch.float32, device=cuda)
         self.all = torch.empty((self.world, 2, M), dtype=torch.float32, device=cuda)
@@ -338,11 +343,16 @@ class ShardedGreedyHead:
     def forward(self, x):
         lib, M = self.dev.lib, self.desc.M
         stream = self.torch.cuda.current_stream().cuda_stream
-        _lib.check(lib.vaicu_linear_run(self.plan, stream, x.data_ptr(), self.w.data_ptr(), None, None, self.logits.data_ptr(),
-                                        self.ws.data_ptr()), "vaicu_linear_run")
-        _lib.check(lib.vaicu_argmax_pairs_run(stream, self.logits.data_ptr(), self.desc.o_dtype, M, self.count, self.count,
-                                              self.begin, self.arg_ws.data_ptr(), self.mine[0].data_ptr(), self.mine[1].data_ptr()),
-                   "vaicu_argmax_pairs_run")
+        if self.fused_ws is not None and x.data_ptr() % 16 == 0 and self.w.data_ptr() % 16 == 0:
+            _lib.check(lib.vaicu_linear_run_argmax(self.plan, stream, x.data_ptr(), self.w.data_ptr(), None, None, None,
+                                                   self.fused_ws.data_ptr(), self.begin, self.mine[0].data_ptr(),
+                                                   self.mine[1].data_ptr()), "vaicu_linear_run_argmax")
+        else:
+            _lib.check(lib.vaicu_linear_run(self.plan, stream, x.data_ptr(), self.w.data_ptr(), None, None, self.logits.data_ptr(),
+                                            self.ws.data_ptr()), "vaicu_linear_run")
+            _lib.check(lib.vaicu_argmax_pairs_run(stream, self.logits.data_ptr(), self.desc.o_dtype, M, self.count, self.count,
+                                                  self.begin, self.arg_ws.data_ptr(), self.mine[0].data_ptr(), self.mine[1].data_ptr()),
+                       "vaicu_argmax_pairs_run")
         if self.world == 1:
             return self.mine[1].view(self.torch.int32)
         self.dist.all_gather_into_tensor(self.all, self.mine)
