@@ -196,7 +196,8 @@ def test_argmax_shares_the_linear_launch(M, K, V, w_dtype, o_dtype, device):
     np.testing.assert_array_equal(one(Tensor.from_numpy(x[::-1].copy())).to_u32(), two(Tensor.from_numpy(x[::-1].copy())).to_u32())
     logits = orc.linear_f64(x, seen(w, DT[w_dtype]), seen(b, DT[w_dtype]))
     top2 = np.sort(logits, axis=1)[:, -2:]
-    clear = (top2[:, 1] - top2[:, 0]) > (1e-2 if o_dtype else 1e-4)
+    # 16-bit logits tie after rounding (bf16 resolves 1/32 near 4.0): only rows whose top two stay apart count
+    clear = (top2[:, 1] - top2[:, 0]) > ({"bf16": 0.07, "f16": 0.01}[o_dtype] if o_dtype else 1e-4)
     np.testing.assert_array_equal(tok1[clear], logits.argmax(axis=1)[clear].astype(np.uint32))
 
 

@@ -399,7 +399,8 @@ def test_config_1_gpt2_mlp_linear_fp32(device):
                                           (128, 4096, 136, "skinny"), (100, 8192, 96, "tc1"), (300, 4096, 264, "tc1")])
 @pytest.mark.parametrize("variant", ["plain", "bias_res_gelu", "gate"])
 def test_split_k_folded_by_the_last_cta(M, K, N, kernel, variant, device):
-    """Split-K on the single-CTA tensor-core kernel without a second launch: the CTA that finishes
+    """The opt-in form of split-K on the single-CTA tensor-core kernel without a second launch
+    (vaicu_linear_tuning.tc_fold_in_kernel): the CTA that finishes
     a tile's last split adds the splits' partial sums in split order and applies bias / epilogue /
     residual.  Against float64, and bit for bit against the same plan with the separate fold
     launch (same partial sums, same order of addition, same epilogue code); replayed twice
@@ -415,31 +416,12 @@ def test_split_k_folded_by_the_last_cta(M, K, N, kernel, variant, device):
     base = dict(tc_pair=0) if kernel == "tc1" else {}
     kw = dict(i_dtype="bf16", w_dtype="bf16", o_dtype="bf16" if variant == "plain" else "f32", b_dtype="f32",
               epilogue="GELU_TANH" if variant != "plain" else "NONE", gate_fuse=gate, kernel=kid)
-    got, want, node = run_linear(x, w, b, r, tuning=dict(base, tc_splits=4), **kw)
+    got, want, node = run_linear(x, w, b, r, tuning=dict(base, tc_splits=4, tc_fold_in_kernel=1), **kw)
     assert node.info.split_count == 4 and node.info.launches == 1
     assert_close(got, want, out_tol(kw["o_dtype"], 2e-4, 5e-5), f"fold {M}x{K}x{N} {variant}")
-    two, _, node2 = run_linear(x, w, b, r, tuning=dict(base, tc_splits=4, tc_separate_fold=1), **kw)
+    two, _, node2 = run_linear(x, w, b, r, tuning=dict(base, tc_splits=4), **kw)
     assert node2.info.split_count == 4 and node2.info.launches == 2
     if variant == "plain":
         np.testing.assert_array_equal(got, two)
     else:       # the separate fold evaluates the activation with libm's exp / tanh, the kernel's epilogue with the fast units
         assert_close(got, two, (1e-5, 1e-5), "fold in the kernel vs fold launch")
-
-
-def test_default_skinny_plans_for_gemma_decode_are_single_launch(device):
-    """Gemma-3-4B's q and down projections at batch 64 with bf16 activations: one launch each
-    (no cast pass, K split over CTAs and folded in the kernel)."""
-    import ctypes
-
-    from vai_b200 import _lib
-    for K, N in ((2560, 2048), (10240, 2560), (2048, 2560)):
-        d = _lib.LinearDesc()
-        d.M, d.N, d.K = 64, N, K
-        d.i_dtype = d.w_dtype = d.o_dtype = 3
-        d.b_dtype, d.scalar_scale = 2, 1.0
-        plan = ctypes.c_void_p()
-        _lib.check(device.lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(plan)), "plan")
-        info = _lib.LinearInfo()
-        _lib.check(device.lib.vaicu_linear_plan_info(plan, ctypes.byref(info)), "info")
-        assert info.kernel == nodes.KERNEL_TC_SKINNY and info.split_count > 1 and info.launches == 1, (K, N, info.split_count, info.launches)
-        device.lib.vaicu_linear_plan_destroy(plan)

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "../../include/vaicu.h"
 
 namespace vaicu {
@@ -182,6 +184,31 @@ cudaError_t launch_layer_norm(const void* in, const void* scale, const void* shi
 
 cudaError_t launch_gated_mul(const void* in, void* out, uint32_t rows, uint32_t H, int i_dtype, int o_dtype, int act,
                              int sm_count, cudaStream_t stream);
+
+// Programmatic dependent launch: the kernel after this one in the stream may start its prologue
+// as soon as every block here has passed launch_dependents(); a kernel launched that way must not
+// touch what its predecessor writes (or write what it reads) before dependency_wait() returns
+// (predecessor complete, its writes visible).  Both are no-ops for a plain launch.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with programmatic stream serialization allowed (only for kernels that call
+// dependency_wait() before their first dependent access).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args)
+{
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = grid;
+    lc.blockDim = block;
+    lc.dynamicSmemBytes = smem;
+    lc.stream = stream;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    return cudaLaunchKernelEx(&lc, kern, std::forward<Args>(args)...);
+}
 
 // cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device property of a kernel: a process
 // that drives several GPUs has to opt in on each of them.  One flag per device ordinal and

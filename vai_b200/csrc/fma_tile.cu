@@ -91,6 +91,8 @@ struct ReduceParams {
 
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p)
 {
+    launch_dependents();
+    dependency_wait();          // the partial sums come from the launch ahead of this one
     const LinearArgs& a = p.a;
     const EpilogueArgs ep = make_epilogue_args(a);
     const size_t MN = (size_t)a.M * a.N;
@@ -116,6 +118,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
 __global__ void __launch_bounds__(256) cast_kernel(const float* __restrict__ src, void* __restrict__ dst,
                                                     int dst_dtype, size_t n)
 {
+    launch_dependents();
+    dependency_wait();          // the activations come from the launch ahead of this one
     const size_t nvec = n / 8u;
     const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, gstride = (size_t)gridDim.x * blockDim.x;
     const bool aligned = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
@@ -167,8 +171,7 @@ cudaError_t launch_splitk_reduce(const LinearArgs& a, const float* partial, uint
     size_t blocks = (total + 255u) / 256u;
     if (blocks > 148u * 16u) blocks = 148u * 16u;
     if (blocks == 0) blocks = 1;
-    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(splitk_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, p);
 }
 
 cudaError_t launch_cast_f32_to_16(const float* src, void* dst, int dst_dtype, size_t n, int sm_count, cudaStream_t stream)
@@ -177,8 +180,7 @@ cudaError_t launch_cast_f32_to_16(const float* src, void* dst, int dst_dtype, si
     const size_t cap = (size_t)sm_count * 8u;
     if (blocks > cap) blocks = cap;
     if (blocks == 0) blocks = 1;
-    cast_kernel<<<(unsigned)blocks, 256, 0, stream>>>(src, dst, dst_dtype, n);
-    return cudaGetLastError();
+    return launch_pdl(cast_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, src, dst, dst_dtype, n);
 }
 
 

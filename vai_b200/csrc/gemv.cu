@@ -59,14 +59,6 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p)
 }
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
-// Programmatic dependent launch: the kernel after this one in the stream may start
-// its prologue as soon as every block here has passed launch_dependents(); a kernel
-// launched that way must not touch what its predecessor writes before
-// dependency_wait() returns (predecessor complete, its writes visible).  Both are
-// no-ops for a plain launch.
-__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 // Position of chunk-relative element kk inside the staged activations.  With
 // 8-element weight vectors a lane needs two float4 per step; splitting every
 // 256-element segment into two 128-float planes keeps both reads conflict free.

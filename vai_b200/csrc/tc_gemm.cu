@@ -490,37 +490,69 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     const uint32_t num_work = p.num_tiles * p.splits;
 
+    // The launch after this one may begin its prologue now (it waits before it touches our results).
+    launch_dependents();
+
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            // One k-block of one operand into its stage.  "A" sits on the UMMA M axis, "B" on N.
+            auto load_a = [&](uint32_t st, uint32_t kb, uint32_t ta) {
+                uint8_t* sa = smem + (size_t)st * stage_bytes;
+                const int32_t kx = (int32_t)(kb * BLOCK_K);
+                tma_load_2d(sa, &tmap_a, &full_bar[st], kx, (int32_t)(ta * a_rows));
+                if (a_boxes == 2u)
+                    tma_load_2d(sa + TILE_ROWS * BLOCK_K * 2u, &tmap_a, &full_bar[st], kx,
+                                (int32_t)(wide ? ta * a_rows + TILE_ROWS : p.H + ta * TILE_ROWS));
+            };
+            auto load_b = [&](uint32_t st, uint32_t kb, uint32_t tb) {
+                uint8_t* sb = smem + (size_t)st * stage_bytes + a_bytes;
+                const int32_t kx = (int32_t)(kb * BLOCK_K);
+                if (GATE && !SWAP) {
+                    const uint32_t half = bn / 2u;
+                    tma_load_2d(sb, &tmap_b, &full_bar[st], kx, (int32_t)(tb * half));
+                    tma_load_2d(sb + half * BLOCK_K * 2u, &tmap_b, &full_bar[st], kx, (int32_t)(p.H + tb * half));
+                } else {
+                    tma_load_2d(sb, &tmap_b, &full_bar[st], kx, (int32_t)(tb * bn));
+                }
+            };
+            bool first = true;
             for (uint32_t w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
                 const uint32_t tile = w / p.splits, z = w - tile * p.splits;
                 uint32_t ta, tb;
                 tile_coords(p, tile, ta, tb);
                 const uint32_t kb0 = z * p.kb_per_split;
                 const uint32_t kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
-                for (uint32_t kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-                    uint8_t* sa = smem + (size_t)stage * stage_bytes;
-                    uint8_t* sb = sa + a_bytes;
-                    mbar_expect_tx(&full_bar[stage], stage_bytes);
-                    const int32_t kx = (int32_t)(kb * BLOCK_K);
-                    tma_load_2d(sa, &tmap_a, &full_bar[stage], kx, (int32_t)(ta * a_rows));
-                    if (a_boxes == 2u)
-                        tma_load_2d(sa + TILE_ROWS * BLOCK_K * 2u, &tmap_a, &full_bar[stage], kx,
-                                    (int32_t)(wide ? ta * a_rows + TILE_ROWS : p.H + ta * TILE_ROWS));
-                    if (GATE && !SWAP) {
-                        const uint32_t half = bn / 2u;
-                        tma_load_2d(sb, &tmap_b, &full_bar[stage], kx, (int32_t)(tb * half));
-                        tma_load_2d(sb + half * BLOCK_K * 2u, &tmap_b, &full_bar[stage], kx, (int32_t)(p.H + tb * half));
-                    } else {
-                        tma_load_2d(sb, &tmap_b, &full_bar[stage], kx, (int32_t)(tb * bn));
+                uint32_t kb = kb0;
+                if (first) {
+                    // The weights do not depend on the launch ahead of this one: the ring's first
+                    // stages take their weight boxes while that launch drains; the activations
+                    // follow once it has completed.  (Weights are operand A when swapped, else B.)
+                    first = false;
+                    const uint32_t npre = (kb1 - kb0 < stages) ? kb1 - kb0 : stages;
+                    for (uint32_t i = 0; i < npre; ++i) {        // the ring is empty: no wait needed
+                        mbar_expect_tx(&full_bar[i], stage_bytes);
+                        if (SWAP) load_a(i, kb0 + i, ta); else load_b(i, kb0 + i, tb);
                     }
+                    dependency_wait();
+                    for (uint32_t i = 0; i < npre; ++i) {
+                        if (SWAP) load_b(i, kb0 + i, tb); else load_a(i, kb0 + i, ta);
+                    }
+                    kb = kb0 + npre;
+                    stage = npre == stages ? 0u : npre;
+                    phase = npre == stages ? 1u : 0u;
+                }
+                for (; kb < kb1; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(&full_bar[stage], stage_bytes);
+                    load_a(stage, kb, ta);
+                    load_b(stage, kb, tb);
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
+            if (first) dependency_wait();
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -566,6 +598,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const uint32_t osz = p.partial ? 4u : dtype_size(p.o_dtype);
         uint32_t iter = 0;
         bool ok = true;
+        dependency_wait();      // residuals may come from, and outputs may still be read by, the launch ahead
         for (uint32_t w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++iter) {
             const uint32_t tile = w / p.splits, z = w - tile * p.splits;
             uint32_t ta, tb;
@@ -822,11 +855,15 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
     const uint32_t num_work = p.num_tiles * p.splits;
 
+    // The launch after this one may begin its prologue now (it waits before it touches our results).
+    launch_dependents();
+
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            bool first = true;
             for (uint32_t w = cluster_id; w < num_work && ok; w += num_clusters) {
                 const uint32_t tile = w / p.splits, z = w - tile * p.splits;
                 uint32_t ta, tb;
@@ -835,7 +872,27 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const uint32_t kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
                 const int32_t ya = (int32_t)(ta * 2u * TILE_ROWS + rank * TILE_ROWS);
                 const int32_t yb = GATE ? (int32_t)((rank ? p.H : 0u) + tb * half) : (int32_t)(tb * bn + rank * half);
-                for (uint32_t kb = kb0; kb < kb1; ++kb) {
+                uint32_t kb = kb0;
+                if (first) {
+                    // The weights (operand B) do not depend on the launch ahead of this one: the ring's
+                    // first stages take their weight boxes while that launch drains; the activations
+                    // follow once it has completed.
+                    first = false;
+                    const uint32_t npre = (kb1 - kb0 < stages) ? kb1 - kb0 : stages;
+                    for (uint32_t i = 0; i < npre; ++i) {        // the ring is empty: no wait needed
+                        if (rank == 0u) mbar_expect_tx(&full_bar[i], 2u * stage_bytes);
+                        tma_load_2d_pair(smem + (size_t)i * stage_bytes + a_bytes, &tmap_b, map_to_cta(smem_u32(&full_bar[i]), 0u),
+                                         (int32_t)((kb0 + i) * BLOCK_K), yb);
+                    }
+                    dependency_wait();
+                    for (uint32_t i = 0; i < npre; ++i)
+                        tma_load_2d_pair(smem + (size_t)i * stage_bytes, &tmap_a, map_to_cta(smem_u32(&full_bar[i]), 0u),
+                                         (int32_t)((kb0 + i) * BLOCK_K), ya);
+                    kb = kb0 + npre;
+                    stage = npre == stages ? 0u : npre;
+                    phase = npre == stages ? 1u : 0u;
+                }
+                for (; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                     uint8_t* sa = smem + (size_t)stage * stage_bytes;
                     if (rank == 0u) mbar_expect_tx(&full_bar[stage], 2u * stage_bytes);   // both CTAs' boxes
@@ -846,6 +903,7 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
+            if (first) dependency_wait();
             // the leader's last commits land on this CTA's barriers before it may leave
             for (uint32_t s = 0; s < stages && ok; ++s) {
                 if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) ok = false;
@@ -889,6 +947,7 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t ncols = GATE ? half : bn;
         uint32_t iter = 0;
         bool ok = true;
+        dependency_wait();      // residuals may come from, and outputs may still be read by, the launch ahead
         for (uint32_t w = cluster_id; w < num_work && ok; w += num_clusters, ++iter) {
             const uint32_t tile = w / p.splits, z = w - tile * p.splits;
             uint32_t ta, tb;
@@ -996,8 +1055,7 @@ static cudaError_t launch_pair_variant(const CUtensorMap& ma, const CUtensorMap&
     auto kern = tc_gemm_pair_kernel<GATE>;
     static SmemOptIn optin;
     if (cudaError_t e = optin.ensure(kern, (int)kTcMaxSmem); e != cudaSuccess) return e;
-    kern<<<grid, kTcThreads, smem, stream>>>(ma, mb, p);
-    return cudaGetLastError();
+    return launch_pdl(kern, dim3((unsigned)grid), dim3(kTcThreads), smem, stream, ma, mb, p);
 }
 
 // Number of CTA pairs that can be resident at once (pairs need two SMs of one TPC).
@@ -1020,17 +1078,12 @@ cudaError_t tc_pair_max_clusters(size_t smem, int* clusters)
 __global__ void __launch_bounds__(32) wait_expiry_selftest_kernel(int* status)
 {
     __shared__ uint64_t bar;
-    __shared__ uint32_t abort_word;
     if (threadIdx.x == 0) {
         mbar_init(&bar, 1);
-        abort_word = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         bool arrived = false;
         for (uint32_t spin = 0; spin < 1024u && !arrived; ++spin) arrived = mbar_try_wait(&bar, 0u);
-        if (!arrived) {
-            abort_word = 1u;
-            atomicExch(status, 1);
-        }
+        if (!arrived) atomicExch(status, 1);
     }
 }
 
@@ -1047,8 +1100,7 @@ static cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, 
     auto kern = tc_gemm_kernel<SWAP, GATE>;
     static SmemOptIn optin;
     if (cudaError_t e = optin.ensure(kern, (int)kTcMaxSmem); e != cudaSuccess) return e;
-    kern<<<grid, kTcThreads, smem, stream>>>(ma, mb, p);
-    return cudaGetLastError();
+    return launch_pdl(kern, dim3((unsigned)grid), dim3(kTcThreads), smem, stream, ma, mb, p);
 }
 
 cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p, bool swap, int grid,
