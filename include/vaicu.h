@@ -214,9 +214,10 @@ typedef struct vaicu_linear_tuning {
     int32_t  gemv_unroll;   /* k-steps in flight per lane at M = 1: 2 or 4; 0                   */
     int32_t  gemv_grid;     /* blocks of the weight-streaming kernel; 0                         */
     int32_t  gemv_plain_launch; /* 1: no programmatic dependent launch (plain stream order)     */
-    int32_t  tc_fold_in_kernel; /* 1: split-K partials of the single-CTA tensor-core kernel are folded by
-                                   the tile's last CTA instead of by a second launch (measured
-                                   slower on B200: the fold then runs on one SM per tile)       */
+    int32_t  tc_fold;           /* split-K of the single-CTA tensor-core kernels: 1 = the CTAs that hold a
+                                   tile's splits fold it together inside the kernel (one launch; measured
+                                   slower on B200 than the dependent fold launch), 2 = a second launch
+                                   folds; 0: the second launch                                  */
 } vaicu_linear_tuning;
 VAICU_API int vaicu_linear_plan_create_tuned(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_linear_tuning* tuning,
                                              vaicu_linear_plan** out);

@@ -398,13 +398,14 @@ def test_config_1_gpt2_mlp_linear_fp32(device):
 @pytest.mark.parametrize("M,K,N,kernel", [(64, 10240, 2560, "skinny"), (64, 2560, 2048, "skinny"), (33, 4096, 200, "skinny"),
                                           (128, 4096, 136, "skinny"), (100, 8192, 96, "tc1"), (300, 4096, 264, "tc1")])
 @pytest.mark.parametrize("variant", ["plain", "bias_res_gelu", "gate"])
-def test_split_k_folded_by_the_last_cta(M, K, N, kernel, variant, device):
-    """The opt-in form of split-K on the single-CTA tensor-core kernel without a second launch
-    (vaicu_linear_tuning.tc_fold_in_kernel): the CTA that finishes
-    a tile's last split adds the splits' partial sums in split order and applies bias / epilogue /
-    residual.  Against float64, and bit for bit against the same plan with the separate fold
-    launch (same partial sums, same order of addition, same epilogue code); replayed twice
-    through one recording, so the per-tile counters have to come back to zero."""
+def test_split_k_folded_inside_the_kernel(M, K, N, kernel, variant, device):
+    """Split-K on the single-CTA tensor-core kernels without a second launch (an option,
+    vaicu_linear_tuning.tc_fold = 1; the default is a dependent fold launch): the CTAs that hold a
+    tile's splits publish their partial sums, wait (bounded) for each other, and each folds a slice
+    of the tile in split order with bias / epilogue / residual.  Against float64, and bit for bit
+    against the same plan with the separate fold launch (same partial sums, same order of addition,
+    same epilogue code); replayed through one recording, so the per-tile counters have to come
+    back to zero."""
     rng = np.random.default_rng(M + K + N)
     gate = variant == "gate"
     rows = 2 * N if gate else N
@@ -416,12 +417,9 @@ def test_split_k_folded_by_the_last_cta(M, K, N, kernel, variant, device):
     base = dict(tc_pair=0) if kernel == "tc1" else {}
     kw = dict(i_dtype="bf16", w_dtype="bf16", o_dtype="bf16" if variant == "plain" else "f32", b_dtype="f32",
               epilogue="GELU_TANH" if variant != "plain" else "NONE", gate_fuse=gate, kernel=kid)
-    got, want, node = run_linear(x, w, b, r, tuning=dict(base, tc_splits=4, tc_fold_in_kernel=1), **kw)
+    got, want, node = run_linear(x, w, b, r, tuning=dict(base, tc_splits=4, tc_fold=1), **kw)
     assert node.info.split_count == 4 and node.info.launches == 1
     assert_close(got, want, out_tol(kw["o_dtype"], 2e-4, 5e-5), f"fold {M}x{K}x{N} {variant}")
-    two, _, node2 = run_linear(x, w, b, r, tuning=dict(base, tc_splits=4), **kw)
+    two, _, node2 = run_linear(x, w, b, r, tuning=dict(base, tc_splits=4, tc_fold=2), **kw)
     assert node2.info.split_count == 4 and node2.info.launches == 2
-    if variant == "plain":
-        np.testing.assert_array_equal(got, two)
-    else:       # the separate fold evaluates the activation with libm's exp / tanh, the kernel's epilogue with the fast units
-        assert_close(got, two, (1e-5, 1e-5), "fold in the kernel vs fold launch")
+    np.testing.assert_array_equal(got, two)

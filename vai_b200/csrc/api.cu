@@ -348,7 +348,7 @@ int validate_tuning(const vaicu_linear_tuning& t)
     if (k != 0 && k != 1 && k != 2 && k != 4 && k != 8) return VAICU_ERR_INVALID_VALUE;
     if (t.gemv_unroll != 0 && t.gemv_unroll != 2 && t.gemv_unroll != 4) return VAICU_ERR_INVALID_VALUE;
     if (t.gemv_grid < 0) return VAICU_ERR_INVALID_VALUE;
-    if (t.tc_fold_in_kernel != 0 && t.tc_fold_in_kernel != 1) return VAICU_ERR_INVALID_VALUE;
+    if (t.tc_fold < 0 || t.tc_fold > 2) return VAICU_ERR_INVALID_VALUE;
     return VAICU_OK;
 }
 
@@ -405,8 +405,8 @@ int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_lin
         pl->workspace_bytes = pl->ws_cast_bytes + pl->ws_partial_bytes;
         // unaligned operands fall back to the FMA tile kernel at run time
         if (pl->fma_ws_bytes > pl->workspace_bytes) pl->workspace_bytes = pl->fma_ws_bytes;
-        if (pl->tcp.splits > 1u && !pl->tcp.pair && pl->tune.tc_fold_in_kernel) {
-            // the last CTA of a tile folds its splits: a few bytes of device state that live with the plan
+        if (pl->tcp.splits > 1u && !pl->tcp.pair && pl->tune.tc_fold == 1) {
+            // the CTAs of a tile's splits fold it together: a counter per tile, device state that lives with the plan
             const size_t bytes = align_up((size_t)pl->tcp.num_tiles * sizeof(unsigned int), 256u);
             cudaError_t e = cudaSetDevice(dev->ordinal);
             if (e == cudaSuccess) e = cudaMalloc(&pl->tile_done, bytes);

@@ -608,7 +608,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tc_fence_after();
             const uint32_t t_buf = tmem_base + ((q * 32u) << 16) + buf * acc_cols;
             float bias_n = 0.0f, bias_up = 0.0f;
-            if (SWAP && (!p.partial || p.tile_done) && p.bias_mode == OPERAND_PER_COLUMN) {
+            if (SWAP && !p.partial && p.bias_mode == OPERAND_PER_COLUMN) {
                 const uint32_t n = ta * TILE_ROWS + row_in_tile;
                 if (n < out_cols) {
                     bias_n = load_as_f32(p.bias, p.b_dtype, n);
@@ -655,61 +655,84 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
 
             if (p.partial && p.tile_done) {
-                // Split-K without a second launch: the CTA that finishes the LAST split of this tile
-                // folds all splits' partial sums (in split order, whoever comes last) and stores the
-                // outputs.  Nobody waits for anybody: a ticket per tile decides.
-                // The rendezvous of the four epilogue warps goes through mbarriers, like every other
-                // wait of this kernel, so that it is bounded too.
+                // Split-K without a second launch: the CTAs that hold the splits of one tile fold it
+                // together.  Each publishes its partial sums and counts itself in; once all `splits`
+                // have, each adds up a slice of the tile (every split's partial, in split order, so
+                // the result does not depend on who arrived when) and stores the finished outputs.
+                // The splits of a tile are neighbouring work items, hence run at the same time on
+                // CTAs that are all resident (one per SM): the wait is short, and bounded like every
+                // other wait of this kernel.
                 const uint32_t fold_parity = iter & 1u;
                 __threadfence();                                         // this thread's partials, device-wide
                 __syncwarp();
                 if (lane == 0) mbar_arrive(fold_in);
                 if (threadIdx.x == 64u) {
-                    uint32_t mine = 0u;
-                    if (mbar_wait(fold_in, fold_parity, abort_flag)) mine = atomicAdd(p.tile_done + tile, 1u) == p.splits - 1u ? 1u : 0u;
-                    *fold_flag = mine;
+                    uint32_t go = 0u;
+                    if (mbar_wait(fold_in, fold_parity, abort_flag)) {
+                        unsigned int* counter = p.tile_done + tile;
+                        atomicAdd(counter, 1u);
+                        for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+                            unsigned int seen;
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+                            if (seen >= p.splits) { go = 1u; break; }
+                            __nanosleep(64);
+                        }
+                        if (go) {
+                            // counted in a second time once past the wait; the last one through leaves zero behind
+                            if (atomicAdd(counter, 1u) == 2u * p.splits - 1u) atomicExch(counter, 0u);
+                        } else {
+                            *abort_flag = 1u;
+                        }
+                    }
+                    *fold_flag = go;
                     mbar_arrive(fold_out);
                 }
                 if (!mbar_wait(fold_out, fold_parity, abort_flag)) { ok = false; break; }
-                if (*fold_flag) {
-                    __threadfence();
+                if (!*fold_flag) { ok = false; break; }
+                __threadfence();
+                {
+                    EpilogueArgs ep;
+                    ep.bias = p.bias; ep.res = p.res; ep.b_dtype = p.b_dtype; ep.o_dtype = p.o_dtype;
+                    ep.has_bias = p.has_bias; ep.has_res = p.has_res; ep.residual_order = p.residual_order;
+                    ep.epilogue = p.epilogue; ep.bias_elems = p.bias_elems; ep.res_elems = p.res_elems; ep.scale = p.scale;
                     const size_t MN = (size_t)p.M * p.N;
+                    // the axis this CTA takes a slice of: activation rows when swapped (a thread owns an
+                    // output column), output columns otherwise (a thread owns an activation row)
+                    const uint32_t base = SWAP ? tb * bn : (GATE ? tb * (bn / 2u) : tb * bn);
+                    const uint32_t limit = SWAP ? p.M : out_cols;
+                    const uint32_t span = SWAP ? bn : ncols;
+                    const uint32_t extent = base >= limit ? 0u : (limit - base < span ? limit - base : span);
+                    const uint32_t per = (extent + p.splits - 1u) / p.splits;
+                    const uint32_t lo = z * per, hi = (lo + per < extent) ? lo + per : extent;
                     for (uint32_t sub = 0; sub < (wide ? 2u : 1u); ++sub) {
-                        const uint32_t row = ta * a_rows + sub * TILE_ROWS + row_in_tile;   // SWAP: output column n; else activation row m
-                        for (uint32_t c0 = 0; c0 < ncols; c0 += 16u) {
-                            float v[16], u[16];
+                        const uint32_t row = ta * a_rows + sub * TILE_ROWS + row_in_tile;   // swapped: output column; else activation row
+                        if (row >= (SWAP ? out_cols : p.M)) continue;
+                        for (uint32_t i = lo; i < hi; i += 4u) {
+                            float g[4] = {0.0f, 0.0f, 0.0f, 0.0f}, u[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                            size_t at[4];
 #pragma unroll
-                            for (int c = 0; c < 16; ++c) { v[c] = 0.0f; u[c] = 0.0f; }
-                            if (SWAP) {
-                                if (row >= out_cols) continue;
-                                const uint32_t m0 = tb * bn + c0;
-                                for (uint32_t zz = 0; zz < p.splits; ++zz) {
-                                    const float* P = p.partial + zz * MN;
+                            for (uint32_t q = 0; q < 4u; ++q) {
+                                const uint32_t j = base + ((i + q < hi) ? i + q : hi - 1u);
+                                at[q] = SWAP ? (size_t)j * p.N + row : (size_t)row * p.N + j;
+                            }
+                            for (uint32_t zz = 0; zz < p.splits; ++zz) {
+                                const float* P = p.partial + zz * MN;
 #pragma unroll
-                                    for (uint32_t c = 0; c < 16u; ++c)
-                                        if (m0 + c < p.M) {
-                                            v[c] += __ldcg(P + (size_t)(m0 + c) * p.N + row);
-                                            if (GATE) u[c] += __ldcg(P + (size_t)(m0 + c) * p.N + p.H + row);
-                                        }
+                                for (uint32_t q = 0; q < 4u; ++q) {
+                                    g[q] += __ldcg(P + at[q]);
+                                    if (GATE) u[q] += __ldcg(P + at[q] + p.H);
                                 }
-                                emit_cols16<GATE>(p, v, u, row, m0, out_cols, bias_n, bias_up);
-                            } else {
-                                const uint32_t j0 = (GATE ? tb * (bn / 2u) : tb * bn) + c0;
-                                if (row >= p.M || j0 >= out_cols) continue;
-                                for (uint32_t zz = 0; zz < p.splits; ++zz) {
-                                    const float* P = p.partial + zz * MN + (size_t)row * p.N;
+                            }
 #pragma unroll
-                                    for (uint32_t c = 0; c < 16u; ++c)
-                                        if (j0 + c < out_cols) {
-                                            v[c] += __ldcg(P + j0 + c);
-                                            if (GATE) u[c] += __ldcg(P + p.H + j0 + c);
-                                        }
-                                }
-                                emit_rows16<GATE>(p, v, u, row, j0, out_cols, dtype_size(p.o_dtype));
+                            for (uint32_t q = 0; q < 4u; ++q) {
+                                if (i + q >= hi) continue;
+                                const uint32_t m = SWAP ? base + i + q : row, n = SWAP ? row : base + i + q;
+                                const size_t flat = (size_t)m * out_cols + n;
+                                const float v = GATE ? finish_gated(ep, g[q], u[q], n, p.H, flat) : finish_output(ep, g[q], flat);
+                                store_from_f32(p.O, p.o_dtype, (size_t)m * p.ldo + p.col0 + n, v);
                             }
                         }
                     }
-                    if (threadIdx.x == 64u) p.tile_done[tile] = 0u;      // ready for the next launch
                 }
             }
         }
