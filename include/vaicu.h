@@ -285,6 +285,34 @@ VAICU_API int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count,
 VAICU_API int vaicu_linear_run_scatter(vaicu_linear_plan* plan, vaicu_stream_t stream, const void* I, const void* W,
                                        const void* bias, void* const* dsts, int n_dst, uint32_t ldo, uint32_t col0,
                                        void* workspace);
+/* Row-parallel Linear (this GPU holds a slice of K: columns [k0, k1) of W and of the activations) whose
+ * partial sums go straight to the GPUs that will fold them: row m of the plan's [M, N] output belongs to
+ * GPU m / (M / n_dst), and the epilogue stores it, tile by tile with plain stores over NVLink, into that
+ * GPU's staging buffer at dsts[owner][(slot * M / n_dst + m % (M / n_dst)) * N + n], in the plan's o_dtype.
+ * Every staging buffer holds n_dst slabs of [M / n_dst, N]; `slot` is this rank.  The reduce-scatter of a
+ * tensor-parallel MLP thereby overlaps the GEMM instead of following it.  After a vaicu_peer_barrier_run
+ * each GPU folds its slabs with vaicu_partial_fold_run.  Plain tensor-core plans only (no bias, epilogue,
+ * residual, scale, gate or split-K: those belong to the fold); M divisible by n_dst; 16-byte aligned
+ * destinations.  No counterpart in the single-device reference. */
+VAICU_API int vaicu_linear_run_reduce_scatter(vaicu_linear_plan* plan, vaicu_stream_t stream, const void* I, const void* W,
+                                              void* const* dsts, int n_dst, int slot, void* workspace);
+/* The fold after it: O[row0 + i, n] = scale * sum over p < n_parts of parts[p][i][n] (+ residual[row0 + i, n]),
+ * i < rows, parts [n_parts][rows][N] in part_dtype (summed in fp32, in slab order), residual and outputs [.., N]
+ * in o_dtype; the finished rows are stored into every dsts[d] (this GPU's output and its peers': the
+ * all-gather of the row slabs), followed by another vaicu_peer_barrier_run before anyone reads them. */
+VAICU_API int vaicu_partial_fold_run(vaicu_device* dev, vaicu_stream_t stream, const void* parts, uint32_t n_parts, uint32_t rows,
+                                     uint32_t N, int part_dtype, const void* residual, float scale, int o_dtype,
+                                     void* const* dsts, int n_dst, uint32_t row0);
+/* Barrier between the streams of the `world` (<= 8) GPUs of a split Linear, as one single-warp kernel per
+ * GPU: rank r stores the next epoch into slot r of every rank's flag array (flag_arrays[t], `world`
+ * uint32 each, zero at the start, shared through vaicu_ipc_*), then waits until every slot of its own
+ * array has reached that epoch.  Stores a rank made to its peers in earlier kernels of its stream are
+ * visible to them behind the barrier.  epoch_counter is 4 bytes of this GPU's memory, zero at the start.
+ * All ranks must enqueue their barriers in the same order.  The wait is bounded (about half a second):
+ * when a peer never arrives the kernel sets the status word read by vaicu_device_status and returns. */
+VAICU_API int vaicu_peer_barrier_run(vaicu_device* dev, vaicu_stream_t stream, void* const* flag_arrays, int world, int rank,
+                                     void* epoch_counter);
+
 /* Share a vaicu_buffer_alloc'ed range with the other processes of this host: export fills a
  * 64-byte handle to send to them, open maps a peer's range into this process (peer access
  * over NVLink), close unmaps it.  No counterpart in the reference. */

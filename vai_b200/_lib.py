@@ -88,6 +88,11 @@ SIGNATURES = {
                                               ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p)]),
     "vaicu_linear_run_scatter": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
                                                                         ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]),
+    "vaicu_linear_run_reduce_scatter": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "vaicu_partial_fold_run": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
+                                              ctypes.c_int, ctypes.c_void_p, ctypes.c_float, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+                                              ctypes.c_int, ctypes.c_uint32]),
+    "vaicu_peer_barrier_run": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
     "vaicu_ipc_export": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "vaicu_ipc_open": (ctypes.c_int, [ctypes.c_void_p, c_void_pp]),
     "vaicu_ipc_close": (ctypes.c_int, [ctypes.c_void_p]),

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libvaicu.so")
-SOURCES = ["api.cu", "gemv.cu", "fma_tile.cu", "tc_gemm.cu", "argmax.cu", "rms_norm.cu", "topk.cu", "gated_mul.cu"]
+SOURCES = ["api.cu", "gemv.cu", "fma_tile.cu", "tc_gemm.cu", "argmax.cu", "rms_norm.cu", "topk.cu", "gated_mul.cu", "peer.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

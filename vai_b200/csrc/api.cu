@@ -752,6 +752,7 @@ namespace {
 struct OutputSpec {
     uint32_t n_dst, ldo, col0;
     void* dst[8];
+    uint32_t rs_rows, rs_slot;      // row-parallel run: rows per owner (0 = off) and this rank's slab in the owners' staging
 };
 int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W, const void* bias,
              const void* residual, void* O, void* workspace, const OutputSpec* spec);
@@ -761,6 +762,62 @@ int vaicu_linear_run(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I
                      const void* residual, void* O, void* workspace)
 {
     return run_impl(pl, stream, I, W, bias, residual, O, workspace, nullptr);
+}
+
+int vaicu_linear_run_reduce_scatter(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W,
+                                    void* const* dsts, int n_dst, int slot, void* workspace)
+{
+    if (!pl || !dsts || n_dst < 1 || n_dst > 8 || slot < 0 || slot >= n_dst) return VAICU_ERR_INVALID_VALUE;
+    const vaicu_linear_desc& d = pl->d;
+    // partial sums only: anything after the dot product belongs to the fold that follows the exchange
+    if (!pl->tc || pl->tcp.splits > 1u || d.has_residual || d.has_bias || d.gate_fuse || d.epilogue != VAICU_EPILOGUE_NONE ||
+        d.scalar_scale != 1.0f)
+        return VAICU_ERR_UNSUPPORTED;
+    if (d.M % (uint32_t)n_dst) return VAICU_ERR_INVALID_VALUE;
+    OutputSpec spec{};
+    spec.n_dst = (uint32_t)n_dst;
+    spec.ldo = d.N;
+    spec.col0 = 0;
+    spec.rs_rows = d.M / (uint32_t)n_dst;
+    spec.rs_slot = (uint32_t)slot;
+    for (int i = 0; i < n_dst; ++i) {
+        if (!dsts[i]) return VAICU_ERR_INVALID_VALUE;
+        if (reinterpret_cast<uintptr_t>(dsts[i]) & 15u) return VAICU_ERR_ALIGNMENT;
+        spec.dst[i] = dsts[i];
+    }
+    return run_impl(pl, stream, I, W, nullptr, nullptr, dsts[0], workspace, &spec);
+}
+
+int vaicu_partial_fold_run(vaicu_device* dev, vaicu_stream_t stream, const void* parts, uint32_t n_parts, uint32_t rows, uint32_t N,
+                           int part_dtype, const void* residual, float scale, int o_dtype, void* const* dsts, int n_dst, uint32_t row0)
+{
+    if (!dev || !parts || !dsts || n_parts == 0 || rows == 0 || N == 0 || n_dst < 1 || n_dst > 8) return VAICU_ERR_INVALID_VALUE;
+    if (!valid_dtype(part_dtype) || !valid_dtype(o_dtype)) return VAICU_ERR_INVALID_VALUE;
+    if ((uint64_t)(row0 + rows) * N >= (1ull << 32)) return VAICU_ERR_INVALID_VALUE;
+    if (reinterpret_cast<uintptr_t>(parts) & 15u) return VAICU_ERR_ALIGNMENT;
+    for (int i = 0; i < n_dst; ++i) {
+        if (!dsts[i]) return VAICU_ERR_INVALID_VALUE;
+        if (reinterpret_cast<uintptr_t>(dsts[i]) & (dtype_size(o_dtype) - 1u)) return VAICU_ERR_ALIGNMENT;
+    }
+    if (residual && (reinterpret_cast<uintptr_t>(residual) & (dtype_size(o_dtype) - 1u))) return VAICU_ERR_ALIGNMENT;
+    VAICU_CUDA(launch_partial_fold(parts, n_parts, rows, N, part_dtype, residual, scale, o_dtype, dsts, (uint32_t)n_dst, row0,
+                                   dev->sm_count, (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
+int vaicu_peer_barrier_run(vaicu_device* dev, vaicu_stream_t stream, void* const* flag_arrays, int world, int rank, void* epoch_counter)
+{
+    if (!dev || !flag_arrays || !epoch_counter || world < 1 || world > 8 || rank < 0 || rank >= world) return VAICU_ERR_INVALID_VALUE;
+    uint32_t* flags[8] = {};
+    for (int i = 0; i < world; ++i) {
+        if (!flag_arrays[i]) return VAICU_ERR_INVALID_VALUE;
+        if (reinterpret_cast<uintptr_t>(flag_arrays[i]) & 3u) return VAICU_ERR_ALIGNMENT;
+        flags[i] = reinterpret_cast<uint32_t*>(flag_arrays[i]);
+    }
+    if (reinterpret_cast<uintptr_t>(epoch_counter) & 3u) return VAICU_ERR_ALIGNMENT;
+    VAICU_CUDA(launch_peer_barrier(flags, world, rank, reinterpret_cast<uint32_t*>(epoch_counter), dev->status_word,
+                                   (cudaStream_t)stream));
+    return VAICU_OK;
 }
 
 namespace {
@@ -903,6 +960,8 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
     if (spec) {
         t.n_dst = spec->n_dst; t.ldo = spec->ldo; t.col0 = spec->col0;
         for (uint32_t i = 0; i < spec->n_dst; ++i) t.dst[i] = spec->dst[i];
+        t.rs_rows = spec->rs_rows;
+        t.rs_slot = spec->rs_slot;
         if (t.pair && spec->n_dst > 1u) {
             // stores to peers go out as whole 128-byte row segments: one ring stage less, 16 KB of staging
             const uint32_t stage_bytes = 128u * 128u + (t.bn / 2u) * 128u;

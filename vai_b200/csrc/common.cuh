@@ -182,6 +182,9 @@ cudaError_t launch_rms_norm(const void* in, const void* scale, const void* shift
 cudaError_t launch_layer_norm(const void* in, const void* scale, const void* shift, const void* res, void* out, uint32_t rows,
                             uint32_t feat, int i_dtype, int w_dtype, int o_dtype, float eps, int sm_count, cudaStream_t stream);
 
+cudaError_t launch_peer_barrier(uint32_t* const* flags, int world, int rank, uint32_t* epoch, int* status, cudaStream_t stream);
+cudaError_t launch_partial_fold(const void* parts, uint32_t n_parts, uint32_t rows, uint32_t N, int part_dtype, const void* residual,
+                                float scale, int o_dtype, void* const* dsts, uint32_t n_dst, uint32_t row0, int sm_count, cudaStream_t stream);
 cudaError_t launch_gated_mul(const void* in, void* out, uint32_t rows, uint32_t H, int i_dtype, int o_dtype, int act,
                              int sm_count, cudaStream_t stream);
 

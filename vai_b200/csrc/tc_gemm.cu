@@ -352,10 +352,15 @@ __device__ __forceinline__ void emit_rows16(const TcParams& p, float* v, float* 
 {
     const uint32_t n_valid = out_cols - j0 < 16u ? out_cols - j0 : 16u;
     finish_row16<GATE>(p, v, u, m, j0, out_cols, n_valid);
-    // O may be a column slab of wider destinations (ldo, col0), one per GPU
-    const size_t flat0 = (size_t)m * p.ldo + p.col0 + j0;
+    // O may be a column slab of wider destinations (ldo, col0), one per GPU; a row-parallel run
+    // sends the row to the one GPU that owns it
+    uint32_t owner;
+    size_t row;
+    output_row(p, m, owner, row);
+    const size_t flat0 = row * p.ldo + p.col0 + j0;
     const bool vec_ok = n_valid == 16u && (((size_t)flat0 * osz) % 16u == 0u) && p.o_aligned16;
     for (uint32_t d = 0; d < p.n_dst; ++d) {
+        if (owner != 0xFFFFFFFFu && d != owner) continue;
         void* dst = p.n_dst == 1u ? p.O : p.dst[d];
         if (vec_ok) store16(dst, p.o_dtype, flat0, v, true);
         else
@@ -370,6 +375,16 @@ __device__ __forceinline__ void emit_cols16(const TcParams& p, float* v, float* 
                                             float bias_n, float bias_up)
 {
     finish_col16<GATE>(p, v, u, n, m0, out_cols, bias_n, bias_up);
+    if (p.rs_rows) {                       // row-parallel run: each activation row goes to its owner's staging
+        for (uint32_t c = 0; c < 16u; ++c) {
+            if (m0 + c >= p.M) break;
+            uint32_t owner;
+            size_t row;
+            output_row(p, m0 + c, owner, row);
+            store_from_f32(p.dst[owner], p.o_dtype, row * p.ldo + p.col0 + n, v[c]);
+        }
+        return;
+    }
     for (uint32_t d = 0; d < p.n_dst; ++d) {
         void* dst = p.n_dst == 1u ? p.O : p.dst[d];
         if (p.o_dtype == VAICU_DTYPE_F32) {
@@ -1041,9 +1056,13 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t rr = it * 4u + (lane >> 3), chunk = lane & 7u;
                     const uint4 val = *reinterpret_cast<const uint4*>(staging + (size_t)q * 4096u + (size_t)rr * 128u + ((chunk ^ (rr & 7u)) * 16u));
                     if (m_base + rr < p.M) {
-                        const size_t byte_off = ((size_t)(m_base + rr) * p.ldo + p.col0 + j_seg) * osz + (size_t)chunk * 16u;
+                        uint32_t owner;
+                        size_t row;
+                        output_row(p, m_base + rr, owner, row);
+                        const size_t byte_off = (row * p.ldo + p.col0 + j_seg) * osz + (size_t)chunk * 16u;
                         for (uint32_t d = 0; d < p.n_dst; ++d)
-                            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.n_dst == 1u ? p.O : p.dst[d]) + byte_off) = val;
+                            if (owner == 0xFFFFFFFFu || d == owner)
+                                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.n_dst == 1u ? p.O : p.dst[d]) + byte_off) = val;
                     }
                 }
                 __syncwarp();

@@ -43,8 +43,24 @@ struct TcParams {
     uint32_t staged;       // CTA-pair kernel: finished tiles go through shared memory so that stores to the
                            // destinations (peers over NVLink) are whole 128-byte row segments
     void* dst[8];
+    // Row-parallel run (rs_rows > 0): the outputs are partial sums over this GPU's slice of K, and
+    // row m belongs to GPU m / rs_rows, which folds the ranks' partials.  Element (m, j) then goes to
+    // dst[m / rs_rows][(rs_slot * rs_rows + m % rs_rows) * ldo + j]: this rank's slab of the owner's staging.
+    uint32_t rs_rows, rs_slot;
     float scale;
 };
+
+// Where output row m goes: the destination buffer and the row index inside it.
+__host__ __device__ inline void output_row(const TcParams& p, uint32_t m, uint32_t& owner, size_t& row)
+{
+    if (p.rs_rows) {
+        owner = m / p.rs_rows;
+        row = (size_t)p.rs_slot * p.rs_rows + (m - owner * p.rs_rows);
+    } else {
+        owner = 0xFFFFFFFFu;      // every destination takes the row
+        row = m;
+    }
+}
 
 // Tile order: groups of `group` A-tiles (UMMA-M side) sweep all B-tiles before the
 // next group starts, so CTAs running at the same time share operand slabs in L2.

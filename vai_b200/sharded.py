@@ -143,11 +143,63 @@ class _CudaView:
         self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 3}
 
 
+def share_buffer(device, dist, nbytes, zero=False):
+    """One cudaMalloc'ed range per rank, opened by every other rank through CUDA IPC.  Returns
+    (own DeviceBuffer, [pointer to rank r's range for r in range(world)], [opened pointers to close])."""
+    from .engine import DeviceBuffer
+    lib = device.lib
+    rank, world = dist.get_rank(), dist.get_world_size()
+    own = DeviceBuffer(device, nbytes)
+    if zero:
+        _lib.check(lib.vaicu_memset(own.ptr, 0, nbytes, None), "vaicu_memset")
+        device.synchronize()
+    handle = (ctypes.c_uint8 * 64)()
+    _lib.check(lib.vaicu_ipc_export(own.ptr, handle), "vaicu_ipc_export")
+    handles = [None] * world
+    dist.all_gather_object(handles, bytes(handle))
+    by_rank, opened = [], []
+    for r, raw in enumerate(handles):
+        if r == rank:
+            by_rank.append(own.ptr)
+            continue
+        p = ctypes.c_void_p()
+        _lib.check(lib.vaicu_ipc_open((ctypes.c_uint8 * 64).from_buffer_copy(raw), ctypes.byref(p)), "vaicu_ipc_open")
+        opened.append(p)
+        by_rank.append(p.value)
+    return own, by_rank, opened
+
+
+class PeerBarrier:
+    """Barrier between the ranks' streams without a library collective: one single-warp kernel per
+    GPU that signals every peer through flag words in their memory and waits, bounded, for theirs
+    (vaicu_peer_barrier_run).  What a rank stored into its peers' buffers before the barrier is
+    visible to them after it.  A few microseconds, where a 4-byte NCCL all-reduce costs tens."""
+
+    def __init__(self, device, dist):
+        from .engine import DeviceBuffer
+        self.dev, self.rank, self.world = device, dist.get_rank(), dist.get_world_size()
+        self.flags, by_rank, self._opened = share_buffer(device, dist, 256, zero=True)
+        self.ptrs = (ctypes.c_void_p * self.world)(*by_rank)
+        self.epoch = DeviceBuffer(device, 256)
+        _lib.check(device.lib.vaicu_memset(self.epoch.ptr, 0, 256, None), "vaicu_memset")
+        device.synchronize()
+        dist.barrier()          # every rank's flags are zero and mapped before the first kernel signals
+
+    def run(self, stream):
+        _lib.check(self.dev.lib.vaicu_peer_barrier_run(self.dev.handle, stream, self.ptrs, self.world, self.rank, self.epoch.ptr),
+                   "vaicu_peer_barrier_run")
+
+    def close(self):
+        for p in self._opened:
+            self.dev.lib.vaicu_ipc_close(p)
+        self._opened = []
+
+
 class FusedGatherLinear(ShardedLinear):
     """Column-split Linear whose tensor-core epilogue writes this rank's slab straight into
     every rank's [M, n_out] output (vaicu_linear_run_scatter): the all-gather happens
-    tile by tile as plain stores over NVLink, and the only collective left is a tiny
-    stream-ordered all-reduce that tells every rank that all slabs have landed.
+    tile by tile as plain stores over NVLink, followed by a barrier kernel (PeerBarrier) that
+    tells every rank that all slabs have landed; no library collective is left on the path.
 
     The outputs are cudaMalloc'ed ranges shared through CUDA IPC handles; no TMA descriptor
     and no multicast load touches peer memory — peers are only ever stored to.
@@ -158,7 +210,7 @@ class FusedGatherLinear(ShardedLinear):
     neighbour and ends with itself.  (2) A fast rank may start call n + 1 while a slow rank's
     consumers of call n still read its output; two outputs alternate by call parity, so a
     store of call n + 1 lands in the buffer nobody has read since call n - 1, and the flag
-    all-reduce of call n (which every rank passes only after its readers of call n - 1 were
+    barrier of call n (which every rank passes only after its readers of call n - 1 were
     enqueued ahead of it on the same stream) orders that reuse."""
 
     def __init__(self, device, dist, full_desc, w_local, bias_local=None):
@@ -205,7 +257,7 @@ class FusedGatherLinear(ShardedLinear):
             view = torch.as_tensor(_CudaView(out.ptr, (self.desc.M, self.n_out), typestr), device=cuda)
             self.results.append(view.view(torch.bfloat16) if self.desc.o_dtype == 3 else view)
         self.calls = 0
-        self.flag = torch.zeros(1, dtype=torch.float32, device=cuda)
+        self.barrier = PeerBarrier(device, dist)
 
     def forward(self, x):
         stream = self.torch.cuda.current_stream().cuda_stream
@@ -215,12 +267,13 @@ class FusedGatherLinear(ShardedLinear):
                                                          self.b.data_ptr() if self.b is not None else None,
                                                          self.ptrs[parity], self.world, self.n_out, self.begin,
                                                          self.ws.data_ptr()), "vaicu_linear_run_scatter")
-        # every rank's kernel precedes its contribution on the stream: when the reduction
-        # returns, all slabs are in this rank's output
-        self.dist.all_reduce(self.flag)
+        # every rank's kernel precedes its signal on the stream: behind the barrier all slabs
+        # are in this rank's output
+        self.barrier.run(stream)
         return self.results[parity]
 
     def close(self):
+        self.barrier.close()
         for p in self._opened:
             self.dev.lib.vaicu_ipc_close(p)
         self._opened = []
@@ -297,6 +350,90 @@ class RowParallelLinear:
         return out
 
     def close(self):
+        if self.plan:
+            self.dev.lib.vaicu_linear_plan_destroy(self.plan)
+            self.plan = None
+
+
+class FusedRowParallelLinear:
+    """`down` split along K with the reduction done by this package's kernels over NVLink instead
+    of an all-reduce after the GEMM:
+
+      1. the GEMM's epilogue stores every finished tile of partial sums straight into the staging
+         buffer of the GPU that owns those rows (vaicu_linear_run_reduce_scatter): the
+         reduce-scatter traffic overlaps the remaining tiles;
+      2. barrier; each GPU adds the `world` slabs it received for its M / world rows, applies scale and
+         residual, and stores the finished rows into every GPU's output (vaicu_partial_fold_run): that
+         is the all-gather;
+      3. barrier; the [M, N] output is complete everywhere.
+
+    Partial sums cross the link in `part_dtype` and are added in fp32.  fp32 is the default of the
+    callers here: 16-bit partials halve the bytes but lose accuracy where the ranks' partial sums
+    cancel (the rounding is relative to the partials, not to their sum).
+    Two barriers per call order every reuse of the staging and output buffers across calls."""
+
+    def __init__(self, device, dist, M, N, K, w_local, w_dtype, part_dtype=0, scalar_scale=1.0):
+        import torch
+
+        from .engine import Dtype
+        self.torch, self.dist, self.dev = torch, dist, device
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        if M % self.world:
+            raise ValueError("M must be divisible by the number of ranks")
+        self.M, self.N, self.rows = M, N, M // self.world
+        self.k_begin, self.k_count = shard_k(K, self.world, self.rank)
+        self.part_dtype = Dtype(part_dtype)
+        self.o_dtype = Dtype(w_dtype)
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = M, N, self.k_count
+        d.i_dtype = d.w_dtype = int(w_dtype)
+        d.o_dtype = int(self.part_dtype)
+        d.b_dtype = int(Dtype.NONE)
+        d.scalar_scale = 1.0
+        d.split_size = max(32, self.k_count)         # one K span: the partials leave through the epilogue
+        self.desc, self.scale, self.w = d, float(scalar_scale), w_local
+        lib = device.lib
+        h = ctypes.c_void_p()
+        _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
+        self.plan = h
+        self.info = _lib.LinearInfo()
+        _lib.check(lib.vaicu_linear_plan_info(h, ctypes.byref(self.info)), "info")
+        cuda = torch.device("cuda", device.ordinal)
+        self.ws = torch.empty(max(self.info.workspace_bytes, 256), dtype=torch.uint8, device=cuda)
+        psz = 4 if self.part_dtype == Dtype.F32 else 2
+        osz = 4 if self.o_dtype == Dtype.F32 else 2
+        self._opened = []
+        self.staging, by_rank, opened = share_buffer(device, dist, self.world * self.rows * N * psz)
+        self._opened += opened
+        self.staging_ptrs = (ctypes.c_void_p * self.world)(*by_rank)
+        self.out, by_rank, opened = share_buffer(device, dist, M * N * osz)
+        self._opened += opened
+        order = destination_order(self.rank, self.world)
+        self.out_ptrs = (ctypes.c_void_p * self.world)(*[by_rank[r] for r in order])
+        typestr = {0: "<f4", 1: "<f2", 3: "<u2"}[int(self.o_dtype)]
+        view = torch.as_tensor(_CudaView(self.out.ptr, (M, N), typestr), device=cuda)
+        self.result = view.view(torch.bfloat16) if self.o_dtype == Dtype.BF16 else view
+        self.barrier = PeerBarrier(device, dist)
+
+    def forward(self, x_slice, residual=None):
+        """x_slice: this rank's columns [k0, k1) of the activations, contiguous [M, k_count];
+        residual: the full [M, N] residual in the output dtype (every rank holds it), or None."""
+        lib = self.dev.lib
+        stream = self.torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.vaicu_linear_run_reduce_scatter(self.plan, stream, x_slice.data_ptr(), self.w.data_ptr(), self.staging_ptrs,
+                                                       self.world, self.rank, self.ws.data_ptr()), "vaicu_linear_run_reduce_scatter")
+        self.barrier.run(stream)
+        _lib.check(lib.vaicu_partial_fold_run(self.dev.handle, stream, self.staging.ptr, self.world, self.rows, self.N,
+                                              int(self.part_dtype), residual.data_ptr() if residual is not None else None, self.scale,
+                                              int(self.o_dtype), self.out_ptrs, self.world, self.rank * self.rows), "vaicu_partial_fold_run")
+        self.barrier.run(stream)
+        return self.result
+
+    def close(self):
+        self.barrier.close()
+        for p in self._opened:
+            self.dev.lib.vaicu_ipc_close(p)
+        self._opened = []
         if self.plan:
             self.dev.lib.vaicu_linear_plan_destroy(self.plan)
             self.plan = None
@@ -609,6 +746,24 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5, p
 
         local_ms = _timed(torch, dist, cuda, mlp_local, iters, warmup)
         total_ms = _timed(torch, dist, cuda, mlp, iters, warmup)
+        # the same MLP with the reduction done by the GEMM's epilogue, a fold kernel and two barrier
+        # kernels over NVLink (no library collective)
+        fused_ms, fused_err, fused_how = None, None, None
+        if dist is not None and world > 1 and M % world == 0:
+            # fp32 partial sums: the ranks' partials cancel in part, so rounding them to 16 bits first costs
+            # up to 2^-9 of the LARGER magnitude (measured: 6 % of the outputs off by more than 2e-2 of
+            # max(|ref|, 0.05) with bf16 partials at M = 8192, none with fp32)
+            part = Dtype.F32
+            rp = FusedRowParallelLinear(device, dist, M, p["d"], p["ffn"], w_down, Dtype.BF16, part_dtype=part)
+
+            def mlp_fused():
+                lin.local_forward(x)
+                return rp.forward(lin.slab)
+
+            yf = mlp_fused().clone()
+            fused_ms = _timed(torch, dist, cuda, mlp_fused, iters, warmup)
+            fused_how = (f"reduce-scatter fused into the down GEMM's epilogue ({'bf16' if part == Dtype.BF16 else 'fp32'} partial sums "
+                         "stored to the rows' owners over NVLink), fold kernel that stores the finished rows to every GPU, two barrier kernels")
         # float64 on sampled outputs: hidden = act(gate) * value in bf16 (as the column-split Linear stores it), then down
         lin.local_forward(x)
         y = down.forward(lin.slab).clone()
@@ -624,13 +779,22 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5, p
             want = hid @ wd_host.double().numpy().T
             have = y[torch.as_tensor(rows)].double().cpu().numpy()
             err = float(np.max(np.abs(have - want) / np.maximum(np.abs(want), 0.05)))
+            if fused_ms is not None:
+                have = yf[torch.as_tensor(rows)].double().cpu().numpy()
+                fused_err = float(np.max(np.abs(have - want) / np.maximum(np.abs(want), 0.05)))
         t1 = kept["t1_us"] + down_t1_us
         flops_all = 2.0 * M * (2 * p["ffn"]) * p["d"] + 2.0 * M * p["d"] * p["ffn"]
         bytes_all = (2 * p["ffn"] * p["d"] + p["d"] * p["ffn"]) * 2 + M * p["d"] * 2 * 2 + M * p["ffn"] * 2 * 2
-        e = figures("mlp: gate|value column split -> down split along K", flops_all, bytes_all, t1, total_ms * 1e3, local_ms * 1e3,
-                    f"one NCCL all-reduce of the fp32 partial outputs [{M}, {p['d']}] ({M * p['d'] * 4} bytes)")
+        best_ms, how = total_ms, f"one NCCL all-reduce of the fp32 partial outputs [{M}, {p['d']}] ({M * p['d'] * 4} bytes)"
+        if fused_ms is not None and fused_ms < total_ms:
+            best_ms, how = fused_ms, fused_how
+        e = figures("mlp: gate|value column split -> down split along K", flops_all, bytes_all, t1, best_ms * 1e3, local_ms * 1e3, how)
         e.update({"down_K_per_gpu": kc, "allreduce_bytes": M * p["d"] * 4, "gate_up_plus_down_local_us": round(local_ms * 1e3, 1),
-                  "with_allreduce_us": round(total_ms * 1e3, 1), "max_rel_err_vs_float64": err})
+                  "nccl_allreduce_us": round(total_ms * 1e3, 1),
+                  "fused_reduce_scatter_us": None if fused_ms is None else round(fused_ms * 1e3, 1),
+                  "max_rel_err_vs_float64": {"nccl": err, "fused": fused_err}})
+        if fused_ms is not None:
+            rp.close()
         out["layers"]["mlp_column_then_row_parallel"] = e
         down.close()
     lib.vaicu_linear_plan_destroy(lin.plan)
@@ -645,6 +809,7 @@ def sharded_report(device, dist, peaks):
     prefill = bench_sharded(device, dist, "llama-3.2-3b", 8192, iters=5, warmup=2, peaks=peaks)
     keep = ("layer", "bound", "t1_us", "tN_us", "local_us", "speedup", "efficiency", "aggregate_TFLOPs", "aggregate_GBps",
             "frac_of_N_x_roofline", "collective", "collective_share", "nccl_allgather_us", "fused_gather_us",
+            "nccl_allreduce_us", "fused_reduce_scatter_us",
             "fused_gather_matches_nccl", "greedy_head_matches_argmax_of_gathered_logits", "max_rel_err_vs_float64")
     report = {"world": decode["world"], "bound_checked": "sampled outputs within 2e-2 of float64 (bf16 operands, fp32 accumulate)"}
     for key, res in (("gemma3_4b_decode_M64", decode), ("llama32_3b_prefill_M8192", prefill)):
