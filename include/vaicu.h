@@ -414,6 +414,22 @@ VAICU_API int vaicu_topk_workspace_bytes(uint32_t M, uint32_t N, uint32_t k, siz
 VAICU_API int vaicu_topk_sample_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, uint32_t k,
                                     float temperature, const float* u_device, void* workspace, void* out_u32);
 
+/* TopKSampling over a vocabulary split across GPUs (vai/nodes/topk-sampling.h:33-57 applied in two steps; the
+ * reference is single-device).  Step 1 on every GPU: the k best logits of each row of its slab, in rank order
+ * (value descending, index ascending), as k (fp32 bits, uint32 index) pairs per row with index_base (the
+ * slab's first vocabulary entry) added; a slab narrower than k pads with (lowest float, 0xFFFFFFFF).
+ *   logits     [M, N] with a row stride of `ld` elements: a window of wider rows works
+ *   workspace  vaicu_topk_workspace_bytes(M, N, k) bytes (0 for rows of at most 2048 columns)
+ *   out_pairs  [M, k] pairs, 8-byte aligned
+ * The GPUs all-gather their [M, k] lists (8 k bytes per row and GPU instead of logits).  Step 2 on every
+ * GPU with the same uniform: merge `groups` lists per row — list g of row m at pairs[g * group_stride + m *
+ * list_len], strides in pairs — keep the best k of the union and sample as vaicu_topk_sample_run does.  The
+ * token equals the one the single-GPU node draws from the whole row. */
+VAICU_API int vaicu_topk_candidates_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, size_t ld,
+                                        uint32_t k, uint32_t index_base, void* workspace, void* out_pairs);
+VAICU_API int vaicu_topk_merge_sample_run(vaicu_stream_t stream, const void* pairs, uint32_t groups, size_t group_stride, uint32_t M,
+                                          uint32_t list_len, uint32_t k, float temperature, const float* u_device, void* out_u32);
+
 /* Column-split helper for the multi-GPU layout: the desc of rank `rank` of
  * `world` when W's rows (output columns) are split evenly; for gate_fuse the
  * split is per half.  Fills row offsets into W / bias for that rank. No

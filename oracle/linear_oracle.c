@@ -488,6 +488,80 @@ int vai_oracle_topk_sample(const float* in, uint32_t M, uint32_t N, uint32_t K, 
     return 0;
 }
 
+/* TopKSampling over a vocabulary split across GPUs (no counterpart in the single-device reference;
+ * the same rules applied in two steps).  Step 1, per slab: the k best of each row of the slab's
+ * logits [M, n_slab] in (value descending, index ascending) order with index_base added to the
+ * column index; a slab narrower than k pads its list with (lowest float, 0xFFFFFFFF).  Step 2:
+ * merge `groups` such lists per row (list g of row m at vals / idxs [g * group_stride + m * k]) into the k
+ * best of their union in the same order, then the reference's softmax + inverse-CDF sample
+ * (vai/shaders/topk-sampling.comp:237-258).  The top-k of a union lies within the union of the
+ * parts' top-k, so the two steps give exactly what vai_oracle_topk_sample gives on whole rows. */
+int vai_oracle_topk_candidates(const float* in, uint32_t M, uint32_t N, uint32_t K, uint32_t index_base, float* out_val,
+                               uint32_t* out_idx)
+{
+    if (K == 0 || K > 128u) return 1;
+    for (uint32_t row = 0; row < M; ++row) {
+        const float* x = in + (size_t)row * N;
+        float* tv = out_val + (size_t)row * K;
+        uint32_t* ti = out_idx + (size_t)row * K;
+        for (uint32_t r = 0; r < K; ++r) {
+            float bv = -3.4028235e38f;
+            uint32_t bi = 0xFFFFFFFFu;
+            if (r < N)
+                for (uint32_t i = 0; i < N; ++i) {
+                    const float v = x[i];
+                    const uint32_t gi = index_base + i;
+                    if (r > 0 && !(v < tv[r - 1] || (v == tv[r - 1] && gi > ti[r - 1]))) continue;
+                    if (v > bv || (v == bv && gi < bi)) { bv = v; bi = gi; }
+                }
+            tv[r] = bv;
+            ti[r] = bi;
+        }
+    }
+    return 0;
+}
+
+int vai_oracle_topk_merge_sample(const float* vals, const uint32_t* idxs, uint32_t groups, size_t group_stride, uint32_t M,
+                                 uint32_t list_len, uint32_t K, float temperature, float u, uint32_t* out)
+{
+    if (K == 0 || K > 128u || groups == 0 || list_len == 0) return 1;
+    float top_v[128];
+    uint32_t top_i[128];
+    uint32_t pos[64];
+    if (groups > 64u) return 1;
+    for (uint32_t row = 0; row < M; ++row) {
+        for (uint32_t g = 0; g < groups; ++g) pos[g] = 0;
+        for (uint32_t r = 0; r < K; ++r) {
+            float bv = -3.4028235e38f;
+            uint32_t bi = 0xFFFFFFFFu, bg = 0xFFFFFFFFu;
+            for (uint32_t g = 0; g < groups; ++g) {
+                if (pos[g] >= list_len) continue;
+                const size_t at = (size_t)g * group_stride + (size_t)row * list_len + pos[g];
+                const float v = vals[at];
+                const uint32_t i = idxs[at];
+                if (i == 0xFFFFFFFFu) continue;                       /* padding of a narrow slab */
+                if (bg == 0xFFFFFFFFu || v > bv || (v == bv && i < bi)) { bv = v; bi = i; bg = g; }
+            }
+            top_v[r] = bv;
+            top_i[r] = bi;
+            if (bg != 0xFFFFFFFFu) pos[bg]++;
+        }
+        const float inv_t = 1.0f / (temperature > 1e-6f ? temperature : 1e-6f);
+        const float m = top_v[0];
+        float z = 0.0f;
+        for (uint32_t r = 0; r < K; ++r) z += expf((top_v[r] - m) * inv_t);
+        const float target = u * z;
+        float cum = 0.0f;
+        uint32_t chosen = top_i[0];
+        for (uint32_t r = 0; r < K; ++r) {
+            cum += expf((top_v[r] - m) * inv_t);
+            if (cum >= target) { chosen = top_i[r]; break; }
+        }
+        out[row] = chosen;
+    }
+    return 0;
+}
+
 /* GatedMul as a node of its own (vai/shaders/gated-mul.comp:38-49): one output element
  * per thread, row = e / H, src = row * 2H + (e - row * H); O[e] = epilogue(I[src]) * I[src + H]
  * in fp32, I and O in their own dtypes. */

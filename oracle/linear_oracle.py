@@ -277,6 +277,33 @@ def topk_sample_c(logits, k, temperature, u):
     return out
 
 
+def topk_candidates_c(logits, k, index_base=0):
+    """Per-slab step of the vocabulary-split top-k: (values [M, k] fp32, indices [M, k] uint32), the k
+    best of each row in rank order with index_base added; short slabs pad with (lowest, 0xFFFFFFFF)."""
+    a = np.ascontiguousarray(logits, dtype=np.float32)
+    vals = np.empty((a.shape[0], k), dtype=np.float32)
+    idxs = np.empty((a.shape[0], k), dtype=np.uint32)
+    rc = lib().vai_oracle_topk_candidates(_ptr(a), ctypes.c_uint32(a.shape[0]), ctypes.c_uint32(a.shape[1]), ctypes.c_uint32(k),
+                                          ctypes.c_uint32(index_base), _ptr(vals), _ptr(idxs))
+    if rc != 0:
+        raise RuntimeError(f"oracle returned {rc}")
+    return vals, idxs
+
+
+def topk_merge_sample_c(vals, idxs, k, temperature, u):
+    """Merge step: vals / idxs [groups, M, list_len] candidate lists -> sampled uint32 [M]."""
+    v = np.ascontiguousarray(vals, dtype=np.float32)
+    i = np.ascontiguousarray(idxs, dtype=np.uint32)
+    groups, M, list_len = v.shape
+    out = np.empty(M, dtype=np.uint32)
+    rc = lib().vai_oracle_topk_merge_sample(_ptr(v), _ptr(i), ctypes.c_uint32(groups), ctypes.c_size_t(M * list_len), ctypes.c_uint32(M),
+                                            ctypes.c_uint32(list_len), ctypes.c_uint32(k), ctypes.c_float(temperature), ctypes.c_float(u),
+                                            _ptr(out))
+    if rc != 0:
+        raise RuntimeError(f"oracle returned {rc}")
+    return out
+
+
 def topk_probabilities_f64(logits, k, temperature):
     """float64 view of the same distribution: (indices [M, k] in rank order, probabilities
     [M, k]); ties rank the lower index first."""

@@ -123,3 +123,56 @@ def test_row_parallel_split_matches_unsplit(world, tmp_path):
     for rank in range(world):
         got = np.load(os.path.join(str(tmp_path), f"row{rank}.npy"))
         np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+
+
+def _topk_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, V, k, temperature, logits, us = _topk_problem()
+        begin, count = sharded.shard_rows(V, world, rank)
+        vals, idxs = orc.topk_candidates_c(logits[:, begin:begin + count], k, begin)     # this rank's slab only
+        mine = torch.from_numpy(np.stack([vals.view(np.int32), idxs.view(np.int32)], axis=-1).copy())     # [M, k, 2]: 8 k bytes per row
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        allv = np.stack([g.numpy()[..., 0].copy().view(np.float32) for g in gathered])
+        alli = np.stack([g.numpy()[..., 1].copy().view(np.uint32) for g in gathered])
+        tokens = np.stack([orc.topk_merge_sample_c(allv, alli, min(k, V), temperature, float(u)) for u in us])
+        np.save(os.path.join(out_dir, f"topk{rank}.npy"), tokens)
+    finally:
+        dist.destroy_process_group()
+
+
+def _topk_problem():
+    rng = np.random.default_rng(21)
+    M, V, k, temperature = 2, 5003, 40, 0.8
+    logits = (rng.standard_normal((M, V)) * 2).astype(np.float32)
+    logits[0, 100] = logits[0, 4000] = logits[0].max() + 0.5        # equal maxima in different slabs
+    us = np.random.default_rng(22).random(1000, dtype=np.float32)
+    return M, V, k, temperature, logits, us
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_vocabulary_split_topk_draws_the_single_gpu_token(world, tmp_path):
+    """TopKSampling over vocabulary slabs (vai_b200.sharded.ShardedTopKHead's arithmetic, with the C
+    restatement standing in for the kernels): per-rank k candidates with their vocabulary offset, an
+    all-gather of 8 k bytes per row and rank, the same merge + sample on every rank — the token the
+    unsplit node draws, for 1000 seeded uniforms, ties across slabs included."""
+    mp.spawn(_topk_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    M, V, k, temperature, logits, us = _topk_problem()
+    want = np.stack([orc.topk_sample_c(logits, k, temperature, float(u)) for u in us])
+    for rank in range(world):
+        np.testing.assert_array_equal(np.load(tmp_path / f"topk{rank}.npy"), want)
+    assert len(np.unique(want[:, 0])) > 10          # the uniforms do reach many ranks of the distribution
+
+
+def test_destination_order_spreads_the_ranks_over_the_peers():
+    """Every rank starts with its right-hand neighbour and ends with itself, so that at step i the
+    `world` ranks store to `world` different GPUs."""
+    for world in (1, 2, 4, 8):
+        orders = [sharded.destination_order(r, world) for r in range(world)]
+        for r, o in enumerate(orders):
+            assert sorted(o) == list(range(world)) and o[-1] == r
+        for step in range(world):
+            assert sorted(o[step] for o in orders) == list(range(world))

@@ -162,3 +162,46 @@ def test_topk_node_ranks_ties_by_index(n, pos, k, u, want, device):
     net = _net(k, 1e-3)
     net.s.set_uniform(u)
     assert int(net(Tensor.from_numpy(x)).to_u32()[0]) == want
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,V,bounds", [(2, 9000, [0, 1500, 4700, 9000]), (1, 128256, [0, 32064, 64128, 96192, 128256]),
+                                        (3, 60, [0, 7, 30, 60])])
+@pytest.mark.parametrize("k", [1, 40, 128])
+def test_vocabulary_slabs_merge_to_the_nodes_sample(M, V, bounds, k, device):
+    """vaicu_topk_candidates_run per vocabulary slab (windows of the wide rows, with the slab's offset;
+    one of them narrower than k in the small case), then vaicu_topk_merge_sample_run: the token of the
+    unsplit node (restatement) for several uniforms, and the candidate lists equal to the restatement's."""
+    import ctypes
+
+    from vai_b200 import _lib
+    from vai_b200.engine import DeviceBuffer
+    lib = device.lib
+    rng = np.random.default_rng(M + V + k)
+    x = (rng.standard_normal((M, V)) * 2).astype(np.float32)
+    x[0, bounds[1] - 1] = x[0, bounds[-1] - 1] = x[0].max() + 1.0          # a tie across slabs
+    xb = DeviceBuffer(device, x.nbytes)
+    xb.upload(x)
+    groups = len(bounds) - 1
+    pairs = DeviceBuffer(device, groups * M * k * 8)
+    keep = []
+    for g in range(groups):
+        n = bounds[g + 1] - bounds[g]
+        nbytes = ctypes.c_size_t()
+        _lib.check(lib.vaicu_topk_workspace_bytes(M, n, k, ctypes.byref(nbytes)), "ws")
+        ws = DeviceBuffer(device, max(nbytes.value, 256))
+        keep.append(ws)
+        _lib.check(lib.vaicu_topk_candidates_run(None, xb.ptr + bounds[g] * 4, 0, M, n, V, k, bounds[g], ws.ptr,
+                                                 pairs.ptr + g * M * k * 8), "vaicu_topk_candidates_run")
+    device.synchronize()
+    raw = pairs.download(np.empty((groups, M, k, 2), dtype=np.uint32))
+    for g in range(groups):
+        vals, idxs = orc.topk_candidates_c(x[:, bounds[g]:bounds[g + 1]], k, bounds[g])
+        np.testing.assert_array_equal(raw[g, :, :, 1], idxs)
+        np.testing.assert_array_equal(raw[g, :, :, 0], vals.view(np.uint32))
+    ub, out = DeviceBuffer(device, 4), DeviceBuffer(device, M * 4)
+    for u in US:
+        ub.upload(np.array([u], dtype=np.float32))
+        _lib.check(lib.vaicu_topk_merge_sample_run(None, pairs.ptr, groups, M * k, M, k, min(k, V), 1.3, ub.ptr, out.ptr), "merge")
+        device.synchronize()
+        np.testing.assert_array_equal(out.download(np.empty(M, dtype=np.uint32)), orc.topk_sample_c(x, k, 1.3, u), err_msg=f"u={u}")

@@ -1148,6 +1148,35 @@ int vaicu_topk_sample_run(vaicu_stream_t stream, const void* logits, int dtype, 
     return VAICU_OK;
 }
 
+int vaicu_topk_candidates_run(vaicu_stream_t stream, const void* logits, int dtype, uint32_t M, uint32_t N, size_t ld, uint32_t k,
+                              uint32_t index_base, void* workspace, void* out_pairs)
+{
+    if (!logits || !out_pairs || M == 0 || N == 0 || k == 0 || k > 128u || ld < N) return VAICU_ERR_INVALID_VALUE;
+    if (!valid_dtype(dtype)) return VAICU_ERR_INVALID_VALUE;
+    if ((uint64_t)index_base + N > (1ull << 32)) return VAICU_ERR_INVALID_VALUE;
+    const uint32_t G = topk_groups(N);
+    if (G > 1u && !workspace) return VAICU_ERR_WORKSPACE;
+    if (G > 256u) return VAICU_ERR_TOO_LARGE;
+    if ((reinterpret_cast<uintptr_t>(logits) & (dtype_size(dtype) - 1u)) || (reinterpret_cast<uintptr_t>(out_pairs) & 7u) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 7u))
+        return VAICU_ERR_ALIGNMENT;
+    VAICU_CUDA(launch_topk(logits, dtype, M, N, ld, k, index_base, 1.0f, nullptr, workspace, nullptr, out_pairs, (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
+int vaicu_topk_merge_sample_run(vaicu_stream_t stream, const void* pairs, uint32_t groups, size_t group_stride, uint32_t M,
+                                uint32_t list_len, uint32_t k, float temperature, const float* u_device, void* out_u32)
+{
+    if (!pairs || !u_device || !out_u32 || groups == 0 || groups > 256u || M == 0 || list_len == 0 || k == 0 || k > 128u)
+        return VAICU_ERR_INVALID_VALUE;
+    if (k > list_len * groups || group_stride < (size_t)M * list_len) return VAICU_ERR_INVALID_VALUE;
+    if ((reinterpret_cast<uintptr_t>(pairs) & 7u) || (reinterpret_cast<uintptr_t>(u_device) & 3u) || (reinterpret_cast<uintptr_t>(out_u32) & 3u))
+        return VAICU_ERR_ALIGNMENT;
+    VAICU_CUDA(launch_topk_merge_sample(pairs, groups, group_stride, M, list_len, k, temperature, u_device,
+                                        reinterpret_cast<uint32_t*>(out_u32), (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
 int vaicu_linear_shard_desc(const vaicu_linear_desc* full, int rank, int world, vaicu_linear_desc* shard,
                             uint32_t* w_row_begin, uint32_t* w_row_count)
 {

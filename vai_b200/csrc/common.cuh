@@ -172,6 +172,10 @@ uint32_t argmax_parts(uint32_t N);
 uint32_t topk_groups(uint32_t N);
 cudaError_t launch_topk_sample(const void* logits, int dtype, uint32_t M, uint32_t N, uint32_t K, float temperature,
                                const float* u, void* workspace, uint32_t* out, cudaStream_t stream);
+cudaError_t launch_topk(const void* logits, int dtype, uint32_t M, uint32_t N, size_t ld, uint32_t K, uint32_t index_base,
+                        float temperature, const float* u, void* workspace, uint32_t* out, void* list_out, cudaStream_t stream);
+cudaError_t launch_topk_merge_sample(const void* pairs, uint32_t groups, size_t group_stride, uint32_t M, uint32_t list_len,
+                                     uint32_t k, float temperature, const float* u, uint32_t* out, cudaStream_t stream);
 cudaError_t launch_argmax_pairs(const void* in, int dtype, uint32_t M, uint32_t N, size_t ld, uint32_t index_base, void* workspace,
                                 float* out_val, uint32_t* out_idx, cudaStream_t stream);
 cudaError_t launch_argmax_merge(const float* vals, const uint32_t* idxs, uint32_t groups, size_t group_stride, uint32_t M,

@@ -41,13 +41,21 @@ struct TopkParams {
     uint32_t k;               // min(K, row width of the logits)
     int32_t dtype;
     float temperature;
+    // vocabulary slabs: the logits are a window of wider rows / the candidates carry global indices
+    size_t ld;                // stage 1: elements between rows of the logits
+    uint32_t index_base;      // stage 1: added to every column index
+    // stage 2 reads list l of row r at cand_in[l * list_stride + r * row_stride] (entries)
+    size_t list_stride, row_stride;
+    uint32_t list_len;        // entries per list in cand_in (>= k; the tail may be padding)
+    uint2* list_out;          // stage 2: write the merged, sorted k_out entries per row here instead of sampling
+    uint32_t k_out;           // entries per row in list_out (>= k: the tail is padded with sentinels)
 };
 
 // One warp merges `nlists` descending lists of `len` (value, index) entries each, stored
 // back to back at `lists`, into the best `k` of their union, in order, at top_v / top_i.
 // Lane l walks lists l, l + 32, ...: their heads live in registers, SLOTS lists per lane at most.
 template <uint32_t SLOTS>
-__device__ __forceinline__ void merge_lists(const uint2* lists, uint32_t nlists, uint32_t len, uint32_t k, float* top_v,
+__device__ __forceinline__ void merge_lists(const uint2* lists, uint32_t nlists, size_t stride, uint32_t len, uint32_t k, float* top_v,
                                             uint32_t* top_i, uint32_t lane)
 {
     float hv[SLOTS];
@@ -57,7 +65,7 @@ __device__ __forceinline__ void merge_lists(const uint2* lists, uint32_t nlists,
         const uint32_t l = lane + 32u * j;
         pos[j] = 0u;
         if (l < nlists && len > 0u) {
-            const uint2 c = lists[(size_t)l * len];
+            const uint2 c = lists[(size_t)l * stride];
             hv[j] = __uint_as_float(c.x); hi[j] = c.y;
         } else {
             hv[j] = kLowest; hi[j] = 0xFFFFFFFFu;
@@ -83,7 +91,7 @@ __device__ __forceinline__ void merge_lists(const uint2* lists, uint32_t nlists,
             if (hi[j] == bi && hv[j] == bv && bi != 0xFFFFFFFFu) {
                 const uint32_t l = lane + 32u * j;
                 if (++pos[j] < len) {
-                    const uint2 c = lists[(size_t)l * len + pos[j]];
+                    const uint2 c = lists[(size_t)l * stride + pos[j]];
                     hv[j] = __uint_as_float(c.x); hi[j] = c.y;
                 } else {
                     hv[j] = kLowest; hi[j] = 0xFFFFFFFFu;
@@ -128,10 +136,11 @@ __global__ void __launch_bounds__(kPartThreads) topk_slice_kernel(const TopkPara
     const uint32_t slice = (p.N + G - 1u) / G;
     const uint32_t s0 = g * slice, s1 = (s0 + slice < p.N) ? s0 + slice : p.N;
     for (uint32_t i = s0 + tid; i < s1; i += kPartThreads) {
-        const float v = load_as_f32(p.logits, p.dtype, (size_t)row * p.N + i);
+        const float v = load_as_f32(p.logits, p.dtype, (size_t)row * p.ld + i);
+        const uint32_t gi = p.index_base + i;
         // insertion into the descending list (fully unrolled: the list stays in registers)
-        if (outranks(v, i, lv[kList - 1], li[kList - 1])) {
-            lv[kList - 1] = v; li[kList - 1] = i;
+        if (outranks(v, gi, lv[kList - 1], li[kList - 1])) {
+            lv[kList - 1] = v; li[kList - 1] = gi;
 #pragma unroll
             for (int q = kList - 1; q > 0; --q) {
                 if (outranks(lv[q], li[q], lv[q - 1], li[q - 1])) {
@@ -161,9 +170,14 @@ __global__ void __launch_bounds__(kPartThreads) topk_slice_kernel(const TopkPara
     }
     __syncthreads();
     if (warp != 0u) return;
-    merge_lists<1>(warp_list, kWarps, p.k, p.k, top_v, top_i, lane);
+    merge_lists<1>(warp_list, kWarps, p.k, p.k, p.k, top_v, top_i, lane);
     if (SAMPLE) {
         if (lane == 0u) p.out[row] = sample(top_v, top_i, p.k, p.temperature, *p.u);
+    } else if (p.list_out) {
+        // the row fits this block and its sorted list is the result: k entries, then padding
+        for (uint32_t r = lane; r < p.k_out; r += 32u)
+            p.list_out[(size_t)row * p.k_out + r] = r < p.k ? make_uint2(__float_as_uint(top_v[r]), top_i[r])
+                                                           : make_uint2(__float_as_uint(kLowest), 0xFFFFFFFFu);
     } else {
         for (uint32_t r = lane; r < p.k; r += 32u)
             p.cand_out[((size_t)row * G + g) * p.k + r] = make_uint2(__float_as_uint(top_v[r]), top_i[r]);
@@ -177,16 +191,24 @@ __global__ void __launch_bounds__(32) topk_merge_kernel(const TopkParams p, uint
     __shared__ float top_v[kMaxK];
     __shared__ uint32_t top_i[kMaxK];
     const uint32_t row = blockIdx.x, lane = threadIdx.x, G = p.N;
-    const uint2* lists = p.cand_in + (size_t)row * G * p.k;
+    const uint2* lists = p.cand_in + (size_t)row * p.row_stride;
+    size_t stride = p.list_stride;
     if (lists_in_smem) {
-        for (uint32_t i = lane; i < G * p.k; i += 32u) staged[i] = lists[i];
+        for (uint32_t i = lane; i < G * p.list_len; i += 32u) staged[i] = lists[(size_t)(i / p.list_len) * stride + i % p.list_len];
         __syncwarp();
         lists = staged;
+        stride = p.list_len;
     }
-    if (G <= 64u) merge_lists<2>(lists, G, p.k, p.k, top_v, top_i, lane);
-    else if (G <= 128u) merge_lists<4>(lists, G, p.k, p.k, top_v, top_i, lane);
-    else merge_lists<8>(lists, G, p.k, p.k, top_v, top_i, lane);
-    if (lane == 0u) p.out[row] = sample(top_v, top_i, p.k, p.temperature, *p.u);
+    if (G <= 64u) merge_lists<2>(lists, G, stride, p.list_len, p.k, top_v, top_i, lane);
+    else if (G <= 128u) merge_lists<4>(lists, G, stride, p.list_len, p.k, top_v, top_i, lane);
+    else merge_lists<8>(lists, G, stride, p.list_len, p.k, top_v, top_i, lane);
+    if (p.list_out) {
+        for (uint32_t r = lane; r < p.k_out; r += 32u)
+            p.list_out[(size_t)row * p.k_out + r] = r < p.k ? make_uint2(__float_as_uint(top_v[r]), top_i[r])
+                                                           : make_uint2(__float_as_uint(kLowest), 0xFFFFFFFFu);
+    } else if (lane == 0u) {
+        p.out[row] = sample(top_v, top_i, p.k, p.temperature, *p.u);
+    }
 }
 
 }  // namespace
@@ -194,19 +216,42 @@ __global__ void __launch_bounds__(32) topk_merge_kernel(const TopkParams p, uint
 // Blocks per row in stage 1 (1: single launch).
 uint32_t topk_groups(uint32_t N) { return (N + kSlice - 1u) / kSlice; }
 
-cudaError_t launch_topk_sample(const void* logits, int dtype, uint32_t M, uint32_t N, uint32_t K, float temperature,
-                               const float* u, void* workspace, uint32_t* out, cudaStream_t stream)
+namespace {
+// Stage 2 over `G` lists per row; samples into `out`, or writes the merged list to `list_out`.
+cudaError_t launch_merge(const TopkParams& q, uint32_t M, uint32_t G, cudaStream_t stream)
+{
+    const size_t bytes = (size_t)G * q.list_len * sizeof(uint2);
+    const bool in_smem = bytes <= 200u * 1024u;
+    if (in_smem && bytes > 48u * 1024u) {
+        static SmemOptIn optin;
+        if (cudaError_t e = optin.ensure(topk_merge_kernel, (int)(200u * 1024u)); e != cudaSuccess) return e;
+    }
+    topk_merge_kernel<<<M, 32, in_smem ? bytes : 0, stream>>>(q, in_smem ? 1u : 0u);
+    return cudaGetLastError();
+}
+}  // namespace
+
+// `list_out` null: the TopKSampling node (sample into `out`).  `list_out` set: the per-slab step of a
+// vocabulary-split head — the sorted top-K list of each row of this slab, indices offset by index_base.
+cudaError_t launch_topk(const void* logits, int dtype, uint32_t M, uint32_t N, size_t ld, uint32_t K, uint32_t index_base,
+                        float temperature, const float* u, void* workspace, uint32_t* out, void* list_out, cudaStream_t stream)
 {
     TopkParams p{};
     p.logits = logits; p.dtype = dtype; p.temperature = temperature; p.u = u; p.out = out;
     p.N = N;
+    p.ld = ld;
+    p.index_base = index_base;
     p.k = K < N ? K : N;
+    p.list_out = reinterpret_cast<uint2*>(list_out);
+    p.k_out = K;
     const uint32_t G = topk_groups(N);
     if (G == 1u) {
-        topk_slice_kernel<true><<<dim3(1, M), kPartThreads, 0, stream>>>(p);
+        if (list_out) topk_slice_kernel<false><<<dim3(1, M), kPartThreads, 0, stream>>>(p);
+        else topk_slice_kernel<true><<<dim3(1, M), kPartThreads, 0, stream>>>(p);
         return cudaGetLastError();
     }
     p.cand_out = reinterpret_cast<uint2*>(workspace);
+    p.list_out = nullptr;                       // the slices feed stage 2
     topk_slice_kernel<false><<<dim3(G, M), kPartThreads, 0, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -215,14 +260,36 @@ cudaError_t launch_topk_sample(const void* logits, int dtype, uint32_t M, uint32
     q.cand_in = reinterpret_cast<const uint2*>(workspace);
     q.cand_out = nullptr;
     q.N = G;
-    const size_t bytes = (size_t)G * p.k * sizeof(uint2);
-    const bool in_smem = bytes <= 200u * 1024u;
-    if (in_smem && bytes > 48u * 1024u) {
-        e = cudaFuncSetAttribute(topk_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200u * 1024u));
-        if (e != cudaSuccess) return e;
-    }
-    topk_merge_kernel<<<M, 32, in_smem ? bytes : 0, stream>>>(q, in_smem ? 1u : 0u);
-    return cudaGetLastError();
+    q.list_len = p.k;
+    q.list_stride = p.k;
+    q.row_stride = (size_t)G * p.k;
+    q.list_out = reinterpret_cast<uint2*>(list_out);
+    return launch_merge(q, M, G, stream);
+}
+
+cudaError_t launch_topk_sample(const void* logits, int dtype, uint32_t M, uint32_t N, uint32_t K, float temperature,
+                               const float* u, void* workspace, uint32_t* out, cudaStream_t stream)
+{
+    return launch_topk(logits, dtype, M, N, N, K, 0u, temperature, u, workspace, out, nullptr, stream);
+}
+
+// Merge step of a vocabulary-split head: `groups` sorted lists per row (one per GPU, list_len entries each,
+// padding allowed at the tail), list g of row m at pairs[g * group_stride + m * list_len]; keeps the best k
+// of their union and samples.
+cudaError_t launch_topk_merge_sample(const void* pairs, uint32_t groups, size_t group_stride, uint32_t M, uint32_t list_len,
+                                     uint32_t k, float temperature, const float* u, uint32_t* out, cudaStream_t stream)
+{
+    TopkParams q{};
+    q.cand_in = reinterpret_cast<const uint2*>(pairs);
+    q.N = groups;
+    q.k = k;
+    q.list_len = list_len;
+    q.list_stride = group_stride;
+    q.row_stride = list_len;
+    q.temperature = temperature;
+    q.u = u;
+    q.out = out;
+    return launch_merge(q, M, groups, stream);
 }
 
 }  // namespace vaicu

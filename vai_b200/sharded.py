@@ -503,6 +503,68 @@ class ShardedGreedyHead:
             self.plan = None
 
 
+class ShardedTopKHead:
+    """Vocabulary-split lm_head followed by top-k sampling without gathering logits (vAi's
+    TopKSampling node, vai/nodes/topk-sampling.h:33-57, in two steps): every rank runs its slab of
+    the head and reduces it to its k best (value, token) pairs per row in rank order
+    (vaicu_topk_candidates_run, tokens offset by the slab's first vocabulary entry), the ranks
+    all-gather those lists (8 k bytes per row and GPU), and each merges them and samples with the
+    same uniform (vaicu_topk_merge_sample_run).  The token is the one the single-GPU node draws
+    from the whole row: the top-k of a union lies within the union of the parts' top-k."""
+
+    def __init__(self, device, dist, full_desc, w_local, k=40, temperature=1.0):
+        import torch
+        self.torch, self.dist, self.dev = torch, dist, device
+        self.rank = dist.get_rank() if dist is not None else 0
+        self.world = dist.get_world_size() if dist is not None else 1
+        self.desc, self.begin, self.count = shard_desc(full_desc, self.rank, self.world)
+        self.w, self.k, self.temperature, self.vocab = w_local, int(k), float(temperature), int(full_desc.N)
+        lib = device.lib
+        h = ctypes.c_void_p()
+        _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(self.desc), ctypes.byref(h)), "plan")
+        self.plan = h
+        self.info = _lib.LinearInfo()
+        _lib.check(lib.vaicu_linear_plan_info(h, ctypes.byref(self.info)), "info")
+        cuda = torch.device("cuda", device.ordinal)
+        M = self.desc.M
+        o_dt = {0: torch.float32, 1: torch.float16, 3: torch.bfloat16}[self.desc.o_dtype]
+        self.ws = torch.empty(max(self.info.workspace_bytes, 256), dtype=torch.uint8, device=cuda)
+        self.logits = torch.empty((M, self.count), dtype=o_dt, device=cuda)
+        n = ctypes.c_size_t()
+        _lib.check(lib.vaicu_topk_workspace_bytes(M, self.count, self.k, ctypes.byref(n)), "vaicu_topk_workspace_bytes")
+        self.topk_ws = torch.empty(max(n.value, 256), dtype=torch.uint8, device=cuda)
+        self.mine = torch.empty((M, self.k, 2), dtype=torch.int32, device=cuda)            # (value bits, token) pairs
+        self.all = torch.empty((self.world, M, self.k, 2), dtype=torch.int32, device=cuda)
+        self.uniform = torch.zeros(1, dtype=torch.float32, device=cuda)
+        self.tokens = torch.empty(M, dtype=torch.int32, device=cuda)
+
+    def set_uniform(self, u):
+        """The uniform in [0, 1) of the next forward: the same value on every rank."""
+        self.uniform.fill_(float(u))
+
+    def forward(self, x):
+        lib, M = self.dev.lib, self.desc.M
+        stream = self.torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.vaicu_linear_run(self.plan, stream, x.data_ptr(), self.w.data_ptr(), None, None, self.logits.data_ptr(),
+                                        self.ws.data_ptr()), "vaicu_linear_run")
+        _lib.check(lib.vaicu_topk_candidates_run(stream, self.logits.data_ptr(), self.desc.o_dtype, M, self.count, self.count, self.k,
+                                                 self.begin, self.topk_ws.data_ptr(), self.mine.data_ptr()), "vaicu_topk_candidates_run")
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.all, self.mine)
+            lists = self.all
+        else:
+            lists = self.mine
+        _lib.check(lib.vaicu_topk_merge_sample_run(stream, lists.data_ptr(), self.world, M * self.k, M, self.k, min(self.k, self.vocab),
+                                                   self.temperature, self.uniform.data_ptr(), self.tokens.data_ptr()),
+                   "vaicu_topk_merge_sample_run")
+        return self.tokens
+
+    def close(self):
+        if self.plan:
+            self.dev.lib.vaicu_linear_plan_destroy(self.plan)
+            self.plan = None
+
+
 def _tiled_weight(torch, rows, k, seed):
     """[rows, k] bf16 ~N(0, 0.02) on the host, the same on every rank: one seeded pool of 2^24 + 977
     values repeated (the odd length keeps rows from lining up), so that a 1.3 GB matrix takes a
@@ -711,6 +773,28 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5, p
             g.update({"greedy_head_us": round(greedy_ms * 1e3, 1), "greedy_exchange_bytes_per_gpu": 8 * M,
                       "greedy_head_matches_argmax_of_gathered_logits": bool(torch.equal(tok.long(), want)),
                       "note": "t1_us is the one-GPU lm_head without its argmax pass"})
+            # top-k sampling without the logits: k candidates per row and GPU are exchanged
+            tk = ShardedTopKHead(device, dist, full, lin.w, k=40, temperature=0.8)
+            full_logits = torch.empty_like(ref).copy_(ref).float().contiguous()
+            n_ws = ctypes.c_size_t()
+            _lib.check(lib.vaicu_topk_workspace_bytes(M, n_rows, 40, ctypes.byref(n_ws)), "vaicu_topk_workspace_bytes")
+            ws_full = torch.empty(max(n_ws.value, 256), dtype=torch.uint8, device=cuda)
+            one = torch.empty(M, dtype=torch.int32, device=cuda)
+            same = True
+            for uu in (0.0, 0.21, 0.5, 0.77, 0.98):
+                tk.set_uniform(uu)
+                got_tok = tk.forward(x).clone()
+                stream = torch.cuda.current_stream().cuda_stream
+                _lib.check(lib.vaicu_topk_sample_run(stream, ref.data_ptr(), int(Dtype.BF16), M, n_rows, 40, 0.8, tk.uniform.data_ptr(),
+                                                     ws_full.data_ptr(), one.data_ptr()), "vaicu_topk_sample_run")
+                torch.cuda.synchronize()
+                same = same and bool(torch.equal(got_tok, one))
+            topk_ms = _timed(torch, dist, cuda, lambda: tk.forward(x), iters, warmup)
+            g["topk_head_us"] = round(topk_ms * 1e3, 1)
+            g["topk_head_matches_single_gpu_node"] = same
+            g["topk_exchange_bytes_per_gpu"] = 8 * 40 * M
+            del full_logits
+            tk.close()
             out["layers"]["lm_head_greedy"] = g
             entry["greedy_head_us"] = g["greedy_head_us"]
             entry["greedy_head_matches_argmax_of_gathered_logits"] = g["greedy_head_matches_argmax_of_gathered_logits"]
@@ -810,7 +894,8 @@ def sharded_report(device, dist, peaks):
     keep = ("layer", "bound", "t1_us", "tN_us", "local_us", "speedup", "efficiency", "aggregate_TFLOPs", "aggregate_GBps",
             "frac_of_N_x_roofline", "collective", "collective_share", "nccl_allgather_us", "fused_gather_us",
             "nccl_allreduce_us", "fused_reduce_scatter_us",
-            "fused_gather_matches_nccl", "greedy_head_matches_argmax_of_gathered_logits", "max_rel_err_vs_float64")
+            "fused_gather_matches_nccl", "greedy_head_matches_argmax_of_gathered_logits", "topk_head_us",
+            "topk_head_matches_single_gpu_node", "max_rel_err_vs_float64")
     report = {"world": decode["world"], "bound_checked": "sampled outputs within 2e-2 of float64 (bf16 operands, fp32 accumulate)"}
     for key, res in (("gemma3_4b_decode_M64", decode), ("llama32_3b_prefill_M8192", prefill)):
         rows = []
@@ -820,7 +905,8 @@ def sharded_report(device, dist, peaks):
             for v in (errs.values() if isinstance(errs, dict) else [errs]):
                 if v is not None and not v <= 2e-2:
                     raise RuntimeError(f"{key} / {layer['layer']}: relative error {v} against float64 exceeds 2e-2")
-            if layer.get("fused_gather_matches_nccl") is False or layer.get("greedy_head_matches_argmax_of_gathered_logits") is False:
+            if (layer.get("fused_gather_matches_nccl") is False or layer.get("greedy_head_matches_argmax_of_gathered_logits") is False
+                    or layer.get("topk_head_matches_single_gpu_node") is False):
                 raise RuntimeError(f"{key} / {layer['layer']}: sharded result differs from the gathered reference")
         report[key] = rows
     return report
