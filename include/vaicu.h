@@ -218,6 +218,8 @@ typedef struct vaicu_linear_tuning {
                                    tile's splits fold it together inside the kernel (one launch; measured
                                    slower on B200 than the dependent fold launch), 2 = a second launch
                                    folds; 0: the second launch                                  */
+    int32_t  tc_tail_strips;    /* CTA-pair kernel: column strips per tile in the last, partial round of
+                                   tiles: 1 = none, 2 or 4; 0: the widest that fits the idle clusters     */
 } vaicu_linear_tuning;
 VAICU_API int vaicu_linear_plan_create_tuned(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_linear_tuning* tuning,
                                              vaicu_linear_plan** out);

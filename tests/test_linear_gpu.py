@@ -423,3 +423,25 @@ def test_split_k_folded_inside_the_kernel(M, K, N, kernel, variant, device):
     two, _, node2 = run_linear(x, w, b, r, tuning=dict(base, tc_splits=4, tc_fold=2), **kw)
     assert node2.info.split_count == 4 and node2.info.launches == 2
     np.testing.assert_array_equal(got, two)
+
+
+@pytest.mark.parametrize("M,K,N,gate,residual", [(2560, 256, 2048, False, True), (2560, 320, 2048, True, False), (2600, 192, 2000, False, False)])
+@pytest.mark.parametrize("strips", [0, 2, 4])
+def test_tail_round_in_column_strips(M, K, N, gate, residual, strips, device):
+    """CTA-pair kernel when the tile count leaves a partial last round (80 tiles of 256 x 256 on 74
+    clusters here): the leftover tiles are cut into column strips of 128 or 64, one work item each.
+    Same dot products in the same order as whole tiles, so the outputs equal the unstripped run bit for
+    bit; against float64 as well.  With a residual, whose chunks the epilogue requests ahead of use."""
+    rng = np.random.default_rng(M + N + strips)
+    rows = 2 * N if gate else N
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((rows, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(rows).astype(np.float32)
+    r = rng.standard_normal((M, N)).astype(np.float32) if residual else None
+    kw = dict(i_dtype="bf16", w_dtype="bf16", o_dtype="bf16" if residual else "f32", b_dtype="f32", epilogue="SILU", gate_fuse=gate,
+              kernel=nodes.KERNEL_TC_GEMM)
+    got, want, node = run_linear(x, w, b, r, tuning=dict(tc_pair=1, tc_bn=256, tc_tail_strips=strips), **kw)
+    assert node.info.tile_m == 256
+    assert_close(got, want, out_tol(kw["o_dtype"], 2e-4, 5e-5), f"strips {strips} {M}x{K}x{N}")
+    whole, _, _ = run_linear(x, w, b, r, tuning=dict(tc_pair=1, tc_bn=256, tc_tail_strips=1), **kw)
+    np.testing.assert_array_equal(got, whole)

@@ -175,3 +175,37 @@ def test_odd_pointer_is_rejected(device):
     device.synchronize()
     assert o.untouched()
     lib.vaicu_linear_plan_destroy(plan)
+
+
+def test_plan_keeps_descriptors_for_two_buffers_per_operand(device):
+    """One tensor-core plan run over alternating activation buffers (what a caller with double-buffered
+    activations does), then a third: every run reads the buffer it was given."""
+    lib = device.lib
+    rng = np.random.default_rng(3)
+    M, K, N = 64, 512, 256
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    xs = [rng.standard_normal((M, K)).astype(np.float32) for _ in range(3)]
+    wb = DeviceBuffer(device, N * K * 2)
+    wb.upload(encode(w, Dtype.BF16))
+    xbs = []
+    for x in xs:
+        b = DeviceBuffer(device, M * K * 2)
+        b.upload(encode(x, Dtype.BF16))
+        xbs.append(b)
+    out = DeviceBuffer(device, M * N * 4)
+    d = _lib.LinearDesc()
+    d.M, d.N, d.K = M, N, K
+    d.i_dtype = d.w_dtype = int(Dtype.BF16)
+    d.o_dtype, d.b_dtype, d.scalar_scale = 0, 2, 1.0
+    plan = ctypes.c_void_p()
+    _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(plan)), "plan")
+    info = _lib.LinearInfo()
+    lib.vaicu_linear_plan_info(plan, ctypes.byref(info))
+    ws = DeviceBuffer(device, max(int(info.workspace_bytes), 256))
+    wants = [orc.linear_f64(seen(x, Dtype.BF16), seen(w, Dtype.BF16)) for x in xs]
+    for which in (0, 1, 0, 1, 2, 0, 2, 1):
+        _lib.check(lib.vaicu_linear_run(plan, None, xbs[which].ptr, wb.ptr, None, None, out.ptr, ws.ptr), "run")
+        device.synchronize()
+        got = out.download(np.empty((M, N), dtype=np.float32))
+        assert_close(got, wants[which], (2e-4, 5e-5), f"buffer {which}")
+    lib.vaicu_linear_plan_destroy(plan)

@@ -33,7 +33,8 @@ class LinearTuning(ctypes.Structure):
     _fields_ = [("kernel", ctypes.c_int32), ("tc_pair", ctypes.c_int32), ("tc_wide", ctypes.c_int32),
                 ("tc_bn", ctypes.c_uint32), ("tc_splits", ctypes.c_uint32), ("gemv_rows", ctypes.c_int32),
                 ("gemv_k_warps", ctypes.c_int32), ("gemv_unroll", ctypes.c_int32), ("gemv_grid", ctypes.c_int32),
-                ("gemv_plain_launch", ctypes.c_int32), ("tc_fold", ctypes.c_int32)]
+                ("gemv_plain_launch", ctypes.c_int32), ("tc_fold", ctypes.c_int32),
+                ("tc_tail_strips", ctypes.c_int32)]
 
     def __init__(self, **kw):
         super().__init__()

@@ -121,9 +121,13 @@ struct vaicu_linear_plan {
     int tc_grid;
     size_t tc_smem;
     size_t ws_cast_bytes, ws_partial_bytes;
-    CUtensorMap map_a, map_b;
-    const void* map_a_base;
-    const void* map_b_base;
+    // TMA descriptors are made on first use of a base pointer and kept: two per operand, so that a caller
+    // that alternates two activation (or weight) buffers re-encodes nothing after the first two runs.
+    // map_b_tail: the weights with the strip box of the tail round.
+    CUtensorMap map_a[2], map_b[2], map_b_tail[2];
+    const void* map_a_base[2];
+    const void* map_b_base[2];
+    uint32_t map_a_next, map_b_next;
     size_t workspace_bytes;
     uint32_t launches;
     // split-K on the single-CTA tensor-core kernel: finished-splits count per tile, owned by the plan
@@ -323,6 +327,34 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
         if ((uint32_t)clusters > work) clusters = (int)work;
         pl->tc_grid = 2 * clusters;
     }
+    // Last round of the CTA-pair kernel: when the tile count leaves a partial round (384 tiles on 74
+    // clusters: 5 full rounds and 14 tiles), those tiles are cut into column strips so that the round is
+    // shorter and keeps more clusters busy: as many strips per tile (2 or 4) as there are clusters for.
+    t.tail_first = t.num_tiles;
+    t.tail_split = 1u;
+    t.idesc_tail = t.idesc;
+    if (t.pair && t.splits == 1u && pl->tune.tc_tail_strips != 1) {
+        const uint32_t clusters = (uint32_t)pl->tc_grid / 2u;
+        const uint32_t rem = clusters ? t.num_tiles % clusters : 0u;
+        uint32_t strips = 1u;
+        if (rem && t.num_tiles > clusters) {
+            for (uint32_t c = 2u; c <= 4u; c *= 2u) {
+                const uint32_t width = bn / c;
+                if (bn % c || width % 32u || rem * c > clusters) continue;
+                strips = c;
+            }
+        }
+        if (pl->tune.tc_tail_strips > 1) {
+            const uint32_t c = (uint32_t)pl->tune.tc_tail_strips;
+            strips = (rem && bn % c == 0u && (bn / c) % 32u == 0u) ? c : 1u;
+        }
+        if (strips > 1u) {
+            t.tail_first = t.num_tiles - rem;
+            t.tail_split = strips;
+            const uint32_t fmt2 = d.w_dtype == VAICU_DTYPE_BF16 ? 1u : 0u;
+            t.idesc_tail = (1u << 4) | (fmt2 << 7) | (fmt2 << 10) | (((bn / strips) >> 3) << 17) | ((256u >> 4) << 24);
+        }
+    }
     pl->tc_swap = swap;
     pl->tc_cast = d.i_dtype == VAICU_DTYPE_F32;
     pl->ws_cast_bytes = pl->tc_cast ? align_up((size_t)d.M * d.K * 2u, 256u) : 0;
@@ -349,6 +381,7 @@ int validate_tuning(const vaicu_linear_tuning& t)
     if (t.gemv_unroll != 0 && t.gemv_unroll != 2 && t.gemv_unroll != 4) return VAICU_ERR_INVALID_VALUE;
     if (t.gemv_grid < 0) return VAICU_ERR_INVALID_VALUE;
     if (t.tc_fold < 0 || t.tc_fold > 2) return VAICU_ERR_INVALID_VALUE;
+    if (t.tc_tail_strips != 0 && t.tc_tail_strips != 1 && t.tc_tail_strips != 2 && t.tc_tail_strips != 4) return VAICU_ERR_INVALID_VALUE;
     return VAICU_OK;
 }
 
@@ -426,7 +459,8 @@ int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_lin
     pl->kernel = kernel;
     pl->last_kernel = 0;
     pl->last_vectorized = 0;
-    pl->map_a_base = pl->map_b_base = nullptr;
+    pl->map_a_base[0] = pl->map_a_base[1] = pl->map_b_base[0] = pl->map_b_base[1] = nullptr;
+    pl->map_a_next = pl->map_b_next = 0u;
     *out = pl;
     return VAICU_OK;
 }
@@ -936,18 +970,29 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
     const bool gate = d.gate_fuse != 0;
     const void* a_base = pl->tc_swap ? W : act;
     const void* b_base = pl->tc_swap ? act : W;
-    if (a_base != pl->map_a_base) {
+    uint32_t ia = a_base == pl->map_a_base[0] ? 0u : (a_base == pl->map_a_base[1] ? 1u : 2u);
+    if (ia == 2u) {                           // a base pointer not seen before: encode into the older slot
+        ia = pl->map_a_next;
+        pl->map_a_next ^= 1u;
         const uint32_t rows = pl->tc_swap ? d.N : d.M;
-        int rc = encode_map(&pl->map_a, a_base, d.w_dtype, rows, d.K, 128u);
+        int rc = encode_map(&pl->map_a[ia], a_base, d.w_dtype, rows, d.K, 128u);
         if (rc != VAICU_OK) return rc;
-        pl->map_a_base = a_base;
+        pl->map_a_base[ia] = a_base;
     }
-    if (b_base != pl->map_b_base) {
+    uint32_t ib = b_base == pl->map_b_base[0] ? 0u : (b_base == pl->map_b_base[1] ? 1u : 2u);
+    if (ib == 2u) {
+        ib = pl->map_b_next;
+        pl->map_b_next ^= 1u;
         const uint32_t rows = pl->tc_swap ? d.M : d.N;
         const uint32_t box = ((gate && !pl->tc_swap) || pl->tcp.pair) ? pl->tcp.bn / 2u : pl->tcp.bn;
-        int rc = encode_map(&pl->map_b, b_base, d.w_dtype, rows, d.K, box);
+        int rc = encode_map(&pl->map_b[ib], b_base, d.w_dtype, rows, d.K, box);
         if (rc != VAICU_OK) return rc;
-        pl->map_b_base = b_base;
+        pl->map_b_tail[ib] = pl->map_b[ib];
+        if (pl->tcp.tail_split > 1u) {
+            rc = encode_map(&pl->map_b_tail[ib], b_base, d.w_dtype, rows, d.K, pl->tcp.bn / pl->tcp.tail_split / 2u);
+            if (rc != VAICU_OK) return rc;
+        }
+        pl->map_b_base[ib] = b_base;
     }
     TcParams t = pl->tcp;
     t.O = O; t.bias = a.bias; t.res = a.res; t.partial = partial;
@@ -973,7 +1018,7 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
             }
         }
     }
-    VAICU_CUDA(launch_tc_gemm(pl->map_a, pl->map_b, t, pl->tc_swap, pl->tc_grid, smem, s));
+    VAICU_CUDA(launch_tc_gemm(pl->map_a[ia], pl->map_b[ib], pl->map_b_tail[ib], t, pl->tc_swap, pl->tc_grid, smem, s));
     if (partial && !t.tile_done) VAICU_CUDA(launch_splitk_reduce(a, partial, t.splits, s));
     return VAICU_OK;
 }

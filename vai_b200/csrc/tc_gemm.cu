@@ -250,11 +250,53 @@ __device__ __forceinline__ void load16(const void* base, int dt, size_t idx0, ui
     }
 }
 
+// Sixteen residual values of one output row, requested early and unpacked when the accumulators are
+// ready: the epilogue of the CTA-pair kernel asks for the next chunk's residual before it works on the
+// current one, so that the load's latency is not paid once per chunk.
+struct ResRaw {
+    uint4 q[4];
+    bool valid;
+};
+__device__ __forceinline__ void res_issue(const TcParams& p, uint32_t m, uint32_t j0, uint32_t out_cols, ResRaw& r)
+{
+    r.valid = false;
+    if (p.res_mode != OPERAND_FULL || p.partial || m >= p.M || j0 + 16u > out_cols) return;
+    const uint32_t osz = dtype_size(p.o_dtype);
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(p.res) + ((size_t)m * out_cols + j0) * osz;
+    if (addr & 15u) return;
+    const uint4* s = reinterpret_cast<const uint4*>(addr);
+    r.q[0] = s[0];
+    r.q[1] = s[1];
+    if (osz == 4u) { r.q[2] = s[2]; r.q[3] = s[3]; }
+    r.valid = true;
+}
+__device__ __forceinline__ void res_unpack(int dt, const ResRaw& r, float* t)
+{
+    if (dt == VAICU_DTYPE_F32) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            t[4 * k] = __uint_as_float(r.q[k].x); t[4 * k + 1] = __uint_as_float(r.q[k].y);
+            t[4 * k + 2] = __uint_as_float(r.q[k].z); t[4 * k + 3] = __uint_as_float(r.q[k].w);
+        }
+        return;
+    }
+    const uint32_t w[8] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        if (dt == VAICU_DTYPE_F16) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+            t[2 * k] = f.x; t[2 * k + 1] = f.y;
+        } else {
+            t[2 * k] = __uint_as_float(w[k] << 16); t[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+        }
+    }
+}
+
 // 16 consecutive output columns [j0, j0+16) of activation row m (kernel without swap).
 // v: accumulators (gate half with GATE), u: value-half accumulators.
 template <bool GATE>
 __device__ __forceinline__ void finish_row16(const TcParams& p, float* v, float* u, uint32_t m, uint32_t j0,
-                                             uint32_t out_cols, uint32_t n_valid)
+                                             uint32_t out_cols, uint32_t n_valid, const ResRaw* pre = nullptr)
 {
     const size_t flat0 = (size_t)m * out_cols + j0;
     float t[16];
@@ -273,7 +315,8 @@ __device__ __forceinline__ void finish_row16(const TcParams& p, float* v, float*
             v[c] += load_as_f32(p.bias, p.b_dtype, p.bias_mode == OPERAND_MODULO ? i % p.bias_elems : i);
         }
     }
-    if (p.res_mode == OPERAND_FULL) load16(p.res, p.o_dtype, flat0, n_valid, t);
+    if (p.res_mode == OPERAND_FULL && pre && pre->valid) res_unpack(p.o_dtype, *pre, t);
+    else if (p.res_mode == OPERAND_FULL) load16(p.res, p.o_dtype, flat0, n_valid, t);
     else if (p.res_mode == OPERAND_PER_COLUMN) load16(p.res, p.o_dtype, j0, n_valid, t);
     else if (p.res_mode == OPERAND_MODULO)
         for (uint32_t c = 0; c < 16u; ++c) t[c] = load_as_f32(p.res, p.o_dtype, (flat0 + (c < n_valid ? c : n_valid - 1u)) % p.res_elems);
@@ -348,10 +391,10 @@ __device__ __forceinline__ void finish_col16(const TcParams& p, float* v, float*
 // output columns [j0, j0 + 16): bias / epilogue / residual / scale, then the stores.
 template <bool GATE>
 __device__ __forceinline__ void emit_rows16(const TcParams& p, float* v, float* u, uint32_t m, uint32_t j0, uint32_t out_cols,
-                                            uint32_t osz)
+                                            uint32_t osz, const ResRaw* pre = nullptr)
 {
     const uint32_t n_valid = out_cols - j0 < 16u ? out_cols - j0 : 16u;
-    finish_row16<GATE>(p, v, u, m, j0, out_cols, n_valid);
+    finish_row16<GATE>(p, v, u, m, j0, out_cols, n_valid, pre);
     // O may be a column slab of wider destinations (ldo, col0), one per GPU; a row-parallel run
     // sends the row to the one GPU that owns it
     uint32_t owner;
@@ -411,7 +454,8 @@ __device__ __forceinline__ void emit_cols16(const TcParams& p, float* v, float* 
 // half with GATE).  Either raw split-K partials or the finished outputs are stored.
 template <bool GATE>
 __device__ __forceinline__ void store_rows16(const TcParams& p, const uint32_t* r0, const uint32_t* r1, uint32_t m,
-                                             uint32_t tb, uint32_t c0, uint32_t z, uint32_t out_cols, uint32_t osz)
+                                             uint32_t tb, uint32_t c0, uint32_t z, uint32_t out_cols, uint32_t osz,
+                                             const ResRaw* pre = nullptr)
 {
     const uint32_t bn = p.bn;
     if (p.partial) {
@@ -440,7 +484,7 @@ __device__ __forceinline__ void store_rows16(const TcParams& p, const uint32_t* 
         float v[16], u[16];
 #pragma unroll
         for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
-        emit_rows16<GATE>(p, v, u, m, j0, out_cols, osz);
+        emit_rows16<GATE>(p, v, u, m, j0, out_cols, osz, pre);
     }
 }
 
@@ -847,7 +891,8 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar)
 // With GATE the leader's half of B holds the gate rows and the peer's the value rows.
 template <bool GATE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
-tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcParams p)
+tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_b_tail, const TcParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
@@ -879,6 +924,7 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        if (p.tail_split > 1u) prefetch_tmap(&tmap_b_tail);
     }
     __syncthreads();
     if (warp == 1) {
@@ -891,7 +937,7 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t num_work = p.num_tiles * p.splits;
+    const uint32_t num_work = work_items(p);
 
     // The launch after this one may begin its prologue now (it waits before it touches our results).
     launch_dependents();
@@ -903,13 +949,17 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             bool ok = true;
             bool first = true;
             for (uint32_t w = cluster_id; w < num_work && ok; w += num_clusters) {
-                const uint32_t tile = w / p.splits, z = w - tile * p.splits;
+                uint32_t tile, z, strip, bw;
+                work_item(p, w, tile, z, strip, bw);
+                const uint32_t bh = bw / 2u;                       // rows of B this CTA stages for the item
                 uint32_t ta, tb;
                 tile_coords(p, tile, ta, tb);
                 const uint32_t kb0 = z * p.kb_per_split;
                 const uint32_t kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
                 const int32_t ya = (int32_t)(ta * 2u * TILE_ROWS + rank * TILE_ROWS);
-                const int32_t yb = GATE ? (int32_t)((rank ? p.H : 0u) + tb * half) : (int32_t)(tb * bn + rank * half);
+                const int32_t yb = GATE ? (int32_t)((rank ? p.H : 0u) + tb * half + strip * bh) : (int32_t)(tb * bn + strip * bw + rank * bh);
+                const CUtensorMap* mb = bw == bn ? &tmap_b : &tmap_b_tail;
+                const uint32_t item_bytes = a_bytes + bh * BLOCK_K * 2u;      // per CTA and k-block
                 uint32_t kb = kb0;
                 if (first) {
                     // The weights (operand B) do not depend on the launch ahead of this one: the ring's
@@ -918,8 +968,8 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     first = false;
                     const uint32_t npre = (kb1 - kb0 < stages) ? kb1 - kb0 : stages;
                     for (uint32_t i = 0; i < npre; ++i) {        // the ring is empty: no wait needed
-                        if (rank == 0u) mbar_expect_tx(&full_bar[i], 2u * stage_bytes);
-                        tma_load_2d_pair(smem + (size_t)i * stage_bytes + a_bytes, &tmap_b, map_to_cta(smem_u32(&full_bar[i]), 0u),
+                        if (rank == 0u) mbar_expect_tx(&full_bar[i], 2u * item_bytes);
+                        tma_load_2d_pair(smem + (size_t)i * stage_bytes + a_bytes, mb, map_to_cta(smem_u32(&full_bar[i]), 0u),
                                          (int32_t)((kb0 + i) * BLOCK_K), yb);
                     }
                     dependency_wait();
@@ -933,11 +983,11 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 for (; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                     uint8_t* sa = smem + (size_t)stage * stage_bytes;
-                    if (rank == 0u) mbar_expect_tx(&full_bar[stage], 2u * stage_bytes);   // both CTAs' boxes
+                    if (rank == 0u) mbar_expect_tx(&full_bar[stage], 2u * item_bytes);   // both CTAs' boxes
                     const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0u);
                     const int32_t kx = (int32_t)(kb * BLOCK_K);
                     tma_load_2d_pair(sa, &tmap_a, bar, kx, ya);
-                    tma_load_2d_pair(sa + a_bytes, &tmap_b, bar, kx, yb);
+                    tma_load_2d_pair(sa + a_bytes, mb, bar, kx, yb);
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -954,7 +1004,9 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t stage = 0, phase = 0, iter = 0;
             bool ok = true;
             for (uint32_t w = cluster_id; w < num_work && ok; w += num_clusters, ++iter) {
-                const uint32_t tile = w / p.splits, z = w - tile * p.splits;
+                uint32_t tile, z, strip, bw;
+                work_item(p, w, tile, z, strip, bw);
+                const uint32_t idesc = bw == bn ? p.idesc : p.idesc_tail;
                 const uint32_t kb0 = z * p.kb_per_split;
                 const uint32_t kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
                 const uint32_t buf = iter & 1u, use = iter >> 1;
@@ -969,7 +1021,7 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint64_t b_desc = make_smem_desc(sa + a_bytes);
 #pragma unroll
                     for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k)
-                        umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(&empty_bar[stage]);    // frees the stage in both CTAs
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
@@ -982,31 +1034,48 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t row_in_tile = q * 32u + lane;
         const uint32_t out_cols = GATE ? p.H : p.N;
         const uint32_t osz = p.partial ? 4u : dtype_size(p.o_dtype);
-        const uint32_t ncols = GATE ? half : bn;
         uint32_t iter = 0;
         bool ok = true;
         dependency_wait();      // residuals may come from, and outputs may still be read by, the launch ahead
         for (uint32_t w = cluster_id; w < num_work && ok; w += num_clusters, ++iter) {
-            const uint32_t tile = w / p.splits, z = w - tile * p.splits;
+            uint32_t tile, z, strip, bw;
+            work_item(p, w, tile, z, strip, bw);
+            const uint32_t bh = bw / 2u;
+            const uint32_t ncols = GATE ? bh : bw;                    // output columns of this item
+            const uint32_t strip_off = strip * ncols;                 // ... and where they start inside the tile
             uint32_t ta, tb;
             tile_coords(p, tile, ta, tb);
+            const uint32_t m = ta * 2u * TILE_ROWS + rank * TILE_ROWS + row_in_tile;
+            const uint32_t j_item = (GATE ? tb * half : tb * bn) + strip_off;
+            // this row's residual for the item: toward L2 while the accumulator is still being computed,
+            // and the first chunk into registers
+            const bool res_rows = !p.partial && p.res_mode == OPERAND_FULL && m < p.M;
+            if (res_rows) {
+                const uint32_t rsz = dtype_size(p.o_dtype);
+                const uint8_t* rp = reinterpret_cast<const uint8_t*>(p.res) + ((size_t)m * out_cols + j_item) * rsz;
+                const uint32_t span = (j_item + ncols <= out_cols ? ncols : (j_item < out_cols ? out_cols - j_item : 0u)) * rsz;
+                for (uint32_t b = 0; b < span; b += 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + b));
+            }
             const uint32_t buf = iter & 1u, use = iter >> 1;
             if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((q * 32u) << 16) + buf * acc_cols;
-            const uint32_t m = ta * 2u * TILE_ROWS + rank * TILE_ROWS + row_in_tile;
             // columns per 128-byte row segment of the output
             const uint32_t seg_cols = 128u / osz;
+            ResRaw res_next;
+            res_issue(p, m, j_item, out_cols, res_next);
             for (uint32_t c0 = 0; c0 < ncols;) {
-                const uint32_t j_seg = (GATE ? tb * half : tb * bn) + c0;
+                const uint32_t j_seg = j_item + c0;
                 const bool stage_it = p.staged && !p.partial && c0 + seg_cols <= ncols && j_seg + seg_cols <= out_cols &&
                                       p.o_aligned16 && (((size_t)p.ldo * osz) % 16u == 0u) && (((size_t)(p.col0 + j_seg) * osz) % 16u == 0u);
                 if (!stage_it) {
+                    const ResRaw res_cur = res_next;
+                    if (c0 + 16u < ncols) res_issue(p, m, j_seg + 16u, out_cols, res_next);      // in flight while this chunk is finished
                     uint32_t r0[16], r1[16];
                     tmem_ld16(t_row + c0, r0);
-                    if (GATE) tmem_ld16(t_row + c0 + half, r1);
+                    if (GATE) tmem_ld16(t_row + c0 + bh, r1);
                     tmem_ld_wait();
-                    store_rows16<GATE>(p, r0, r1, m, tb, c0, z, out_cols, osz);
+                    store_rows16<GATE>(p, r0, r1, m, tb, strip_off + c0, z, out_cols, osz, &res_cur);
                     c0 += 16u;
                     continue;
                 }
@@ -1016,7 +1085,7 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 for (uint32_t g = 0; g < seg_cols; g += 16u) {
                     uint32_t r0[16], r1[16];
                     tmem_ld16(t_row + c0 + g, r0);
-                    if (GATE) tmem_ld16(t_row + c0 + g + half, r1);
+                    if (GATE) tmem_ld16(t_row + c0 + g + bh, r1);
                     tmem_ld_wait();
                     float v[16], u[16];
 #pragma unroll
@@ -1091,13 +1160,13 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 }
 
 template <bool GATE>
-static cudaError_t launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, size_t smem,
-                                       cudaStream_t stream)
+static cudaError_t launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb_tail, const TcParams& p,
+                                       int grid, size_t smem, cudaStream_t stream)
 {
     auto kern = tc_gemm_pair_kernel<GATE>;
     static SmemOptIn optin;
     if (cudaError_t e = optin.ensure(kern, (int)kTcMaxSmem); e != cudaSuccess) return e;
-    return launch_pdl(kern, dim3((unsigned)grid), dim3(kTcThreads), smem, stream, ma, mb, p);
+    return launch_pdl(kern, dim3((unsigned)grid), dim3(kTcThreads), smem, stream, ma, mb, mb_tail, p);
 }
 
 // Number of CTA pairs that can be resident at once (pairs need two SMs of one TPC).
@@ -1145,12 +1214,12 @@ static cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, 
     return launch_pdl(kern, dim3((unsigned)grid), dim3(kTcThreads), smem, stream, ma, mb, p);
 }
 
-cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p, bool swap, int grid,
-                           size_t smem, cudaStream_t stream)
+cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b_tail, const TcParams& p,
+                           bool swap, int grid, size_t smem, cudaStream_t stream)
 {
     const bool gate = p.gate != 0;
-    if (p.pair) return gate ? launch_pair_variant<true>(map_a, map_b, p, grid, smem, stream)
-                            : launch_pair_variant<false>(map_a, map_b, p, grid, smem, stream);
+    if (p.pair) return gate ? launch_pair_variant<true>(map_a, map_b, map_b_tail, p, grid, smem, stream)
+                            : launch_pair_variant<false>(map_a, map_b, map_b_tail, p, grid, smem, stream);
     if (swap) return gate ? launch_variant<true, true>(map_a, map_b, p, grid, smem, stream)
                           : launch_variant<true, false>(map_a, map_b, p, grid, smem, stream);
     return gate ? launch_variant<false, true>(map_a, map_b, p, grid, smem, stream)

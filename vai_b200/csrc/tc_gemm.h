@@ -47,8 +47,33 @@ struct TcParams {
     // row m belongs to GPU m / rs_rows, which folds the ranks' partials.  Element (m, j) then goes to
     // dst[m / rs_rows][(rs_slot * rs_rows + m % rs_rows) * ldo + j]: this rank's slab of the owner's staging.
     uint32_t rs_rows, rs_slot;
+    // CTA-pair kernel, last (partial) round of tiles: each of the tiles from tail_first on is cut into
+    // tail_split column strips of bn / tail_split, one work item each, so that the round keeps more clusters
+    // busy for a shorter time (tail_split = 1: off).  idesc_tail is the instruction descriptor of a strip.
+    uint32_t tail_first, tail_split, idesc_tail;
     float scale;
 };
+
+// Work item -> tile, K split, column strip and UMMA N of that item.
+__host__ __device__ inline void work_item(const TcParams& p, uint32_t w, uint32_t& tile, uint32_t& z, uint32_t& strip, uint32_t& width)
+{
+    if (p.tail_split > 1u && w >= p.tail_first) {
+        const uint32_t r = w - p.tail_first;
+        tile = p.tail_first + r / p.tail_split;
+        strip = r - (r / p.tail_split) * p.tail_split;
+        width = p.bn / p.tail_split;
+        z = 0u;
+    } else {
+        tile = w / p.splits;
+        z = w - tile * p.splits;
+        strip = 0u;
+        width = p.bn;
+    }
+}
+__host__ __device__ inline uint32_t work_items(const TcParams& p)
+{
+    return p.tail_split > 1u ? p.tail_first + (p.num_tiles - p.tail_first) * p.tail_split : p.num_tiles * p.splits;
+}
 
 // Where output row m goes: the destination buffer and the row index inside it.
 __host__ __device__ inline void output_row(const TcParams& p, uint32_t m, uint32_t& owner, size_t& row)
@@ -78,7 +103,8 @@ __host__ __device__ inline void tile_coords(const TcParams& p, uint32_t tile, ui
 cudaError_t tc_pair_max_clusters(size_t smem, int* clusters);
 // One tiny launch whose bounded mbarrier wait is made to run out; sets *status as the GEMM kernels do.
 cudaError_t launch_wait_expiry_selftest(int* status, cudaStream_t stream);
-cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p, bool swap, int grid,
-                           size_t smem, cudaStream_t stream);
+// map_b_tail: the weights' map with the strip box of the tail round (CTA-pair kernel with tail_split > 1; else any valid map).
+cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b_tail, const TcParams& p,
+                           bool swap, int grid, size_t smem, cudaStream_t stream);
 
 }  // namespace vaicu
