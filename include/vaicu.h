@@ -267,14 +267,23 @@ VAICU_API int vaicu_linear_run_argmax(vaicu_linear_plan* plan, vaicu_stream_t st
                                       uint32_t index_base, float* out_val, void* out_u32);
 
 /* Two or three Linears that read the same activations (q / k / v of a block) as ONE
- * launch over the concatenation of their weight rows: plans[i] was created for
- * W[i] -> O[i]; all must be plain (no bias, epilogue, residual, scale or gate), share
- * M, K and dtypes, and resolve to the weight-streaming kernel with 16-byte aligned
- * operands.  Returns VAICU_ERR_UNSUPPORTED otherwise, and the caller issues the runs
- * one by one.  No counterpart in the reference, which records one dispatch per node
- * (linear.h:2706-2748); this only removes launch latency between sibling nodes. */
+ * Linear over their weight rows side by side: plans[i] was created for W[i] -> O[i]; all
+ * must be plain (no bias, epilogue, residual, scale or gate), share M, K and dtypes, and
+ * resolve to the same kernel, with 16-byte aligned operands:
+ *   - the weight-streaming kernel: one launch, no workspace;
+ *   - the swapped tensor-core kernel (8 < M <= 128), every N a multiple of 128: one GEMM
+ *     launch that leaves fp32 partial sums of all members plus one fold that stores the
+ *     members' outputs (where three runs would be three GEMMs and three folds); fp32
+ *     activations are rounded to the weights' type once.  Needs `workspace` of
+ *     vaicu_linear_group_workspace_bytes (256-byte aligned).
+ * Returns VAICU_ERR_UNSUPPORTED otherwise, and the caller issues the runs one by one.
+ * The first plan keeps the group's state (TMA descriptors by weight pointer); it must
+ * outlive the other members' use in groups.  No counterpart in the reference, which records
+ * one dispatch per node (linear.h:2706-2748); this only removes launch latency and idle SMs
+ * between sibling nodes. */
+VAICU_API int vaicu_linear_group_workspace_bytes(vaicu_linear_plan* const* plans, int count, size_t* out_bytes);
 VAICU_API int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_stream_t stream,
-                                     const void* I, const void* const* W, void* const* O);
+                                     const void* I, const void* const* W, void* const* O, void* workspace);
 
 /* Column-split Linear whose output slab is written straight into wider buffers: element
  * (m, j) of the plan's output goes to dsts[i][m * ldo + col0 + j] for every i < n_dst

@@ -187,6 +187,55 @@ static void mlp_on_gpu(bool useGraph)
     EXPECT(net.recordingCount() == (useGraph ? 2u : 1u));
 }
 
+// q / k / v: three plain Linears over the same activations are recorded as one launch (weight-streaming
+// kernel at M = 2, swapped tensor-core kernel with bf16 weights at M = 40); their sum goes on through o.
+static void siblings_on_gpu(uint32_t M, bool bf16, bool group)
+{
+    const uint32_t D = 256, NQ = 256, NK = 128;
+    std::vector<float> x(M * D), wq(NQ * D), wk(NK * D), wv(NK * D);
+    unsigned s = 99 + M;
+    auto rnd = [&] { s = s * 1664525u + 1013904223u; return ((s >> 8) & 0xFFFF) / 32768.0f - 1.0f; };
+    for (auto& v : x) v = rnd();
+    // values with few mantissa bits: exact in bf16, so the float64 reference needs no rounding model
+    auto coarse = [&] { return std::round(rnd() * 16.0f) / 64.0f; };
+    for (auto& v : wq) v = coarse();
+    for (auto& v : wk) v = coarse();
+    for (auto& v : wv) v = coarse();
+    if (bf16) for (auto& v : x) v = std::round(v * 32.0f) / 32.0f;
+    initVAIEngine(0);
+    NeuralNet net({.wDefaultDtype = Dtype::Fp32, .groupSiblings = group});
+    Linear q({.inDim = D, .outDim = NQ}), k({.inDim = D, .outDim = NK}), v({.inDim = D, .outDim = NK});
+    net.input("x") - q - net.output("q");
+    net.input("x") - k - net.output("k");
+    net.input("x") - v - net.output("v");
+    net.finish();
+    auto put = [&](Linear& l, uint32_t n, const std::vector<float>& w) {
+        if (!bf16) { l["weight"] = Tensor({n, D}, Dtype::Fp32); l["weight"].upload(w.data()); return; }
+        std::vector<uint16_t> bits(w.size());
+        for (size_t i = 0; i < w.size(); ++i) { uint32_t u; std::memcpy(&u, &w[i], 4); bits[i] = (uint16_t)(u >> 16); }   // exact
+        l["weight"] = Tensor({n, D}, Dtype::Bf16); l["weight"].upload(bits.data());
+    };
+    put(q, NQ, wq); put(k, NK, wk); put(v, NK, wv);
+    vaicu_device_synchronize(deviceHandle());
+    auto res = net({{"x", HostTensor::fromFloats({M, D}, x)}});
+    auto again = net({{"x", HostTensor::fromFloats({M, D}, x)}});
+    EXPECT(q.leadsGroup() == group && k.launchTaken() == group && v.launchTaken() == group);
+    double worst = 0;
+    auto check_one = [&](const char* name, uint32_t n, const std::vector<float>& w) {
+        const std::vector<float> y = res.at(name).floats();
+        EXPECT(y == again.at(name).floats());
+        for (uint32_t m = 0; m < M; ++m)
+            for (uint32_t j = 0; j < n; ++j) {
+                double acc = 0;
+                for (uint32_t c = 0; c < D; ++c) acc += double(x[m * D + c]) * w[j * D + c];
+                worst = std::fmax(worst, std::fabs(acc - y[m * n + j]) / std::fmax(1.0, std::fabs(acc)));
+            }
+    };
+    check_one("q", NQ, wq); check_one("k", NK, wk); check_one("v", NK, wv);
+    std::printf("siblings M=%u bf16=%d grouped=%d worst rel err %.3g\n", M, (int)bf16, (int)group, worst);
+    EXPECT(worst < 1e-4);
+}
+
 // x -> gate; then: a (relu); else: b; both -> c -> "main"; a second input y -> d -> "side".
 struct GatedNet {
     NeuralNet net{{.wDefaultDtype = Dtype::Fp32}};
@@ -382,6 +431,10 @@ int main(int argc, char** argv)
         gated_mlp_on_gpu(true, false);
         gated_mlp_on_gpu(false, false);
         gated_mlp_on_gpu(true, true);
+        siblings_on_gpu(2, false, true);
+        siblings_on_gpu(2, false, false);
+        siblings_on_gpu(40, true, true);
+        siblings_on_gpu(40, true, false);
     }
     std::printf(fails ? "FAILED (%d)\n" : "ok\n", fails);
     return fails ? 1 : 0;

@@ -309,7 +309,7 @@ def test_grouped_siblings_match_separate_runs(M, w_dtype, device):
     n = len(rows)
     _lib.check(lib.vaicu_linear_run_group((ctypes.c_void_p * n)(*plans), n, None, xb.ptr,
                                           (ctypes.c_void_p * n)(*[b.ptr for b in wbufs]),
-                                          (ctypes.c_void_p * n)(*[b.ptr for b in obufs])), "group")
+                                          (ctypes.c_void_p * n)(*[b.ptr for b in obufs]), None), "group")
     device.synchronize()
     for nrows, ob, want in zip(rows, obufs, wants):
         got = ob.download(np.empty((M, nrows), dtype=np.float32))
@@ -319,8 +319,91 @@ def test_grouped_siblings_match_separate_runs(M, w_dtype, device):
     h = ctypes.c_void_p()
     _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
     rc = lib.vaicu_linear_run_group((ctypes.c_void_p * 2)(plans[0], h), 2, None, xb.ptr,
-                                    (ctypes.c_void_p * 2)(wbufs[0].ptr, wbufs[2].ptr), (ctypes.c_void_p * 2)(obufs[0].ptr, obufs[2].ptr))
+                                    (ctypes.c_void_p * 2)(wbufs[0].ptr, wbufs[2].ptr), (ctypes.c_void_p * 2)(obufs[0].ptr, obufs[2].ptr), None)
     assert rc == 2
+
+
+@pytest.mark.parametrize("M,K,rows,i_dtype,o_dtype,splits", [
+    (64, 2560, [2048, 1024, 1024], "bf16", "bf16", 0),      # Gemma-3-4B q / k / v
+    (64, 512, [256, 128], "bf16", "f32", 0),
+    (100, 1024, [128, 384, 128], "f32", "f16", 0),          # fp32 activations: rounded once for the group
+    (16, 320, [128, 128, 256], "f16", "f16", 1),            # one split: the fold still stores the outputs
+    (128, 2048, [1280, 256, 256], "bf16", "bf16", 5),
+])
+def test_grouped_siblings_on_the_tensor_core_kernel(M, K, rows, i_dtype, o_dtype, splits, device):
+    """vaicu_linear_run_group for 8 < M <= 128: one swapped GEMM over the members' weight rows side by
+    side and one fold, bit-identical to the members' own runs when those split K the same way, and
+    within the 16-bit bounds of float64 otherwise."""
+    import ctypes
+
+    from vai_b200 import _lib
+    from vai_b200.engine import DeviceBuffer, bits_to_f32, encode
+    from gpu_util import DT
+    lib = device.lib
+    rng = np.random.default_rng(M + K)
+    w_dtype = "bf16" if i_dtype == "f32" else i_dtype
+    dt, it, ot = DT[w_dtype], DT[i_dtype], DT[o_dtype]
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    xb = DeviceBuffer(device, M * K * (4 if i_dtype == "f32" else 2))
+    xb.upload(encode(x, it))
+    xs = seen(seen(x, it), dt)
+    plans, wbufs, obufs, wants, singles = [], [], [], [], []
+    for n in rows:
+        w = (rng.standard_normal((n, K)) / np.sqrt(K)).astype(np.float32)
+        wb = DeviceBuffer(device, n * K * 2)
+        wb.upload(encode(w, dt))
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = M, n, K
+        d.i_dtype, d.w_dtype, d.o_dtype, d.b_dtype = int(it), int(dt), int(ot), 2
+        d.scalar_scale = 1.0
+        h = ctypes.c_void_p()
+        t = _lib.LinearTuning(tc_splits=splits)
+        _lib.check(lib.vaicu_linear_plan_create_tuned(device.handle, ctypes.byref(d), ctypes.byref(t), ctypes.byref(h)), "plan")
+        info = _lib.LinearInfo()
+        _lib.check(lib.vaicu_linear_plan_info(h, ctypes.byref(info)), "info")
+        assert info.kernel == 4
+        plans.append(h)
+        wbufs.append(wb)
+        osz = 4 if o_dtype == "f32" else 2
+        obufs.append(DeviceBuffer(device, M * n * osz))
+        wants.append(orc.linear_f64(xs, seen(w, dt)))
+        if splits:
+            # the member alone, same K split: the same partial sums in the same order
+            ws1 = DeviceBuffer(device, max(int(info.workspace_bytes), 256))
+            o1 = DeviceBuffer(device, M * n * osz)
+            _lib.check(lib.vaicu_linear_run(h, None, xb.ptr, wb.ptr, None, None, o1.ptr, ws1.ptr), "run")
+            device.synchronize()
+            singles.append(o1.download(np.empty((M, n), dtype=np.float32 if o_dtype == "f32" else np.uint16)))
+    n = len(rows)
+    parr = (ctypes.c_void_p * n)(*plans)
+    need = ctypes.c_size_t()
+    _lib.check(lib.vaicu_linear_group_workspace_bytes(parr, n, ctypes.byref(need)), "group workspace")
+    assert need.value > 0
+    guard = 512
+    ws = DeviceBuffer(device, need.value + 2 * guard)
+    _lib.check(lib.vaicu_memset(ws.ptr, 0xA5, need.value + 2 * guard, None), "memset")
+    warr = (ctypes.c_void_p * n)(*[b.ptr for b in wbufs])
+    oarr = (ctypes.c_void_p * n)(*[b.ptr for b in obufs])
+    # without a workspace the call is refused before anything is launched
+    assert lib.vaicu_linear_run_group(parr, n, None, xb.ptr, warr, oarr, None) != 0
+    for _ in range(2):          # the second call reuses the cached descriptors
+        _lib.check(lib.vaicu_linear_run_group(parr, n, None, xb.ptr, warr, oarr, ws.ptr + guard), "group")
+    device.synchronize()
+    device.check_status()
+    edge = ws.download(np.empty(need.value + 2 * guard, dtype=np.uint8))
+    assert (edge[:guard] == 0xA5).all() and (edge[-guard:] == 0xA5).all()
+    tol = (1e-4, 1e-4) if o_dtype == "f32" else (2e-2, 2e-2)
+    for i, (nrows, ob, want) in enumerate(zip(rows, obufs, wants)):
+        raw = ob.download(np.empty((M, nrows), dtype=np.float32 if o_dtype == "f32" else np.uint16))
+        got = raw if o_dtype == "f32" else bits_to_f32(raw, ot)
+        assert_close(got, want, tol, f"group member {i}")
+        if splits:
+            np.testing.assert_array_equal(raw, singles[i])
+    # members that are not whole weight tiles are declined
+    d.N = 200
+    h = ctypes.c_void_p()
+    _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
+    assert lib.vaicu_linear_group_workspace_bytes((ctypes.c_void_p * 2)(plans[0], h), 2, ctypes.byref(need)) == 2
 
 
 @pytest.mark.parametrize("M,K,N,gate", [(64, 512, 384, False), (33, 256, 200, False), (300, 512, 520, False), (64, 512, 256, True)])

@@ -116,3 +116,42 @@ def test_peer_barrier_alone_on_one_gpu(device):
     word = ctypes.c_int()
     assert lib.vaicu_device_status(device.handle, ctypes.byref(word)) == 8 and word.value != 0
     assert lib.vaicu_device_status(device.handle, ctypes.byref(word)) == 0
+
+
+def test_block_chain_replayed_as_one_graph_matches_float64(device):
+    """The one-GPU form of the chain that the multi-GPU report times (TensorParallelBlocks, tp off): two
+    Gemma-3-4B-shaped blocks at batch 64 captured into one CUDA graph; the replayed output against float64
+    over the stored bf16 weights, with the intermediates rounded to bf16 where the chain stores them."""
+    torch = pytest.importorskip("torch")
+    from vai_b200.sharded import TensorParallelBlocks
+    M = 64
+    chain = TensorParallelBlocks(device, None, "gemma-3-4b", M, 2, 2, False)
+    assert chain.group is not None                     # q / k / v run as one group at this batch
+    cuda = torch.device("cuda", device.ordinal)
+    x0 = torch.randn(M, 2560, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    xd = x0.to(cuda)
+    out = chain.capture(xd)
+    for _ in range(3):
+        chain.graph.replay()
+    torch.cuda.synchronize()
+    device.check_status()
+    got = out.float().cpu().numpy()
+
+    def r16(t):
+        return t.to(torch.bfloat16).double()
+
+    x = x0.double()
+    for w in chain.weights:
+        wq, wo, wg, wd = (w[k].cpu().double() for k in ("q", "o", "g", "d"))
+        q = r16(x @ wq.T)
+        h = r16(0.5 * (q @ wo.T) + x0.double())
+        acc = h @ wg.T
+        H = acc.shape[1] // 2
+        g, u = acc[:, :H], acc[:, H:]
+        act = 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+        hid = r16(act * u)
+        x = r16(0.25 * (hid @ wd.T) + x0.double())
+    want = x.numpy()
+    err = np.abs(got - want) / np.maximum(np.abs(want), 0.05)
+    assert err.max() < 2e-2, err.max()
+    chain.close()

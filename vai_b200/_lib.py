@@ -85,8 +85,10 @@ SIGNATURES = {
     "vaicu_linear_run": (ctypes.c_int, [ctypes.c_void_p] * 8),
     "vaicu_linear_argmax_workspace_bytes": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
     "vaicu_linear_run_argmax": (ctypes.c_int, [ctypes.c_void_p] * 8 + [ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p]),
+    "vaicu_linear_group_workspace_bytes": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+                                                          ctypes.POINTER(ctypes.c_size_t)]),
     "vaicu_linear_run_group": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
-                                              ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p)]),
+                                              ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]),
     "vaicu_linear_run_scatter": (ctypes.c_int, [ctypes.c_void_p] * 5 + [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
                                                                         ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]),
     "vaicu_linear_run_reduce_scatter": (ctypes.c_int, [ctypes.c_void_p] * 4 + [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),

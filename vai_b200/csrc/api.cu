@@ -137,6 +137,22 @@ struct vaicu_linear_plan {
     // 16-byte-vector form of that kernel: differs from `kernel` when a view's alignment sent
     // the call to a fallback
     int last_kernel, last_vectorized;
+    // this plan as the first member of a group on the tensor-core kernel (vaicu_linear_run_group)
+    struct GroupState* group;
+};
+
+// Two or three plans on the swapped tensor-core kernel run as one Linear over their weights' rows
+// side by side: the plan of that virtual Linear and the TMA descriptors of the members' tensors.
+struct GroupState {
+    const vaicu_linear_plan* members[3];
+    int count;
+    vaicu_linear_plan* virt;
+    uint32_t rows[3];
+    CUtensorMap maps_w[3];
+    const void* w_base[3];
+    CUtensorMap map_act[2];
+    const void* act_base[2];
+    uint32_t act_next;
 };
 
 namespace {
@@ -234,6 +250,7 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
     memset(&t, 0, sizeof(t));
     t.M = d.M; t.N = d.N; t.K = d.K; t.H = H;
     t.kblocks = ceil_div(d.K, 64u);
+    t.grp_t1 = t.grp_t2 = kNoGroup;
     uint32_t bn;
     if (swap) {
         bn = (uint32_t)align_up(d.M, 16u);
@@ -399,6 +416,7 @@ int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_lin
     pl->d = *desc;
     pl->tune = tuning;
     pl->tile_done = nullptr;
+    pl->group = nullptr;
     if (!pl->d.has_bias) { pl->d.bias_elems = 0; pl->d.b_dtype = VAICU_DTYPE_NONE; }
     if (!pl->d.has_residual) pl->d.residual_elems = 0;
     // a [N] bias under M == 1 "covers O" (elems 0); name it per-row so every kernel takes the cheap index
@@ -745,6 +763,10 @@ int vaicu_linear_plan_destroy(vaicu_linear_plan* plan)
         cudaSetDevice(plan->dev->ordinal);
         cudaFree(plan->tile_done);
     }
+    if (plan->group) {
+        vaicu_linear_plan_destroy(plan->group->virt);
+        delete plan->group;
+    }
     delete plan;
     return VAICU_OK;
 }
@@ -1048,37 +1070,148 @@ int vaicu_ipc_close(void* ptr)
     return VAICU_OK;
 }
 
-int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_stream_t stream, const void* I,
-                           const void* const* W, void* const* O)
+namespace {
+// Members of a group: one device and kernel family, one activation matrix, nothing after the dot product.
+int group_members_ok(vaicu_linear_plan* const* plans, int count)
 {
-    if (!plans || !W || !O || !I || count < 2 || count > 3) return VAICU_ERR_INVALID_VALUE;
+    if (!plans || count < 2 || count > 3 || !plans[0]) return VAICU_ERR_INVALID_VALUE;
     const vaicu_linear_plan* p0 = plans[0];
-    if (!p0) return VAICU_ERR_INVALID_VALUE;
-    uint32_t rows[3] = {0, 0, 0};
     uint64_t total = 0;
-    if (!aligned16(I)) return VAICU_ERR_UNSUPPORTED;
     for (int i = 0; i < count; ++i) {
         const vaicu_linear_plan* pl = plans[i];
-        if (!pl || !W[i] || !O[i]) return VAICU_ERR_INVALID_VALUE;
+        if (!pl) return VAICU_ERR_INVALID_VALUE;
         const vaicu_linear_desc& d = pl->d;
         const vaicu_linear_desc& d0 = p0->d;
-        // one kernel family, one activation matrix, nothing after the dot product
-        if (pl->dev != p0->dev || pl->kernel != VAICU_KERNEL_GEMV || !pl->gemv_vec.vectorized) return VAICU_ERR_UNSUPPORTED;
+        if (pl->dev != p0->dev || pl->kernel != p0->kernel) return VAICU_ERR_UNSUPPORTED;
+        if (pl->kernel == VAICU_KERNEL_GEMV) {
+            if (!pl->gemv_vec.vectorized) return VAICU_ERR_UNSUPPORTED;
+        } else if (pl->kernel == VAICU_KERNEL_TC_SKINNY) {
+            if (d.N % 128u) return VAICU_ERR_UNSUPPORTED;      // members are whole numbers of weight tiles
+        } else {
+            return VAICU_ERR_UNSUPPORTED;
+        }
         if (d.M != d0.M || d.K != d0.K || d.i_dtype != d0.i_dtype || d.w_dtype != d0.w_dtype || d.o_dtype != d0.o_dtype)
             return VAICU_ERR_UNSUPPORTED;
         if (d.has_bias || d.has_residual || d.epilogue != VAICU_EPILOGUE_NONE || d.gate_fuse || d.scalar_scale != 1.0f)
             return VAICU_ERR_UNSUPPORTED;
-        if (!aligned16(W[i])) return VAICU_ERR_UNSUPPORTED;
-        rows[i] = d.N;
         total += d.N;
     }
     if (total * p0->d.M >= (1ull << 32)) return VAICU_ERR_UNSUPPORTED;
-    vaicu_linear_desc all = p0->d;
-    all.N = (uint32_t)total;
-    LinearArgs a = make_args(all, I, W[0], nullptr, nullptr, O[0]);
-    const GemvConfig cfg = choose_gemv(a, p0->dev->sm_count, true, &p0->tune);
-    if (!cfg.vectorized) return VAICU_ERR_UNSUPPORTED;
-    VAICU_CUDA(launch_gemv_group(a, cfg, (uint32_t)count, rows, W, O, (cudaStream_t)stream));
+    return VAICU_OK;
+}
+
+// The cached state of a tensor-core group, (re)built when the members change.
+int group_state(vaicu_linear_plan* const* plans, int count, GroupState** out)
+{
+    vaicu_linear_plan* p0 = plans[0];
+    GroupState* g = p0->group;
+    bool same = g && g->count == count;
+    for (int i = 0; same && i < count; ++i) same = g->members[i] == plans[i];
+    if (!same) {
+        if (g) { vaicu_linear_plan_destroy(g->virt); delete g; p0->group = nullptr; }
+        g = new (std::nothrow) GroupState();
+        if (!g) return VAICU_ERR_INVALID_VALUE;
+        memset(g, 0, sizeof(*g));
+        vaicu_linear_desc all = p0->d;
+        uint32_t total = 0;
+        for (int i = 0; i < count; ++i) { g->members[i] = plans[i]; g->rows[i] = plans[i]->d.N; total += plans[i]->d.N; }
+        all.N = total;
+        g->count = count;
+        vaicu_linear_tuning tune = default_tuning();
+        tune.kernel = VAICU_KERNEL_TC_SKINNY;
+        tune.tc_splits = p0->tune.tc_splits;
+        int rc = build_plan(p0->dev, &all, tune, &g->virt);
+        if (rc != VAICU_OK) { delete g; return rc == VAICU_ERR_INVALID_VALUE ? VAICU_ERR_UNSUPPORTED : rc; }
+        p0->group = g;
+    }
+    *out = g;
+    return VAICU_OK;
+}
+}  // namespace
+
+int vaicu_linear_group_workspace_bytes(vaicu_linear_plan* const* plans, int count, size_t* out_bytes)
+{
+    if (!out_bytes) return VAICU_ERR_INVALID_VALUE;
+    int rc = group_members_ok(plans, count);
+    if (rc != VAICU_OK) return rc;
+    *out_bytes = 0;
+    if (plans[0]->kernel == VAICU_KERNEL_GEMV) return VAICU_OK;
+    GroupState* g = nullptr;
+    rc = group_state(plans, count, &g);
+    if (rc != VAICU_OK) return rc;
+    const vaicu_linear_plan* v = g->virt;
+    *out_bytes = v->ws_cast_bytes + align_up((size_t)v->tcp.splits * v->d.M * v->d.N * sizeof(float), 256u);
+    return VAICU_OK;
+}
+
+int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_stream_t stream, const void* I,
+                           const void* const* W, void* const* O, void* workspace)
+{
+    if (!W || !O || !I) return VAICU_ERR_INVALID_VALUE;
+    int rc = group_members_ok(plans, count);
+    if (rc != VAICU_OK) return rc;
+    vaicu_linear_plan* p0 = plans[0];
+    uint32_t rows[3] = {0, 0, 0};
+    uint64_t total = 0;
+    for (int i = 0; i < count; ++i) {
+        if (!W[i] || !O[i]) return VAICU_ERR_INVALID_VALUE;
+        if (!aligned16(W[i])) return VAICU_ERR_UNSUPPORTED;
+        rows[i] = plans[i]->d.N;
+        total += rows[i];
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    if (p0->kernel == VAICU_KERNEL_GEMV) {
+        if (!aligned16(I)) return VAICU_ERR_UNSUPPORTED;
+        vaicu_linear_desc all = p0->d;
+        all.N = (uint32_t)total;
+        LinearArgs a = make_args(all, I, W[0], nullptr, nullptr, O[0]);
+        const GemvConfig cfg = choose_gemv(a, p0->dev->sm_count, true, &p0->tune);
+        if (!cfg.vectorized) return VAICU_ERR_UNSUPPORTED;
+        VAICU_CUDA(launch_gemv_group(a, cfg, (uint32_t)count, rows, W, O, s));
+        return VAICU_OK;
+    }
+    // swapped tensor-core kernel: one launch leaves the partial sums of all members, one fold stores the outputs
+    for (int i = 0; i < count; ++i)
+        if (!aligned16(O[i])) return VAICU_ERR_UNSUPPORTED;
+    GroupState* g = nullptr;
+    rc = group_state(plans, count, &g);
+    if (rc != VAICU_OK) return rc;
+    vaicu_linear_plan* v = g->virt;
+    const vaicu_linear_desc& d = v->d;
+    if (!v->tc_cast && !aligned16(I)) return VAICU_ERR_UNSUPPORTED;
+    if (v->tc_cast && (reinterpret_cast<uintptr_t>(I) & 3u)) return VAICU_ERR_ALIGNMENT;
+    if (!workspace) return VAICU_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return VAICU_ERR_ALIGNMENT;
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    const void* act = I;
+    if (v->tc_cast) {
+        VAICU_CUDA(launch_cast_f32_to_16(reinterpret_cast<const float*>(I), ws, d.w_dtype, (size_t)d.M * d.K, p0->dev->sm_count, s));
+        act = ws;
+    }
+    float* partial = reinterpret_cast<float*>(ws + v->ws_cast_bytes);
+    for (int i = 0; i < count; ++i) {
+        if (g->w_base[i] == W[i]) continue;
+        rc = encode_map(&g->maps_w[i], W[i], d.w_dtype, rows[i], d.K, 128u);
+        if (rc != VAICU_OK) return rc;
+        g->w_base[i] = W[i];
+    }
+    if (count == 2) g->maps_w[2] = g->maps_w[1];
+    uint32_t ib = act == g->act_base[0] ? 0u : (act == g->act_base[1] ? 1u : 2u);
+    if (ib == 2u) {
+        ib = g->act_next;
+        g->act_next ^= 1u;
+        rc = encode_map(&g->map_act[ib], act, d.w_dtype, d.M, d.K, v->tcp.bn);
+        if (rc != VAICU_OK) return rc;
+        g->act_base[ib] = act;
+    }
+    TcParams t = v->tcp;
+    t.O = nullptr; t.bias = nullptr; t.res = nullptr; t.partial = partial; t.tile_done = nullptr;
+    t.n_dst = 1u; t.ldo = d.N; t.col0 = 0u;
+    t.grp_t1 = rows[0] / 128u;
+    t.grp_t2 = count > 2 ? (rows[0] + rows[1]) / 128u : kNoGroup;
+    VAICU_CUDA(launch_tc_gemm_group(g->maps_w, g->map_act[ib], t, v->tc_grid, v->tc_smem, s));
+    VAICU_CUDA(launch_group_fold(partial, t.splits, d.M, (uint32_t)count, rows, O, d.o_dtype, s));
+    for (int i = 0; i < count; ++i) { plans[i]->last_kernel = VAICU_KERNEL_TC_SKINNY; plans[i]->last_vectorized = 1; }
     return VAICU_OK;
 }
 

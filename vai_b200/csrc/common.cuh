@@ -165,6 +165,9 @@ cudaError_t launch_gemv_group(const LinearArgs& a, const GemvConfig& cfg, uint32
 struct FmaTileConfig { uint32_t split_count, split_size; };
 cudaError_t launch_fma_tile(const LinearArgs& a, const FmaTileConfig& cfg, float* partial, cudaStream_t stream);
 cudaError_t launch_splitk_reduce(const LinearArgs& a, const float* partial, uint32_t split_count, cudaStream_t stream);
+// partial [splits][M][sum of rows] -> the members' dense outputs (rows[i] % 4 == 0, O[i] 16-byte aligned)
+cudaError_t launch_group_fold(const float* partial, uint32_t splits, uint32_t M, uint32_t count, const uint32_t* rows,
+                              void* const* O, int o_dtype, cudaStream_t stream);
 cudaError_t launch_cast_f32_to_16(const float* src, void* dst, int dst_dtype, size_t n, int sm_count, cudaStream_t stream);
 
 cudaError_t launch_argmax(const void* in, int dtype, uint32_t M, uint32_t N, uint32_t* out, cudaStream_t stream);

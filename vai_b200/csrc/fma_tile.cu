@@ -43,16 +43,38 @@ __global__ void __launch_bounds__(TT) fma_tile_kernel(const FmaParams p)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 
+    // Four consecutive k of one row of each operand per thread, held in registers for one trip:
+    // the loads of trip i + 1 are in flight while trip i is multiplied out of shared memory.
+    const uint32_t lm = m0 + lrow, ln = n0 + lrow;
+    const bool quad_i = a.i_dtype == VAICU_DTYPE_F32 && a.K % 4u == 0 && kbeg % 4u == 0 && (reinterpret_cast<uintptr_t>(a.I) & 15u) == 0;
+    const bool quad_w = a.w_dtype == VAICU_DTYPE_F32 && a.K % 4u == 0 && kbeg % 4u == 0 && (reinterpret_cast<uintptr_t>(a.W) & 15u) == 0;
+    float ra[4], rb[4];
+    auto fetch = [&](uint32_t k0) {
+        const uint32_t k = k0 + lk;
+        if (quad_i && lm < a.M && k + 3u < kend) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.I) + (size_t)lm * a.K + k));
+            ra[0] = v.x; ra[1] = v.y; ra[2] = v.z; ra[3] = v.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ra[e] = (k + e < kend && lm < a.M) ? load_as_f32(a.I, a.i_dtype, (size_t)lm * a.K + k + e) : 0.0f;
+        }
+        if (quad_w && ln < a.N && k + 3u < kend) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.W) + (size_t)ln * a.K + k));
+            rb[0] = v.x; rb[1] = v.y; rb[2] = v.z; rb[3] = v.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) rb[e] = (k + e < kend && ln < a.N) ? load_as_f32(a.W, a.w_dtype, (size_t)ln * a.K + k + e) : 0.0f;
+        }
+    };
+    if (kbeg < kend) fetch(kbeg);
     for (uint32_t k0 = kbeg; k0 < kend; k0 += BK) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const uint32_t k = k0 + lk + e;
-            const bool kin = k < kend;
-            const uint32_t m = m0 + lrow, n = n0 + lrow;
-            As[lk + e][lrow] = (kin && m < a.M) ? load_as_f32(a.I, a.i_dtype, (size_t)m * a.K + k) : 0.0f;
-            Bs[lk + e][lrow] = (kin && n < a.N) ? load_as_f32(a.W, a.w_dtype, (size_t)n * a.K + k) : 0.0f;
+            As[lk + e][lrow] = ra[e];
+            Bs[lk + e][lrow] = rb[e];
         }
         __syncthreads();
+        if (k0 + BK < kend) fetch(k0 + BK);
 #pragma unroll
         for (int k = 0; k < BK; ++k) {
             const float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
@@ -115,6 +137,54 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
     }
 }
 
+// Fold of a group's split-K partials (q / k / v computed as one swapped tensor-core launch): the partial
+// sums are [splits][M][N] over the members' rows side by side; the members' outputs are separate
+// dense tensors.  Four columns per thread: members are multiples of 128 rows, so a quad never straddles two.
+struct GroupFoldParams {
+    const float* partial;
+    uint32_t splits, M, N, count;
+    uint32_t start[4];          // first column of member i; start[count] = N
+    void* O[3];
+    int o_dtype;
+};
+
+__global__ void __launch_bounds__(256) group_fold_kernel(const GroupFoldParams p)
+{
+    launch_dependents();
+    dependency_wait();          // the partial sums come from the launch ahead of this one
+    const size_t MN = (size_t)p.M * p.N;
+    const uint32_t quads_per_row = p.N / 4u;
+    const size_t total = (size_t)p.M * quads_per_row;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t m = (uint32_t)(idx / quads_per_row);
+        const uint32_t n = (uint32_t)(idx - (size_t)m * quads_per_row) * 4u;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float* src = p.partial + (size_t)m * p.N + n;
+        for (uint32_t z = 0; z < p.splits; ++z) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(src + z * MN));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        uint32_t j = 0;
+        if (p.count > 2u && n >= p.start[2]) j = 2u;
+        else if (n >= p.start[1]) j = 1u;
+        const uint32_t width = p.start[j + 1u] - p.start[j];
+        const size_t at = (size_t)m * width + (n - p.start[j]);
+        if (p.o_dtype == VAICU_DTYPE_F32) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.O[j]) + at) = acc;
+        } else {
+            uint2 o;
+            if (p.o_dtype == VAICU_DTYPE_F16) {
+                __half2 h0 = __floats2half2_rn(acc.x, acc.y), h1 = __floats2half2_rn(acc.z, acc.w);
+                o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+            } else {
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x, acc.y), h1 = __floats2bfloat162_rn(acc.z, acc.w);
+                o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+            }
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.O[j]) + at) = o;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) cast_kernel(const float* __restrict__ src, void* __restrict__ dst,
                                                     int dst_dtype, size_t n)
 {
@@ -148,6 +218,22 @@ __global__ void __launch_bounds__(256) cast_kernel(const float* __restrict__ src
 }
 
 }  // namespace
+
+cudaError_t launch_group_fold(const float* partial, uint32_t splits, uint32_t M, uint32_t count, const uint32_t* rows,
+                              void* const* O, int o_dtype, cudaStream_t stream)
+{
+    GroupFoldParams p{};
+    p.partial = partial; p.splits = splits; p.M = M; p.count = count; p.o_dtype = o_dtype;
+    uint32_t at = 0;
+    for (uint32_t i = 0; i < count; ++i) { p.start[i] = at; p.O[i] = O[i]; at += rows[i]; }
+    for (uint32_t i = count; i < 4u; ++i) p.start[i] = at;
+    p.N = at;
+    const size_t total = (size_t)M * (at / 4u);
+    size_t blocks = (total + 255u) / 256u;
+    if (blocks > 148u * 8u) blocks = 148u * 8u;
+    if (blocks == 0) blocks = 1;
+    return launch_pdl(group_fold_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, p);
+}
 
 cudaError_t launch_fma_tile(const LinearArgs& a, const FmaTileConfig& cfg, float* partial, cudaStream_t stream)
 {

@@ -496,7 +496,8 @@ __device__ __forceinline__ void store_rows16(const TcParams& p, const uint32_t* 
 //       and two MMAs per k-step fill two accumulators.
 template <bool SWAP, bool GATE>
 __global__ void __launch_bounds__(kTcThreads, 1)
-tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcParams p)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_a1, const __grid_constant__ CUtensorMap tmap_a2, const TcParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment is required by the 128-byte swizzle atoms
@@ -537,6 +538,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        if (SWAP && !GATE && p.grp_t1 != kNoGroup) {
+            prefetch_tmap(&tmap_a1);
+            prefetch_tmap(&tmap_a2);
+        }
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, p.tmem_cols);
@@ -561,6 +566,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             auto load_a = [&](uint32_t st, uint32_t kb, uint32_t ta) {
                 uint8_t* sa = smem + (size_t)st * stage_bytes;
                 const int32_t kx = (int32_t)(kb * BLOCK_K);
+                if (SWAP && !GATE && ta >= p.grp_t1) {
+                    // a group of Linears over the same activations: the weight tiles of the second and
+                    // third member come from their own tensors (members are whole numbers of tiles)
+                    const bool third = ta >= p.grp_t2;
+                    tma_load_2d(sa, third ? &tmap_a2 : &tmap_a1, &full_bar[st], kx,
+                                (int32_t)((ta - (third ? p.grp_t2 : p.grp_t1)) * a_rows));
+                    return;
+                }
                 tma_load_2d(sa, &tmap_a, &full_bar[st], kx, (int32_t)(ta * a_rows));
                 if (a_boxes == 2u)
                     tma_load_2d(sa + TILE_ROWS * BLOCK_K * 2u, &tmap_a, &full_bar[st], kx,
@@ -1205,13 +1218,21 @@ cudaError_t launch_wait_expiry_selftest(int* status, cudaStream_t stream)
 }
 
 template <bool SWAP, bool GATE>
-static cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int grid, size_t smem,
-                                  cudaStream_t stream)
+static cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma1, const CUtensorMap& ma2,
+                                  const TcParams& p, int grid, size_t smem, cudaStream_t stream)
 {
     auto kern = tc_gemm_kernel<SWAP, GATE>;
     static SmemOptIn optin;
     if (cudaError_t e = optin.ensure(kern, (int)kTcMaxSmem); e != cudaSuccess) return e;
-    return launch_pdl(kern, dim3((unsigned)grid), dim3(kTcThreads), smem, stream, ma, mb, p);
+    return launch_pdl(kern, dim3((unsigned)grid), dim3(kTcThreads), smem, stream, ma, mb, ma1, ma2, p);
+}
+
+// Swapped kernel over a group of 2-3 weight tensors that share the activations (p.grp_t1 / p.grp_t2
+// say at which weight tile the second / third begins; p.N is the sum of their rows).
+cudaError_t launch_tc_gemm_group(const CUtensorMap* maps_w, const CUtensorMap& map_act, const TcParams& p, int grid, size_t smem,
+                                 cudaStream_t stream)
+{
+    return launch_variant<true, false>(maps_w[0], map_act, maps_w[1], maps_w[2], p, grid, smem, stream);
 }
 
 cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b_tail, const TcParams& p,
@@ -1220,10 +1241,10 @@ cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, c
     const bool gate = p.gate != 0;
     if (p.pair) return gate ? launch_pair_variant<true>(map_a, map_b, map_b_tail, p, grid, smem, stream)
                             : launch_pair_variant<false>(map_a, map_b, map_b_tail, p, grid, smem, stream);
-    if (swap) return gate ? launch_variant<true, true>(map_a, map_b, p, grid, smem, stream)
-                          : launch_variant<true, false>(map_a, map_b, p, grid, smem, stream);
-    return gate ? launch_variant<false, true>(map_a, map_b, p, grid, smem, stream)
-                : launch_variant<false, false>(map_a, map_b, p, grid, smem, stream);
+    if (swap) return gate ? launch_variant<true, true>(map_a, map_b, map_a, map_a, p, grid, smem, stream)
+                          : launch_variant<true, false>(map_a, map_b, map_a, map_a, p, grid, smem, stream);
+    return gate ? launch_variant<false, true>(map_a, map_b, map_a, map_a, p, grid, smem, stream)
+                : launch_variant<false, false>(map_a, map_b, map_a, map_a, p, grid, smem, stream);
 }
 
 }  // namespace vaicu

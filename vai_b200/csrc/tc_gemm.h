@@ -51,8 +51,13 @@ struct TcParams {
     // tail_split column strips of bn / tail_split, one work item each, so that the round keeps more clusters
     // busy for a shorter time (tail_split = 1: off).  idesc_tail is the instruction descriptor of a strip.
     uint32_t tail_first, tail_split, idesc_tail;
+    // Swapped kernel over a group of weight tensors that share the activations (q / k / v): the weight
+    // tile at which the second / third tensor begins (kNoGroup: a single tensor).  N is the sum of the
+    // members' rows; a group always leaves raw partial sums for the group's fold.
+    uint32_t grp_t1, grp_t2;
     float scale;
 };
+constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
 
 // Work item -> tile, K split, column strip and UMMA N of that item.
 __host__ __device__ inline void work_item(const TcParams& p, uint32_t w, uint32_t& tile, uint32_t& z, uint32_t& strip, uint32_t& width)
@@ -104,6 +109,8 @@ cudaError_t tc_pair_max_clusters(size_t smem, int* clusters);
 // One tiny launch whose bounded mbarrier wait is made to run out; sets *status as the GEMM kernels do.
 cudaError_t launch_wait_expiry_selftest(int* status, cudaStream_t stream);
 // map_b_tail: the weights' map with the strip box of the tail round (CTA-pair kernel with tail_split > 1; else any valid map).
+cudaError_t launch_tc_gemm_group(const CUtensorMap* maps_w, const CUtensorMap& map_act, const TcParams& p, int grid, size_t smem,
+                                 cudaStream_t stream);
 cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b_tail, const TcParams& p,
                            bool swap, int grid, size_t smem, cudaStream_t stream);
 

@@ -698,6 +698,12 @@ class NeuralNet:
             raise RuntimeError("no output is reachable from the inputs given")
         # Nodes of one level do not depend on each other (q / k / v of a block): they go to
         # side streams between a fork and a join, so their launch latencies overlap.
+        def scratch(nbytes):
+            t = Tensor(((nbytes + 3) // 4,), Dtype.F32)
+            t.buffer = self.pool.request(t.nbytes())
+            rec.keep.append(t)
+            return t
+
         by_level = {}
         for n in order:
             if not isinstance(n, (InputNode, OutputNode)):
@@ -712,13 +718,17 @@ class NeuralNet:
                 rest, by_input = [], {}
                 for n in group:
                     if getattr(n, "groupable", None) and n.groupable():
-                        by_input.setdefault((id(n.slots["in0"]), int(n.slots["weight"].dtype), int(n.slots["out0"].dtype)), []).append(n)
+                        by_input.setdefault((id(n.slots["in0"]),) + n.group_key(), []).append(n)
                     else:
                         rest.append(n)
                 for members in by_input.values():
                     while len(members) >= 2:
                         take, members = members[:3], members[3:]
-                        launches.append(type(take[0]).bind_group(take))
+                        fn = type(take[0]).bind_group(take, scratch)
+                        if fn is None:
+                            rest += take
+                        else:
+                            launches.append(fn)
                     rest += members
                 launches += [bound[n] for n in rest]
             else:

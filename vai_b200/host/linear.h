@@ -14,6 +14,7 @@
 
 #include <cstdint>
 #include <cstring>
+#include <functional>
 #include <map>
 #include <memory>
 #include <stdexcept>
@@ -188,6 +189,12 @@ public:
     // Called once per recording after every node is prepared and its buffers are bound, before any
     // run() is recorded: the place for one-time device work that must not be part of the recording.
     virtual void bound(vaicu_stream_t /*stream*/) {}
+    // Sibling nodes that read the same tensor and can share one launch (q / k / v Linears) have
+    // equal, non-empty group keys once prepared.  leadGroup() turns this node into the one that
+    // launches for all `members` (itself first); `scratch(bytes)` hands out device memory that
+    // lives as long as the recording.  Returns false when the members must launch one by one.
+    virtual std::string groupKey() const { return {}; }
+    virtual bool leadGroup(const std::vector<Node*>& /*members*/, const std::function<void*(size_t)>& /*scratch*/) { return false; }
     virtual void prepare() = 0;
     virtual void run(vaicu_stream_t stream) = 0;
 };
@@ -242,7 +249,42 @@ public:
     }
     void absorbGate(vai::Epilogue activation, Dtype oDtype) { gate_ = true; gateActivation_ = activation; gateODtype_ = oDtype; }
     bool gateFused() const { return gate_; }
-    void resetFusion() override { gate_ = false; argmaxReader_ = nullptr; launchTaken_ = false; }
+    void resetFusion() override { gate_ = false; argmaxReader_ = nullptr; launchTaken_ = false; group_.clear(); groupWork_ = nullptr; }
+
+    // Plain (nothing after the dot product) on the weight-streaming kernel, or on the swapped
+    // tensor-core kernel with a whole number of weight tiles: vaicu_linear_run_group can serve
+    // this node together with siblings over the same activations.
+    std::string groupKey() const override
+    {
+        if (!plan_ || hasBias() || config_.acceptResidual || config_.epilogue != vai::Epilogue::None || gate_ ||
+            config_.scalarScale != 1.0f || argmaxReader_ || config_.splitSize)
+            return {};
+        const bool ok = info_.kernel == VAICU_KERNEL_GEMV || (info_.kernel == VAICU_KERNEL_TC_SKINNY && config_.outDim % 128u == 0);
+        if (!ok) return {};
+        return std::to_string(info_.kernel) + "/" + std::to_string((int)(*this)["weight"].dtype()) + "/" +
+               std::to_string((int)(*this)["out0"].dtype());
+    }
+    bool leadGroup(const std::vector<Node*>& members, const std::function<void*(size_t)>& scratch) override
+    {
+        if (members.size() < 2 || members.size() > 3 || members[0] != this) return false;
+        std::vector<Linear*> group;
+        std::vector<vaicu_linear_plan*> plans;
+        auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+        if (!aligned((*this)["in0"].devicePtr())) return false;
+        for (Node* n : members) {
+            Linear* l = static_cast<Linear*>(n);      // equal group keys: every member is a Linear
+            if (!aligned((*l)["weight"].devicePtr()) || !aligned((*l)["out0"].devicePtr())) return false;
+            group.push_back(l);
+            plans.push_back(l->plan_);
+        }
+        size_t bytes = 0;
+        if (vaicu_linear_group_workspace_bytes(plans.data(), (int)plans.size(), &bytes) != VAICU_OK) return false;
+        groupWork_ = bytes ? scratch(bytes) : nullptr;
+        group_ = group;
+        for (size_t i = 1; i < group.size(); ++i) group[i]->takeLaunch();
+        return true;
+    }
+    bool leadsGroup() const { return !group_.empty(); }
 
     // An Argmax that is this node's only reader may share its launch (vaicu_linear_run_argmax)
     // when the plan turns out to be on the weight-streaming kernel; that node then issues the
@@ -310,7 +352,20 @@ public:
     void run(vaicu_stream_t stream) override
     {
         if (!plan_) throw std::logic_error("Linear::run before prepare");
-        if (launchTaken_) return;      // the Argmax behind this node launches the fused kernel
+        if (launchTaken_) return;      // the Argmax behind this node, or the group's first member, launches for it
+        if (!group_.empty()) {
+            vaicu_linear_plan* plans[3];
+            const void* weights[3];
+            void* outs[3];
+            for (size_t i = 0; i < group_.size(); ++i) {
+                plans[i] = group_[i]->plan_;
+                weights[i] = (*group_[i])["weight"].devicePtr();
+                outs[i] = (*group_[i])["out0"].devicePtr();
+            }
+            check(vaicu_linear_run_group(plans, (int)group_.size(), stream, (*this)["in0"].devicePtr(), weights, outs, groupWork_),
+                  "vaicu_linear_run_group");
+            return;
+        }
         const Tensor& partial = (*this)["partial"];
         check(vaicu_linear_run(plan_, stream, (*this)["in0"].devicePtr(), (*this)["weight"].devicePtr(),
                                hasBias() ? (*this)["bias"].devicePtr() : nullptr,
@@ -325,6 +380,8 @@ private:
     vaicu_linear_info info_{};
     Node* argmaxReader_ = nullptr;
     bool launchTaken_ = false;
+    std::vector<Linear*> group_;        // non-empty: this node launches for these siblings (itself first)
+    void* groupWork_ = nullptr;
     bool gate_ = false;
     vai::Epilogue gateActivation_ = vai::Epilogue::None;
     Dtype gateODtype_ = Dtype::Fp32;

@@ -137,6 +137,7 @@ struct NeuralNetConfig {
     bool useGraph = true;                // replay a recorded CUDA graph (else re-enqueue the launches)
     bool fuseGatedMul = true;            // record Linear -> GatedMul as one launch where the wiring allows it
     bool fuseArgmax = true;              // record a weight-streaming Linear -> Argmax as one launch
+    bool groupSiblings = true;           // record plain Linears over the same activations (q / k / v) as one launch
 };
 
 class NeuralNet : public NodeOwner
@@ -376,6 +377,27 @@ private:
                     rec.keep.push_back(t);
                 }
             }
+        }
+        if (config_.groupSiblings) {
+            // Sibling Linears that read the same tensor and do nothing after the dot product share
+            // one launch: the first of them in the order launches for up to three.
+            std::map<std::pair<std::pair<Node*, std::string>, std::string>, std::vector<Node*>> siblings;
+            for (Node* n : rec.order) {
+                const std::string key = n->groupKey();
+                auto in0 = n->links().find("in0");
+                if (!key.empty() && in0 != n->links().end()) siblings[{in0->second, key}].push_back(n);
+            }
+            auto scratch = [&](size_t bytes) {
+                Tensor t({(uint32_t)((bytes + 3) / 4)}, Dtype::Fp32);
+                t.bindPooled(pool_.request(t.numBytes()));
+                rec.keep.push_back(t);
+                return t.devicePtr();
+            };
+            for (auto& [key, members] : siblings)
+                for (size_t at = 0; at + 2 <= members.size(); at += 3) {
+                    std::vector<Node*> take(members.begin() + at, members.begin() + std::min(at + 3, members.size()));
+                    take[0]->leadGroup(take, scratch);
+                }
         }
         for (auto& [name, node] : outputs_) {
             if (node->producers().find("in0") == node->producers().end()) throw std::runtime_error("output " + name + " is not connected");

@@ -183,15 +183,24 @@ class LinearNode(Node):
         return launch
 
     def groupable(self):
-        """Plain (nothing after the dot product) and on the weight-streaming kernel: may
-        share one launch with sibling Linears that read the same activations."""
-        return (self.info is not None and self.info.kernel == KERNEL_GEMV and not self.has_bias()
-                and not self.accept_residual and self.epilogue == Epilogue.NONE and not self.gate_fuse
-                and self.scalar_scale == 1.0 and self._argmax_reader is None)
+        """Plain (nothing after the dot product) and on the weight-streaming kernel, or on the
+        swapped tensor-core kernel with a whole number of weight tiles: may share one launch
+        with sibling Linears that read the same activations."""
+        if self.info is None or self.has_bias() or self.accept_residual or self.epilogue != Epilogue.NONE:
+            return False
+        if self.gate_fuse or self.scalar_scale != 1.0 or self._argmax_reader is not None or self.split_size:
+            return False
+        return self.info.kernel == KERNEL_GEMV or (self.info.kernel == KERNEL_TC_SKINNY and self.out_dim % 128 == 0)
+
+    def group_key(self):
+        """Nodes with equal keys (and the same in0 tensor) may form a group."""
+        return (int(self.info.kernel), int(self["weight"].dtype), int(self["out0"].dtype))
 
     @staticmethod
-    def bind_group(group):
-        """One launch for 2-3 groupable nodes with the same in0 (vaicu_linear_run_group)."""
+    def bind_group(group, scratch):
+        """One launch (plus one fold on the tensor-core kernel) for 2-3 groupable nodes with the
+        same in0 (vaicu_linear_run_group).  `scratch(nbytes)` hands out device memory that lives
+        as long as the recording.  Returns None when the library declines the group."""
         first = group[0]
         dev = first._device()
         n = len(group)
@@ -199,12 +208,21 @@ class LinearNode(Node):
         ws = (ctypes.c_void_p * n)(*[g["weight"].ptr for g in group])
         outs = (ctypes.c_void_p * n)(*[g["out0"].ptr for g in group])
         x = first["in0"].ptr
+        if any(p % 16 for p in [x, *ws, *outs]):
+            return None
+        need = ctypes.c_size_t()
+        if dev.lib.vaicu_linear_group_workspace_bytes(plans, n, ctypes.byref(need)) != 0:
+            return None
+        work = scratch(need.value).ptr if need.value else None
         run = dev.lib.vaicu_linear_run_group
 
         def launch(stream):
-            _lib.check(run(plans, n, stream, x, ws, outs), "vaicu_linear_run_group")
+            _lib.check(run(plans, n, stream, x, ws, outs, work), "vaicu_linear_run_group")
 
-        launch.kernel_launches = 1
+        if first.info.kernel == KERNEL_GEMV:
+            launch.kernel_launches = 1
+        else:
+            launch.kernel_launches = 2 + (1 if first["in0"].dtype == Dtype.F32 else 0)
         return launch
 
     def __del__(self):

@@ -565,6 +565,192 @@ class ShardedTopKHead:
             self.plan = None
 
 
+class _LocalLinear:
+    """One plan with its workspace, run on torch tensors on the current torch stream."""
+
+    def __init__(self, device, M, N, K, gate=False, epilogue=0, residual=False, scale=1.0):
+        import torch
+
+        from .engine import Dtype
+        self.dev = device
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = M, N, K
+        d.i_dtype = d.w_dtype = d.o_dtype = int(Dtype.BF16)
+        d.b_dtype = int(Dtype.NONE)
+        d.has_residual = 1 if residual else 0
+        d.gate_fuse = 1 if gate else 0
+        d.epilogue = int(epilogue)
+        d.scalar_scale = scale
+        h = ctypes.c_void_p()
+        _lib.check(device.lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(h)), "vaicu_linear_plan_create")
+        self.plan = h
+        info = _lib.LinearInfo()
+        _lib.check(device.lib.vaicu_linear_plan_info(h, ctypes.byref(info)), "vaicu_linear_plan_info")
+        self.launches = int(info.launches)
+        self.ws = torch.empty(max(int(info.workspace_bytes), 256), dtype=torch.uint8, device=torch.device("cuda", device.ordinal))
+
+    def run(self, stream, x, w, out, residual=None):
+        _lib.check(self.dev.lib.vaicu_linear_run(self.plan, stream, x.data_ptr(), w.data_ptr(), None,
+                                                 residual.data_ptr() if residual is not None else None, out.data_ptr(),
+                                                 self.ws.data_ptr()), "vaicu_linear_run")
+
+    def close(self):
+        if self.plan:
+            self.dev.lib.vaicu_linear_plan_destroy(self.plan)
+            self.plan = None
+
+
+class TensorParallelBlocks:
+    """The Linear nodes of `n_blocks` transformer blocks of a preset at batch M, wired as the one-GPU
+    bench wires them (q, k, v; o + residual; gate|value with the gate fused; down + residual), either
+    whole on this GPU (tp=False) or tensor-parallel over the ranks (tp=True): q / k / v / o replicated,
+    gate|value split by columns, `down` split along K with the reduce-scatter in its epilogue and the
+    all-gather in its fold (FusedRowParallelLinear) - every launch is one of this package's kernels, so
+    the whole chain is captured into ONE CUDA graph per rank and replayed.  Blocks rotate over `copies`
+    weight sets (seeded; the two forms draw the same values) so that weights come from HBM, not L2."""
+
+    def __init__(self, device, dist, preset, M, n_blocks, copies, tp):
+        import torch
+
+        from . import presets
+        from .engine import Dtype, Epilogue
+        p = presets.PRESETS[preset]
+        self.torch, self.dev, self.M, self.n_blocks = torch, device, M, n_blocks
+        self.tp = bool(tp) and dist is not None and dist.get_world_size() > 1
+        world = dist.get_world_size() if self.tp else 1
+        rank = dist.get_rank() if self.tp else 0
+        d, q, kv, ffn = p["d"], p["q"], p["kv"], p["ffn"]
+        act = int(getattr(Epilogue, p["act"]))
+        cuda = torch.device("cuda", device.ordinal)
+        begin, count = shard_rows(ffn, world, rank)
+        kb, kc = shard_k(ffn, world, rank)
+        if (kb, kc) != (begin, count):
+            raise ValueError("hidden columns and K slices of the ranks do not line up")
+        self.Lq, self.Lk, self.Lv = (_LocalLinear(device, M, n, d) for n in (q, kv, kv))
+        self.Lo = _LocalLinear(device, M, d, q, residual=True, scale=0.5)
+        self.Lg = _LocalLinear(device, M, 2 * count, d, gate=True, epilogue=act)
+        self.Ld = self.rp = None
+        if self.tp:
+            self.rp = FusedRowParallelLinear(device, dist, M, d, ffn, None, Dtype.BF16, part_dtype=Dtype.F32, scalar_scale=0.25)
+        else:
+            self.Ld = _LocalLinear(device, M, d, ffn, residual=True, scale=0.25)
+        self.weights = []
+        for c in range(copies):
+            gen = torch.Generator(device=cuda).manual_seed(4000 + c)
+
+            def draw(rows, cols):
+                return (torch.randn((rows, cols), generator=gen, device=cuda, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+
+            w = {"q": draw(q, d), "k": draw(kv, d), "v": draw(kv, d), "o": draw(d, q)}
+            g_full = draw(2 * ffn, d)
+            w["g"] = slice_weight(g_full, rank, world, True).contiguous() if self.tp else g_full
+            d_full = draw(d, ffn)
+            w["d"] = d_full[:, kb:kb + kc].contiguous() if self.tp else d_full
+            del g_full, d_full
+            self.weights.append(w)
+        bf = dict(dtype=torch.bfloat16, device=cuda)
+        self.q, self.k, self.v = torch.empty((M, q), **bf), torch.empty((M, kv), **bf), torch.empty((M, kv), **bf)
+        self.h, self.slab, self.y = torch.empty((M, d), **bf), torch.empty((M, count), **bf), torch.empty((M, d), **bf)
+        # q / k / v as one launch where the library takes the group (8 < M <= 128, or the weight-streaming kernel)
+        self.group = None
+        plans = (ctypes.c_void_p * 3)(self.Lq.plan, self.Lk.plan, self.Lv.plan)
+        need = ctypes.c_size_t()
+        if device.lib.vaicu_linear_group_workspace_bytes(plans, 3, ctypes.byref(need)) == 0:
+            self.group = (plans, torch.empty(max(need.value, 256), dtype=torch.uint8, device=cuda), (ctypes.c_void_p * 3)(
+                self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr()))
+        per_block = (2 if self.group else 3 * self.Lq.launches) + self.Lo.launches + self.Lg.launches
+        per_block += 4 if self.tp else self.Ld.launches
+        self.launches = per_block * n_blocks
+        self.bytes_per_gpu_block = 2 * (d * (q + 2 * kv) + d * q + 3 * d * count)
+        self.graph = None
+
+    def step(self, x0):
+        """Enqueues all blocks on the current torch stream; returns the last block's output."""
+        lib, stream = self.dev.lib, self.torch.cuda.current_stream().cuda_stream
+        x = x0
+        for b in range(self.n_blocks):
+            w = self.weights[b % len(self.weights)]
+            if self.group:
+                plans, work, outs = self.group
+                ws3 = (ctypes.c_void_p * 3)(w["q"].data_ptr(), w["k"].data_ptr(), w["v"].data_ptr())
+                _lib.check(lib.vaicu_linear_run_group(plans, 3, stream, x.data_ptr(), ws3, outs, work.data_ptr()), "vaicu_linear_run_group")
+            else:
+                self.Lq.run(stream, x, w["q"], self.q)
+                self.Lk.run(stream, x, w["k"], self.k)
+                self.Lv.run(stream, x, w["v"], self.v)
+            self.Lo.run(stream, self.q, w["o"], self.h, residual=x0)
+            self.Lg.run(stream, self.h, w["g"], self.slab)
+            if self.tp:
+                self.rp.w = w["d"]
+                x = self.rp.forward(self.slab, residual=x0)
+            else:
+                self.Ld.run(stream, self.slab, w["d"], self.y, residual=x0)
+                x = self.y
+        return x
+
+    def capture(self, x0):
+        """One eager pass (descriptors, attributes), then the same pass captured; returns the output tensor."""
+        torch = self.torch
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step(x0)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            out = self.step(x0)
+        return out
+
+    def close(self):
+        self.graph = None
+        for lin in (self.Lq, self.Lk, self.Lv, self.Lo, self.Lg, self.Ld):
+            if lin is not None:
+                lin.close()
+        if self.rp is not None:
+            self.rp.close()
+
+
+def bench_blocks(device, dist, preset, M, n_blocks, iters=10, warmup=3):
+    """`n_blocks` blocks' Linear nodes as one replayed CUDA graph: on one GPU (every rank measures that itself)
+    and tensor-parallel over all ranks; device-timed, max over ranks.  The two outputs (same seeded weights
+    and input) are compared on every rank."""
+    import torch
+
+    from . import presets
+    world = dist.get_world_size() if dist is not None else 1
+    cuda = torch.device("cuda", device.ordinal)
+    gen = torch.Generator(device="cpu").manual_seed(77)
+    x0 = torch.randn(M, presets.PRESETS[preset]["d"], generator=gen).to(torch.bfloat16).to(cuda)
+    res = {"preset": preset, "M": M, "blocks": n_blocks, "world": world}
+    outs = {}
+    for tp in ((False, True) if world > 1 else (False,)):
+        probe = TensorParallelBlocks(device, dist, preset, M, 1, 1, tp)
+        per_block = probe.bytes_per_gpu_block
+        probe.close()
+        del probe
+        copies = max(2, min(n_blocks, -(-320_000_000 // per_block)))       # the rotating weight sets exceed L2 (126 MB) well
+        chain = TensorParallelBlocks(device, dist, preset, M, n_blocks, copies, tp)
+        out = chain.capture(x0)
+        ms = _timed(torch, dist, cuda, chain.graph.replay, iters, warmup)
+        torch.cuda.synchronize()
+        outs[tp] = out.float().cpu()
+        key = "tN" if tp else "t1"
+        res[key + "_us_per_block"] = round(ms * 1e3 / n_blocks, 2)
+        res[key + "_launches_per_block"] = chain.launches // n_blocks
+        res[key + "_weight_sets"] = copies
+        _lib.check(device.lib.vaicu_device_status(device.handle, ctypes.byref(ctypes.c_int())), "vaicu_device_status")
+        chain.close()
+        del chain
+        torch.cuda.empty_cache()
+    if world > 1:
+        a, b = outs[True], outs[False]
+        res["max_rel_diff_vs_one_gpu"] = float(((a - b).abs() / b.abs().clamp_min(0.05)).max())
+        res["speedup"] = round(res["t1_us_per_block"] / res["tN_us_per_block"], 2)
+        res["efficiency"] = round(res["speedup"] / world, 3)
+    return res
+
+
 def _tiled_weight(torch, rows, k, seed):
     """[rows, k] bf16 ~N(0, 0.02) on the host, the same on every rank: one seeded pool of 2^24 + 977
     values repeated (the odd length keeps rows from lining up), so that a 1.3 GB matrix takes a
@@ -909,6 +1095,13 @@ def sharded_report(device, dist, peaks):
                     or layer.get("topk_head_matches_single_gpu_node") is False):
                 raise RuntimeError(f"{key} / {layer['layer']}: sharded result differs from the gathered reference")
         report[key] = rows
+    # whole blocks (q, k, v, o replicated; the MLP tensor-parallel) as one replayed CUDA graph per rank
+    report["blocks"] = [bench_blocks(device, dist, "gemma-3-4b", 64, 34, iters=10, warmup=3),
+                        bench_blocks(device, dist, "llama-3.2-3b", 8192, 2, iters=5, warmup=2)]
+    for b in report["blocks"]:
+        diff = b.get("max_rel_diff_vs_one_gpu")
+        if diff is not None and not diff <= 2e-2:
+            raise RuntimeError(f"{b['preset']} blocks: tensor-parallel output differs from the one-GPU chain by {diff}")
     return report
 
 
