@@ -745,7 +745,8 @@ def bench_blocks(device, dist, preset, M, n_blocks, iters=10, warmup=3):
         torch.cuda.empty_cache()
     if world > 1:
         a, b = outs[True], outs[False]
-        res["max_rel_diff_vs_one_gpu"] = float(((a - b).abs() / b.abs().clamp_min(0.05)).max())
+        # unit-scale activations whose sums may cancel: relative to max(|one-GPU value|, 1)
+        res["max_rel_diff_vs_one_gpu"] = float(((a - b).abs() / b.abs().clamp_min(1.0)).max())
         res["speedup"] = round(res["t1_us_per_block"] / res["tN_us_per_block"], 2)
         res["efficiency"] = round(res["speedup"] / world, 3)
     return res
