@@ -359,6 +359,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the prefill / batched-decode / fp32 reports (N = 1)")
+    ap.add_argument("--min-timed-ms", type=float, default=500.0,
+                    help="the K-step region is repeated until this much has been timed (0: once; for profiler runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     if args.impl == "reference":
@@ -398,7 +400,7 @@ def main():
 
     sampler = ClockSampler(local)
     sampler.start()
-    regions = timed_repeats(resident_region, dist, dev)
+    regions = timed_repeats(resident_region, dist, dev, args.min_timed_ms)
     clocks = sampler.stop()
     dev.check_status()
     ms = statistics.median(regions)             # one K-step region, max over ranks, median of the repeats
@@ -421,7 +423,7 @@ def main():
             net2(x)
         return ev.stop_ms(net2.stream)
 
-    e2e_regions = timed_repeats(e2e_region, dist, dev)
+    e2e_regions = timed_repeats(e2e_region, dist, dev, args.min_timed_ms)
     net_e2e = net2
     e2e_ms = statistics.median(e2e_regions)
     e2e_tok_s = world * args.steps / (e2e_ms / 1e3)

@@ -220,6 +220,11 @@ typedef struct vaicu_linear_tuning {
                                    folds; 0: the second launch                                  */
     int32_t  tc_tail_strips;    /* CTA-pair kernel: column strips per tile in the last, partial round of
                                    tiles: 1 = none, 2 or 4; 0: the widest that fits the idle clusters     */
+    uint32_t tc_tile_rows;      /* swapped tensor-core kernel: weight rows per tile, a multiple of 8 up to
+                                   128 (the MMA stays 128 rows tall; shorter tiles spread a layer with few
+                                   weight rows over all SMs); 0                                   */
+    uint32_t tc_stages;         /* tensor-core kernels: at most this many stages in the shared-memory ring
+                                   (2..8); 0: as many as fit                                       */
 } vaicu_linear_tuning;
 VAICU_API int vaicu_linear_plan_create_tuned(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_linear_tuning* tuning,
                                              vaicu_linear_plan** out);

@@ -256,6 +256,46 @@ def test_256_row_tiles(M, K, N, gate, mode, bn, device):
     assert_close(got, want, (2e-4, 5e-5), f"{mode} {M}x{K}x{N} gate={gate} bn={bn}")
 
 
+@pytest.mark.parametrize("M", [9, 64, 100])
+@pytest.mark.parametrize("rows,N,gate,splits", [(72, 1000, False, 0), (40, 520, True, 0), (8, 136, False, 0), (120, 777, True, 0),
+                                                (56, 600, False, 3), (96, 264, True, 2)])
+def test_short_weight_tiles_of_the_swapped_kernel(M, rows, N, gate, splits, device):
+    """Weight tiles of fewer than 128 rows (tc_tile_rows) on the swapped tensor-core kernel: the copy fills
+    `rows` rows of a 128-row slot, the MMA spans the slot, and the lanes past `rows` are never stored -
+    every output row must come from exactly one tile.  Ragged N, bias + residual or the fused gate, with
+    and without a K split."""
+    rng = np.random.default_rng(M + rows + N)
+    K = 576
+    n_w = 2 * N if gate else N
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((n_w, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(n_w).astype(np.float32)
+    r = None if gate else rng.standard_normal((M, N)).astype(np.float32)
+    got, want, node = run_linear(x, w, b, r, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", b_dtype="f32",
+                                 epilogue="SILU", gate_fuse=gate, kernel=nodes.KERNEL_TC_SKINNY,
+                                 tuning=dict(tc_tile_rows=rows, tc_splits=max(splits, 1)))
+    assert node.info.tile_n == rows and node.info.split_count == max(splits, 1)
+    assert_close(got, want, (2e-4, 5e-5), f"tile rows {rows} M={M} N={N} gate={gate} splits={splits}")
+    # the same result, bit for bit, as full 128-row tiles: K is walked in the same order
+    full, _, _ = run_linear(x, w, b, r, i_dtype="bf16", w_dtype="bf16", o_dtype="f32", b_dtype="f32",
+                            epilogue="SILU", gate_fuse=gate, kernel=nodes.KERNEL_TC_SKINNY,
+                            tuning=dict(tc_tile_rows=128, tc_splits=max(splits, 1)))
+    np.testing.assert_array_equal(got, full)
+
+
+def test_planner_spreads_a_layer_with_few_weight_tiles_over_the_sms(device):
+    """A gate|value layer at batch 64 whose 128-row tiles would occupy a third of the SMs is planned with
+    shorter tiles, one per SM, and without a K split."""
+    rng = np.random.default_rng(5)
+    H = 40 * device.sm_count
+    x = rng.standard_normal((64, 256)).astype(np.float32)
+    w = (rng.standard_normal((2 * H, 256)) / 16.0).astype(np.float32)
+    got, want, node = run_linear(x, w, i_dtype="bf16", w_dtype="bf16", o_dtype="bf16", epilogue="GELU_TANH", gate_fuse=True)
+    assert node.info.kernel == nodes.KERNEL_TC_SKINNY and node.info.split_count == 1
+    assert node.info.tile_n == 40
+    assert_close(got, want, (2e-2, 2e-2), "planned short tiles")
+
+
 @pytest.mark.parametrize("M,K,N,splits", [(256, 4096, 256, 4), (520, 2048, 300, 3)])
 def test_pair_tiles_split_k_match_single_cta(M, K, N, splits, device):
     """Split-K on CTA pairs (raw partials + fold) against the float64 expectation, and the

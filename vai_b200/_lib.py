@@ -34,7 +34,8 @@ class LinearTuning(ctypes.Structure):
                 ("tc_bn", ctypes.c_uint32), ("tc_splits", ctypes.c_uint32), ("gemv_rows", ctypes.c_int32),
                 ("gemv_k_warps", ctypes.c_int32), ("gemv_unroll", ctypes.c_int32), ("gemv_grid", ctypes.c_int32),
                 ("gemv_plain_launch", ctypes.c_int32), ("tc_fold", ctypes.c_int32),
-                ("tc_tail_strips", ctypes.c_int32)]
+                ("tc_tail_strips", ctypes.c_int32), ("tc_tile_rows", ctypes.c_uint32),
+                ("tc_stages", ctypes.c_uint32)]
 
     def __init__(self, **kw):
         super().__init__()

@@ -256,11 +256,31 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
     t.kblocks = ceil_div(d.K, 64u);
     t.grp_t1 = t.grp_t2 = kNoGroup;
     uint32_t bn;
+    t.tile_rows = 128u;
     if (swap) {
         bn = (uint32_t)align_up(d.M, 16u);
         if (bn > 128u) bn = 128u;
-        t.tiles_a = ceil_div(H, 128u);
         t.tiles_b = ceil_div(d.M, bn);
+        // Weight rows per tile.  128 fills the MMA; but a layer with fewer 128-row tiles than SMs leaves
+        // SMs without work, and a CTA streams its weights no faster than about one SM's share of the HBM
+        // bandwidth.  Shorter tiles (the MMA still spans 128 rows, the rest of the slot is not loaded and
+        // its lanes are not read) spread such a layer over all SMs without a K split and its fold.  Among the
+        // heights that give more than half a tile per SM (fewer tiles are split along K below) and keep
+        // the weights the larger part of what a CTA loads, pick the one with the fewest bytes per CTA:
+        // rounds x (weight rows + activation rows) per k-block.
+        const uint32_t boxes = gate ? 2u : 1u;
+        uint32_t best_rows = 128u;
+        uint64_t best_cost = ~0ull;
+        for (uint32_t rows = 128u; rows >= 32u && !d.split_size; rows -= 8u) {
+            if (boxes * rows < bn) break;
+            const uint32_t tiles = ceil_div(H, rows) * t.tiles_b;
+            if (tiles * 2u <= sms) continue;
+            const uint64_t cost = (uint64_t)ceil_div(tiles, sms) * (boxes * rows + bn);
+            if (cost < best_cost) { best_cost = cost; best_rows = rows; }
+        }
+        if (pl->tune.tc_tile_rows) best_rows = pl->tune.tc_tile_rows;
+        t.tile_rows = best_rows;
+        t.tiles_a = ceil_div(H, t.tile_rows);
     } else {
         // CTA pairs (cta_group::2): two neighbouring SMs share one 256-row tile and each
         // stages half of the weights' tile; both accumulator buffers stay in use.
@@ -323,6 +343,7 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
     const uint32_t stage_bytes = a_bytes + (t.pair ? bn / 2u : bn) * 128u;      // per CTA
     uint32_t stages = (uint32_t)((kTcMaxSmem - 2048u) / stage_bytes);
     if (stages > 8u) stages = 8u;
+    if (pl->tune.tc_stages && pl->tune.tc_stages < stages) stages = pl->tune.tc_stages;
     t.stages = stages;
     pl->tc_smem = (size_t)stages * stage_bytes + 1024u + 256u;
     const uint32_t acc_cols = a_boxes * bn;
@@ -402,6 +423,8 @@ int validate_tuning(const vaicu_linear_tuning& t)
     if (t.gemv_unroll != 0 && t.gemv_unroll != 2 && t.gemv_unroll != 4) return VAICU_ERR_INVALID_VALUE;
     if (t.gemv_grid < 0) return VAICU_ERR_INVALID_VALUE;
     if (t.tc_fold < 0 || t.tc_fold > 2) return VAICU_ERR_INVALID_VALUE;
+    if (t.tc_stages == 1u || t.tc_stages > 8u) return VAICU_ERR_INVALID_VALUE;
+    if (t.tc_tile_rows && (t.tc_tile_rows < 8u || t.tc_tile_rows > 128u || t.tc_tile_rows % 8u)) return VAICU_ERR_INVALID_VALUE;
     if (t.tc_tail_strips != 0 && t.tc_tail_strips != 1 && t.tc_tail_strips != 2 && t.tc_tail_strips != 4) return VAICU_ERR_INVALID_VALUE;
     return VAICU_OK;
 }
@@ -788,7 +811,7 @@ int vaicu_linear_plan_info(const vaicu_linear_plan* plan, vaicu_linear_info* out
         out->split_count = plan->tcp.splits;
         const uint32_t outc = (plan->tcp.gate && !plan->tc_swap) ? plan->tcp.bn / 2u : plan->tcp.bn;
         out->tile_m = plan->tc_swap ? outc : ((plan->tcp.wide || plan->tcp.pair) ? 256u : 128u);
-        out->tile_n = plan->tc_swap ? 128u : outc;
+        out->tile_n = plan->tc_swap ? plan->tcp.tile_rows : outc;
     }
     return VAICU_OK;
 }
@@ -1001,7 +1024,7 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
         ia = pl->map_a_next;
         pl->map_a_next ^= 1u;
         const uint32_t rows = pl->tc_swap ? d.N : d.M;
-        int rc = encode_map(&pl->map_a[ia], a_base, d.w_dtype, rows, d.K, 128u);
+        int rc = encode_map(&pl->map_a[ia], a_base, d.w_dtype, rows, d.K, pl->tc_swap ? pl->tcp.tile_rows : 128u);
         if (rc != VAICU_OK) return rc;
         pl->map_a_base[ia] = a_base;
     }
@@ -1124,6 +1147,8 @@ int group_state(vaicu_linear_plan* const* plans, int count, GroupState** out)
         vaicu_linear_tuning tune = default_tuning();
         tune.kernel = VAICU_KERNEL_TC_SKINNY;
         tune.tc_splits = p0->tune.tc_splits;
+        tune.tc_stages = p0->tune.tc_stages;
+        tune.tc_tile_rows = 128u;          // members begin at multiples of 128 rows
         int rc = build_plan(p0->dev, &all, tune, &g->virt);
         if (rc != VAICU_OK) { delete g; return rc == VAICU_ERR_INVALID_VALUE ? VAICU_ERR_UNSUPPORTED : rc; }
         p0->group = g;

@@ -35,7 +35,8 @@ namespace {
 constexpr uint32_t BLOCK_K = 64;          // 64 x 2 bytes = one 128-byte swizzle row
 constexpr uint32_t UMMA_K = 16;
 constexpr uint32_t TILE_ROWS = 128;       // UMMA M
-constexpr uint32_t kTcThreads = 192;
+constexpr uint32_t kTcThreads = 192;        // producer warp, MMA warp, 4 epilogue warps
+constexpr uint32_t kTcThreadsSwap = 320;    // swapped kernel: 8 epilogue warps, two per quarter of the TMEM lanes
 constexpr uint32_t kSpinLimit = 1u << 24; // bounded waits (each probe may sleep in hardware)
 
 // ---- PTX wrappers ---------------------------------------------------------
@@ -490,12 +491,26 @@ __device__ __forceinline__ void store_rows16(const TcParams& p, const uint32_t* 
 
 }  // namespace
 
+#ifdef VAICU_TC_TRACE
+// Development aid (not built by default): phase time stamps of every CTA of the single-CTA kernel.
+__device__ unsigned long long g_tc_trace[256 * 16];
+__device__ __forceinline__ void tc_trace(uint32_t slot)
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (blockIdx.x < 256u) g_tc_trace[blockIdx.x * 16u + slot] = t;
+}
+#define TC_TRACE(slot) tc_trace(slot)
+#else
+#define TC_TRACE(slot)
+#endif
+
 // SWAP: A (TMEM lanes) = weights, B (TMEM columns) = activations.
 // GATE: fused Linear + GatedMul.  Non-swap: the B stage holds bn/2 gate rows then
 //       bn/2 value rows; swap: the A stage holds 128 gate rows then 128 value rows
 //       and two MMAs per k-step fill two accumulators.
 template <bool SWAP, bool GATE>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(SWAP ? kTcThreadsSwap : kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_a1, const __grid_constant__ CUtensorMap tmap_a2, const TcParams p)
 {
@@ -505,15 +520,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t bn = p.bn;
+    if (threadIdx.x == 0) TC_TRACE(0);
     // wide: two 128-row A boxes per stage and two MMAs per k-step give a 256-row tile;
     // the weights' B tile is then fetched once per 256 rows instead of once per 128,
     // which is what the operand traffic from L2 allows at full tensor rate.
     const bool wide = !SWAP && p.wide != 0u;
     const uint32_t a_boxes = ((GATE && SWAP) || wide) ? 2u : 1u;
-    const uint32_t a_rows = wide ? 2u * TILE_ROWS : TILE_ROWS;   // rows per tile on the A side
+    // Swapped: a weight tile may hold fewer than 128 rows (p.tile_rows, a multiple of 8), so that a layer
+    // with fewer than one 128-row tile per SM still spreads over all SMs.  The MMA stays 128 rows tall; the
+    // rows of the slot that the copy does not fill are whatever the slot held, and the accumulator lanes
+    // they feed are never read.
+    const uint32_t tile_rows = SWAP ? p.tile_rows : TILE_ROWS;
+    const uint32_t a_rows = wide ? 2u * TILE_ROWS : tile_rows;   // rows per tile on the A side
     const uint32_t a_bytes = a_boxes * TILE_ROWS * BLOCK_K * 2u;
     const uint32_t b_bytes = bn * BLOCK_K * 2u;
     const uint32_t stage_bytes = a_bytes + b_bytes;        // multiple of 1024 (bn % 8 == 0)
+    const uint32_t tx_bytes = a_boxes * tile_rows * BLOCK_K * 2u + b_bytes;     // what the copies of one stage deliver
     const uint32_t stages = p.stages;
     const uint32_t acc_cols = a_boxes * bn;            // TMEM columns per accumulator buffer
     const uint32_t acc_bufs = p.acc_bufs;              // 2: epilogue overlaps the next tile; 1: 512 columns in use
@@ -530,8 +552,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (uint32_t b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
-        mbar_init(fold_in, 4);
+        // epilogue warps: 4, or 8 that share each quarter of the accumulator's lanes by column chunks (swapped
+        // kernel: its CTAs often hold a single tile, whose epilogue nothing overlaps)
+        const uint32_t epi_warps = (blockDim.x >> 5) - 2u;
+        for (uint32_t b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], epi_warps); }
+        mbar_init(fold_in, epi_warps);
         mbar_init(fold_out, 1);
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -551,6 +576,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) TC_TRACE(1);
 
     const uint32_t num_work = p.num_tiles * p.splits;
 
@@ -577,7 +603,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 tma_load_2d(sa, &tmap_a, &full_bar[st], kx, (int32_t)(ta * a_rows));
                 if (a_boxes == 2u)
                     tma_load_2d(sa + TILE_ROWS * BLOCK_K * 2u, &tmap_a, &full_bar[st], kx,
-                                (int32_t)(wide ? ta * a_rows + TILE_ROWS : p.H + ta * TILE_ROWS));
+                                (int32_t)(wide ? ta * a_rows + TILE_ROWS : p.H + ta * tile_rows));
             };
             auto load_b = [&](uint32_t st, uint32_t kb, uint32_t tb) {
                 uint8_t* sb = smem + (size_t)st * stage_bytes + a_bytes;
@@ -605,10 +631,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     first = false;
                     const uint32_t npre = (kb1 - kb0 < stages) ? kb1 - kb0 : stages;
                     for (uint32_t i = 0; i < npre; ++i) {        // the ring is empty: no wait needed
-                        mbar_expect_tx(&full_bar[i], stage_bytes);
+                        mbar_expect_tx(&full_bar[i], tx_bytes);
                         if (SWAP) load_a(i, kb0 + i, ta); else load_b(i, kb0 + i, tb);
                     }
+                    TC_TRACE(2);
                     dependency_wait();
+                    TC_TRACE(3);
                     for (uint32_t i = 0; i < npre; ++i) {
                         if (SWAP) load_b(i, kb0 + i, tb); else load_a(i, kb0 + i, ta);
                     }
@@ -618,13 +646,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 for (; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(&full_bar[stage], stage_bytes);
+                    mbar_expect_tx(&full_bar[stage], tx_bytes);
                     load_a(stage, kb, ta);
                     load_b(stage, kb, tb);
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
             if (first) dependency_wait();
+            TC_TRACE(4);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -642,6 +671,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (uint32_t kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
+                    if (iter == 0 && kb == kb0) TC_TRACE(5);
                     const uint32_t sa = smem_u32(smem + (size_t)stage * stage_bytes);
                     const uint32_t sb = sa + a_bytes;
                     const uint64_t a_desc = make_smem_desc(sa);
@@ -660,12 +690,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) umma_commit(&acc_full[buf]);     // accumulator complete
+                TC_TRACE(6);
             }
         }
     } else {
         // ---------------- epilogue warps ----------------
         const uint32_t q = warp & 3u;                    // TMEM lane quarter this warp may read
         const uint32_t row_in_tile = q * 32u + lane;
+        const uint32_t col_groups = ((blockDim.x >> 5) - 2u) >> 2;   // warps per lane quarter: 1 or 2
+        const uint32_t col_group = (warp - 2u) >> 2;                 // this warp's share of the 16-column chunks
         const uint32_t out_cols = GATE ? p.H : p.N;      // width of O
         const uint32_t osz = p.partial ? 4u : dtype_size(p.o_dtype);
         uint32_t iter = 0;
@@ -678,10 +711,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t buf = iter % acc_bufs, use = iter / acc_bufs;
             if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
+            if (threadIdx.x == 64u) TC_TRACE(7);
             const uint32_t t_buf = tmem_base + ((q * 32u) << 16) + buf * acc_cols;
             float bias_n = 0.0f, bias_up = 0.0f;
             if (SWAP && !p.partial && p.bias_mode == OPERAND_PER_COLUMN) {
-                const uint32_t n = ta * TILE_ROWS + row_in_tile;
+                const uint32_t n = ta * tile_rows + row_in_tile;
                 if (n < out_cols) {
                     bias_n = load_as_f32(p.bias, p.b_dtype, n);
                     if (GATE) bias_up = load_as_f32(p.bias, p.b_dtype, (size_t)p.H + n);
@@ -689,10 +723,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
             // columns of the accumulator that map to distinct outputs
             const uint32_t ncols = (GATE && !SWAP) ? bn / 2u : bn;
+            // swapped with short weight tiles: lanes past tile_rows belong to the next tile
+            const bool row_live = !SWAP || row_in_tile < tile_rows;
+            const bool warp_live = !SWAP || q * 32u < tile_rows;
             for (uint32_t sub = 0; sub < (wide ? 2u : 1u); ++sub) {
             const uint32_t t_row = t_buf + sub * bn;                         // second accumulator of a wide tile
             const uint32_t row_base = ta * a_rows + sub * TILE_ROWS;
-            for (uint32_t c0 = 0; c0 < ncols; c0 += 16u) {
+            for (uint32_t c0 = col_group * 16u; warp_live && c0 < ncols; c0 += 16u * col_groups) {
                 uint32_t r0[16], r1[16];
                 tmem_ld16(t_row + c0, r0);
                 if (GATE) tmem_ld16(t_row + c0 + (SWAP ? bn : bn / 2u), r1);
@@ -702,7 +739,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 } else if (p.partial) {
                     float* P = p.partial + (size_t)z * p.M * p.N;
                     const uint32_t n = row_base + row_in_tile;
-                    const bool row_ok = GATE ? (n < p.H) : (n < p.N);
+                    const bool row_ok = row_live && (GATE ? (n < p.H) : (n < p.N));
 #pragma unroll
                     for (uint32_t c = 0; c < 16u; ++c) {
                         const uint32_t m = tb * bn + c0 + c;
@@ -713,7 +750,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     }
                 } else {
                     const uint32_t n = row_base + row_in_tile;
-                    if (n < out_cols) {
+                    if (row_live && n < out_cols) {
                         float v[16], u[16];
 #pragma unroll
                         for (int c = 0; c < 16; ++c) { v[c] = __uint_as_float(r0[c]); u[c] = GATE ? __uint_as_float(r1[c]) : 0.0f; }
@@ -725,6 +762,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (threadIdx.x == 64u) TC_TRACE(8);
 
             if (p.partial && p.tile_done) {
                 // Split-K without a second launch: the CTAs that hold the splits of one tile fold it
@@ -778,8 +816,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint32_t lo = z * per, hi = (lo + per < extent) ? lo + per : extent;
                     for (uint32_t sub = 0; sub < (wide ? 2u : 1u); ++sub) {
                         const uint32_t row = ta * a_rows + sub * TILE_ROWS + row_in_tile;   // swapped: output column; else activation row
-                        if (row >= (SWAP ? out_cols : p.M)) continue;
-                        for (uint32_t i = lo; i < hi; i += 4u) {
+                        if (row >= (SWAP ? out_cols : p.M) || !row_live) continue;
+                        for (uint32_t i = lo + 4u * col_group; i < hi; i += 4u * col_groups) {
                             float g[4] = {0.0f, 0.0f, 0.0f, 0.0f}, u[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                             size_t at[4];
 #pragma unroll
@@ -824,7 +862,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tc_fence_after();
         tmem_dealloc(tmem_base, p.tmem_cols);
     }
+    if (threadIdx.x == 0) TC_TRACE(9);
 }
+
+#ifdef VAICU_TC_TRACE
+extern "C" __attribute__((visibility("default"))) int vaicu_debug_tc_trace(unsigned long long* out)
+{
+    return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(g_tc_trace));
+}
+#endif
 
 
 // ---- CTA-pair variant ------------------------------------------------------
@@ -1224,7 +1270,7 @@ static cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, 
     auto kern = tc_gemm_kernel<SWAP, GATE>;
     static SmemOptIn optin;
     if (cudaError_t e = optin.ensure(kern, (int)kTcMaxSmem); e != cudaSuccess) return e;
-    return launch_pdl(kern, dim3((unsigned)grid), dim3(kTcThreads), smem, stream, ma, mb, ma1, ma2, p);
+    return launch_pdl(kern, dim3((unsigned)grid), dim3(SWAP ? kTcThreadsSwap : kTcThreads), smem, stream, ma, mb, ma1, ma2, p);
 }
 
 // Swapped kernel over a group of 2-3 weight tensors that share the activations (p.grp_t1 / p.grp_t2

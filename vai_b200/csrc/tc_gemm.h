@@ -55,6 +55,8 @@ struct TcParams {
     // tile at which the second / third tensor begins (kNoGroup: a single tensor).  N is the sum of the
     // members' rows; a group always leaves raw partial sums for the group's fold.
     uint32_t grp_t1, grp_t2;
+    // Swapped kernel: weight rows per tile (a multiple of 8, at most 128; see plan_tc).
+    uint32_t tile_rows;
     float scale;
 };
 constexpr uint32_t kNoGroup = 0xFFFFFFFFu;

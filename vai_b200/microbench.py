@@ -151,7 +151,8 @@ def run(M, K, N, i_dtype="f32", w_dtype="bf16", o_dtype="f32", epilogue="NONE", 
     return res
 
 
-def run_group(M, K, rows, i_dtype="bf16", w_dtype="bf16", o_dtype="bf16", copies=0, iters=50, warmup=5, device=None, graph=False):
+def run_group(M, K, rows, i_dtype="bf16", w_dtype="bf16", o_dtype="bf16", copies=0, iters=50, warmup=5, device=None, graph=False,
+              tuning=None):
     """2-3 plain Linears over the same activations through vaicu_linear_run_group (q / k / v of a block)."""
     dev = device or Device.default()
     lib = dev.lib
@@ -176,7 +177,8 @@ def run_group(M, K, rows, i_dtype="bf16", w_dtype="bf16", o_dtype="bf16", copies
             d.i_dtype, d.w_dtype, d.o_dtype, d.b_dtype = int(i_dt), int(w_dt), int(o_dt), int(Dtype.NONE)
             d.scalar_scale = 1.0
             h = ctypes.c_void_p()
-            _lib.check(lib.vaicu_linear_plan_create(dev.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
+            t = _lib.LinearTuning(**(tuning or {}))
+            _lib.check(lib.vaicu_linear_plan_create_tuned(dev.handle, ctypes.byref(d), ctypes.byref(t), ctypes.byref(h)), "plan")
             plans.append(h)
             weights.append(wb)
         sets.append(((ctypes.c_void_p * n)(*plans), (ctypes.c_void_p * n)(*[b.ptr for b in weights]), weights))
@@ -255,7 +257,7 @@ def main():
     tuning = {k: int(v) for k, v in (kv.split("=") for kv in a.tune.split(",") if kv)} or None
     if a.group:
         rows = [int(r) for r in a.group.split(",")]
-        print(json.dumps(run_group(a.M, a.K, rows, a.i_dtype, a.w_dtype, a.o_dtype, a.copies, a.iters, a.warmup, graph=a.graph)))
+        print(json.dumps(run_group(a.M, a.K, rows, a.i_dtype, a.w_dtype, a.o_dtype, a.copies, a.iters, a.warmup, graph=a.graph, tuning=tuning)))
         return
     if a.N <= 0:
         ap.error("--N or --group is required")

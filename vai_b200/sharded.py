@@ -173,7 +173,10 @@ class PeerBarrier:
     """Barrier between the ranks' streams without a library collective: one single-warp kernel per
     GPU that signals every peer through flag words in their memory and waits, bounded, for theirs
     (vaicu_peer_barrier_run).  What a rank stored into its peers' buffers before the barrier is
-    visible to them after it.  A few microseconds, where a 4-byte NCCL all-reduce costs tens."""
+    visible to them after it.  A few microseconds, where a 4-byte NCCL all-reduce costs tens.
+    The wait is bounded (about half a second): ranks are expected to enqueue their steps together, as
+    the ranks of a serving job do; a rank that finds no peer within the limit records the device
+    status word (vaicu_device_status -> VAICU_ERR_TIMEOUT) and carries on."""
 
     def __init__(self, device, dist):
         from .engine import DeviceBuffer
@@ -724,13 +727,15 @@ def bench_blocks(device, dist, preset, M, n_blocks, iters=10, warmup=3):
     x0 = torch.randn(M, presets.PRESETS[preset]["d"], generator=gen).to(torch.bfloat16).to(cuda)
     res = {"preset": preset, "M": M, "blocks": n_blocks, "world": world}
     outs = {}
+    # both forms rotate over the same weight sets (the chains must compute the same function): as many as
+    # the form with the fewest bytes per GPU needs to exceed L2 (126 MB) well
+    probe = TensorParallelBlocks(device, dist, preset, M, 1, 1, world > 1)
+    copies = max(2, min(n_blocks, -(-320_000_000 // probe.bytes_per_gpu_block)))
+    probe.close()
+    del probe
     for tp in ((False, True) if world > 1 else (False,)):
-        probe = TensorParallelBlocks(device, dist, preset, M, 1, 1, tp)
-        per_block = probe.bytes_per_gpu_block
-        probe.close()
-        del probe
-        copies = max(2, min(n_blocks, -(-320_000_000 // per_block)))       # the rotating weight sets exceed L2 (126 MB) well
         chain = TensorParallelBlocks(device, dist, preset, M, n_blocks, copies, tp)
+        _host_align(torch, dist)
         out = chain.capture(x0)
         ms = _timed(torch, dist, cuda, chain.graph.replay, iters, warmup)
         torch.cuda.synchronize()
@@ -739,7 +744,7 @@ def bench_blocks(device, dist, preset, M, n_blocks, iters=10, warmup=3):
         res[key + "_us_per_block"] = round(ms * 1e3 / n_blocks, 2)
         res[key + "_launches_per_block"] = chain.launches // n_blocks
         res[key + "_weight_sets"] = copies
-        _lib.check(device.lib.vaicu_device_status(device.handle, ctypes.byref(ctypes.c_int())), "vaicu_device_status")
+        _check_status(device, f"{preset} blocks: a barrier between the ranks gave up waiting")
         chain.close()
         del chain
         torch.cuda.empty_cache()
@@ -763,8 +768,23 @@ def _tiled_weight(torch, rows, k, seed):
     return pool.repeat(reps)[:total].view(rows, k)
 
 
+def _host_align(torch, dist):
+    """Brings the ranks' host threads together.  The barrier kernels between the ranks' streams wait
+    for about half a second at most: a rank must not enqueue one while another rank is still busy on
+    its host (the float64 checks run on rank 0 only)."""
+    if dist is not None:
+        torch.cuda.synchronize()
+        dist.barrier()
+
+
+def _check_status(device, where):
+    """Raises if a kernel on this GPU gave up a bounded wait since the last check."""
+    _lib.check(device.lib.vaicu_device_status(device.handle, ctypes.byref(ctypes.c_int())), where)
+
+
 def _timed(torch, dist, cuda, fn, iters, warmup):
     """Device-timed milliseconds per call of fn, max over ranks."""
+    _host_align(torch, dist)
     for _ in range(warmup):
         fn()
     if dist is not None:
@@ -918,6 +938,7 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5, p
         fused_ms, fused_equal, err_fused = None, None, None
         if dist is not None and world > 1:
             fused = FusedGatherLinear(device, dist, full, lin.w, None)
+            _host_align(torch, dist)
             got = fused.forward(x)
             # the same plan run densely on this rank and gathered by NCCL: must be bit-identical
             stream = torch.cuda.current_stream().cuda_stream
@@ -1031,6 +1052,7 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5, p
                 lin.local_forward(x)
                 return rp.forward(lin.slab)
 
+            _host_align(torch, dist)
             yf = mlp_fused().clone()
             fused_ms = _timed(torch, dist, cuda, mlp_fused, iters, warmup)
             fused_how = (f"reduce-scatter fused into the down GEMM's epilogue ({'bf16' if part == Dtype.BF16 else 'fp32'} partial sums "
@@ -1069,6 +1091,8 @@ def bench_sharded(device, dist, preset="gemma-3-4b", M=64, iters=20, warmup=5, p
         out["layers"]["mlp_column_then_row_parallel"] = e
         down.close()
     lib.vaicu_linear_plan_destroy(lin.plan)
+    torch.cuda.synchronize()
+    _check_status(device, f"{preset} M={M}: a barrier between the ranks gave up waiting")
     return out
 
 
