@@ -215,9 +215,11 @@ typedef struct vaicu_linear_tuning {
     int32_t  gemv_grid;     /* blocks of the weight-streaming kernel; 0                         */
     int32_t  gemv_plain_launch; /* 1: no programmatic dependent launch (plain stream order)     */
     int32_t  tc_fold;           /* split-K of the single-CTA tensor-core kernels: 1 = the CTAs that hold a
-                                   tile's splits fold it together inside the kernel (one launch; measured
-                                   slower on B200 than the dependent fold launch), 2 = a second launch
-                                   folds; 0: the second launch                                  */
+                                   tile's splits fold it together inside the kernel through global memory
+                                   (one launch; measured slower on B200 than the dependent fold launch),
+                                   2 = a second launch folds, 3 = the splits of a tile run as one cluster
+                                   of 2, 4 or 8 CTAs (tc_splits, if given) and fold through distributed
+                                   shared memory (swapped kernel; measured no faster than 2); 0: 2   */
     int32_t  tc_tail_strips;    /* CTA-pair kernel: column strips per tile in the last, partial round of
                                    tiles: 1 = none, 2 or 4; 0: the widest that fits the idle clusters     */
     uint32_t tc_tile_rows;      /* swapped tensor-core kernel: weight rows per tile, a multiple of 8 up to

@@ -144,5 +144,6 @@ def test_layer_norm_feeds_gpt2_fc1(device):
     got = net(Tensor.from_numpy(x)).to_numpy()
     normed = seen(orc.layer_norm_f64(x, scale, shift).astype(np.float32), Dtype.F16)
     want = orc.linear_f64(normed, seen(w, Dtype.F16), seen(b, Dtype.F16), epilogue=orc.EPILOGUES["GELU_TANH"])
-    assert net.lin.info.launches == 1 + (net.lin.info.split_count > 1)     # 16-bit activations: no cast pass (a split-K fold is the only second launch)
+    # 16-bit activations: no cast pass; a split-K fold is the only possible second launch (none when the splits fold inside clusters)
+    assert net.lin.info.launches <= 1 + (net.lin.info.split_count > 1)
     assert_close(got, want, (5e-3, 5e-3), "ln -> fc1")

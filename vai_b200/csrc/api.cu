@@ -341,11 +341,51 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
     const uint32_t a_boxes = ((gate && swap) || t.wide) ? 2u : 1u;
     const uint32_t a_bytes = a_boxes * 128u * 128u;
     const uint32_t stage_bytes = a_bytes + (t.pair ? bn / 2u : bn) * 128u;      // per CTA
-    uint32_t stages = (uint32_t)((kTcMaxSmem - 2048u) / stage_bytes);
-    if (stages > 8u) stages = 8u;
-    if (pl->tune.tc_stages && pl->tune.tc_stages < stages) stages = pl->tune.tc_stages;
-    t.stages = stages;
-    pl->tc_smem = (size_t)stages * stage_bytes + 1024u + 256u;
+    auto size_ring = [&](uint32_t extra) {
+        uint32_t stages = (uint32_t)((kTcMaxSmem - 2048u - extra) / stage_bytes);
+        if (stages > 8u) stages = 8u;
+        if (pl->tune.tc_stages && pl->tune.tc_stages < stages) stages = pl->tune.tc_stages;
+        t.stages = stages;
+        pl->tc_smem = (size_t)stages * stage_bytes + 1024u + 256u + extra;
+    };
+    size_ring(0u);
+    // Split-K folded inside clusters (swapped kernel), on request (tc_fold = 3): the S splits of a tile run as
+    // one cluster and add their accumulators up through distributed shared memory, so neither the fp32
+    // partial sums nor the fold launch exist.  S is 2, 4 or 8 (each CTA finishes bn / S activation rows, a
+    // multiple of 16) and all clusters must be resident at once.  Not the default: measured on B200 the two
+    // cluster barriers and the remote reads take as long as the dependent fold launch they replace (q of a
+    // 4B-class model at batch 64: 8.1 us either way), and the fold launch handles bias / residual with far
+    // more threads (attention output + residual: 12.6 us in clusters, 8.7 us with the fold launch).
+    t.cfold = 0u;
+    if (swap && !gate && t.splits > 1u && !d.split_size && pl->tune.tc_fold == 3) {
+        const uint64_t per_kb = (uint64_t)t.tile_rows * 128u + bn * 128u;      // bytes a CTA loads per k-block
+        uint32_t best = 0u;
+        uint64_t best_cost = ~0ull;
+        for (uint32_t S = 8u; S >= 2u; S /= 2u) {
+            if (bn % S || (bn / S) % 16u) continue;
+            if (pl->tune.tc_splits && pl->tune.tc_splits != S) continue;      // the caller's split count stands
+            const uint32_t kbs = ceil_div(t.kblocks, S);
+            if (kbs < 2u || ceil_div(t.kblocks, kbs) != S) continue;
+            if (t.num_tiles * S > sms) continue;
+            const uint64_t cost = (uint64_t)kbs * per_kb + 32u * 1024u;
+            if (cost < best_cost) { best_cost = cost; best = S; }
+        }
+        if (best) {
+            const uint32_t keep_kb = t.kb_per_split, keep_splits = t.splits;
+            t.cfold = best;
+            t.splits = best;
+            t.kb_per_split = ceil_div(t.kblocks, best);
+            size_ring(bn * 128u * 4u);
+            int clusters = 0;
+            if (t.stages < 2u || tc_swap_max_clusters(pl->tc_smem, best, &clusters) != cudaSuccess || (uint32_t)clusters < t.num_tiles) {
+                cudaGetLastError();
+                t.cfold = 0u;
+                t.splits = keep_splits;
+                t.kb_per_split = keep_kb;
+                size_ring(0u);
+            }
+        }
+    }
     const uint32_t acc_cols = a_boxes * bn;
     t.acc_bufs = 2u * acc_cols <= 512u ? 2u : 1u;
     uint32_t cols = 32u;
@@ -359,7 +399,7 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
     t.scale = d.scalar_scale;
     t.status = pl->dev->status_word;
     const uint32_t work = t.num_tiles * t.splits;
-    pl->tc_grid = (int)(work < sms ? work : sms);
+    pl->tc_grid = (int)((work < sms || t.cfold) ? work : sms);      // cluster fold: one work item per CTA
     if (t.pair) {
         int clusters = 0;
         if (tc_pair_max_clusters(pl->tc_smem, &clusters) != cudaSuccess || clusters <= 0) {
@@ -400,7 +440,7 @@ void plan_tc(vaicu_linear_plan* pl, bool swap)
     pl->tc_swap = swap;
     pl->tc_cast = d.i_dtype == VAICU_DTYPE_F32;
     pl->ws_cast_bytes = pl->tc_cast ? align_up((size_t)d.M * d.K * 2u, 256u) : 0;
-    pl->ws_partial_bytes = t.splits > 1u ? (size_t)t.splits * d.M * d.N * sizeof(float) : 0;
+    pl->ws_partial_bytes = (t.splits > 1u && !t.cfold) ? (size_t)t.splits * d.M * d.N * sizeof(float) : 0;
 }
 
 vaicu_linear_tuning default_tuning()
@@ -422,7 +462,7 @@ int validate_tuning(const vaicu_linear_tuning& t)
     if (k != 0 && k != 1 && k != 2 && k != 4 && k != 8) return VAICU_ERR_INVALID_VALUE;
     if (t.gemv_unroll != 0 && t.gemv_unroll != 2 && t.gemv_unroll != 4) return VAICU_ERR_INVALID_VALUE;
     if (t.gemv_grid < 0) return VAICU_ERR_INVALID_VALUE;
-    if (t.tc_fold < 0 || t.tc_fold > 2) return VAICU_ERR_INVALID_VALUE;
+    if (t.tc_fold < 0 || t.tc_fold > 3) return VAICU_ERR_INVALID_VALUE;
     if (t.tc_stages == 1u || t.tc_stages > 8u) return VAICU_ERR_INVALID_VALUE;
     if (t.tc_tile_rows && (t.tc_tile_rows < 8u || t.tc_tile_rows > 128u || t.tc_tile_rows % 8u)) return VAICU_ERR_INVALID_VALUE;
     if (t.tc_tail_strips != 0 && t.tc_tail_strips != 1 && t.tc_tail_strips != 2 && t.tc_tail_strips != 4) return VAICU_ERR_INVALID_VALUE;
@@ -495,7 +535,7 @@ int build_plan(vaicu_device* dev, const vaicu_linear_desc* desc, const vaicu_lin
                 return cuda_fail(e, "split-K tile counters");
             }
         }
-        pl->launches = 1u + (pl->tc_cast ? 1u : 0u) + ((pl->tcp.splits > 1u && !pl->tile_done) ? 1u : 0u);
+        pl->launches = 1u + (pl->tc_cast ? 1u : 0u) + ((pl->tcp.splits > 1u && !pl->tile_done && !pl->tcp.cfold) ? 1u : 0u);
         break;
     default:
         delete pl;
@@ -1015,7 +1055,7 @@ int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const 
         VAICU_CUDA(launch_cast_f32_to_16(reinterpret_cast<const float*>(I), ws, d.w_dtype, (size_t)d.M * d.K, pl->dev->sm_count, s));
         act = ws;
     }
-    float* partial = pl->tcp.splits > 1u ? reinterpret_cast<float*>(ws + pl->ws_cast_bytes) : nullptr;
+    float* partial = (pl->tcp.splits > 1u && !pl->tcp.cfold) ? reinterpret_cast<float*>(ws + pl->ws_cast_bytes) : nullptr;
     const bool gate = d.gate_fuse != 0;
     const void* a_base = pl->tc_swap ? W : act;
     const void* b_base = pl->tc_swap ? act : W;
@@ -1169,7 +1209,7 @@ int vaicu_linear_group_workspace_bytes(vaicu_linear_plan* const* plans, int coun
     rc = group_state(plans, count, &g);
     if (rc != VAICU_OK) return rc;
     const vaicu_linear_plan* v = g->virt;
-    *out_bytes = v->ws_cast_bytes + align_up((size_t)v->tcp.splits * v->d.M * v->d.N * sizeof(float), 256u);
+    *out_bytes = v->ws_cast_bytes + (v->tcp.cfold ? 0u : align_up((size_t)v->tcp.splits * v->d.M * v->d.N * sizeof(float), 256u));
     return VAICU_OK;
 }
 
@@ -1209,7 +1249,8 @@ int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_str
     const vaicu_linear_desc& d = v->d;
     if (!v->tc_cast && !aligned16(I)) return VAICU_ERR_UNSUPPORTED;
     if (v->tc_cast && (reinterpret_cast<uintptr_t>(I) & 3u)) return VAICU_ERR_ALIGNMENT;
-    if (!workspace) return VAICU_ERR_WORKSPACE;
+    const bool in_cluster = v->tcp.cfold != 0u;       // the K splits fold inside clusters: no partial sums, no fold launch
+    if (!workspace && (v->tc_cast || !in_cluster)) return VAICU_ERR_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(workspace) & 255u) return VAICU_ERR_ALIGNMENT;
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
     const void* act = I;
@@ -1234,12 +1275,13 @@ int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_str
         g->act_base[ib] = act;
     }
     TcParams t = v->tcp;
-    t.O = nullptr; t.bias = nullptr; t.res = nullptr; t.partial = partial; t.tile_done = nullptr;
+    t.O = nullptr; t.bias = nullptr; t.res = nullptr; t.partial = in_cluster ? nullptr : partial; t.tile_done = nullptr;
     t.n_dst = 1u; t.ldo = d.N; t.col0 = 0u;
     t.grp_t1 = rows[0] / 128u;
     t.grp_t2 = count > 2 ? (rows[0] + rows[1]) / 128u : kNoGroup;
+    for (int i = 0; i < count; ++i) t.dst[i] = O[i];
     VAICU_CUDA(launch_tc_gemm_group(g->maps_w, g->map_act[ib], t, v->tc_grid, v->tc_smem, s));
-    VAICU_CUDA(launch_group_fold(partial, t.splits, d.M, (uint32_t)count, rows, O, d.o_dtype, s));
+    if (!in_cluster) VAICU_CUDA(launch_group_fold(partial, t.splits, d.M, (uint32_t)count, rows, O, d.o_dtype, s));
     for (int i = 0; i < count; ++i) { plans[i]->last_kernel = VAICU_KERNEL_TC_SKINNY; plans[i]->last_vectorized = 1; }
     return VAICU_OK;
 }

@@ -220,6 +220,28 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
     return cudaLaunchKernelEx(&lc, kern, std::forward<Args>(args)...);
 }
 
+// The same, as thread-block clusters of `cluster` CTAs along x (the grid is a multiple of it).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster,
+                               Args&&... args)
+{
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = grid;
+    lc.blockDim = block;
+    lc.dynamicSmemBytes = smem;
+    lc.stream = stream;
+    lc.attrs = attr;
+    lc.numAttrs = 2;
+    return cudaLaunchKernelEx(&lc, kern, std::forward<Args>(args)...);
+}
+
 // cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device property of a kernel: a process
 // that drives several GPUs has to opt in on each of them.  One flag per device ordinal and
 // kernel instantiation; the attribute call itself is idempotent, so a race between two threads

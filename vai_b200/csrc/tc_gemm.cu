@@ -491,6 +491,34 @@ __device__ __forceinline__ void store_rows16(const TcParams& p, const uint32_t* 
 
 }  // namespace
 
+// Forms that address another CTA of the cluster.
+namespace {
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of this CTA's shared-memory location `local` inside CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr)
+{
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
+}  // namespace
+
 #ifdef VAICU_TC_TRACE
 // Development aid (not built by default): phase time stamps of every CTA of the single-CTA kernel.
 __device__ unsigned long long g_tc_trace[256 * 16];
@@ -549,6 +577,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fold_out + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     volatile uint32_t* fold_flag = tmem_slot + 2;     // epilogue warps: "this CTA folds the tile's splits"
+    // Split-K folded inside a cluster (p.cfold CTAs = the K splits of one tile): every CTA leaves its raw
+    // accumulator here, [bn columns][128 lanes] fp32, for its cluster mates to read.
+    float* red = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes + 256u);
+    const bool cfold = SWAP && !GATE && p.cfold != 0u;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -736,6 +768,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 tmem_ld_wait();
                 if (!SWAP) {
                     store_rows16<GATE>(p, r0, r1, row_base + row_in_tile, tb, c0, z, out_cols, osz);
+                } else if (cfold) {
+#pragma unroll
+                    for (uint32_t c = 0; c < 16u; ++c) red[(c0 + c) * TILE_ROWS + row_in_tile] = __uint_as_float(r0[c]);
                 } else if (p.partial) {
                     float* P = p.partial + (size_t)z * p.M * p.N;
                     const uint32_t n = row_base + row_in_tile;
@@ -848,6 +883,60 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     }
 
+    if (cfold) {
+        // The CTAs of the cluster hold the K splits of one tile (split z = rank in the cluster; one work
+        // item per CTA).  Every thread of every CTA passes both cluster barriers exactly once, whatever
+        // happened before (all waits above are bounded): first "all accumulators are in shared memory",
+        // then "nobody reads my shared memory any more".  Between them CTA z adds up columns
+        // [z, z + 1) * bn / cfold of all splits, in split order like the fold kernel, and finishes them.
+        __syncwarp();
+        if (threadIdx.x == 64u) TC_TRACE(10);
+        cluster_sync_all();
+        if (threadIdx.x == 64u) TC_TRACE(11);
+        if (warp >= 2 && !*abort_flag) {
+            const uint32_t q = warp & 3u, row_in_tile = q * 32u + lane;
+            const uint32_t col_groups = ((blockDim.x >> 5) - 2u) >> 2, col_group = (warp - 2u) >> 2;
+            const uint32_t tile = blockIdx.x / p.splits, z = blockIdx.x - tile * p.splits;
+            uint32_t ta, tb;
+            tile_coords(p, tile, ta, tb);
+            const uint32_t n = ta * tile_rows + row_in_tile;
+            const uint32_t per = bn / p.cfold;                       // a multiple of 16
+            const bool live = row_in_tile < tile_rows && n < p.N;
+            const uint32_t red_u32 = smem_u32(red);
+            float bias_n = 0.0f;
+            if (live && p.bias_mode == OPERAND_PER_COLUMN) bias_n = load_as_f32(p.bias, p.b_dtype, n);
+            for (uint32_t k = col_group; k < per / 16u && q * 32u < tile_rows; k += col_groups) {
+                const uint32_t c0 = z * per + k * 16u;
+                float v[16], u[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) { v[c] = 0.0f; u[c] = 0.0f; }
+                for (uint32_t r = 0; r < p.cfold; ++r) {
+                    const uint32_t src = map_to_cta(red_u32 + (c0 * TILE_ROWS + row_in_tile) * 4u, r);
+#pragma unroll
+                    for (uint32_t c = 0; c < 16u; ++c) v[c] += ld_cluster_f32(src + c * TILE_ROWS * 4u);
+                }
+                if (!live) continue;
+                const uint32_t m0 = tb * bn + c0;
+                if (p.grp_t1 != kNoGroup) {
+                    // a group: plain sums into the member that owns weight row n
+                    const uint32_t n1 = p.grp_t1 * TILE_ROWS, n2 = p.grp_t2 == kNoGroup ? p.N : p.grp_t2 * TILE_ROWS;
+                    const uint32_t j = n >= n2 ? 2u : (n >= n1 ? 1u : 0u);
+                    const uint32_t first = j == 2u ? n2 : (j == 1u ? n1 : 0u);
+                    const uint32_t width = (j == 0u ? n1 : (j == 1u ? n2 : p.N)) - first;
+#pragma unroll
+                    for (uint32_t c = 0; c < 16u; ++c)
+                        if (m0 + c < p.M) store_from_f32(p.dst[j], p.o_dtype, (size_t)(m0 + c) * width + (n - first), v[c]);
+                } else {
+                    emit_cols16<false>(p, v, u, n, m0, p.N, bias_n, 0.0f);
+                }
+            }
+        }
+        __syncwarp();
+        if (threadIdx.x == 64u) TC_TRACE(12);
+        cluster_sync_all();
+        if (threadIdx.x == 64u) TC_TRACE(13);
+    }
+
     // ---------------- teardown ----------------
     tc_fence_before();
     __syncthreads();
@@ -876,24 +965,6 @@ extern "C" __attribute__((visibility("default"))) int vaicu_debug_tc_trace(unsig
 // ---- CTA-pair variant ------------------------------------------------------
 // PTX wrappers for the forms that address the peer CTA of a 2-CTA cluster.
 namespace {
-__device__ __forceinline__ uint32_t cluster_ctarank()
-{
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// Address of this CTA's shared-memory location `local` inside CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
-{
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all()
-{
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
@@ -1270,7 +1341,29 @@ static cudaError_t launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, 
     auto kern = tc_gemm_kernel<SWAP, GATE>;
     static SmemOptIn optin;
     if (cudaError_t e = optin.ensure(kern, (int)kTcMaxSmem); e != cudaSuccess) return e;
+    if (SWAP && !GATE && p.cfold)
+        return launch_pdl_cluster(kern, dim3((unsigned)grid), dim3(kTcThreadsSwap), smem, stream, p.cfold, ma, mb, ma1, ma2, p);
     return launch_pdl(kern, dim3((unsigned)grid), dim3(SWAP ? kTcThreadsSwap : kTcThreads), smem, stream, ma, mb, ma1, ma2, p);
+}
+
+// Clusters of `cluster` CTAs of the swapped kernel that can be resident at once.
+cudaError_t tc_swap_max_clusters(size_t smem, unsigned cluster, int* clusters)
+{
+    auto kern = tc_gemm_kernel<true, false>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcMaxSmem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cluster, 1, 1);
+    cfg.blockDim = dim3(kTcThreadsSwap, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaOccupancyMaxActiveClusters(clusters, kern, &cfg);
 }
 
 // Swapped kernel over a group of 2-3 weight tensors that share the activations (p.grp_t1 / p.grp_t2

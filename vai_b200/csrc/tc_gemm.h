@@ -57,6 +57,10 @@ struct TcParams {
     uint32_t grp_t1, grp_t2;
     // Swapped kernel: weight rows per tile (a multiple of 8, at most 128; see plan_tc).
     uint32_t tile_rows;
+    // Swapped kernel, split-K folded inside a cluster: cfold = splits = CTAs per cluster, one work item per
+    // CTA, the partial sums cross through distributed shared memory and no workspace or second launch is
+    // needed (0: off).  For a group, dst[0..2] are the members' outputs.
+    uint32_t cfold;
     float scale;
 };
 constexpr uint32_t kNoGroup = 0xFFFFFFFFu;
@@ -108,6 +112,7 @@ __host__ __device__ inline void tile_coords(const TcParams& p, uint32_t tile, ui
 }
 
 cudaError_t tc_pair_max_clusters(size_t smem, int* clusters);
+cudaError_t tc_swap_max_clusters(size_t smem, unsigned cluster, int* clusters);
 // One tiny launch whose bounded mbarrier wait is made to run out; sets *status as the GEMM kernels do.
 cudaError_t launch_wait_expiry_selftest(int* status, cudaStream_t stream);
 // map_b_tail: the weights' map with the strip box of the tail round (CTA-pair kernel with tail_split > 1; else any valid map).

@@ -222,7 +222,11 @@ class LinearNode(Node):
         if first.info.kernel == KERNEL_GEMV:
             launch.kernel_launches = 1
         else:
-            launch.kernel_launches = 2 + (1 if first["in0"].dtype == Dtype.F32 else 0)
+            # GEMM (+ the cast of fp32 activations) (+ the fold, unless the K splits fold inside clusters:
+            # then the group needs no room for partial sums)
+            cast = first["in0"].dtype == Dtype.F32
+            cast_bytes = -(-first["in0"].num_elements() * 2 // 256) * 256 if cast else 0
+            launch.kernel_launches = 1 + int(cast) + int(need.value > cast_bytes)
         return launch
 
     def __del__(self):
