@@ -2,7 +2,10 @@
 vai/shaders/topk-sampling.comp).  The reference ships no test or golden vector for this node,
 so the C restatement of the shader is checked against an independent float64 formulation of
 the same distribution (parity unpinned), and the CUDA node against the restatement, exactly:
-the sample is an index."""
+the sample is an index.  Two anchors to the reference do exist and are checked here: with k = 1 the
+node returns the golden output of the reference's Argmax test, and equal logits rank by index.  The
+vocabulary-split form (candidates per slab with the slab's offset, then merge + sample) must return
+the same token as the node over the whole row."""
 import numpy as np
 import pytest
 

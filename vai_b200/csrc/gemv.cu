@@ -84,6 +84,9 @@ struct GemvParams {
     void* seg_o[3];
     // Argmax folded into the launch (am.out_idx != null): plain Linears only, no gate, no group.
     GemvArgmax am;
+#ifdef VAICU_GEMV_TRACE
+    uint32_t trace_id;   // which launch of the recorded chain this is
+#endif
 };
 
 // Four consecutive activations (chunk-relative kk, kk % 4 == 0) of row m -> fp32 in
@@ -144,6 +147,21 @@ __device__ __forceinline__ void load_x_direct(const LinearArgs& a, uint32_t k, f
 // the R/2 value rows of the same output columns.  Sums are kept as float2 pairs
 // (even / odd elements) and advanced with the packed fp32 FMA of sm_100, which
 // halves the FMA issue count: the kernel must stay memory-bound up to M = 8.
+#ifdef VAICU_GEMV_TRACE
+// Development aid (not built by default): phase time stamps of every block of every launch of a recorded chain.
+__device__ unsigned long long g_gemv_trace[96 * 512 * 6];
+static unsigned g_gemv_trace_next = 0;
+__device__ __forceinline__ void gemv_trace(uint32_t launch, uint32_t slot)
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (launch < 96u && blockIdx.x < 512u) g_gemv_trace[((size_t)launch * 512u + blockIdx.x) * 6u + slot] = t;
+}
+#define GEMV_TRACE(slot) do { if (threadIdx.x == 0) gemv_trace(p.trace_id, slot); } while (0)
+#else
+#define GEMV_TRACE(slot)
+#endif
+
 template <typename TW, int M, int R, int U>
 __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_kernel(const GemvParams p)
 {
@@ -155,6 +173,7 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
     float* red = smem_f + (size_t)M * p.k_pad;        // [kWarps][R*M]
 
     launch_dependents();
+    GEMV_TRACE(0);
 
     const LinearArgs& a = p.a;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -215,7 +234,9 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
                 for (int r = 0; r < R; ++r) wv[u][r] = v ? ldg_stream(rowp[r] + kk) : make_uint4(0, 0, 0, 0);
             }
             preloaded = true;
+            GEMV_TRACE(1);
             dependency_wait();
+            GEMV_TRACE(2);
             if (DIRECT) staged = true;
         }
         float2 acc[R][M];
@@ -291,6 +312,7 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
             }
         }
 
+        if (pb == blockIdx.x) GEMV_TRACE(3);
         // fold the pair and the 32 lanes of each warp
         float sums[R][M];
 #pragma unroll
@@ -351,6 +373,7 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
         }
         if (KS > 1u) __syncthreads();   // red is reused by the next row group
     }
+    GEMV_TRACE(4);
 
     if (with_argmax) {
         // 1. the block's candidate per batch row: lanes r * M + m of the store warps hold results
@@ -458,8 +481,23 @@ cudaError_t launch_one(const GemvParams& p, const GemvConfig& cfg, cudaStream_t 
     lc.stream = stream;
     lc.attrs = attr;
     lc.numAttrs = cfg.plain_launch ? 0 : 1;
+#ifdef VAICU_GEMV_TRACE
+    GemvParams traced = p;
+    traced.trace_id = g_gemv_trace_next++;
+    return cudaLaunchKernelEx(&lc, kern, traced);
+#else
     return cudaLaunchKernelEx(&lc, kern, p);
+#endif
 }
+
+#ifdef VAICU_GEMV_TRACE
+extern "C" __attribute__((visibility("default"))) int vaicu_debug_gemv_trace(unsigned long long* out, unsigned* next, int reset)
+{
+    if (next) *next = g_gemv_trace_next;
+    if (reset) { g_gemv_trace_next = 0; return 0; }
+    return (int)cudaMemcpyFromSymbol(out, g_gemv_trace, sizeof(g_gemv_trace));
+}
+#endif
 
 template <typename TW>
 cudaError_t launch_typed(const GemvParams& p, const GemvConfig& cfg, cudaStream_t stream)

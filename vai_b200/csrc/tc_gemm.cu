@@ -359,12 +359,21 @@ __device__ __forceinline__ void finish_col16(const TcParams& p, float* v, float*
             v[c] += load_as_f32(p.bias, p.b_dtype, p.bias_mode == OPERAND_MODULO ? i % p.bias_elems : i);
         }
     }
-    if (p.res_mode != OPERAND_NONE) {
+    if (p.res_mode == OPERAND_FULL) {
+        // the common case: one residual per output, 16 independent loads down this thread's column
+#pragma unroll
         for (uint32_t c = 0; c < 16u; ++c) {
             const uint32_t m = m0 + c < p.M ? m0 + c : p.M - 1u;
-            const size_t flat = (size_t)m * out_cols + n;
-            t[c] = load_as_f32(p.res, p.o_dtype,
-                               p.res_mode == OPERAND_FULL ? flat : (p.res_mode == OPERAND_PER_COLUMN ? n : flat % p.res_elems));
+            t[c] = load_as_f32(p.res, p.o_dtype, (size_t)m * out_cols + n);
+        }
+    } else if (p.res_mode == OPERAND_PER_COLUMN) {
+        const float r = load_as_f32(p.res, p.o_dtype, n);
+#pragma unroll
+        for (uint32_t c = 0; c < 16u; ++c) t[c] = r;
+    } else if (p.res_mode != OPERAND_NONE) {
+        for (uint32_t c = 0; c < 16u; ++c) {
+            const uint32_t m = m0 + c < p.M ? m0 + c : p.M - 1u;
+            t[c] = load_as_f32(p.res, p.o_dtype, ((size_t)m * out_cols + n) % p.res_elems);
         }
     }
     const bool before = p.res_mode != OPERAND_NONE && p.residual_order == VAICU_RESIDUAL_BEFORE_EPILOGUE;
