@@ -108,6 +108,14 @@ __device__ __forceinline__ float finish_output(const EpilogueArgs& e, float acc,
                                                               : e.scale * apply_epilogue(e.epilogue, a) + r;
 }
 
+// The same with the bias and residual values already in registers (read ahead of the dot product).
+__device__ __forceinline__ float finish_output_pre(const EpilogueArgs& e, float acc, float bias, float res)
+{
+    const float a = acc + bias;
+    return e.residual_order == VAICU_RESIDUAL_BEFORE_EPILOGUE ? e.scale * apply_epilogue(e.epilogue, a + res)
+                                                              : e.scale * apply_epilogue(e.epilogue, a) + res;
+}
+
 // Fused Linear + GatedMul (vAi vai/nodes/gated-mul.h:9-20): gate and value
 // accumulators of output column j; bias holds 2H entries, gate half first.
 // `flat` indexes O [M, H]; bias index is the weight row.

@@ -163,7 +163,7 @@ __device__ __forceinline__ void gemv_trace(uint32_t launch, uint32_t slot)
 #endif
 
 template <typename TW, int M, int R, int U>
-__global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_kernel(const GemvParams p)
+__global__ void __launch_bounds__(kThreads, (M == 1 && R * U <= 8) ? 3 : 2) gemv_kernel(const GemvParams p)
 {
     constexpr int VEC = WTraits<TW>::VEC;
     constexpr int PAIRS = VEC / 2;
@@ -196,10 +196,10 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
     float am_best = kArgmaxLowest;          // this lane's best output so far (its batch row m = lane % M)
     uint32_t am_at = 0xFFFFFFFFu;
 
-    for (uint32_t pb = blockIdx.x; pb < nblocks; pb += gridDim.x) {
-        const uint32_t g = pb * RG + rg;              // may be >= ngroups: rows clamp, stores skip
-        const uint32_t j0 = g * C;
-        const TW* rowp[R];
+    // Row pointers of the R rows this warp takes in block-task pb.
+    const TW* rowp[R];
+    auto set_rows = [&](uint32_t pb) {
+        const uint32_t j0 = (pb * RG + rg) * C;       // may be past the last group: rows clamp, stores skip
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             uint32_t row;
@@ -214,10 +214,27 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
                 rowp[r] = Wp + (size_t)row * K;
             }
         }
+    };
+    // The first trip of a task's weights (first activation chunk) into registers.
+    const uint32_t first_span = p.k_chunk < K ? p.k_chunk : K;
+    auto preload = [&]() {
+        const uint32_t iters0 = (first_span + stride - 1u) / stride;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const uint32_t kk = kk0 + (uint32_t)u * stride;
+            const bool v = ((uint32_t)u < iters0) && (kk < first_span);
+#pragma unroll
+            for (int r = 0; r < R; ++r) wv[u][r] = v ? ldg_stream(rowp[r] + kk) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    if (blockIdx.x < nblocks) set_rows(blockIdx.x);
+
+    for (uint32_t pb = blockIdx.x; pb < nblocks; pb += gridDim.x) {
+        const uint32_t g = pb * RG + rg;              // may be >= ngroups: rows clamp, stores skip
+        const uint32_t j0 = g * C;
         if (!staged) {
             // The weights do not depend on the previous kernel: pull this warp's first
             // vectors toward L2 while that kernel drains, then wait for its results.
-            const uint32_t first_span = p.k_chunk < K ? p.k_chunk : K;
 #pragma unroll
             for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -225,19 +242,23 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
                     if (kk0 + it * stride < first_span) prefetch_l2(rowp[r] + kk0 + it * stride);
             // ... and this warp's first trip goes all the way into registers: its loads are
             // in flight while the wait below and the activation staging run
-            const uint32_t iters0 = (first_span + stride - 1u) / stride;
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const uint32_t kk = kk0 + (uint32_t)u * stride;
-                const bool v = ((uint32_t)u < iters0) && (kk < first_span);
-#pragma unroll
-                for (int r = 0; r < R; ++r) wv[u][r] = v ? ldg_stream(rowp[r] + kk) : make_uint4(0, 0, 0, 0);
-            }
+            preload();
             preloaded = true;
             GEMV_TRACE(1);
             dependency_wait();
             GEMV_TRACE(2);
             if (DIRECT) staged = true;
+        }
+        // Bias and residual of the output this lane will store, requested ahead of the dot product
+        // (the residual may come from the launch ahead: after the wait above).
+        float early_bias = 0.0f, early_res = 0.0f;
+        if (!gate && !p.nseg && ks == 0u && g < ngroups && lane < (uint32_t)(R * M)) {
+            const uint32_t n = j0 + lane / M;
+            if (n < a.N) {
+                const size_t flat = (size_t)(lane % M) * a.N + n;
+                early_bias = read_bias(ep, flat);
+                early_res = read_res(ep, flat);
+            }
         }
         float2 acc[R][M];
 #pragma unroll
@@ -313,6 +334,13 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
         }
 
         if (pb == blockIdx.x) GEMV_TRACE(3);
+        // The next task's first trip is requested now, so that it is in flight while this task's sums
+        // are folded and stored (the registers of this task's last trip are free).
+        if (pb + gridDim.x < nblocks) {
+            set_rows(pb + gridDim.x);
+            preload();
+            preloaded = true;
+        }
         // fold the pair and the 32 lanes of each warp
         float sums[R][M];
 #pragma unroll
@@ -351,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, (M == 1 && U == 2) ? 3 : 2) gemv_ker
                             store_from_f32(p.seg_o[sg], a.o_dtype, (size_t)m * width + (n - p.seg_begin[sg]), mine);
                         } else {
                             const size_t flat = (size_t)m * a.N + n;
-                            const float v = finish_output(ep, mine, flat);
+                            const float v = finish_output_pre(ep, mine, early_bias, early_res);
                             if (!with_argmax || p.am.write_logits) store_from_f32(a.O, a.o_dtype, flat, v);
                             // the Argmax node reads the stored logits: compare what the store would hold
                             if (with_argmax) argmax_take(round_through(a.o_dtype, v), p.am.index_base + n, am_best, am_at);
