@@ -256,6 +256,47 @@ def test_256_row_tiles(M, K, N, gate, mode, bn, device):
     assert_close(got, want, (2e-4, 5e-5), f"{mode} {M}x{K}x{N} gate={gate} bn={bn}")
 
 
+@pytest.mark.parametrize("w_dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("tuning", [dict(gemv_unroll=2), dict(gemv_unroll=4), dict(gemv_unroll=4, gemv_rows=2),
+                                    dict(gemv_unroll=4, gemv_k_warps=4), dict(gemv_unroll=2, gemv_k_warps=8, gemv_grid=5),
+                                    dict(gemv_unroll=4, gemv_grid=3)])
+@pytest.mark.parametrize("variant", ["bias_res", "gate"])
+def test_weight_streaming_geometries_at_batch_1(w_dtype, tuning, variant, device):
+    """Both depths of the batch-1 weight-streaming kernel (two or four k-steps of weight vectors in flight
+    per lane), with K splits over the warps and grids small enough that every block takes several tasks
+    (the next task's first trip is then requested before the current task's sums are folded): ragged N and
+    a K that leaves partial trips, bias + residual read ahead of the dot product, or the fused gate."""
+    rng = np.random.default_rng(7 + len(w_dtype))
+    K, N = 1096, 203
+    gate = variant == "gate"
+    rows = 2 * N if gate else N
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    w = (rng.standard_normal((rows, K)) / np.sqrt(K)).astype(np.float32)
+    b = rng.standard_normal(rows).astype(np.float32)
+    r = None if gate else rng.standard_normal((1, N)).astype(np.float32)
+    got, want, node = run_linear(x, w, b, r, w_dtype=w_dtype, epilogue="SILU", gate_fuse=gate, residual_order="BEFORE_EPILOGUE" if not gate else "AFTER_EPILOGUE",
+                                 scalar_scale=1.0 if gate else 0.5, kernel=nodes.KERNEL_GEMV, tuning=tuning)
+    assert node.info.kernel == nodes.KERNEL_GEMV
+    assert_close(got, want, (1e-5, 1e-5) if w_dtype == "f32" else (2e-4, 5e-5), f"{variant} {w_dtype} {tuning}")
+
+
+def test_large_batch_1_layers_take_the_deeper_form(device):
+    """A 32 MB layer at batch 1 is planned with four k-steps in flight (the planner's threshold is what the
+    resident blocks request in one trip); the result is the same as with two, bit for bit, when K is split
+    over the warps the same way."""
+    rng = np.random.default_rng(3)
+    K, N = 8192, 2048
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    r = rng.standard_normal((1, N)).astype(np.float32)
+    auto, want, node = run_linear(x, w, None, r, w_dtype="bf16")
+    assert node.info.kernel == nodes.KERNEL_GEMV
+    assert_close(auto, want, (2e-4, 5e-5), "auto")
+    four, _, _ = run_linear(x, w, None, r, w_dtype="bf16", tuning=dict(gemv_unroll=4, gemv_k_warps=4))
+    two, _, _ = run_linear(x, w, None, r, w_dtype="bf16", tuning=dict(gemv_unroll=2, gemv_k_warps=4))
+    np.testing.assert_array_equal(four, two)
+
+
 @pytest.mark.parametrize("M", [9, 64, 100])
 @pytest.mark.parametrize("rows,N,gate,splits", [(72, 1000, False, 0), (40, 520, True, 0), (8, 136, False, 0), (120, 777, True, 0),
                                                 (56, 600, False, 3), (96, 264, True, 2)])

@@ -567,8 +567,15 @@ GemvConfig choose_gemv(const LinearArgs& a, int sm_count, bool ptrs_aligned16, c
     // tasks in flight together (no ragged second round), and at least half the
     // resident slots used; so few rows get a smaller R and a deeper K split, while
     // every warp keeps two 16-byte steps.
-    // M = 1 comes in two depths: U = 2 k-steps in flight at 3 blocks per SM, or U = 4 at 2
-    c.unroll = (a.M == 1u && tuning && tuning->gemv_unroll == 4) ? 4 : 2;
+    // M = 1 comes in two depths: U = 2 k-steps in flight at 3 blocks per SM (96 KB per SM), or U = 4 at
+    // 2 blocks per SM (128 KB per SM).  A layer whose weights the resident blocks request in one trip at
+    // U = 2 (14.5 MB on 148 SMs) gains nothing from the deeper form and loses resident slots to it; a larger
+    // layer is bound by the bytes in flight (measured in the recorded Llama-3.2-1B step: gate|value and down
+    // at U = 4 take 9 us off 529, the lm_head is unchanged, o at U = 4 adds 11 us).
+    const uint64_t one_trip = (uint64_t)sm_count * 3u * (uint64_t)kThreads * 2u * 4u * 16u;
+    const uint64_t weight_bytes = (uint64_t)a.N * a.K * (a.w_dtype == VAICU_DTYPE_F32 ? 4u : 2u);
+    c.unroll = (a.M == 1u && weight_bytes > one_trip) ? 4 : 2;
+    if (a.M == 1u && tuning && (tuning->gemv_unroll == 2 || tuning->gemv_unroll == 4)) c.unroll = tuning->gemv_unroll;
     const uint32_t capacity = (uint32_t)sm_count * ((a.M == 1u && c.unroll == 2) ? 3u : 2u);
     // Measured: a deeper K split than needed is costly (lm_head 76 -> 108 us with ks = 2:
     // every pass then ends in a block-wide fold), so K is split only until about half
