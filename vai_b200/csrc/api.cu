@@ -1178,7 +1178,8 @@ int group_state(vaicu_linear_plan* const* plans, int count, GroupState** out)
     vaicu_linear_plan* p0 = plans[0];
     GroupState* g = p0->group;
     bool same = g && g->count == count;
-    for (int i = 0; same && i < count; ++i) same = g->members[i] == plans[i];
+    // the same plans as last time, and still of the same sizes (a destroyed member's address may be reused)
+    for (int i = 0; same && i < count; ++i) same = g->members[i] == plans[i] && g->rows[i] == plans[i]->d.N;
     if (!same) {
         if (g) { vaicu_linear_plan_destroy(g->virt); delete g; p0->group = nullptr; }
         g = new (std::nothrow) GroupState();
