@@ -522,6 +522,7 @@ class NeuralNet:
         self._pinned_ptrs = []
         self._pin_sink = self._pinned_ptrs
         self._input_names = self._input_order = None
+        self._gate_nodes = None
         self.h2d_bytes = self.d2h_bytes = 0
         NeuralNet._tls.net = self
 
@@ -831,9 +832,11 @@ class NeuralNet:
         # a recording is made for the inputs that came (and the gates as they stand): nodes
         # that need an input left out are not part of it
         key = tuple([(k, fed[k].shape, fed[k].dtype) for k in names if k in fed])
-        gates = tuple(n.is_open() for n in self._nodes if isinstance(n, GateNode))
-        if gates:
-            key += (("gates",) + gates,)
+        # the gate nodes are looked up once per node count, not on every call (a step is a few hundred microseconds)
+        if self._gate_nodes is None or self._gate_nodes[0] != len(self._nodes):
+            self._gate_nodes = (len(self._nodes), [n for n in self._nodes if isinstance(n, GateNode)])
+        if self._gate_nodes[1]:
+            key += (("gates",) + tuple(n.is_open() for n in self._gate_nodes[1]),)
         if self._dirty:           # a parameter or a wire changed: every recording is stale
             self._drop_recordings()
             self._dirty = False
