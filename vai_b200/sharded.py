@@ -568,6 +568,180 @@ class ShardedTopKHead:
             self.plan = None
 
 
+def _node_base():
+    from .engine import Node
+    return Node
+
+
+class RowParallelLinearNode(_node_base()):
+    """The down projection of a tensor-parallel MLP as a node of the engine, so that a whole block
+    records into one CUDA graph per rank like any other chain of nodes.
+
+    Slots: in0 = this rank's K slice of the activations [.., K / world] (what its column-split
+    gate|value Linear + GatedMul produced), weight = its [N, K / world] slice, residual (optional) = the
+    full [.., N] residual, out0 = the full [.., N] result on EVERY rank.  The formula is the Linear's
+    with no bias or epilogue: out0 = s * (in0 . W^T summed over the ranks) + residual.
+
+    run() enqueues, all on the net's stream and all kernels of this package: the GEMM whose epilogue
+    stores every finished tile of partial sums (fp32) into the staging buffer of the GPU that owns those
+    rows; a barrier kernel; the fold of this GPU's rows, which stores the finished rows into every GPU's
+    out0; a second barrier kernel.  out0 and the staging buffer are allocated by the node (they are
+    shared with the other ranks through CUDA IPC), not by the net's pool.  The ranks must record and
+    run their nets in step, as the ranks of one job do.  M (the product of in0's leading axes) must be
+    a multiple of the number of ranks and larger than 8 (the tensor-core kernels), weights 16-bit."""
+
+    def __init__(self, in_dim, out_dim, dist, accept_residual=False, scalar_scale=1.0):
+        from .engine import INPUT, OUTPUT, PERSISTENT, TEMPORARY
+        super().__init__()
+        self.in_dim, self.out_dim, self.dist = in_dim, out_dim, dist
+        self.accept_residual, self.scalar_scale = accept_residual, float(scalar_scale)
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.add_slot("in0", INPUT)
+        self.add_slot("out0", OUTPUT)
+        self.add_slot("weight", PERSISTENT)
+        self.add_slot("partial", TEMPORARY)
+        if accept_residual:
+            self.add_slot("residual", INPUT)
+        self._plans = {}
+        self._shared = {}
+        self._plan = self.info = None
+
+    def _device(self):
+        from .engine import Device
+        return self.net.device if self.net is not None else Device.default()
+
+    def prepare(self):
+        from .engine import Dtype, Tensor
+        x, w = self["in0"], self["weight"]
+        if x.shape[-1] != self.in_dim or tuple(w.shape) != (self.out_dim, self.in_dim):
+            raise ValueError("in0 / weight do not match this rank's K slice")
+        if w.dtype not in (Dtype.F16, Dtype.BF16) or x.dtype != w.dtype:
+            raise ValueError("the row-parallel node takes 16-bit weights and activations of the same type")
+        o_dtype = self.o_dtype if self.o_dtype != Dtype.NONE else (self.net.o_default_dtype if self.net else Dtype.F32)
+        M = 1
+        for s_ in x.shape[:-1]:
+            M *= s_
+        if M % self.world or M <= 8:
+            raise ValueError("M must be a multiple of the number of ranks and larger than 8")
+        dev = self._device()
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = M, self.out_dim, self.in_dim
+        d.i_dtype = d.w_dtype = int(w.dtype)
+        d.o_dtype, d.b_dtype = int(Dtype.F32), int(Dtype.NONE)      # fp32 partial sums cross the link
+        d.scalar_scale = 1.0
+        d.split_size = max(32, self.in_dim)                         # one K span: the partials leave through the epilogue
+        key = bytes(d)
+        if key not in self._plans:
+            h = ctypes.c_void_p()
+            _lib.check(dev.lib.vaicu_linear_plan_create(dev.handle, ctypes.byref(d), ctypes.byref(h)), "vaicu_linear_plan_create")
+            info = _lib.LinearInfo()
+            _lib.check(dev.lib.vaicu_linear_plan_info(h, ctypes.byref(info)), "vaicu_linear_plan_info")
+            self._plans[key] = (h, info)
+        self._plan, self.info = self._plans[key]
+        skey = (M, int(o_dtype))
+        if skey not in self._shared:
+            rows = M // self.world
+            osz = 4 if o_dtype == Dtype.F32 else 2
+            staging, st_ptrs, opened1 = share_buffer(dev, self.dist, self.world * rows * self.out_dim * 4)
+            out, out_ptrs, opened2 = share_buffer(dev, self.dist, M * self.out_dim * osz)
+            order = destination_order(self.rank, self.world)
+            self._shared[skey] = dict(rows=rows, staging=staging, out=out, opened=opened1 + opened2,
+                                      staging_ptrs=(ctypes.c_void_p * self.world)(*st_ptrs),
+                                      out_ptrs=(ctypes.c_void_p * self.world)(*[out_ptrs[r] for r in order]),
+                                      barrier=PeerBarrier(dev, self.dist))
+        self._live = self._shared[skey]
+        ws = self.info.workspace_bytes
+        self.slots["partial"] = Tensor((ws // 4,), Dtype.F32) if ws else Tensor()
+        out_t = Tensor(tuple(x.shape[:-1]) + (self.out_dim,), o_dtype)
+        out_t.buffer = self._live["out"]            # bound here: the net's pool leaves it alone
+        self.slots["out0"] = out_t
+        if self.accept_residual and self["residual"].dtype != o_dtype:
+            raise ValueError("residual dtype must equal the output dtype")
+
+    def bind(self):
+        dev, lib = self._device(), self._device().lib
+        sh = self._live
+        x, w = self["in0"].ptr, self["weight"].ptr
+        r = self["residual"].ptr if self.accept_residual else None
+        ws = self["partial"].ptr if self["partial"].valid_shape() else None
+        plan, world, rank, N, scale = self._plan, self.world, self.rank, self.out_dim, self.scalar_scale
+        o_dtype = int(self["out0"].dtype)
+        barrier = sh["barrier"]
+
+        def launch(stream):
+            _lib.check(lib.vaicu_linear_run_reduce_scatter(plan, stream, x, w, sh["staging_ptrs"], world, rank, ws),
+                       "vaicu_linear_run_reduce_scatter")
+            barrier.run(stream)
+            _lib.check(lib.vaicu_partial_fold_run(dev.handle, stream, sh["staging"].ptr, world, sh["rows"], N, 0, r, scale,
+                                                  o_dtype, sh["out_ptrs"], world, rank * sh["rows"]), "vaicu_partial_fold_run")
+            barrier.run(stream)
+
+        launch.kernel_launches = int(self.info.launches) + 3
+        return launch
+
+    def close(self):
+        lib = self._device().lib
+        for sh in self._shared.values():
+            sh["barrier"].close()
+            for p in sh["opened"]:
+                lib.vaicu_ipc_close(p)
+        self._shared = {}
+        for h, _ in self._plans.values():
+            lib.vaicu_linear_plan_destroy(h)
+        self._plans = {}
+
+
+def tensor_parallel_mlp_check(device, dist, M=64, d=512, ffn=1024, blocks=2, seed=0):
+    """Builds `blocks` gated MLPs (gate|value column split as a plain LinearNode over this rank's weight
+    rows -> GatedMulNode -> RowParallelLinearNode + residual) as ONE net per rank, runs it twice (the second
+    call replays the recorded graph) and compares with float64 on rank 0's host.  Returns the worst error
+    relative to max(|want|, 1) and the number of launches recorded."""
+    import vai_b200
+    from .engine import Dtype, Epilogue, Tensor
+    from .nodes import GatedMulNode, LinearNode
+    rank, world = dist.get_rank(), dist.get_world_size()
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((M, d)).astype(np.float32)
+    x = np.asarray(vai_b200.engine.bits_to_f32(vai_b200.engine.encode(x, Dtype.BF16), Dtype.BF16))     # bf16-exact input
+    net = vai_b200.NeuralNet(w_default_dtype=Dtype.BF16, o_default_dtype=Dtype.BF16, device=device)
+    begin, count = shard_rows(ffn, world, rank)
+    flow = x0 = net.input("x")
+    weights, nodes_rp = [], []
+    for _ in range(blocks):
+        wg = (rng.standard_normal((2 * ffn, d)) / np.sqrt(d)).astype(np.float32)
+        wd = (rng.standard_normal((d, ffn)) / np.sqrt(ffn)).astype(np.float32)
+        weights.append((wg, wd))
+        gate_up = LinearNode(in_dim=d, out_dim=2 * count)
+        gate_up["weight"] = Tensor.from_numpy(slice_weight(wg, rank, world, True), dtype=Dtype.BF16)
+        down = RowParallelLinearNode(count, d, dist, accept_residual=True, scalar_scale=0.25)
+        down["weight"] = Tensor.from_numpy(np.ascontiguousarray(wd[:, begin:begin + count]), dtype=Dtype.BF16)
+        flow - gate_up - GatedMulNode(activation=Epilogue.SILU) - down
+        x0 - "residual" / down
+        flow = vai_b200.engine.Flow(down)
+        nodes_rp.append(down)
+    flow - net.output("y")
+    got = net(Tensor.from_numpy(x, dtype=Dtype.BF16)).to_numpy()
+    again = net(Tensor.from_numpy(x, dtype=Dtype.BF16)).to_numpy()
+    rec = next(iter(net._recordings.values()))
+    device.check_status()
+    if not np.array_equal(got, again):
+        raise RuntimeError("the replayed tensor-parallel net differs from its first run")
+
+    def r16(a):
+        return np.asarray(vai_b200.engine.bits_to_f32(vai_b200.engine.encode(a.astype(np.float32), Dtype.BF16), Dtype.BF16), dtype=np.float64)
+
+    cur = x.astype(np.float64)
+    for wg, wd in weights:
+        acc = cur @ r16(wg).T
+        g, u = acc[:, :ffn], acc[:, ffn:]
+        hid = r16(g / (1.0 + np.exp(-g)) * u)
+        cur = r16(0.25 * (hid @ r16(wd).T) + x)
+    err = float(np.max(np.abs(got - cur) / np.maximum(np.abs(cur), 1.0)))
+    for n in nodes_rp:
+        n.close()
+    return err, rec.kernel_launches
+
+
 class _LocalLinear:
     """One plan with its workspace, run on torch tensors on the current torch stream."""
 
@@ -1143,6 +1317,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--preset", default="gemma-3-4b")
     ap.add_argument("--M", type=int, default=64)
+    ap.add_argument("--nodes-check", action="store_true",
+                    help="run the tensor-parallel MLP built from engine nodes (RowParallelLinearNode) against float64 instead")
     a = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -1152,6 +1328,15 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         d = dist
+    if a.nodes_check:
+        if d is None:           # one rank: a process group of one, so that the same code path runs
+            dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29549", rank=0, world_size=1)
+            d = dist
+        err, launches = tensor_parallel_mlp_check(Device(local), d, M=a.M)
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"tp_nodes": {"world": world, "max_rel_err_vs_float64": err, "launches_recorded": launches}}))
+        dist.destroy_process_group()
+        return
     res = bench_sharded(Device(local), d, a.preset, a.M)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(res))
