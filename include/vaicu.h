@@ -303,6 +303,17 @@ VAICU_API int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count,
 VAICU_API int vaicu_linear_run_scatter(vaicu_linear_plan* plan, vaicu_stream_t stream, const void* I, const void* W,
                                        const void* bias, void* const* dsts, int n_dst, uint32_t ldo, uint32_t col0,
                                        void* workspace);
+/* A Linear whose whole (dense) output is written to n_dst buffers at once (1..8): this GPU's and, through
+ * vaicu_ipc_open, its peers'.  With dsts[i] = the address of this rank's row block inside rank i's
+ * [M_total, N] tensor, ranks that each run the Linear on their own rows of the activations assemble the
+ * full result everywhere inside their GEMM epilogues (an all-gather along rows, as a sequence-parallel
+ * block needs in front of its column-split MLP).  Bias, epilogue, residual and scale as in
+ * vaicu_linear_run (they index the plan's own [M, N]).  Tensor-core plans without split-K only;
+ * destinations 16-byte aligned; the ranks synchronise (vaicu_peer_barrier_run) before anyone reads.
+ * No counterpart in the single-device reference. */
+VAICU_API int vaicu_linear_run_broadcast(vaicu_linear_plan* plan, vaicu_stream_t stream, const void* I, const void* W,
+                                         const void* bias, const void* residual, void* const* dsts, int n_dst,
+                                         void* workspace);
 /* Row-parallel Linear (this GPU holds a slice of K: columns [k0, k1) of W and of the activations) whose
  * partial sums go straight to the GPUs that will fold them: row m of the plan's [M, N] output belongs to
  * GPU m / (M / n_dst), and the epilogue stores it, tile by tile with plain stores over NVLink, into that

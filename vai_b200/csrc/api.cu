@@ -1019,6 +1019,25 @@ int vaicu_linear_run_scatter(vaicu_linear_plan* pl, vaicu_stream_t stream, const
     return run_impl(pl, stream, I, W, bias, nullptr, dsts[0], workspace, &spec);
 }
 
+int vaicu_linear_run_broadcast(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W, const void* bias,
+                               const void* residual, void* const* dsts, int n_dst, void* workspace)
+{
+    if (!pl || !dsts || n_dst < 1 || n_dst > 8) return VAICU_ERR_INVALID_VALUE;
+    const vaicu_linear_desc& d = pl->d;
+    // the tensor-core kernels' epilogues store to several destinations; a split-K fold does not
+    if (!pl->tc || pl->tcp.splits > 1u) return VAICU_ERR_UNSUPPORTED;
+    OutputSpec spec{};
+    spec.n_dst = (uint32_t)n_dst;
+    spec.ldo = d.gate_fuse ? d.N / 2u : d.N;      // dense destinations: bias and residual index them like O
+    spec.col0 = 0;
+    for (int i = 0; i < n_dst; ++i) {
+        if (!dsts[i]) return VAICU_ERR_INVALID_VALUE;
+        if (reinterpret_cast<uintptr_t>(dsts[i]) & 15u) return VAICU_ERR_ALIGNMENT;
+        spec.dst[i] = dsts[i];
+    }
+    return run_impl(pl, stream, I, W, bias, residual, dsts[0], workspace, &spec);
+}
+
 namespace {
 int run_impl(vaicu_linear_plan* pl, vaicu_stream_t stream, const void* I, const void* W, const void* bias,
              const void* residual, void* O, void* workspace, const OutputSpec* spec)

@@ -745,13 +745,14 @@ def tensor_parallel_mlp_check(device, dist, M=64, d=512, ffn=1024, blocks=2, see
 class _LocalLinear:
     """One plan with its workspace, run on torch tensors on the current torch stream."""
 
-    def __init__(self, device, M, N, K, gate=False, epilogue=0, residual=False, scale=1.0):
+    def __init__(self, device, M, N, K, gate=False, epilogue=0, residual=False, scale=1.0, split_size=0):
         import torch
 
         from .engine import Dtype
         self.dev = device
         d = _lib.LinearDesc()
         d.M, d.N, d.K = M, N, K
+        d.split_size = split_size
         d.i_dtype = d.w_dtype = d.o_dtype = int(Dtype.BF16)
         d.b_dtype = int(Dtype.NONE)
         d.has_residual = 1 if residual else 0
@@ -784,9 +785,17 @@ class TensorParallelBlocks:
     gate|value split by columns, `down` split along K with the reduce-scatter in its epilogue and the
     all-gather in its fold (FusedRowParallelLinear) - every launch is one of this package's kernels, so
     the whole chain is captured into ONE CUDA graph per rank and replayed.  Blocks rotate over `copies`
-    weight sets (seeded; the two forms draw the same values) so that weights come from HBM, not L2."""
+    weight sets (seeded; the two forms draw the same values) so that weights come from HBM, not L2.
 
-    def __init__(self, device, dist, preset, M, n_blocks, copies, tp):
+    seq=True (with tp, M / world > 128) is the sequence-parallel form of the same block: every rank runs
+    q / k / v / o on its own M / world rows only; the epilogue of its o GEMM stores those rows of the
+    hidden state into every rank's [M, d] buffer (vaicu_linear_run_broadcast: the all-gather along rows
+    rides in the GEMM); gate|value runs on all rows over this rank's columns; down's reduce-scatter
+    delivers the partial sums of a rank's rows to that rank, whose fold writes only its own rows.  The
+    exchange moves the same bytes as the tensor-parallel form, but the four "replicated" layers now scale
+    with the number of GPUs.  step() then takes and returns this rank's rows."""
+
+    def __init__(self, device, dist, preset, M, n_blocks, copies, tp, seq=False):
         import torch
 
         from . import presets
@@ -796,6 +805,12 @@ class TensorParallelBlocks:
         self.tp = bool(tp) and dist is not None and dist.get_world_size() > 1
         world = dist.get_world_size() if self.tp else 1
         rank = dist.get_rank() if self.tp else 0
+        self.seq = bool(seq) and self.tp
+        self.rank, self.world = rank, world
+        if self.seq and (M % world or M // world <= 128):
+            raise ValueError("the sequence-parallel form needs more than 128 rows per rank")
+        rows = M // world if self.seq else M        # rows of the activations that q / k / v / o see on this rank
+        self.rows = rows
         d, q, kv, ffn = p["d"], p["q"], p["kv"], p["ffn"]
         act = int(getattr(Epilogue, p["act"]))
         cuda = torch.device("cuda", device.ordinal)
@@ -803,8 +818,8 @@ class TensorParallelBlocks:
         kb, kc = shard_k(ffn, world, rank)
         if (kb, kc) != (begin, count):
             raise ValueError("hidden columns and K slices of the ranks do not line up")
-        self.Lq, self.Lk, self.Lv = (_LocalLinear(device, M, n, d) for n in (q, kv, kv))
-        self.Lo = _LocalLinear(device, M, d, q, residual=True, scale=0.5)
+        self.Lq, self.Lk, self.Lv = (_LocalLinear(device, rows, n, d) for n in (q, kv, kv))
+        self.Lo = _LocalLinear(device, rows, d, q, residual=True, scale=0.5, split_size=max(32, q) if self.seq else 0)
         self.Lg = _LocalLinear(device, M, 2 * count, d, gate=True, epilogue=act)
         self.Ld = self.rp = None
         if self.tp:
@@ -826,8 +841,18 @@ class TensorParallelBlocks:
             del g_full, d_full
             self.weights.append(w)
         bf = dict(dtype=torch.bfloat16, device=cuda)
-        self.q, self.k, self.v = torch.empty((M, q), **bf), torch.empty((M, kv), **bf), torch.empty((M, kv), **bf)
-        self.h, self.slab, self.y = torch.empty((M, d), **bf), torch.empty((M, count), **bf), torch.empty((M, d), **bf)
+        self.q, self.k, self.v = torch.empty((rows, q), **bf), torch.empty((rows, kv), **bf), torch.empty((rows, kv), **bf)
+        self.slab, self.y = torch.empty((M, count), **bf), torch.empty((rows, d), **bf)
+        self._opened = []
+        if self.seq:
+            # the hidden state [M, d] of every rank, shared: each rank's o GEMM writes its rows into all of them
+            self.h_buf, by_rank, self._opened = share_buffer(device, dist, M * d * 2)
+            self.h = torch.as_tensor(_CudaView(self.h_buf.ptr, (M, d), "<u2"), device=cuda).view(torch.bfloat16)
+            order = destination_order(rank, world)
+            self.h_dsts = (ctypes.c_void_p * world)(*[by_rank[r] + rank * rows * d * 2 for r in order])
+            self.y_dst = (ctypes.c_void_p * 1)(self.y.data_ptr())
+        else:
+            self.h = torch.empty((M, d), **bf)
         # q / k / v as one launch where the library takes the group (8 < M <= 128, or the weight-streaming kernel)
         self.group = None
         plans = (ctypes.c_void_p * 3)(self.Lq.plan, self.Lk.plan, self.Lv.plan)
@@ -836,7 +861,7 @@ class TensorParallelBlocks:
             self.group = (plans, torch.empty(max(need.value, 256), dtype=torch.uint8, device=cuda), (ctypes.c_void_p * 3)(
                 self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr()))
         per_block = (2 if self.group else 3 * self.Lq.launches) + self.Lo.launches + self.Lg.launches
-        per_block += 4 if self.tp else self.Ld.launches
+        per_block += (4 if self.seq else 4) if self.tp else self.Ld.launches      # tp: GEMM, barrier, fold, barrier; seq: barrier, GEMM, barrier, fold
         self.launches = per_block * n_blocks
         self.bytes_per_gpu_block = 2 * (d * (q + 2 * kv) + d * q + 3 * d * count)
         self.graph = None
@@ -844,6 +869,8 @@ class TensorParallelBlocks:
     def step(self, x0):
         """Enqueues all blocks on the current torch stream; returns the last block's output."""
         lib, stream = self.dev.lib, self.torch.cuda.current_stream().cuda_stream
+        if self.seq and x0.shape[0] != self.rows:
+            x0 = x0[self.rank * self.rows:(self.rank + 1) * self.rows]          # this rank's rows (a contiguous view)
         x = x0
         for b in range(self.n_blocks):
             w = self.weights[b % len(self.weights)]
@@ -855,6 +882,19 @@ class TensorParallelBlocks:
                 self.Lq.run(stream, x, w["q"], self.q)
                 self.Lk.run(stream, x, w["k"], self.k)
                 self.Lv.run(stream, x, w["v"], self.v)
+            if self.seq:
+                rp = self.rp
+                _lib.check(lib.vaicu_linear_run_broadcast(self.Lo.plan, stream, self.q.data_ptr(), w["o"].data_ptr(), None, x0.data_ptr(),
+                                                          self.h_dsts, self.world, self.Lo.ws.data_ptr()), "vaicu_linear_run_broadcast")
+                rp.barrier.run(stream)          # every rank's rows of the hidden state are in this rank's buffer
+                self.Lg.run(stream, self.h, w["g"], self.slab)
+                _lib.check(lib.vaicu_linear_run_reduce_scatter(rp.plan, stream, self.slab.data_ptr(), w["d"].data_ptr(), rp.staging_ptrs,
+                                                               self.world, self.rank, rp.ws.data_ptr()), "vaicu_linear_run_reduce_scatter")
+                rp.barrier.run(stream)          # the partial sums of this rank's rows have arrived from every rank
+                _lib.check(lib.vaicu_partial_fold_run(self.dev.handle, stream, rp.staging.ptr, self.world, self.rows, rp.N, int(rp.part_dtype),
+                                                      x0.data_ptr(), rp.scale, int(rp.o_dtype), self.y_dst, 1, 0), "vaicu_partial_fold_run")
+                x = self.y
+                continue
             self.Lo.run(stream, self.q, w["o"], self.h, residual=x0)
             self.Lg.run(stream, self.h, w["g"], self.slab)
             if self.tp:
@@ -886,12 +926,15 @@ class TensorParallelBlocks:
                 lin.close()
         if self.rp is not None:
             self.rp.close()
+        for p in self._opened:
+            self.dev.lib.vaicu_ipc_close(p)
+        self._opened = []
 
 
 def bench_blocks(device, dist, preset, M, n_blocks, iters=10, warmup=3):
-    """`n_blocks` blocks' Linear nodes as one replayed CUDA graph: on one GPU (every rank measures that itself)
-    and tensor-parallel over all ranks; device-timed, max over ranks.  The two outputs (same seeded weights
-    and input) are compared on every rank."""
+    """`n_blocks` blocks' Linear nodes as one replayed CUDA graph: on one GPU (every rank measures that itself),
+    tensor-parallel over all ranks (t N), and - with more than 128 rows per rank - sequence-parallel (t S);
+    device-timed, max over ranks.  The outputs (same seeded weights and input) are compared on every rank."""
     import torch
 
     from . import presets
@@ -907,14 +950,18 @@ def bench_blocks(device, dist, preset, M, n_blocks, iters=10, warmup=3):
     copies = max(2, min(n_blocks, -(-320_000_000 // probe.bytes_per_gpu_block)))
     probe.close()
     del probe
-    for tp in ((False, True) if world > 1 else (False,)):
-        chain = TensorParallelBlocks(device, dist, preset, M, n_blocks, copies, tp)
+    forms = [("t1", False, False)]
+    if world > 1:
+        forms.append(("tN", True, False))
+        if M % world == 0 and M // world > 128:
+            forms.append(("tS", True, True))          # sequence-parallel: q / k / v / o on this rank's rows only
+    for key, tp, seq in forms:
+        chain = TensorParallelBlocks(device, dist, preset, M, n_blocks, copies, tp, seq)
         _host_align(torch, dist)
         out = chain.capture(x0)
         ms = _timed(torch, dist, cuda, chain.graph.replay, iters, warmup)
         torch.cuda.synchronize()
-        outs[tp] = out.float().cpu()
-        key = "tN" if tp else "t1"
+        outs[key] = out.float().cpu()
         res[key + "_us_per_block"] = round(ms * 1e3 / n_blocks, 2)
         res[key + "_launches_per_block"] = chain.launches // n_blocks
         res[key + "_weight_sets"] = copies
@@ -923,11 +970,18 @@ def bench_blocks(device, dist, preset, M, n_blocks, iters=10, warmup=3):
         del chain
         torch.cuda.empty_cache()
     if world > 1:
-        a, b = outs[True], outs[False]
+        a, b = outs["tN"], outs["t1"]
         # unit-scale activations whose sums may cancel: relative to max(|one-GPU value|, 1)
         res["max_rel_diff_vs_one_gpu"] = float(((a - b).abs() / b.abs().clamp_min(1.0)).max())
         res["speedup"] = round(res["t1_us_per_block"] / res["tN_us_per_block"], 2)
         res["efficiency"] = round(res["speedup"] / world, 3)
+        if "tS" in outs:
+            rank, rows = dist.get_rank(), M // world
+            mine = b[rank * rows:(rank + 1) * rows]               # the sequence-parallel chain returns this rank's rows
+            diff = float(((outs["tS"] - mine).abs() / mine.abs().clamp_min(1.0)).max())
+            res["max_rel_diff_vs_one_gpu"] = max(res["max_rel_diff_vs_one_gpu"], diff)
+            res["sequence_parallel_speedup"] = round(res["t1_us_per_block"] / res["tS_us_per_block"], 2)
+            res["sequence_parallel_efficiency"] = round(res["sequence_parallel_speedup"] / world, 3)
     return res
 
 
