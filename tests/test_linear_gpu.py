@@ -543,6 +543,74 @@ def test_scatter_run_writes_slabs_into_wider_outputs(M, K, N, gate, device):
         np.testing.assert_array_equal(got[:, col0 + N:], canary[:, col0 + N:])
 
 
+@pytest.mark.parametrize("rows,K,N", [(160, 512, 520), (48, 256, 264), (256, 320, 1000)])
+def test_broadcast_run_assembles_row_blocks_with_residual(rows, K, N, device):
+    """vaicu_linear_run_broadcast on one GPU: two "ranks" run the same Linear (bias, residual, scale) on their
+    own rows of the activations and each writes its block of rows into BOTH full-height outputs (what the o
+    projection of a sequence-parallel block does to its own and its peers' hidden state); the assembled
+    outputs equal the dense run over all rows, bit for bit."""
+    import ctypes
+
+    from vai_b200 import _lib
+    from vai_b200.engine import DeviceBuffer, encode
+    from vai_b200 import Dtype
+    lib = device.lib
+    rng = np.random.default_rng(rows + N)
+    M = 2 * rows
+    x = encode(rng.standard_normal((M, K)).astype(np.float32), Dtype.BF16)
+    w = encode((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32), Dtype.BF16)
+    b = encode(rng.standard_normal(N).astype(np.float32), Dtype.BF16)
+    r = encode(rng.standard_normal((M, N)).astype(np.float32), Dtype.BF16)
+    bufs = {}
+    for name, arr in (("x", x), ("w", w), ("b", b), ("r", r)):
+        bufs[name] = DeviceBuffer(device, arr.nbytes)
+        bufs[name].upload(arr)
+
+    def plan_for(m):
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = m, N, K
+        d.i_dtype = d.w_dtype = d.o_dtype = d.b_dtype = int(Dtype.BF16)
+        d.has_bias, d.bias_elems, d.has_residual = 1, N, 1
+        d.scalar_scale = 0.5
+        d.split_size = max(32, K)          # one K span: the outputs leave through the GEMM's epilogue
+        h = ctypes.c_void_p()
+        _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
+        info = _lib.LinearInfo()
+        lib.vaicu_linear_plan_info(h, ctypes.byref(info))
+        return h, DeviceBuffer(device, max(info.workspace_bytes, 256))
+
+    whole, ws_whole = plan_for(M)
+    dense = DeviceBuffer(device, M * N * 2)
+    _lib.check(lib.vaicu_linear_run(whole, None, bufs["x"].ptr, bufs["w"].ptr, bufs["b"].ptr, bufs["r"].ptr, dense.ptr, ws_whole.ptr), "run")
+    part, ws_part = plan_for(rows)
+    outs = [DeviceBuffer(device, M * N * 2 + 512) for _ in range(2)]
+    for o in outs:
+        _lib.check(lib.vaicu_memset(o.ptr, 0xC3, M * N * 2 + 512, None), "memset")
+    for rank in range(2):
+        off = rank * rows
+        dsts = (ctypes.c_void_p * 2)(*[o.ptr + off * N * 2 for o in outs])
+        _lib.check(lib.vaicu_linear_run_broadcast(part, None, bufs["x"].ptr + off * K * 2, bufs["w"].ptr, bufs["b"].ptr,
+                                                  bufs["r"].ptr + off * N * 2, dsts, 2, ws_part.ptr), "broadcast")
+    device.synchronize()
+    device.check_status()
+    want = dense.download(np.empty((M, N), dtype=np.uint16))
+    for o in outs:
+        raw = o.download(np.empty(M * N + 256, dtype=np.uint16))
+        np.testing.assert_array_equal(raw[:M * N].reshape(M, N), want)
+        assert (raw[M * N:] == 0xC3C3).all()
+    # a plan that folds K splits in a second launch cannot broadcast
+    d = _lib.LinearDesc()
+    d.M, d.N, d.K = 64, 128, 4096
+    d.i_dtype = d.w_dtype = d.o_dtype = int(Dtype.BF16)
+    d.b_dtype, d.scalar_scale = 2, 1.0
+    h = ctypes.c_void_p()
+    _lib.check(lib.vaicu_linear_plan_create(device.handle, ctypes.byref(d), ctypes.byref(h)), "plan")
+    info = _lib.LinearInfo()
+    lib.vaicu_linear_plan_info(h, ctypes.byref(info))
+    if info.split_count > 1:
+        assert lib.vaicu_linear_run_broadcast(h, None, bufs["x"].ptr, bufs["w"].ptr, None, None, (ctypes.c_void_p * 1)(outs[0].ptr), 1, ws_part.ptr) == 2
+
+
 def test_config_1_gpt2_mlp_linear_fp32(device):
     """The single-node configuration of the benchmark list at its exact size: X [128, 768] fp32
     ~N(0, 1) seed 0, W [3072, 768] fp32 ~N(0, 0.02), bias ~N(0, 0.02), fused GELU(tanh), output
