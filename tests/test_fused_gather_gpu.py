@@ -60,6 +60,8 @@ def test_row_parallel_node_in_a_recorded_net_one_rank():
     process group of one rank: every kernel of the exchange runs, against float64."""
     res = _nodes_check(1, 0)
     assert res["max_rel_err_vs_float64"] < 2e-2, res
+    # the vocabulary-split lm_head node + Argmax node of the same check
+    assert res["head_max_rel_err_vs_float64"] < 1e-3 and res["head_token_mismatches"] == 0, res
     # per block: gate|value with the GatedMul merged (1, or 2 with a split-K fold), down GEMM, barrier, fold, barrier
     assert 2 * 5 <= res["launches_recorded"] <= 2 * 6, res
 
@@ -70,3 +72,4 @@ def test_row_parallel_node_in_a_recorded_net_two_gpus():
         pytest.skip("needs two GPUs")
     res = _nodes_check(2, 29543)
     assert res["world"] == 2 and res["max_rel_err_vs_float64"] < 2e-2, res
+    assert res["head_max_rel_err_vs_float64"] < 1e-3 and res["head_token_mismatches"] == 0, res

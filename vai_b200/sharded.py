@@ -691,6 +691,140 @@ class RowParallelLinearNode(_node_base()):
         self._plans = {}
 
 
+class ColumnParallelLinearNode(_node_base()):
+    """A Linear split by output columns (rows of W) over the ranks whose full output appears on every rank,
+    as a node of the engine: in0 = the activations [.., K] (every rank holds them), weight = this rank's
+    rows [count, K] of the full [N, K] weight (vaicu_linear_shard_desc / shard_rows say which), bias
+    (optional) = its entries for those rows, out0 = the full [.., N] result on EVERY rank.
+
+    run() enqueues on the net's stream: a barrier kernel (every rank's readers of the previous run's out0
+    were enqueued ahead of it), the GEMM whose epilogue stores this rank's column slab into every rank's out0
+    over NVLink (vaicu_linear_run_scatter), and a second barrier kernel (all slabs have landed).  out0 is
+    allocated by the node (it is shared with the other ranks through CUDA IPC), not by the net's pool.  The
+    ranks record and run their nets in step.  More than 8 rows of activations, 16-bit weights."""
+
+    def __init__(self, in_dim, out_dim_full, dist, epilogue=0, scalar_scale=1.0):
+        from .engine import INPUT, OUTPUT, PERSISTENT, TEMPORARY
+        super().__init__()
+        self.in_dim, self.out_dim, self.dist = in_dim, out_dim_full, dist
+        self.epilogue, self.scalar_scale = int(epilogue), float(scalar_scale)
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.begin, self.count = shard_rows(out_dim_full, self.world, self.rank)
+        for name, kind in (("in0", INPUT), ("out0", OUTPUT), ("weight", PERSISTENT), ("bias", PERSISTENT), ("partial", TEMPORARY)):
+            self.add_slot(name, kind)
+        self._plans = {}
+        self._shared = {}
+        self._plan = self.info = None
+
+    def _device(self):
+        from .engine import Device
+        return self.net.device if self.net is not None else Device.default()
+
+    def prepare(self):
+        from .engine import Dtype, Tensor
+        x, w = self["in0"], self["weight"]
+        if x.shape[-1] != self.in_dim or tuple(w.shape) != (self.count, self.in_dim):
+            raise ValueError("weight must hold this rank's rows of the full weight")
+        if w.dtype not in (Dtype.F16, Dtype.BF16):
+            raise ValueError("the column-parallel node takes 16-bit weights")
+        o_dtype = self.o_dtype if self.o_dtype != Dtype.NONE else (self.net.o_default_dtype if self.net else Dtype.F32)
+        M = 1
+        for s_ in x.shape[:-1]:
+            M *= s_
+        if M <= 8:
+            raise ValueError("the slab leaves through a tensor-core epilogue: more than 8 rows of activations")
+        has_bias = self["bias"].valid_shape()
+        dev = self._device()
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = M, self.count, self.in_dim
+        d.i_dtype, d.w_dtype, d.o_dtype = int(x.dtype), int(w.dtype), int(o_dtype)
+        d.b_dtype = int(self["bias"].dtype) if has_bias else int(Dtype.NONE)
+        d.has_bias, d.bias_elems = (1, self.count) if has_bias else (0, 0)
+        d.epilogue, d.scalar_scale = self.epilogue, self.scalar_scale
+        d.split_size = max(32, self.in_dim)                         # one K span: a split-K fold cannot scatter
+        key = bytes(d)
+        if key not in self._plans:
+            h = ctypes.c_void_p()
+            _lib.check(dev.lib.vaicu_linear_plan_create(dev.handle, ctypes.byref(d), ctypes.byref(h)), "vaicu_linear_plan_create")
+            info = _lib.LinearInfo()
+            _lib.check(dev.lib.vaicu_linear_plan_info(h, ctypes.byref(info)), "vaicu_linear_plan_info")
+            self._plans[key] = (h, info)
+        self._plan, self.info = self._plans[key]
+        skey = (M, int(o_dtype))
+        if skey not in self._shared:
+            osz = 4 if o_dtype == Dtype.F32 else 2
+            out, out_ptrs, opened = share_buffer(dev, self.dist, M * self.out_dim * osz)
+            order = destination_order(self.rank, self.world)
+            self._shared[skey] = dict(out=out, opened=opened, barrier=PeerBarrier(dev, self.dist),
+                                      out_ptrs=(ctypes.c_void_p * self.world)(*[out_ptrs[r] for r in order]))
+        self._live = self._shared[skey]
+        ws = self.info.workspace_bytes
+        self.slots["partial"] = Tensor((ws // 4,), Dtype.F32) if ws else Tensor()
+        out_t = Tensor(tuple(x.shape[:-1]) + (self.out_dim,), o_dtype)
+        out_t.buffer = self._live["out"]            # bound here: the net's pool leaves it alone
+        self.slots["out0"] = out_t
+
+    def bind(self):
+        lib = self._device().lib
+        sh = self._live
+        x, w = self["in0"].ptr, self["weight"].ptr
+        b = self["bias"].ptr if self["bias"].valid_shape() else None
+        ws = self["partial"].ptr if self["partial"].valid_shape() else None
+        plan, world, N, begin, barrier = self._plan, self.world, self.out_dim, self.begin, sh["barrier"]
+
+        def launch(stream):
+            barrier.run(stream)
+            _lib.check(lib.vaicu_linear_run_scatter(plan, stream, x, w, b, sh["out_ptrs"], world, N, begin, ws), "vaicu_linear_run_scatter")
+            barrier.run(stream)
+
+        launch.kernel_launches = int(self.info.launches) + 2
+        return launch
+
+    def close(self):
+        lib = self._device().lib
+        for sh in self._shared.values():
+            sh["barrier"].close()
+            for p in sh["opened"]:
+                lib.vaicu_ipc_close(p)
+        self._shared = {}
+        for h, _ in self._plans.values():
+            lib.vaicu_linear_plan_destroy(h)
+        self._plans = {}
+
+
+def column_parallel_head_check(device, dist, M=64, d=512, vocab=4096 + 264, seed=1):
+    """A vocabulary-split lm_head as a node (ColumnParallelLinearNode) followed by the engine's Argmax
+    node, one net per rank, run three times (two replays): the gathered logits against float64 on
+    sampled columns and the tokens against the float64 argmax where the top-2 margin allows.  Returns
+    the worst relative logit error and the number of token mismatches."""
+    import vai_b200
+    from .engine import Dtype, Tensor
+    from .nodes import ArgmaxNode
+    rank, world = dist.get_rank(), dist.get_world_size()
+    rng = np.random.default_rng(seed)
+    enc = lambda a: np.asarray(vai_b200.engine.bits_to_f32(vai_b200.engine.encode(a.astype(np.float32), Dtype.BF16), Dtype.BF16))
+    x = enc(rng.standard_normal((M, d)))
+    w = enc(rng.standard_normal((vocab, d)) / np.sqrt(d))
+    net = vai_b200.NeuralNet(w_default_dtype=Dtype.BF16, o_default_dtype=Dtype.F32, device=device)
+    head = ColumnParallelLinearNode(d, vocab, dist)
+    head["weight"] = Tensor.from_numpy(np.ascontiguousarray(w[head.begin:head.begin + head.count]), dtype=Dtype.BF16)
+    net.input("x") - head - net.output("logits")
+    vai_b200.engine.Flow(head) - ArgmaxNode() - net.output("token")
+    outs = None
+    for _ in range(3):
+        outs = net(Tensor.from_numpy(x, dtype=Dtype.BF16))
+    device.check_status()
+    logits = outs["logits"].to_numpy()
+    tokens = outs["token"].to_u32().reshape(-1)
+    want = x.astype(np.float64) @ w.astype(np.float64).T
+    err = float(np.max(np.abs(logits - want) / np.maximum(np.abs(want), 1.0)))
+    order = np.sort(want, axis=1)
+    clear = (order[:, -1] - order[:, -2]) > 1e-3
+    wrong = int(np.sum((tokens != np.argmax(want, axis=1)) & clear))
+    head.close()
+    return err, wrong
+
+
 def tensor_parallel_mlp_check(device, dist, M=64, d=512, ffn=1024, blocks=2, seed=0):
     """Builds `blocks` gated MLPs (gate|value column split as a plain LinearNode over this rank's weight
     rows -> GatedMulNode -> RowParallelLinearNode + residual) as ONE net per rank, runs it twice (the second
@@ -1387,8 +1521,10 @@ def main():
             dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29549", rank=0, world_size=1)
             d = dist
         err, launches = tensor_parallel_mlp_check(Device(local), d, M=a.M)
+        head_err, head_wrong = column_parallel_head_check(Device(local), d, M=a.M)
         if int(os.environ.get("RANK", "0")) == 0:
-            print(json.dumps({"tp_nodes": {"world": world, "max_rel_err_vs_float64": err, "launches_recorded": launches}}))
+            print(json.dumps({"tp_nodes": {"world": world, "max_rel_err_vs_float64": err, "launches_recorded": launches,
+                                           "head_max_rel_err_vs_float64": head_err, "head_token_mismatches": head_wrong}}))
         dist.destroy_process_group()
         return
     res = bench_sharded(Device(local), d, a.preset, a.M)
