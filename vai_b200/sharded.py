@@ -1485,6 +1485,17 @@ def sharded_report(device, dist, peaks):
     # whole blocks (q, k, v, o replicated; the MLP tensor-parallel) as one replayed CUDA graph per rank
     report["blocks"] = [bench_blocks(device, dist, "gemma-3-4b", 64, 34, iters=10, warmup=3),
                         bench_blocks(device, dist, "llama-3.2-3b", 8192, 2, iters=5, warmup=2)]
+    # the batched-decode step as the sum of its measured parts: 34 replayed blocks + the lm_head with greedy sampling
+    try:
+        head = next(r for r in report["gemma3_4b_decode_M64"] if r["layer"] == "lm_head + greedy sampling")
+        blk = report["blocks"][0]
+        report["gemma3_4b_decode_step_us"] = {
+            "one_gpu": round(blk["blocks"] * blk["t1_us_per_block"] + head["t1_us"], 1),
+            "n_gpus": round(blk["blocks"] * blk["tN_us_per_block"] + head["tN_us"], 1),
+            "how": "34 blocks replayed as one graph per rank (per-block time x 34) + the lm_head (one GPU: its GEMM alone; "
+                   "N GPUs: slab + argmax candidates + exchange + merge)"}
+    except (StopIteration, KeyError):
+        pass
     for b in report["blocks"]:
         diff = b.get("max_rel_diff_vs_one_gpu")
         if diff is not None and not diff <= 2e-2:
