@@ -282,7 +282,10 @@ VAICU_API int vaicu_linear_run_argmax(vaicu_linear_plan* plan, vaicu_stream_t st
  *     launch that leaves fp32 partial sums of all members plus one fold that stores the
  *     members' outputs (where three runs would be three GEMMs and three folds); fp32
  *     activations are rounded to the weights' type once.  Needs `workspace` of
- *     vaicu_linear_group_workspace_bytes (256-byte aligned).
+ *     vaicu_linear_group_workspace_bytes (256-byte aligned);
+ *   - the CTA-pair tensor-core kernel (M > 128), every N a multiple of 256, 16-bit activations: one
+ *     GEMM over the members' 256-column tiles, each stored to its member (fewer partial rounds of
+ *     tiles than three launches); no workspace.
  * Returns VAICU_ERR_UNSUPPORTED otherwise, and the caller issues the runs one by one.
  * The first plan keeps the group's state (TMA descriptors by weight pointer); it must
  * outlive the other members' use in groups.  No counterpart in the reference, which records

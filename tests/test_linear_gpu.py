@@ -490,6 +490,71 @@ def test_grouped_siblings_on_the_tensor_core_kernel(M, K, rows, i_dtype, o_dtype
     assert lib.vaicu_linear_group_workspace_bytes((ctypes.c_void_p * 2)(plans[0], h), 2, ctypes.byref(need)) == 2
 
 
+@pytest.mark.parametrize("M,K,rows,o_dtype", [(300, 512, [512, 256, 256], "bf16"), (1024, 320, [768, 256], "f32"), (2600, 192, [256, 256, 1024], "f16")])
+def test_grouped_siblings_on_the_cta_pair_kernel(M, K, rows, o_dtype, device):
+    """vaicu_linear_run_group for M > 128: one CTA-pair GEMM over the members' 256-column tiles, each tile stored
+    to its member; no workspace; bit-identical to the members' own runs (same tiles, same order of K) and within the
+    16-bit bounds of float64."""
+    import ctypes
+
+    from vai_b200 import _lib
+    from vai_b200.engine import DeviceBuffer, bits_to_f32, encode
+    from gpu_util import DT
+    lib = device.lib
+    rng = np.random.default_rng(M + K)
+    w_dtype = "f16" if o_dtype == "f16" else "bf16"
+    dt, ot = DT[w_dtype], DT[o_dtype]
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    xb = DeviceBuffer(device, M * K * 2)
+    xb.upload(encode(x, dt))
+    xs = seen(x, dt)
+    osz = 4 if o_dtype == "f32" else 2
+    plans, wbufs, obufs, wants, singles = [], [], [], [], []
+    for n in rows:
+        w = (rng.standard_normal((n, K)) / np.sqrt(K)).astype(np.float32)
+        wb = DeviceBuffer(device, n * K * 2)
+        wb.upload(encode(w, dt))
+        d = _lib.LinearDesc()
+        d.M, d.N, d.K = M, n, K
+        d.i_dtype, d.w_dtype, d.o_dtype, d.b_dtype = int(dt), int(dt), int(ot), 2
+        d.scalar_scale = 1.0
+        h = ctypes.c_void_p()
+        t = _lib.LinearTuning(tc_splits=1)          # one K span, as in the group: the same order of addition
+        _lib.check(lib.vaicu_linear_plan_create_tuned(device.handle, ctypes.byref(d), ctypes.byref(t), ctypes.byref(h)), "plan")
+        info = _lib.LinearInfo()
+        _lib.check(lib.vaicu_linear_plan_info(h, ctypes.byref(info)), "info")
+        assert info.kernel == 3
+        plans.append(h)
+        wbufs.append(wb)
+        obufs.append(DeviceBuffer(device, M * n * osz + 512))
+        _lib.check(lib.vaicu_memset(obufs[-1].ptr, 0x5A, M * n * osz + 512, None), "memset")
+        wants.append(orc.linear_f64(xs, seen(w, dt)))
+        ws1 = DeviceBuffer(device, max(int(info.workspace_bytes), 256))
+        o1 = DeviceBuffer(device, M * n * osz)
+        _lib.check(lib.vaicu_linear_run(h, None, xb.ptr, wb.ptr, None, None, o1.ptr, ws1.ptr), "run")
+        device.synchronize()
+        singles.append(o1.download(np.empty((M, n), dtype=np.float32 if o_dtype == "f32" else np.uint16)))
+    n = len(rows)
+    parr = (ctypes.c_void_p * n)(*plans)
+    need = ctypes.c_size_t(7)
+    _lib.check(lib.vaicu_linear_group_workspace_bytes(parr, n, ctypes.byref(need)), "group workspace")
+    assert need.value == 0
+    warr = (ctypes.c_void_p * n)(*[b.ptr for b in wbufs])
+    oarr = (ctypes.c_void_p * n)(*[b.ptr for b in obufs])
+    for _ in range(2):
+        _lib.check(lib.vaicu_linear_run_group(parr, n, None, xb.ptr, warr, oarr, None), "group")
+    device.synchronize()
+    device.check_status()
+    tol = (1e-4, 1e-4) if o_dtype == "f32" else (2e-2, 2e-2)
+    for i, (nrows, ob, want) in enumerate(zip(rows, obufs, wants)):
+        raw8 = ob.download(np.empty(M * nrows * osz + 512, dtype=np.uint8))
+        assert (raw8[M * nrows * osz:] == 0x5A).all()
+        raw = raw8[:M * nrows * osz].view(np.float32 if o_dtype == "f32" else np.uint16).reshape(M, nrows)
+        got = raw if o_dtype == "f32" else bits_to_f32(raw, ot)
+        assert_close(got, want, tol, f"pair group member {i}")
+        np.testing.assert_array_equal(raw, singles[i])
+
+
 @pytest.mark.parametrize("M,K,N,gate", [(64, 512, 384, False), (33, 256, 200, False), (300, 512, 520, False), (64, 512, 256, True)])
 def test_scatter_run_writes_slabs_into_wider_outputs(M, K, N, gate, device):
     """vaicu_linear_run_scatter on one GPU: the plan's output lands as a column slab at col0

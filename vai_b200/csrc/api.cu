@@ -1178,6 +1178,8 @@ int group_members_ok(vaicu_linear_plan* const* plans, int count)
             if (!pl->gemv_vec.vectorized) return VAICU_ERR_UNSUPPORTED;
         } else if (pl->kernel == VAICU_KERNEL_TC_SKINNY) {
             if (d.N % 128u) return VAICU_ERR_UNSUPPORTED;      // members are whole numbers of weight tiles
+        } else if (pl->kernel == VAICU_KERNEL_TC_GEMM) {
+            if (d.N % 256u || d.i_dtype == VAICU_DTYPE_F32) return VAICU_ERR_UNSUPPORTED;   // whole 256-column tiles, no cast pass
         } else {
             return VAICU_ERR_UNSUPPORTED;
         }
@@ -1210,11 +1212,23 @@ int group_state(vaicu_linear_plan* const* plans, int count, GroupState** out)
         all.N = total;
         g->count = count;
         vaicu_linear_tuning tune = default_tuning();
-        tune.kernel = VAICU_KERNEL_TC_SKINNY;
-        tune.tc_splits = p0->tune.tc_splits;
+        tune.kernel = p0->kernel;
         tune.tc_stages = p0->tune.tc_stages;
-        tune.tc_tile_rows = 128u;          // members begin at multiples of 128 rows
+        if (p0->kernel == VAICU_KERNEL_TC_SKINNY) {
+            tune.tc_splits = p0->tune.tc_splits;
+            tune.tc_tile_rows = 128u;          // members begin at multiples of 128 rows
+        } else {
+            // CTA pairs, 256-column tiles (members are multiples of 256 columns), one K span, whole tiles only
+            tune.tc_pair = 1;
+            tune.tc_bn = 256u;
+            tune.tc_splits = 1u;
+            tune.tc_tail_strips = 1;
+        }
         int rc = build_plan(p0->dev, &all, tune, &g->virt);
+        if (rc == VAICU_OK && p0->kernel == VAICU_KERNEL_TC_GEMM && (!g->virt->tcp.pair || g->virt->tcp.splits != 1u)) {
+            vaicu_linear_plan_destroy(g->virt);
+            rc = VAICU_ERR_UNSUPPORTED;
+        }
         if (rc != VAICU_OK) { delete g; return rc == VAICU_ERR_INVALID_VALUE ? VAICU_ERR_UNSUPPORTED : rc; }
         p0->group = g;
     }
@@ -1234,6 +1248,7 @@ int vaicu_linear_group_workspace_bytes(vaicu_linear_plan* const* plans, int coun
     rc = group_state(plans, count, &g);
     if (rc != VAICU_OK) return rc;
     const vaicu_linear_plan* v = g->virt;
+    if (plans[0]->kernel == VAICU_KERNEL_TC_GEMM) return VAICU_OK;      // the members' outputs leave through the epilogue
     *out_bytes = v->ws_cast_bytes + (v->tcp.cfold ? 0u : align_up((size_t)v->tcp.splits * v->d.M * v->d.N * sizeof(float), 256u));
     return VAICU_OK;
 }
@@ -1272,6 +1287,35 @@ int vaicu_linear_run_group(vaicu_linear_plan* const* plans, int count, vaicu_str
     if (rc != VAICU_OK) return rc;
     vaicu_linear_plan* v = g->virt;
     const vaicu_linear_desc& d = v->d;
+    if (p0->kernel == VAICU_KERNEL_TC_GEMM) {
+        // CTA-pair kernel: one GEMM over the members' weight rows side by side (9 rounds of tiles for the q / k / v
+        // of a 3B-class model at M = 8192 where three launches take 6 + 2 + 2), each tile stored to its member
+        if (!aligned16(I)) return VAICU_ERR_UNSUPPORTED;
+        for (int i = 0; i < count; ++i) {
+            if (g->w_base[i] == W[i]) continue;
+            rc = encode_map(&g->maps_w[i], W[i], d.w_dtype, rows[i], d.K, 128u);      // each CTA of a pair stages 128 of the 256 rows
+            if (rc != VAICU_OK) return rc;
+            g->w_base[i] = W[i];
+        }
+        if (count == 2) g->maps_w[2] = g->maps_w[1];
+        uint32_t ia = I == g->act_base[0] ? 0u : (I == g->act_base[1] ? 1u : 2u);
+        if (ia == 2u) {
+            ia = g->act_next;
+            g->act_next ^= 1u;
+            rc = encode_map(&g->map_act[ia], I, d.w_dtype, d.M, d.K, 128u);
+            if (rc != VAICU_OK) return rc;
+            g->act_base[ia] = I;
+        }
+        TcParams t = v->tcp;
+        t.O = nullptr; t.bias = nullptr; t.res = nullptr; t.partial = nullptr; t.tile_done = nullptr;
+        t.n_dst = 1u; t.ldo = d.N; t.col0 = 0u; t.o_aligned16 = 1u;
+        t.grp_t1 = rows[0] / 256u;
+        t.grp_t2 = count > 2 ? (rows[0] + rows[1]) / 256u : kNoGroup;
+        for (int i = 0; i < count; ++i) t.dst[i] = O[i];
+        VAICU_CUDA(launch_tc_pair_group(g->map_act[ia], g->maps_w, t, v->tc_grid, v->tc_smem, s));
+        for (int i = 0; i < count; ++i) { plans[i]->last_kernel = VAICU_KERNEL_TC_GEMM; plans[i]->last_vectorized = 1; }
+        return VAICU_OK;
+    }
     if (!v->tc_cast && !aligned16(I)) return VAICU_ERR_UNSUPPORTED;
     if (v->tc_cast && (reinterpret_cast<uintptr_t>(I) & 3u)) return VAICU_ERR_ALIGNMENT;
     const bool in_cluster = v->tcp.cfold != 0u;       // the K splits fold inside clusters: no partial sums, no fold launch

@@ -407,6 +407,19 @@ __device__ __forceinline__ void emit_rows16(const TcParams& p, float* v, float* 
     finish_row16<GATE>(p, v, u, m, j0, out_cols, n_valid, pre);
     // O may be a column slab of wider destinations (ldo, col0), one per GPU; a row-parallel run
     // sends the row to the one GPU that owns it
+    if (p.grp_t1 != kNoGroup) {
+        // a group of plain Linears over the same activations (CTA-pair kernel): columns [0, N) are the members'
+        // outputs side by side, whole tiles each; this chunk goes to the member that owns column j0
+        const uint32_t n1 = p.grp_t1 * p.bn, n2 = p.grp_t2 == kNoGroup ? p.N : p.grp_t2 * p.bn;
+        const uint32_t j = j0 >= n2 ? 2u : (j0 >= n1 ? 1u : 0u);
+        const uint32_t first = j == 2u ? n2 : (j == 1u ? n1 : 0u);
+        const uint32_t width = (j == 0u ? n1 : (j == 1u ? n2 : p.N)) - first;
+        const size_t at = (size_t)m * width + (j0 - first);
+        if (n_valid == 16u && ((at * osz) % 16u == 0u)) store16(p.dst[j], p.o_dtype, at, v, true);
+        else
+            for (uint32_t c = 0; c < n_valid; ++c) store_from_f32(p.dst[j], p.o_dtype, at + c, v[c]);
+        return;
+    }
     uint32_t owner;
     size_t row;
     output_row(p, m, owner, row);
@@ -1031,7 +1044,7 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar)
 template <bool GATE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
 tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_b_tail, const TcParams p)
+                    const __grid_constant__ CUtensorMap tmap_b_tail, const __grid_constant__ CUtensorMap tmap_b2, const TcParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
@@ -1096,8 +1109,15 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 const uint32_t kb0 = z * p.kb_per_split;
                 const uint32_t kb1 = (kb0 + p.kb_per_split < p.kblocks) ? kb0 + p.kb_per_split : p.kblocks;
                 const int32_t ya = (int32_t)(ta * 2u * TILE_ROWS + rank * TILE_ROWS);
-                const int32_t yb = GATE ? (int32_t)((rank ? p.H : 0u) + tb * half + strip * bh) : (int32_t)(tb * bn + strip * bw + rank * bh);
+                int32_t yb = GATE ? (int32_t)((rank ? p.H : 0u) + tb * half + strip * bh) : (int32_t)(tb * bn + strip * bw + rank * bh);
                 const CUtensorMap* mb = bw == bn ? &tmap_b : &tmap_b_tail;
+                if (!GATE && tb >= p.grp_t1) {
+                    // a group: the weight tiles of the second / third member come from their own tensors (the
+                    // tail map's slot carries the second member's map; groups run without column strips)
+                    const bool third = tb >= p.grp_t2;
+                    mb = third ? &tmap_b2 : &tmap_b_tail;
+                    yb = (int32_t)((tb - (third ? p.grp_t2 : p.grp_t1)) * bn + rank * bh);
+                }
                 const uint32_t item_bytes = a_bytes + bh * BLOCK_K * 2u;      // per CTA and k-block
                 uint32_t kb = kb0;
                 if (first) {
@@ -1299,13 +1319,21 @@ tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 }
 
 template <bool GATE>
-static cudaError_t launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb_tail, const TcParams& p,
-                                       int grid, size_t smem, cudaStream_t stream)
+static cudaError_t launch_pair_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb_tail, const CUtensorMap& mb2,
+                                       const TcParams& p, int grid, size_t smem, cudaStream_t stream)
 {
     auto kern = tc_gemm_pair_kernel<GATE>;
     static SmemOptIn optin;
     if (cudaError_t e = optin.ensure(kern, (int)kTcMaxSmem); e != cudaSuccess) return e;
-    return launch_pdl(kern, dim3((unsigned)grid), dim3(kTcThreads), smem, stream, ma, mb, mb_tail, p);
+    return launch_pdl(kern, dim3((unsigned)grid), dim3(kTcThreads), smem, stream, ma, mb, mb_tail, mb2, p);
+}
+
+// CTA-pair kernel over a group of 2-3 weight tensors that share the activations (p.grp_t1 / p.grp_t2: the column
+// tile at which the second / third begins; p.dst[0..2] the members' outputs; no column strips in the tail round).
+cudaError_t launch_tc_pair_group(const CUtensorMap& map_act, const CUtensorMap* maps_w, const TcParams& p, int grid, size_t smem,
+                                 cudaStream_t stream)
+{
+    return launch_pair_variant<false>(map_act, maps_w[0], maps_w[1], maps_w[2], p, grid, smem, stream);
 }
 
 // Number of CTA pairs that can be resident at once (pairs need two SMs of one TPC).
@@ -1387,8 +1415,8 @@ cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, c
                            bool swap, int grid, size_t smem, cudaStream_t stream)
 {
     const bool gate = p.gate != 0;
-    if (p.pair) return gate ? launch_pair_variant<true>(map_a, map_b, map_b_tail, p, grid, smem, stream)
-                            : launch_pair_variant<false>(map_a, map_b, map_b_tail, p, grid, smem, stream);
+    if (p.pair) return gate ? launch_pair_variant<true>(map_a, map_b, map_b_tail, map_b, p, grid, smem, stream)
+                            : launch_pair_variant<false>(map_a, map_b, map_b_tail, map_b, p, grid, smem, stream);
     if (swap) return gate ? launch_variant<true, true>(map_a, map_b, map_a, map_a, p, grid, smem, stream)
                           : launch_variant<true, false>(map_a, map_b, map_a, map_a, p, grid, smem, stream);
     return gate ? launch_variant<false, true>(map_a, map_b, map_a, map_a, p, grid, smem, stream)

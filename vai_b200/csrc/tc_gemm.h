@@ -116,6 +116,8 @@ cudaError_t tc_swap_max_clusters(size_t smem, unsigned cluster, int* clusters);
 // One tiny launch whose bounded mbarrier wait is made to run out; sets *status as the GEMM kernels do.
 cudaError_t launch_wait_expiry_selftest(int* status, cudaStream_t stream);
 // map_b_tail: the weights' map with the strip box of the tail round (CTA-pair kernel with tail_split > 1; else any valid map).
+cudaError_t launch_tc_pair_group(const CUtensorMap& map_act, const CUtensorMap* maps_w, const TcParams& p, int grid, size_t smem,
+                                 cudaStream_t stream);
 cudaError_t launch_tc_gemm_group(const CUtensorMap* maps_w, const CUtensorMap& map_act, const TcParams& p, int grid, size_t smem,
                                  cudaStream_t stream);
 cudaError_t launch_tc_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b_tail, const TcParams& p,

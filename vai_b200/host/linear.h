@@ -259,7 +259,8 @@ public:
         if (!plan_ || hasBias() || config_.acceptResidual || config_.epilogue != vai::Epilogue::None || gate_ ||
             config_.scalarScale != 1.0f || argmaxReader_ || config_.splitSize)
             return {};
-        const bool ok = info_.kernel == VAICU_KERNEL_GEMV || (info_.kernel == VAICU_KERNEL_TC_SKINNY && config_.outDim % 128u == 0);
+        const bool ok = info_.kernel == VAICU_KERNEL_GEMV || (info_.kernel == VAICU_KERNEL_TC_SKINNY && config_.outDim % 128u == 0) ||
+                        (info_.kernel == VAICU_KERNEL_TC_GEMM && config_.outDim % 256u == 0 && (*this)["in0"].dtype() != Dtype::Fp32);
         if (!ok) return {};
         return std::to_string(info_.kernel) + "/" + std::to_string((int)(*this)["weight"].dtype()) + "/" +
                std::to_string((int)(*this)["out0"].dtype());

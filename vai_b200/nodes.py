@@ -183,13 +183,15 @@ class LinearNode(Node):
         return launch
 
     def groupable(self):
-        """Plain (nothing after the dot product) and on the weight-streaming kernel, or on the
-        swapped tensor-core kernel with a whole number of weight tiles: may share one launch
-        with sibling Linears that read the same activations."""
+        """Plain (nothing after the dot product) and on the weight-streaming kernel, or on a
+        tensor-core kernel with a whole number of weight tiles: may share one launch with
+        sibling Linears that read the same activations."""
         if self.info is None or self.has_bias() or self.accept_residual or self.epilogue != Epilogue.NONE:
             return False
         if self.gate_fuse or self.scalar_scale != 1.0 or self._argmax_reader is not None or self.split_size:
             return False
+        if self.info.kernel == KERNEL_TC_GEMM:      # CTA pairs: whole 256-column tiles, 16-bit activations (no cast pass)
+            return self.out_dim % 256 == 0 and self["in0"].dtype != Dtype.F32
         return self.info.kernel == KERNEL_GEMV or (self.info.kernel == KERNEL_TC_SKINNY and self.out_dim % 128 == 0)
 
     def group_key(self):
@@ -219,7 +221,7 @@ class LinearNode(Node):
         def launch(stream):
             _lib.check(run(plans, n, stream, x, ws, outs, work), "vaicu_linear_run_group")
 
-        if first.info.kernel == KERNEL_GEMV:
+        if first.info.kernel in (KERNEL_GEMV, KERNEL_TC_GEMM):
             launch.kernel_launches = 1
         else:
             # GEMM (+ the cast of fp32 activations) (+ the fold, unless the K splits fold inside clusters:
