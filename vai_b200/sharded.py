@@ -994,7 +994,8 @@ class TensorParallelBlocks:
         if device.lib.vaicu_linear_group_workspace_bytes(plans, 3, ctypes.byref(need)) == 0:
             self.group = (plans, torch.empty(max(need.value, 256), dtype=torch.uint8, device=cuda), (ctypes.c_void_p * 3)(
                 self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr()))
-        per_block = (2 if self.group else 3 * self.Lq.launches) + self.Lo.launches + self.Lg.launches
+        group_launches = 1 if need.value == 0 else 2       # GEMM alone, or GEMM + the fold of its K splits
+        per_block = (group_launches if self.group else 3 * self.Lq.launches) + self.Lo.launches + self.Lg.launches
         per_block += (4 if self.seq else 4) if self.tp else self.Ld.launches      # tp: GEMM, barrier, fold, barrier; seq: barrier, GEMM, barrier, fold
         self.launches = per_block * n_blocks
         self.bytes_per_gpu_block = 2 * (d * (q + 2 * kv) + d * q + 3 * d * count)
